@@ -1,0 +1,343 @@
+/*
+ * vbt_b200.h -- C ABI of libvbt_b200.so: a from-scratch sm_100a implementation of the
+ * CUDA backend behind VibeTensor's vt:: data-parallel ops.
+ *
+ * Every entry point takes plain pointers, sizes and strides.  A VibeTensor binding
+ * fills a vbt_b200_tensor from a vbt::core::TensorImpl (data(), dtype(), sizes(),
+ * strides()), allocates the output through VibeTensor's own stream-ordered caching
+ * allocator, passes the current stream, and maps the returned status to the C++
+ * exception class named beside each code.  Nothing here allocates device memory except
+ * where a function says so; nothing synchronises the stream except where it says so.
+ * All launches go to the `stream` argument (a cudaStream_t passed as void*; NULL is the
+ * legacy default stream) on the device that owns the pointers; the library switches to
+ * that device for the call and restores the previous one.
+ *
+ * "Reference" below means the NVlabs/vibetensor source tree; citations are
+ * path:line inside it.
+ */
+#ifndef VBT_B200_H_
+#define VBT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes: the exception the reference throws for the same condition ---- */
+typedef int32_t vbt_b200_status;
+#define VBT_B200_OK 0
+#define VBT_B200_INVALID_ARGUMENT 1 /* std::invalid_argument -> Python ValueError  */
+#define VBT_B200_RUNTIME_ERROR 2    /* std::runtime_error    -> Python RuntimeError */
+#define VBT_B200_OUT_OF_RANGE 3     /* std::out_of_range     -> Python IndexError   */
+#define VBT_B200_CUDA_ERROR 4       /* a CUDA runtime call failed                   */
+
+/* Message of the last non-OK status on the calling thread (thread-local, never NULL). */
+const char* vbt_b200_last_error(void);
+/* Library version (major*1000 + minor) and the sm architecture it was compiled for. */
+int32_t vbt_b200_version(void);
+int32_t vbt_b200_compiled_arch(void);
+
+/* ---- dtypes: ordinals of vbt::core::ScalarType (include/vbt/core/dtype.h:19-30) ---- */
+#define VBT_B200_BOOL 0
+#define VBT_B200_I32 1
+#define VBT_B200_I64 2
+#define VBT_B200_F32 3
+#define VBT_B200_F16 4
+#define VBT_B200_BF16 5
+
+/* Maximum rank accepted, the reference's CUDA broadcast limit
+ * (src/vbt/ops/cuda_elementwise.cu:2974-2979). */
+#define VBT_B200_MAX_NDIM 25
+
+/* A strided view of device memory.  `data` already includes the storage offset
+ * (TensorImpl::data(), include/vbt/core/tensor.h:96-101); strides are in elements and
+ * may be 0 (broadcast) or negative. */
+typedef struct vbt_b200_tensor {
+  void* data;
+  int32_t dtype;
+  int32_t ndim;
+  const int64_t* sizes;
+  const int64_t* strides;
+} vbt_b200_tensor;
+
+/* =====================================================================================
+ * 1. TensorIterator elementwise ops over broadcast / strided views
+ *    replaces: binary_op_dispatcher, unary_op_dispatcher, ternary_op_dispatcher,
+ *    where_op_dispatcher and their *_ti_strided_kernel launches
+ *    (src/vbt/ops/cuda_elementwise.cu:1786-1909, :2645-2782, :2845-2866, :2884-3211),
+ *    the launcher ti_gpu_kernel (include/vbt/core/tensor_iterator/cuda_loops.h:16-48) and
+ *    the offset calculator compute_offset_elems
+ *    (include/vbt/core/tensor_iterator/cuda.h:25-42).
+ *
+ *    `out` is written in place and may be ANY strided view whose shape equals the
+ *    broadcast of the inputs (the reference always allocates a dense output,
+ *    cuda_elementwise.cu:96-110; a binding passes that allocation here).  Inputs must all
+ *    have out's dtype, except: comparison ops write BOOL, `where` takes a BOOL condition.
+ *    No type promotion, as in the reference (:2887).
+ * ===================================================================================== */
+
+/* Broadcast shape of up to 4 operands (src/vbt/core/broadcast.cc); out_sizes has room for
+ * VBT_B200_MAX_NDIM entries.  INVALID_ARGUMENT on incompatible shapes. */
+vbt_b200_status vbt_b200_broadcast_shape(const vbt_b200_tensor* const* operands, int32_t n,
+                                         int64_t* out_sizes, int32_t* out_ndim);
+
+enum vbt_b200_unary_op {
+  VBT_B200_U_RELU = 0,   /* vbt_cuda_relu_impl; relu(NaN)=0, relu(-0.0)=+0.0 (:1622-1630) */
+  VBT_B200_U_NEG,        /* vbt_cuda_neg_impl; integers wrap (:619-628)                    */
+  VBT_B200_U_ABS,        /* vbt_cuda_abs_impl; abs(INT64_MIN)=INT64_MIN (:590-618)         */
+  VBT_B200_U_SQUARE,
+  VBT_B200_U_EXP,
+  VBT_B200_U_LOG,
+  VBT_B200_U_SQRT,
+  VBT_B200_U_RSQRT,
+  VBT_B200_U_SIN,
+  VBT_B200_U_COS,
+  VBT_B200_U_TANH,
+  VBT_B200_U_SIGMOID,    /* 1/(1+exp(-x))                                                 */
+  VBT_B200_U_SILU,       /* reference computes in fp64 (:877-883); here fp32, |err|<=1e-6 */
+  VBT_B200_U_GELU,       /* exact erf form (:884-891); here fp32 erff                     */
+  VBT_B200_U_RECIPROCAL,
+  VBT_B200_U_SIGN,
+  VBT_B200_U_FLOOR,
+  VBT_B200_U_CEIL,
+  VBT_B200_U_TRUNC,
+  VBT_B200_U_ROUND,      /* ties to even (:789-807)                                       */
+  VBT_B200_U_EXPM1,
+  VBT_B200_U_LOG1P,
+  VBT_B200_U_SOFTPLUS,   /* thresholds +-20 (:892-900)                                    */
+  VBT_B200_U_RELU6,
+  VBT_B200_U_HARDTANH,
+  VBT_B200_U_COUNT
+};
+
+enum vbt_b200_binary_op {
+  VBT_B200_B_ADD = 0,  /* vbt_cuda_add_impl (:3351-3356) */
+  VBT_B200_B_SUB,
+  VBT_B200_B_MUL,      /* vbt_cuda_mul_impl */
+  VBT_B200_B_DIV,      /* INT64 rejected, as :2889-2891 */
+  VBT_B200_B_MAXIMUM,  /* NaN from either side propagates (:244-306) */
+  VBT_B200_B_MINIMUM,
+  VBT_B200_B_FMAX,     /* NaN ignored (:1333-1350) */
+  VBT_B200_B_FMIN,
+  VBT_B200_B_EQ,       /* comparisons: out dtype BOOL (:2399-2404, :2406-2530) */
+  VBT_B200_B_NE,
+  VBT_B200_B_LT,
+  VBT_B200_B_GT,
+  VBT_B200_B_LE,
+  VBT_B200_B_GE,
+  VBT_B200_B_COUNT
+};
+
+enum vbt_b200_ternary_op {
+  VBT_B200_T_CLAMP = 0,  /* clamp(v, mn, mx); NaN bound -> NaN (:1259-1266)              */
+  VBT_B200_T_LERP,       /* start + weight*(end-start) (:1267-1271)                      */
+  VBT_B200_T_THRESHOLD,  /* x > thr ? x : value (:1273-1277)                             */
+  VBT_B200_T_ADDCMUL,    /* a + b*c, ONE launch; the reference's vbt_cuda_addcmul_impl
+                            is three launches with two temporaries (:3927-3931); each
+                            intermediate is rounded to the storage dtype as there       */
+  VBT_B200_T_ADDCDIV,    /* a + b/c, likewise (:3933-3937)                               */
+  VBT_B200_T_WHERE_GT0_ADDCMUL, /* where(a > 0, a + b*c, 0) in one launch: the chain
+                            mul -> add -> gt -> where of four reference ops with the same
+                            per-op rounding, so results are bit-identical to the chain   */
+  VBT_B200_T_COUNT
+};
+
+vbt_b200_status vbt_b200_unary(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                               void* stream);
+vbt_b200_status vbt_b200_binary(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                                const vbt_b200_tensor* b, void* stream);
+vbt_b200_status vbt_b200_ternary(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                                 const vbt_b200_tensor* b, const vbt_b200_tensor* c, void* stream);
+/* vbt_cuda_where_impl / vbt_cuda_masked_fill_impl (:3921-3926): cond BOOL; x, y, out same
+ * dtype in {F32, I64, BOOL, F16, BF16} (:2701-2712). */
+vbt_b200_status vbt_b200_where(const vbt_b200_tensor* out, const vbt_b200_tensor* cond,
+                               const vbt_b200_tensor* x, const vbt_b200_tensor* y, void* stream);
+/* Binary op with a host scalar on one side: the reference's CPU 0-d scalar fast path
+ * (:2893-2961).  `scalar` points at one host element of a's dtype (F32 or I64 only, as
+ * there); scalar_on_left selects op(scalar, a) (the reference's ROp functors, :2934). */
+vbt_b200_status vbt_b200_binary_scalar(int32_t op, const vbt_b200_tensor* out,
+                                       const vbt_b200_tensor* a, const void* scalar,
+                                       int32_t scalar_on_left, void* stream);
+/* Strided copy out <- a (same dtype, a broadcast to out's shape): clone_cuda /
+ * clone_strided_to_contig_kernel (src/vbt/core/tensor_ops_cuda.cu:83-91). */
+vbt_b200_status vbt_b200_copy(const vbt_b200_tensor* out, const vbt_b200_tensor* a, void* stream);
+
+/* Named forms of the ops the benchmark configuration chains; each forwards to the
+ * enum entry above.  vbt_cuda_{add,mul,sub,div,gt,relu}_impl (:3351-3393, :3486). */
+vbt_b200_status vbt_b200_add(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                             const vbt_b200_tensor* b, void* stream);
+vbt_b200_status vbt_b200_sub(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                             const vbt_b200_tensor* b, void* stream);
+vbt_b200_status vbt_b200_mul(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                             const vbt_b200_tensor* b, void* stream);
+vbt_b200_status vbt_b200_div(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                             const vbt_b200_tensor* b, void* stream);
+vbt_b200_status vbt_b200_gt(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                            const vbt_b200_tensor* b, void* stream);
+vbt_b200_status vbt_b200_relu(const vbt_b200_tensor* out, const vbt_b200_tensor* a, void* stream);
+
+/* Introspection of the iteration plan the host builds for an elementwise call: the
+ * counterpart of TensorIterBase::export_device_meta / can_use_32bit_indexing
+ * (src/vbt/core/tensor_iterator/core.cc:248-474).  Fills the coalesced iteration shape
+ * (innermost first) and, per operand (out first), the element strides in that order.
+ * `strides` has room for noperands*VBT_B200_MAX_NDIM entries, row per operand.
+ * *kernel: 0 = flat vector kernel, 1 = tiled kernel (vector along dim 0), 2 = tiled
+ * scalar kernel.  *pieces: number of 32-bit-safe launches the call is split into. */
+vbt_b200_status vbt_b200_ti_plan(const vbt_b200_tensor* const* operands, int32_t noperands,
+                                 int64_t* shape, int64_t* strides, int32_t* ndim,
+                                 int32_t* kernel, int32_t* pieces);
+
+/* =====================================================================================
+ * 2. Dim reductions
+ *    replaces: vbt_cuda_{sum,prod,min,max,mean}_impl -> cuda_reduce_dispatch and kernels
+ *    K1/K2/K3 (src/vbt/ops/cuda_reduction.cu:254-416, :907-2070); adds argmax/argmin,
+ *    which the reference only has on CPU (src/vbt/python/tensor_bindings.cc:630-889),
+ *    and BF16/F16 inputs (FP32 accumulation).
+ *
+ *    `out` (and `out_index` for ARGMAX/ARGMIN; INT64) is a caller-allocated dense
+ *    tensor whose shape is the reduced shape (keepdim decides whether reduced dims stay
+ *    as size 1).  dims == NULL / ndims == 0 reduces everything.  Accumulation order is
+ *    fixed by the shapes alone: results are run-to-run deterministic (no float atomics).
+ *    SUM/PROD/MAX/MIN: F32 or I64 (out same dtype); BF16/F16 in -> out BF16/F16 or F32.
+ *    MEAN: F32 ("mean: expected dtype=float32", cuda_reduction.cu:982) or BF16/F16.
+ *    Reduced extent 0: SUM 0, PROD 1, MEAN NaN, MAX/MIN/ARG* -> RUNTIME_ERROR
+ *    "amax: empty" / "amin: empty" (cuda_reduction.cu:1176-1216).
+ *    MAX/MIN/ARGMAX/ARGMIN follow the CPU scan (tensor_bindings.cc:361-379, :630-655):
+ *    strict compare from element 0, first extremum wins, a NaN wins only at position 0.
+ * ===================================================================================== */
+enum vbt_b200_reduce_op {
+  VBT_B200_R_SUM = 0,
+  VBT_B200_R_MEAN,
+  VBT_B200_R_MAX,
+  VBT_B200_R_MIN,
+  VBT_B200_R_PROD,
+  VBT_B200_R_ARGMAX,
+  VBT_B200_R_ARGMIN,
+  VBT_B200_R_COUNT
+};
+
+/* Bytes of scratch the call below needs for these arguments (0 for most shapes; the
+ * split reductions keep per-block partials and a ticket counter there).  A binding takes
+ * it from the caching allocator; contents need no initialisation. */
+size_t vbt_b200_reduce_workspace_bytes(int32_t op, const vbt_b200_tensor* self,
+                                       const int64_t* dims, int32_t ndims);
+vbt_b200_status vbt_b200_reduce(int32_t op, const vbt_b200_tensor* out,
+                                const vbt_b200_tensor* out_index, const vbt_b200_tensor* self,
+                                const int64_t* dims, int32_t ndims, int32_t keepdim,
+                                void* workspace, size_t workspace_bytes, void* stream);
+/* Reduced shape for (self, dims, keepdim): cuda_reduction.cu:749-810.  INVALID_ARGUMENT
+ * "<op>: dim out of range" on a bad dim. */
+vbt_b200_status vbt_b200_reduce_shape(const vbt_b200_tensor* self, const int64_t* dims,
+                                      int32_t ndims, int32_t keepdim, int64_t* out_sizes,
+                                      int32_t* out_ndim);
+
+/* =====================================================================================
+ * 3. Advanced indexing, row gather, scatter-add
+ *    replaces: embedding_gather_f32_kernel / embedding_backward_accum_f32_kernel /
+ *    embedding_bounds_check_i64_kernel (src/vbt/ops/embedding_cuda.cu:32-87, :225-302),
+ *    advanced_index_gather_1d_kernel, advanced_index_cuda_kernel,
+ *    advanced_index_put_cuda_kernel, advanced_index_bounds_normalize_kernel
+ *    (src/vbt/core/indexing_advanced_cuda.cu:662-684, :953-978, :1325-1453) and the Triton
+ *    gather/scatter_add kernels (vibe_kernels/indexing/kernels.py:13-186).
+ *
+ *    Index policy (how an index outside [0, V) is treated):
+ *      WRAP   vt::index / index_put_: i in [-V, V) wraps once, else error
+ *             (src/vbt/core/indexing_advanced.cc:663-675)
+ *      STRICT vt::embedding: negative is an error (embedding_dispatch.cc:437-443)
+ *      CLAMP  Triton scatter/gather-2d: clamp into range, never an error
+ *             (vibe_kernels/indexing/kernels.py:79-80)
+ *    Errors are detected ON DEVICE: a bad index is skipped (gather writes zeros for that
+ *    row, scatter drops it) and recorded in the caller's 16-byte `index_status` block
+ *    {int64 count, int64 first_bad_value}, which the caller zeroes once and may share
+ *    between calls.  vbt_b200_index_status_check copies it back (this one synchronises
+ *    the stream) and returns OUT_OF_RANGE with the reference's message.  index_status may
+ *    be NULL to skip recording.
+ * ===================================================================================== */
+#define VBT_B200_INDEX_WRAP 0
+#define VBT_B200_INDEX_STRICT 1
+#define VBT_B200_INDEX_CLAMP 2
+
+/* out[i, :] = table[idx[i], :].  table [V, D] with arbitrary row stride and unit or
+ * non-unit column stride, any dtype (byte copy, bit exact); idx I64 or I32, any rank,
+ * contiguous; out dense [idx.shape..., D]. */
+vbt_b200_status vbt_b200_index_rows(const vbt_b200_tensor* out, const vbt_b200_tensor* table,
+                                    const vbt_b200_tensor* idx, int32_t policy,
+                                    void* index_status, void* stream);
+/* table[idx[i], :] = values[i, :]            (accumulate == 0; duplicate rows: one of the
+ *                                             writers wins, as on the reference's CUDA path)
+ * table[idx[i], :] += values[i, :]           (accumulate != 0; F32, I64, I32, BF16/F16)
+ * table dense rows ([V, D], column stride 1), values [N, D] dense.  Duplicates are
+ * pre-summed inside each thread block before one atomic per distinct row and column
+ * vector reaches memory.  I64/I32 results are exact (wrap-around); F32 is order-free
+ * only up to rounding.  Uses no scratch memory. */
+vbt_b200_status vbt_b200_index_put_rows(const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
+                                        const vbt_b200_tensor* values, int32_t accumulate,
+                                        int32_t policy, void* index_status, void* stream);
+/* The reference's CUDA advanced-index pattern: one index tensor applied to the LAST dim
+ * (indexing_advanced_cuda.cu:2139-2177): out[b, k] = src[b, idx[k]]; src [B, K0] strided. */
+vbt_b200_status vbt_b200_index_lastdim(const vbt_b200_tensor* out, const vbt_b200_tensor* src,
+                                       const vbt_b200_tensor* idx, int32_t policy,
+                                       void* index_status, void* stream);
+vbt_b200_status vbt_b200_index_put_lastdim(const vbt_b200_tensor* self, const vbt_b200_tensor* idx,
+                                           const vbt_b200_tensor* values, int32_t accumulate,
+                                           int32_t policy, void* index_status, void* stream);
+/* vt::embedding forward (F32 weight [V, D] with non-negative strides, I64 contiguous
+ * indices, STRICT policy) and the dense-gradient backward gw[idx[i], :] += grad[i, :],
+ * skipping rows whose index equals padding_idx (embedding_cuda.cu:66-87). */
+vbt_b200_status vbt_b200_embedding(const vbt_b200_tensor* out, const vbt_b200_tensor* weight,
+                                   const vbt_b200_tensor* idx, void* index_status, void* stream);
+vbt_b200_status vbt_b200_embedding_backward(const vbt_b200_tensor* grad_weight,
+                                            const vbt_b200_tensor* idx,
+                                            const vbt_b200_tensor* grad_out, int64_t padding_idx,
+                                            void* index_status, void* stream);
+/* Synchronises `stream`, reads the status block; OK if count == 0, else OUT_OF_RANGE with
+ * message "<what>: index out of range ..." and clears the block. */
+vbt_b200_status vbt_b200_index_status_check(void* index_status, const char* what, int64_t dim_size,
+                                            void* stream);
+
+/* =====================================================================================
+ * 4. Row ops
+ *    replaces: Triton softmax_kernel + host wrapper (vibe_kernels/softmax/vbt_native.py:39-97,
+ *    :193-259), log_softmax (:262-328) and Triton _rmsnorm_fwd_kernel + host wrapper
+ *    (vibe_kernels/rmsnorm/vbt_native.py:55-103, :340-406).  One global read and one
+ *    global write per element.  x is [rows, cols] with column stride 1 and any row stride;
+ *    out dense, same dtype (F32, BF16, F16); math in FP32.
+ *    softmax:  m = max x;  s = max(sum exp(x-m), 1e-20);  y = exp(x-m)/s
+ *    rmsnorm:  r = rsqrt(sum x^2 / cols + eps);  y = x*r*gamma;  inv_rms[row] = r
+ *              gamma: F32 [cols] or NULL;  inv_rms: F32 [rows] or NULL.
+ * ===================================================================================== */
+vbt_b200_status vbt_b200_softmax(void* out, const void* x, int32_t dtype, int64_t rows,
+                                 int64_t cols, int64_t x_row_stride, int32_t log_softmax,
+                                 void* stream);
+vbt_b200_status vbt_b200_rmsnorm(void* out, float* inv_rms, const void* x, const float* gamma,
+                                 int32_t dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
+                                 float eps, void* stream);
+
+/* =====================================================================================
+ * 5. Fabric: sharded reductions and elementwise on a row-sharded tensor
+ *    sits behind FabricTensor.sharded_1d_row (python/vibetensor/fabric.py:483-533) and
+ *    replaces fabric_binary_kernel (src/vbt/cuda/fabric_elementwise.cu:122-162).
+ *    Each rank reduces its own shard to an FP32 (or I64) partial with the call below;
+ *    the ranks' partials are then combined by an NCCL all-reduce on the same stream, and
+ *    MEAN is finished with vbt_b200_scale_cast once the global row count is known.
+ *    vbt_b200_binary / vbt_b200_unary accept pointers into a peer GPU's memory for the
+ *    INPUTS (plain loads over NVLink, as the reference's Fabric kernel does); outputs
+ *    must be local.
+ * ===================================================================================== */
+/* partial (F32/I64, dense, reduced shape) = local SUM/MAX/MIN of the shard; BF16/F16
+ * shards accumulate and emit FP32.  Same workspace contract as vbt_b200_reduce. */
+vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_tensor* partial,
+                                        const vbt_b200_tensor* shard, const int64_t* dims,
+                                        int32_t ndims, int32_t keepdim, void* workspace,
+                                        size_t workspace_bytes, void* stream);
+/* out[i] = cast(partial[i] * scale): the "divide by the global N and cast" step of a
+ * sharded mean.  partial F32 [n]; out F32/BF16/F16 [n]. */
+vbt_b200_status vbt_b200_scale_cast(void* out, int32_t out_dtype, const float* partial, int64_t n,
+                                    float scale, void* stream);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* VBT_B200_H_ */

@@ -1,0 +1,500 @@
+/*
+ * TEST INFRASTRUCTURE ONLY -- the CPU oracle.  A plain-C, single-threaded restatement of
+ * what VibeTensor's own implementation computes for the vt:: data-parallel op path, used
+ * by tests/, the smoke check and the bench's CPU-baseline leg as the checker.  The product
+ * (libvbt_b200.so and the vibetensor_b200 package) never links, loads or calls it.
+ *
+ * Parity of this restatement is pinned two ways (tests/test_oracle_*.py): against the
+ * golden vectors of the reference's own unit tests, and against the reference's real CPU
+ * code compiled from its sources (oracle/_ref/libvbt_ref_cpu.so, see build_ref.sh) on
+ * seeded random inputs.  Paths with no CPU code in the reference (bf16/f16 elementwise,
+ * where, softmax, RMSNorm) follow its CUDA functors / Triton kernels and are checked
+ * against torch CPU with the reference tests' own tolerances.
+ *
+ * Citations are path:line in the NVlabs/vibetensor tree.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+enum { DT_BOOL = 0, DT_I32 = 1, DT_I64 = 2, DT_F32 = 3, DT_F16 = 4, DT_BF16 = 5 };
+
+static int itemsize(int dt) {
+  switch (dt) {
+    case DT_BOOL: return 1;
+    case DT_I32: return 4;
+    case DT_I64: return 8;
+    case DT_F32: return 4;
+    case DT_F16: return 2;
+    case DT_BF16: return 2;
+  }
+  return 0;
+}
+
+/* ---- storage <-> float, as src/vbt/ops/cuda_elementwise.cu:135-140: widen to float,
+ * compute, store with round-to-nearest-even (__float2bfloat16_rn / __float2half_rn). ---- */
+static float bf16_to_f(uint16_t h) {
+  uint32_t u = (uint32_t)h << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+static uint16_t f_to_bf16(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7fff; /* NaN, canonical as the intrinsic */
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+static float f16_to_f(uint16_t h) {
+  _Float16 x;
+  memcpy(&x, &h, 2);
+  return (float)x;
+}
+static uint16_t f_to_f16(float f) {
+  _Float16 x = (_Float16)f;
+  uint16_t h;
+  memcpy(&h, &x, 2);
+  if (f != f) h = 0x7fff;
+  return h;
+}
+static float load_f(const void* p, int dt) {
+  switch (dt) {
+    case DT_F32: return *(const float*)p;
+    case DT_F16: return f16_to_f(*(const uint16_t*)p);
+    case DT_BF16: return bf16_to_f(*(const uint16_t*)p);
+  }
+  return 0.f;
+}
+static void store_f(void* p, int dt, float v) {
+  switch (dt) {
+    case DT_F32: *(float*)p = v; break;
+    case DT_F16: *(uint16_t*)p = f_to_f16(v); break;
+    case DT_BF16: *(uint16_t*)p = f_to_bf16(v); break;
+  }
+}
+/* value after one store+load round trip: the per-op rounding of a chained expression */
+static float round_to(int dt, float v) {
+  if (dt == DT_F32) return v;
+  if (dt == DT_F16) return f16_to_f(f_to_f16(v));
+  return bf16_to_f(f_to_bf16(v));
+}
+
+/* ---- op codes: must match include/vbt_b200.h ---- */
+enum {
+  U_RELU, U_NEG, U_ABS, U_SQUARE, U_EXP, U_LOG, U_SQRT, U_RSQRT, U_SIN, U_COS, U_TANH,
+  U_SIGMOID, U_SILU, U_GELU, U_RECIPROCAL, U_SIGN, U_FLOOR, U_CEIL, U_TRUNC, U_ROUND,
+  U_EXPM1, U_LOG1P, U_SOFTPLUS, U_RELU6, U_HARDTANH, U_COUNT
+};
+enum {
+  B_ADD, B_SUB, B_MUL, B_DIV, B_MAXIMUM, B_MINIMUM, B_FMAX, B_FMIN,
+  B_EQ, B_NE, B_LT, B_GT, B_LE, B_GE, B_COUNT
+};
+enum { T_CLAMP, T_LERP, T_THRESHOLD, T_ADDCMUL, T_ADDCDIV, T_WHERE_GT0_ADDCMUL, T_COUNT };
+
+/* Functors on float: src/vbt/ops/cuda_elementwise.cu:590-900, :1622-1630.  Several are
+ * written in double there (Silu, Gelu, Reciprocal, Sign, Softplus, Relu6, Hardtanh). */
+static float unary_f(int op, float a) {
+  switch (op) {
+    case U_RELU: return a > 0.f ? a : 0.f;
+    case U_NEG: return -a;
+    case U_ABS: return fabsf(a);
+    case U_SQUARE: return a * a;
+    case U_EXP: return expf(a);
+    case U_LOG: return logf(a);
+    case U_SQRT: return sqrtf(a);
+    case U_RSQRT: return (float)(1.0 / sqrt((double)a));
+    case U_SIN: return sinf(a);
+    case U_COS: return cosf(a);
+    case U_TANH: return tanhf(a);
+    case U_SIGMOID: return 1.0f / (1.0f + expf(-a));
+    case U_SILU: { double x = a; return (float)(x * (1.0 / (1.0 + exp(-x)))); }
+    case U_GELU: { double x = a; return (float)(0.5 * x * (1.0 + erf(x * 0.70710678118654752440))); }
+    case U_RECIPROCAL: return (float)(1.0 / (double)a);
+    case U_SIGN: { double x = a; return (float)((x > 0) - (x < 0)); }
+    case U_FLOOR: return floorf(a);
+    case U_CEIL: return ceilf(a);
+    case U_TRUNC: return truncf(a);
+    case U_ROUND: return nearbyintf(a);
+    case U_EXPM1: return expm1f(a);
+    case U_LOG1P: return log1pf(a);
+    case U_SOFTPLUS: {
+      double x = a;
+      if (x > 20.0) return (float)x;
+      if (x < -20.0) return (float)exp(x);
+      return (float)log1p(exp(x));
+    }
+    case U_RELU6: { double x = a; if (x < 0.0) x = 0.0; if (x > 6.0) x = 6.0; return (float)x; }
+    case U_HARDTANH: { double x = a; if (x < -1.0) x = -1.0; if (x > 1.0) x = 1.0; return (float)x; }
+  }
+  return 0.f;
+}
+static int64_t unary_i64(int op, int64_t a, int* ok) {
+  uint64_t ua = (uint64_t)a;
+  switch (op) {
+    case U_RELU: return a > 0 ? a : 0;
+    case U_NEG: return (int64_t)(0u - ua);
+    case U_ABS: return a < 0 ? (int64_t)(0u - ua) : a;
+    case U_SQUARE: return (int64_t)(ua * ua);
+    case U_SIGN: return (a > 0) - (a < 0);
+    case U_FLOOR: case U_CEIL: case U_TRUNC: case U_ROUND: return a;
+  }
+  *ok = 0; /* transcendental ops reject integral inputs (:121-125) */
+  return 0;
+}
+static float binary_f(int op, float a, float b) {
+  switch (op) {
+    case B_ADD: return a + b;
+    case B_SUB: return a - b;
+    case B_MUL: return a * b;
+    case B_DIV: return a / b;
+    case B_MAXIMUM: if (a != a) return a; if (b != b) return b; return fmaxf(a, b);
+    case B_MINIMUM: if (a != a) return a; if (b != b) return b; return fminf(a, b);
+    case B_FMAX: return fmaxf(a, b);
+    case B_FMIN: return fminf(a, b);
+  }
+  return 0.f;
+}
+static int compare_f(int op, float a, float b) {
+  switch (op) {
+    case B_EQ: return a == b;
+    case B_NE: return a != b;
+    case B_LT: return a < b;
+    case B_GT: return a > b;
+    case B_LE: return a <= b;
+    case B_GE: return a >= b;
+  }
+  return 0;
+}
+static int64_t binary_i64(int op, int64_t a, int64_t b) {
+  switch (op) {
+    case B_ADD: return (int64_t)((uint64_t)a + (uint64_t)b);
+    case B_SUB: return (int64_t)((uint64_t)a - (uint64_t)b);
+    case B_MUL: return (int64_t)((uint64_t)a * (uint64_t)b);
+    case B_MAXIMUM: case B_FMAX: return a > b ? a : b;
+    case B_MINIMUM: case B_FMIN: return a < b ? a : b;
+  }
+  return 0;
+}
+static int compare_i64(int op, int64_t a, int64_t b) {
+  switch (op) {
+    case B_EQ: return a == b;
+    case B_NE: return a != b;
+    case B_LT: return a < b;
+    case B_GT: return a > b;
+    case B_LE: return a <= b;
+    case B_GE: return a >= b;
+  }
+  return 0;
+}
+static float ternary_f(int op, int dt, float a, float b, float c) {
+  switch (op) {
+    case T_CLAMP: /* (v, mn, mx) :1259-1266 */
+      if (b != b || c != c) return NAN;
+      return a < b ? b : (a > c ? c : a);
+    case T_LERP: return fmaf(c, b - a, a); /* start + weight*(end-start), contracted on device */
+    case T_THRESHOLD: return a > b ? a : c;
+    case T_ADDCMUL: return a + round_to(dt, b * c);        /* mul, then add (:3927-3931) */
+    case T_ADDCDIV: return a + round_to(dt, b / c);
+    case T_WHERE_GT0_ADDCMUL: {
+      float t2 = round_to(dt, a + round_to(dt, b * c));
+      return a > 0.f ? t2 : 0.f;
+    }
+  }
+  return 0.f;
+}
+
+/* Generic N-d strided iteration in row-major order of `sizes`; strides in elements. */
+#define MAXD 32
+typedef struct {
+  int ndim;
+  int64_t sizes[MAXD];
+  int64_t idx[MAXD];
+} odo_t;
+static int64_t numel_of(int ndim, const int64_t* sizes) {
+  int64_t n = 1;
+  for (int i = 0; i < ndim; ++i) n *= sizes[i];
+  return n;
+}
+static void odo_init(odo_t* o, int ndim, const int64_t* sizes) {
+  o->ndim = ndim;
+  for (int i = 0; i < ndim; ++i) { o->sizes[i] = sizes[i]; o->idx[i] = 0; }
+}
+static void odo_next(odo_t* o) {
+  for (int d = o->ndim - 1; d >= 0; --d) {
+    if (++o->idx[d] < o->sizes[d]) return;
+    o->idx[d] = 0;
+  }
+}
+static int64_t odo_off(const odo_t* o, const int64_t* strides) {
+  int64_t off = 0;
+  for (int d = 0; d < o->ndim; ++d) off += o->idx[d] * strides[d];
+  return off;
+}
+
+/* out = op(a [, b [, c]]).  nin = 1,2,3.  kind: 0 unary, 1 binary, 2 ternary, 3 where
+ * (a = BOOL cond, b = x, c = y), 4 copy.  Comparison binaries write BOOL bytes. */
+int vbo_elementwise(int kind, int op, int dtype, int ndim, const int64_t* sizes, void* out,
+                    const int64_t* os, const void* a, const int64_t* as, const void* b,
+                    const int64_t* bs, const void* c, const int64_t* cs) {
+  if (ndim > MAXD) return 1;
+  const int64_t n = numel_of(ndim, sizes);
+  const int es = itemsize(dtype);
+  const int is_cmp = (kind == 1 && op >= B_EQ);
+  const int oes = is_cmp ? 1 : es;
+  odo_t o;
+  odo_init(&o, ndim, sizes);
+  for (int64_t i = 0; i < n; ++i, odo_next(&o)) {
+    char* po = (char*)out + odo_off(&o, os) * oes;
+    if (kind == 3) { /* where_ti_strided_kernel :2645-2662 */
+      const uint8_t cond = *((const uint8_t*)a + odo_off(&o, as));
+      const char* px = (const char*)b + odo_off(&o, bs) * es;
+      const char* py = (const char*)c + odo_off(&o, cs) * es;
+      memcpy(po, cond != 0 ? px : py, es);
+      continue;
+    }
+    const char* pa = (const char*)a + odo_off(&o, as) * es;
+    if (kind == 4) { memcpy(po, pa, es); continue; }
+    const char* pb = b ? (const char*)b + odo_off(&o, bs) * es : 0;
+    const char* pc = c ? (const char*)c + odo_off(&o, cs) * es : 0;
+    if (dtype == DT_I64) {
+      int64_t av = *(const int64_t*)pa;
+      if (kind == 0) {
+        int ok = 1;
+        int64_t r = unary_i64(op, av, &ok);
+        if (!ok) return 1;
+        *(int64_t*)po = r;
+      } else if (kind == 1) {
+        int64_t bv = *(const int64_t*)pb;
+        if (op == B_DIV) return 1;
+        if (is_cmp) *(uint8_t*)po = (uint8_t)compare_i64(op, av, bv);
+        else *(int64_t*)po = binary_i64(op, av, bv);
+      } else {
+        return 1;
+      }
+    } else if (dtype == DT_F32 || dtype == DT_F16 || dtype == DT_BF16) {
+      float av = load_f(pa, dtype);
+      if (kind == 0) store_f(po, dtype, unary_f(op, av));
+      else if (kind == 1) {
+        float bv = load_f(pb, dtype);
+        if (is_cmp) *(uint8_t*)po = (uint8_t)compare_f(op, av, bv);
+        else store_f(po, dtype, binary_f(op, av, bv));
+      } else {
+        store_f(po, dtype, ternary_f(op, dtype, av, load_f(pb, dtype), load_f(pc, dtype)));
+      }
+    } else {
+      return 1;
+    }
+  }
+  return 0;
+}
+
+/* ---- reductions: x dense [outer, n, inner]; sequential left-to-right along n, as the
+ * loop callbacks in src/vbt/python/tensor_bindings.cc:290-419, :630-682 and
+ * vbt_default_sum_impl (src/vbt/ops/default_kernels.cc:748-805).  out dense [outer, inner].
+ * op: 0 sum 1 mean 2 max 3 min 4 prod 5 argmax 6 argmin.  For F16/BF16 inputs the
+ * accumulator is float and the result is rounded once to out_dtype (F32 or the input's). */
+int vbo_reduce(int op, int dtype, int out_dtype, int64_t outer, int64_t n, int64_t inner,
+               const void* x, void* out, int64_t* out_idx) {
+  const int es = itemsize(dtype);
+  for (int64_t o = 0; o < outer; ++o) {
+    for (int64_t j = 0; j < inner; ++j) {
+      const char* base = (const char*)x + (o * n * inner + j) * es;
+      const int64_t step = inner * es;
+      const int64_t oi = o * inner + j;
+      if (dtype == DT_I64) {
+        int64_t acc = 0, bi = 0;
+        if (op == 0) { uint64_t s = 0; for (int64_t i = 0; i < n; ++i) s += *(const uint64_t*)(base + i * step); acc = (int64_t)s; }
+        else if (op == 4) { uint64_t s = 1; for (int64_t i = 0; i < n; ++i) s *= *(const uint64_t*)(base + i * step); acc = (int64_t)s; }
+        else if (op == 1) return 1;
+        else {
+          if (n == 0) return 2;
+          acc = *(const int64_t*)base;
+          for (int64_t i = 1; i < n; ++i) {
+            int64_t v = *(const int64_t*)(base + i * step);
+            if ((op == 2 || op == 5) ? (v > acc) : (v < acc)) { acc = v; bi = i; }
+          }
+        }
+        if (out) ((int64_t*)out)[oi] = acc;
+        if (out_idx) out_idx[oi] = bi;
+      } else {
+        float acc = 0.f;
+        int64_t bi = 0;
+        if (op == 0 || op == 1) {
+          for (int64_t i = 0; i < n; ++i) acc += load_f(base + i * step, dtype);
+          if (op == 1) acc = n == 0 ? NAN : acc / (float)(n > 0 ? n : 1);
+        } else if (op == 4) {
+          acc = 1.f;
+          for (int64_t i = 0; i < n; ++i) acc *= load_f(base + i * step, dtype);
+        } else {
+          if (n == 0) return 2;
+          acc = load_f(base, dtype);
+          for (int64_t i = 1; i < n; ++i) {
+            float v = load_f(base + i * step, dtype);
+            if ((op == 2 || op == 5) ? (v > acc) : (v < acc)) { acc = v; bi = i; }
+          }
+        }
+        if (out) store_f((char*)out + oi * itemsize(out_dtype), out_dtype, acc);
+        if (out_idx) out_idx[oi] = bi;
+      }
+    }
+  }
+  return 0;
+}
+
+/* ---- indexing ---- */
+/* policy 0 WRAP (indexing_advanced.cc:663-675), 1 STRICT (embedding_dispatch.cc:437-443),
+ * 2 CLAMP (vibe_kernels/indexing/kernels.py:79-80).  Returns 0 or 3 (out of range). */
+static int norm_index(int64_t* v, int64_t V, int policy) {
+  int64_t i = *v;
+  if (policy == 2) { if (i < 0) i = 0; if (i > V - 1) i = V - 1; *v = i; return V > 0 ? 0 : 3; }
+  if (policy == 0 && i < 0) i += V;
+  if (i < 0 || i >= V) return 3;
+  *v = i;
+  return 0;
+}
+/* out[i, :] = table[idx[i], :]; table strides (s0, s1) in elements; byte copy
+ * (advanced_index_cpu, indexing_advanced.cc:1129-1263; CPU vt::embedding,
+ * embedding_dispatch.cc:292-533).  All indices are validated before any copy. */
+int vbo_gather_rows(int esize, int64_t V, int64_t D, const void* table, int64_t s0, int64_t s1,
+                    const int64_t* idx, int64_t N, int policy, void* out) {
+  for (int64_t i = 0; i < N; ++i) { int64_t v = idx[i]; if (norm_index(&v, V, policy)) return 3; }
+  for (int64_t i = 0; i < N; ++i) {
+    int64_t v = idx[i];
+    norm_index(&v, V, policy);
+    const char* src = (const char*)table + v * s0 * esize;
+    char* dst = (char*)out + i * D * esize;
+    if (s1 == 1) memcpy(dst, src, (size_t)(D * esize));
+    else for (int64_t j = 0; j < D; ++j) memcpy(dst + j * esize, src + j * s1 * esize, esize);
+  }
+  return 0;
+}
+/* table[idx[i], :] (+)= values[i, :] in index order -- sequential accumulation
+ * (advanced_index_put_cpu + accumulate_in_place, indexing_advanced.cc:1267-1473);
+ * overwrite: last writer in linear order wins.  padding_idx rows are skipped when
+ * use_padding != 0 (embedding backward, embedding_cuda.cu:66-87). */
+int vbo_scatter_rows(int dtype, int64_t V, int64_t D, void* table, const int64_t* idx, int64_t N,
+                     const void* values, int accumulate, int policy, int use_padding,
+                     int64_t padding_idx) {
+  const int es = itemsize(dtype);
+  for (int64_t i = 0; i < N; ++i) { int64_t v = idx[i]; if (norm_index(&v, V, policy)) return 3; }
+  for (int64_t i = 0; i < N; ++i) {
+    int64_t v = idx[i];
+    if (use_padding && v == padding_idx) continue;
+    norm_index(&v, V, policy);
+    char* dst = (char*)table + v * D * es;
+    const char* src = (const char*)values + i * D * es;
+    if (!accumulate) { memcpy(dst, src, (size_t)(D * es)); continue; }
+    for (int64_t j = 0; j < D; ++j) {
+      switch (dtype) {
+        case DT_F32: ((float*)dst)[j] += ((const float*)src)[j]; break;
+        case DT_I64: ((uint64_t*)dst)[j] += ((const uint64_t*)src)[j]; break;
+        case DT_I32: ((uint32_t*)dst)[j] += ((const uint32_t*)src)[j]; break;
+        default: return 1;
+      }
+    }
+  }
+  return 0;
+}
+/* out[b, k] = src[b*sb + idx[k]*sk]: the reference's CUDA last-dim pattern
+ * (advanced_index_gather_1d_kernel, indexing_advanced_cuda.cu:953-978). */
+int vbo_index_lastdim(int esize, int64_t B, int64_t K0, const void* src, int64_t sb, int64_t sk,
+                      const int64_t* idx, int64_t K, int policy, void* out) {
+  for (int64_t k = 0; k < K; ++k) { int64_t v = idx[k]; if (norm_index(&v, K0, policy)) return 3; }
+  for (int64_t b = 0; b < B; ++b)
+    for (int64_t k = 0; k < K; ++k) {
+      int64_t v = idx[k];
+      norm_index(&v, K0, policy);
+      memcpy((char*)out + (b * K + k) * esize, (const char*)src + (b * sb + v * sk) * esize, esize);
+    }
+  return 0;
+}
+/* self[b, idx[k]] (+)= values[b, k]; self dense [B, K0]. */
+int vbo_index_put_lastdim(int dtype, int64_t B, int64_t K0, void* self, const int64_t* idx,
+                          int64_t K, const void* values, int accumulate, int policy) {
+  const int es = itemsize(dtype);
+  for (int64_t k = 0; k < K; ++k) { int64_t v = idx[k]; if (norm_index(&v, K0, policy)) return 3; }
+  for (int64_t b = 0; b < B; ++b)
+    for (int64_t k = 0; k < K; ++k) {
+      int64_t v = idx[k];
+      norm_index(&v, K0, policy);
+      char* dst = (char*)self + (b * K0 + v) * es;
+      const char* src = (const char*)values + (b * K + k) * es;
+      if (!accumulate) { memcpy(dst, src, es); continue; }
+      switch (dtype) {
+        case DT_F32: *(float*)dst += *(const float*)src; break;
+        case DT_I64: *(uint64_t*)dst += *(const uint64_t*)src; break;
+        case DT_I32: *(uint32_t*)dst += *(const uint32_t*)src; break;
+        default: return 1;
+      }
+    }
+  return 0;
+}
+
+/* ---- row ops ---- */
+/* Triton softmax_kernel (vibe_kernels/softmax/vbt_native.py:59-97): fp32 math,
+ * m = max x; s = sum exp(x - m); s = max(s, 1e-20); y = exp(x - (log s + m));
+ * log_softmax: y = x - (log s + m) (:262-328). */
+int vbo_softmax(int dtype, int64_t rows, int64_t cols, const void* x, int64_t row_stride,
+                void* out, int log_softmax) {
+  const int es = itemsize(dtype);
+  for (int64_t r = 0; r < rows; ++r) {
+    const char* px = (const char*)x + r * row_stride * es;
+    char* po = (char*)out + r * cols * es;
+    float m = -INFINITY;
+    for (int64_t j = 0; j < cols; ++j) { float v = load_f(px + j * es, dtype); m = fmaxf(m, v); }
+    float s = 0.f;
+    for (int64_t j = 0; j < cols; ++j) s += expf(load_f(px + j * es, dtype) - m);
+    s = fmaxf(s, 1e-20f);
+    const float lse = logf(s) + m;
+    for (int64_t j = 0; j < cols; ++j) {
+      float v = load_f(px + j * es, dtype) - lse;
+      store_f(po + j * es, dtype, log_softmax ? v : expf(v));
+    }
+  }
+  return 0;
+}
+/* Triton _rmsnorm_fwd_kernel (vibe_kernels/rmsnorm/vbt_native.py:75-103):
+ * inv_rms = rsqrt(sum x^2 / cols + eps); y = x * inv_rms * gamma; output cast to the
+ * input dtype (vibe_kernels/rmsnorm/impl/triton_impl.py:99-104). */
+int vbo_rmsnorm(int dtype, int64_t rows, int64_t cols, const void* x, int64_t row_stride,
+                const float* gamma, float eps, void* out, float* inv_rms) {
+  const int es = itemsize(dtype);
+  for (int64_t r = 0; r < rows; ++r) {
+    const char* px = (const char*)x + r * row_stride * es;
+    char* po = (char*)out + r * cols * es;
+    float ss = 0.f;
+    for (int64_t j = 0; j < cols; ++j) { float v = load_f(px + j * es, dtype); ss += v * v; }
+    const float inv = (float)(1.0 / sqrt((double)(ss / (float)cols + eps)));
+    if (inv_rms) inv_rms[r] = inv;
+    for (int64_t j = 0; j < cols; ++j) {
+      float v = load_f(px + j * es, dtype) * inv;
+      if (gamma) v *= gamma[j];
+      store_f(po + j * es, dtype, v);
+    }
+  }
+  return 0;
+}
+
+/* out[i] = cast(partial[i] * scale): finish of a sharded mean. */
+int vbo_scale_cast(int out_dtype, const float* partial, int64_t n, float scale, void* out) {
+  for (int64_t i = 0; i < n; ++i)
+    store_f((char*)out + i * itemsize(out_dtype), out_dtype, partial[i] * scale);
+  return 0;
+}
+
+/* Host mirror of the reference's device offset calculator compute_offset_elems
+ * (include/vbt/core/tensor_iterator/cuda.h:25-42; the same mirror appears in
+ * tests/cpp/tensor_iter_cuda_meta_test.cc:78-91): linear index -> element offset, sizes
+ * and strides innermost-first. */
+int64_t vbo_offset_elems(int64_t linear, int ndim, const int64_t* sizes, const int64_t* strides) {
+  int64_t off = 0;
+  for (int d = 0; d < ndim; ++d) {
+    const int64_t sz = sizes[d];
+    if (sz <= 0) continue;
+    off += (linear % sz) * strides[d];
+    linear /= sz;
+  }
+  return off;
+}
