@@ -25,6 +25,12 @@
 extern "C" {
 #endif
 
+#if defined(__GNUC__)
+#define VBT_B200_API __attribute__((visibility("default")))
+#else
+#define VBT_B200_API
+#endif
+
 /* ---- status codes: the exception the reference throws for the same condition ---- */
 typedef int32_t vbt_b200_status;
 #define VBT_B200_OK 0
@@ -34,10 +40,10 @@ typedef int32_t vbt_b200_status;
 #define VBT_B200_CUDA_ERROR 4       /* a CUDA runtime call failed                   */
 
 /* Message of the last non-OK status on the calling thread (thread-local, never NULL). */
-const char* vbt_b200_last_error(void);
+VBT_B200_API const char* vbt_b200_last_error(void);
 /* Library version (major*1000 + minor) and the sm architecture it was compiled for. */
-int32_t vbt_b200_version(void);
-int32_t vbt_b200_compiled_arch(void);
+VBT_B200_API int32_t vbt_b200_version(void);
+VBT_B200_API int32_t vbt_b200_compiled_arch(void);
 
 /* ---- dtypes: ordinals of vbt::core::ScalarType (include/vbt/core/dtype.h:19-30) ---- */
 #define VBT_B200_BOOL 0
@@ -80,7 +86,7 @@ typedef struct vbt_b200_tensor {
 
 /* Broadcast shape of up to 4 operands (src/vbt/core/broadcast.cc); out_sizes has room for
  * VBT_B200_MAX_NDIM entries.  INVALID_ARGUMENT on incompatible shapes. */
-vbt_b200_status vbt_b200_broadcast_shape(const vbt_b200_tensor* const* operands, int32_t n,
+VBT_B200_API vbt_b200_status vbt_b200_broadcast_shape(const vbt_b200_tensor* const* operands, int32_t n,
                                          int64_t* out_sizes, int32_t* out_ndim);
 
 enum vbt_b200_unary_op {
@@ -144,39 +150,39 @@ enum vbt_b200_ternary_op {
   VBT_B200_T_COUNT
 };
 
-vbt_b200_status vbt_b200_unary(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+VBT_B200_API vbt_b200_status vbt_b200_unary(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                                void* stream);
-vbt_b200_status vbt_b200_binary(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+VBT_B200_API vbt_b200_status vbt_b200_binary(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                                 const vbt_b200_tensor* b, void* stream);
-vbt_b200_status vbt_b200_ternary(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+VBT_B200_API vbt_b200_status vbt_b200_ternary(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                                  const vbt_b200_tensor* b, const vbt_b200_tensor* c, void* stream);
 /* vbt_cuda_where_impl / vbt_cuda_masked_fill_impl (:3921-3926): cond BOOL; x, y, out same
  * dtype in {F32, I64, BOOL, F16, BF16} (:2701-2712). */
-vbt_b200_status vbt_b200_where(const vbt_b200_tensor* out, const vbt_b200_tensor* cond,
+VBT_B200_API vbt_b200_status vbt_b200_where(const vbt_b200_tensor* out, const vbt_b200_tensor* cond,
                                const vbt_b200_tensor* x, const vbt_b200_tensor* y, void* stream);
 /* Binary op with a host scalar on one side: the reference's CPU 0-d scalar fast path
  * (:2893-2961).  `scalar` points at one host element of a's dtype (F32 or I64 only, as
  * there); scalar_on_left selects op(scalar, a) (the reference's ROp functors, :2934). */
-vbt_b200_status vbt_b200_binary_scalar(int32_t op, const vbt_b200_tensor* out,
+VBT_B200_API vbt_b200_status vbt_b200_binary_scalar(int32_t op, const vbt_b200_tensor* out,
                                        const vbt_b200_tensor* a, const void* scalar,
                                        int32_t scalar_on_left, void* stream);
 /* Strided copy out <- a (same dtype, a broadcast to out's shape): clone_cuda /
  * clone_strided_to_contig_kernel (src/vbt/core/tensor_ops_cuda.cu:83-91). */
-vbt_b200_status vbt_b200_copy(const vbt_b200_tensor* out, const vbt_b200_tensor* a, void* stream);
+VBT_B200_API vbt_b200_status vbt_b200_copy(const vbt_b200_tensor* out, const vbt_b200_tensor* a, void* stream);
 
 /* Named forms of the ops the benchmark configuration chains; each forwards to the
  * enum entry above.  vbt_cuda_{add,mul,sub,div,gt,relu}_impl (:3351-3393, :3486). */
-vbt_b200_status vbt_b200_add(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+VBT_B200_API vbt_b200_status vbt_b200_add(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                              const vbt_b200_tensor* b, void* stream);
-vbt_b200_status vbt_b200_sub(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+VBT_B200_API vbt_b200_status vbt_b200_sub(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                              const vbt_b200_tensor* b, void* stream);
-vbt_b200_status vbt_b200_mul(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+VBT_B200_API vbt_b200_status vbt_b200_mul(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                              const vbt_b200_tensor* b, void* stream);
-vbt_b200_status vbt_b200_div(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+VBT_B200_API vbt_b200_status vbt_b200_div(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                              const vbt_b200_tensor* b, void* stream);
-vbt_b200_status vbt_b200_gt(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+VBT_B200_API vbt_b200_status vbt_b200_gt(const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                             const vbt_b200_tensor* b, void* stream);
-vbt_b200_status vbt_b200_relu(const vbt_b200_tensor* out, const vbt_b200_tensor* a, void* stream);
+VBT_B200_API vbt_b200_status vbt_b200_relu(const vbt_b200_tensor* out, const vbt_b200_tensor* a, void* stream);
 
 /* Introspection of the iteration plan the host builds for an elementwise call: the
  * counterpart of TensorIterBase::export_device_meta / can_use_32bit_indexing
@@ -185,7 +191,7 @@ vbt_b200_status vbt_b200_relu(const vbt_b200_tensor* out, const vbt_b200_tensor*
  * `strides` has room for noperands*VBT_B200_MAX_NDIM entries, row per operand.
  * *kernel: 0 = flat vector kernel, 1 = tiled kernel (vector along dim 0), 2 = tiled
  * scalar kernel.  *pieces: number of 32-bit-safe launches the call is split into. */
-vbt_b200_status vbt_b200_ti_plan(const vbt_b200_tensor* const* operands, int32_t noperands,
+VBT_B200_API vbt_b200_status vbt_b200_ti_plan(const vbt_b200_tensor* const* operands, int32_t noperands,
                                  int64_t* shape, int64_t* strides, int32_t* ndim,
                                  int32_t* kernel, int32_t* pieces);
 
@@ -221,15 +227,15 @@ enum vbt_b200_reduce_op {
 /* Bytes of scratch the call below needs for these arguments (0 for most shapes; the
  * split reductions keep per-block partials and a ticket counter there).  A binding takes
  * it from the caching allocator; contents need no initialisation. */
-size_t vbt_b200_reduce_workspace_bytes(int32_t op, const vbt_b200_tensor* self,
+VBT_B200_API size_t vbt_b200_reduce_workspace_bytes(int32_t op, const vbt_b200_tensor* self,
                                        const int64_t* dims, int32_t ndims);
-vbt_b200_status vbt_b200_reduce(int32_t op, const vbt_b200_tensor* out,
+VBT_B200_API vbt_b200_status vbt_b200_reduce(int32_t op, const vbt_b200_tensor* out,
                                 const vbt_b200_tensor* out_index, const vbt_b200_tensor* self,
                                 const int64_t* dims, int32_t ndims, int32_t keepdim,
                                 void* workspace, size_t workspace_bytes, void* stream);
 /* Reduced shape for (self, dims, keepdim): cuda_reduction.cu:749-810.  INVALID_ARGUMENT
  * "<op>: dim out of range" on a bad dim. */
-vbt_b200_status vbt_b200_reduce_shape(const vbt_b200_tensor* self, const int64_t* dims,
+VBT_B200_API vbt_b200_status vbt_b200_reduce_shape(const vbt_b200_tensor* self, const int64_t* dims,
                                       int32_t ndims, int32_t keepdim, int64_t* out_sizes,
                                       int32_t* out_ndim);
 
@@ -262,7 +268,7 @@ vbt_b200_status vbt_b200_reduce_shape(const vbt_b200_tensor* self, const int64_t
 /* out[i, :] = table[idx[i], :].  table [V, D] with arbitrary row stride and unit or
  * non-unit column stride, any dtype (byte copy, bit exact); idx I64 or I32, any rank,
  * contiguous; out dense [idx.shape..., D]. */
-vbt_b200_status vbt_b200_index_rows(const vbt_b200_tensor* out, const vbt_b200_tensor* table,
+VBT_B200_API vbt_b200_status vbt_b200_index_rows(const vbt_b200_tensor* out, const vbt_b200_tensor* table,
                                     const vbt_b200_tensor* idx, int32_t policy,
                                     void* index_status, void* stream);
 /* table[idx[i], :] = values[i, :]            (accumulate == 0; duplicate rows: one of the
@@ -272,29 +278,29 @@ vbt_b200_status vbt_b200_index_rows(const vbt_b200_tensor* out, const vbt_b200_t
  * pre-summed inside each thread block before one atomic per distinct row and column
  * vector reaches memory.  I64/I32 results are exact (wrap-around); F32 is order-free
  * only up to rounding.  Uses no scratch memory. */
-vbt_b200_status vbt_b200_index_put_rows(const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
+VBT_B200_API vbt_b200_status vbt_b200_index_put_rows(const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
                                         const vbt_b200_tensor* values, int32_t accumulate,
                                         int32_t policy, void* index_status, void* stream);
 /* The reference's CUDA advanced-index pattern: one index tensor applied to the LAST dim
  * (indexing_advanced_cuda.cu:2139-2177): out[b, k] = src[b, idx[k]]; src [B, K0] strided. */
-vbt_b200_status vbt_b200_index_lastdim(const vbt_b200_tensor* out, const vbt_b200_tensor* src,
+VBT_B200_API vbt_b200_status vbt_b200_index_lastdim(const vbt_b200_tensor* out, const vbt_b200_tensor* src,
                                        const vbt_b200_tensor* idx, int32_t policy,
                                        void* index_status, void* stream);
-vbt_b200_status vbt_b200_index_put_lastdim(const vbt_b200_tensor* self, const vbt_b200_tensor* idx,
+VBT_B200_API vbt_b200_status vbt_b200_index_put_lastdim(const vbt_b200_tensor* self, const vbt_b200_tensor* idx,
                                            const vbt_b200_tensor* values, int32_t accumulate,
                                            int32_t policy, void* index_status, void* stream);
 /* vt::embedding forward (F32 weight [V, D] with non-negative strides, I64 contiguous
  * indices, STRICT policy) and the dense-gradient backward gw[idx[i], :] += grad[i, :],
  * skipping rows whose index equals padding_idx (embedding_cuda.cu:66-87). */
-vbt_b200_status vbt_b200_embedding(const vbt_b200_tensor* out, const vbt_b200_tensor* weight,
+VBT_B200_API vbt_b200_status vbt_b200_embedding(const vbt_b200_tensor* out, const vbt_b200_tensor* weight,
                                    const vbt_b200_tensor* idx, void* index_status, void* stream);
-vbt_b200_status vbt_b200_embedding_backward(const vbt_b200_tensor* grad_weight,
+VBT_B200_API vbt_b200_status vbt_b200_embedding_backward(const vbt_b200_tensor* grad_weight,
                                             const vbt_b200_tensor* idx,
                                             const vbt_b200_tensor* grad_out, int64_t padding_idx,
                                             void* index_status, void* stream);
 /* Synchronises `stream`, reads the status block; OK if count == 0, else OUT_OF_RANGE with
  * message "<what>: index out of range ..." and clears the block. */
-vbt_b200_status vbt_b200_index_status_check(void* index_status, const char* what, int64_t dim_size,
+VBT_B200_API vbt_b200_status vbt_b200_index_status_check(void* index_status, const char* what, int64_t dim_size,
                                             void* stream);
 
 /* =====================================================================================
@@ -308,10 +314,10 @@ vbt_b200_status vbt_b200_index_status_check(void* index_status, const char* what
  *    rmsnorm:  r = rsqrt(sum x^2 / cols + eps);  y = x*r*gamma;  inv_rms[row] = r
  *              gamma: F32 [cols] or NULL;  inv_rms: F32 [rows] or NULL.
  * ===================================================================================== */
-vbt_b200_status vbt_b200_softmax(void* out, const void* x, int32_t dtype, int64_t rows,
+VBT_B200_API vbt_b200_status vbt_b200_softmax(void* out, const void* x, int32_t dtype, int64_t rows,
                                  int64_t cols, int64_t x_row_stride, int32_t log_softmax,
                                  void* stream);
-vbt_b200_status vbt_b200_rmsnorm(void* out, float* inv_rms, const void* x, const float* gamma,
+VBT_B200_API vbt_b200_status vbt_b200_rmsnorm(void* out, float* inv_rms, const void* x, const float* gamma,
                                  int32_t dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
                                  float eps, void* stream);
 
@@ -328,13 +334,13 @@ vbt_b200_status vbt_b200_rmsnorm(void* out, float* inv_rms, const void* x, const
  * ===================================================================================== */
 /* partial (F32/I64, dense, reduced shape) = local SUM/MAX/MIN of the shard; BF16/F16
  * shards accumulate and emit FP32.  Same workspace contract as vbt_b200_reduce. */
-vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_tensor* partial,
+VBT_B200_API vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_tensor* partial,
                                         const vbt_b200_tensor* shard, const int64_t* dims,
                                         int32_t ndims, int32_t keepdim, void* workspace,
                                         size_t workspace_bytes, void* stream);
 /* out[i] = cast(partial[i] * scale): the "divide by the global N and cast" step of a
  * sharded mean.  partial F32 [n]; out F32/BF16/F16 [n]. */
-vbt_b200_status vbt_b200_scale_cast(void* out, int32_t out_dtype, const float* partial, int64_t n,
+VBT_B200_API vbt_b200_status vbt_b200_scale_cast(void* out, int32_t out_dtype, const float* partial, int64_t n,
                                     float scale, void* stream);
 
 #ifdef __cplusplus

@@ -1,0 +1,293 @@
+"""CUDA elementwise path vs the CPU oracle, through the C ABI (vibetensor_b200.ops is a thin
+ctypes layer).  Bit-exact for add/sub/mul/div, comparisons, where, copies, integer ops and
+the fused chains; 1e-5 (fp32) / 1e-2 (bf16, f16: one storage ulp) for transcendental ops."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests.util import CODE, as_f32, from_np, rand_storage, strided_like, to_np
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_vectors.npz"))
+FLOATS = [torch.float32, torch.bfloat16, torch.float16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from vibetensor_b200 import ops as o
+    return o
+
+
+EXACT_UNARY = ["relu", "neg", "abs", "square", "sign", "floor", "ceil", "trunc", "round", "relu6",
+               "hardtanh", "sqrt"]
+
+
+def _check_unary(ops, port, name, x_np, dtype):
+    got = to_np(ops.unary(name, from_np(x_np, dtype)))
+    want = port.unary(name, x_np, CODE[dtype])
+    if dtype == torch.int64 or name in EXACT_UNARY:
+        np.testing.assert_array_equal(got, want, err_msg=name)
+    else:
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        g, w = as_f32(got, dtype), as_f32(want, dtype)
+        fin = np.isfinite(w)
+        np.testing.assert_array_equal(np.isnan(g), np.isnan(w), err_msg=name)
+        np.testing.assert_allclose(g[fin], w[fin], rtol=tol, atol=tol if dtype != torch.float32 else 1e-6,
+                                   err_msg=name)
+
+
+@pytest.mark.parametrize("dtype", FLOATS)
+@pytest.mark.parametrize("name", oracle.UNARY)
+def test_unary_float(ops, port, name, dtype):
+    rng = np.random.default_rng(11)
+    x = 4 * rng.standard_normal((37, 129), dtype=np.float32)
+    if name in ("log", "sqrt", "rsqrt", "log1p", "reciprocal"):
+        x = np.abs(x) + 0.05
+    x.flat[:6] = [0.0, -0.0, 25.0, -25.0, 0.5, 2.5]
+    _check_unary(ops, port, name, oracle.to_storage(x, CODE[dtype]), dtype)
+
+
+@pytest.mark.parametrize("name", ["relu", "neg", "abs", "square", "sign", "floor", "round"])
+def test_unary_int64(ops, port, name):
+    rng = np.random.default_rng(12)
+    x = rng.integers(-2 ** 62, 2 ** 62, (33, 65)).astype(np.int64)
+    x.flat[:3] = [np.iinfo(np.int64).min, 0, np.iinfo(np.int64).max]
+    _check_unary(ops, port, name, x, torch.int64)
+
+
+def test_unary_rejects_integral_for_transcendental(ops):
+    with pytest.raises(ValueError, match="floating tensor expected"):
+        ops.exp(torch.ones(4, dtype=torch.int64, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", FLOATS + [torch.int64])
+@pytest.mark.parametrize("name", oracle.BINARY)
+def test_binary_broadcast_bit_exact(ops, port, name, dtype):
+    if dtype == torch.int64 and name == "div":
+        with pytest.raises(ValueError):
+            ops.div(torch.ones(2, dtype=dtype, device="cuda"), torch.ones(2, dtype=dtype, device="cuda"))
+        return
+    rng = np.random.default_rng(13)
+    a = rand_storage(rng, (6, 1, 40), dtype)
+    b = rand_storage(rng, (5, 40), dtype)
+    if dtype != torch.int64:
+        a.flat[0] = oracle.to_storage(np.array([np.nan], np.float32), CODE[dtype])[0]
+        b.flat[1] = a.flat[0]
+        b.flat[2] = a.flat[2]  # an equal pair for eq/le/ge
+    got = to_np(ops.binary(name, from_np(a, dtype), from_np(b, dtype)))
+    want = port.binary(name, a, b, CODE[dtype])
+    if dtype == torch.int64 or name in ("eq", "ne", "lt", "gt", "le", "ge"):
+        np.testing.assert_array_equal(got, want)
+    else:
+        g, w = as_f32(got, dtype), as_f32(want, dtype)
+        np.testing.assert_array_equal(np.isnan(g), np.isnan(w))
+        np.testing.assert_array_equal(g[~np.isnan(g)], w[~np.isnan(w)])
+
+
+def test_binary_golden_reference_vectors(ops):
+    a, b = GOLD["ew_a"], GOLD["ew_b"]
+    ta, tb = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    for op in ["add", "sub", "mul", "div"]:
+        np.testing.assert_array_equal(ops.binary(op, ta, tb).cpu().numpy(), GOLD["ew_" + op])
+    for op in ["eq", "ne", "lt", "gt", "le", "ge"]:
+        np.testing.assert_array_equal(to_np(ops.binary(op, ta, tb)), GOLD["ew_" + op])
+    for op in ["relu", "abs", "neg", "reciprocal"]:
+        np.testing.assert_array_equal(ops.unary(op, ta).cpu().numpy(), GOLD["ew_" + op])
+    ai, bi = torch.from_numpy(GOLD["ew_ai"]).cuda(), torch.from_numpy(GOLD["ew_bi"]).cuda()
+    for op in ["add", "sub", "mul"]:
+        np.testing.assert_array_equal(ops.binary(op, ai, bi).cpu().numpy(), GOLD["ew_i64_" + op])
+
+
+def test_broadcast_add_known_answer(ops):
+    # tests/cpp/cuda_elementwise_test.cc:343-394 of the reference
+    rows, cols = 2, 256
+    a = (np.arange(rows)[:, None] * 1000 + np.arange(cols)[None, :]).astype(np.float32)
+    b = (1.5 * np.arange(cols)).astype(np.float32)
+    got = ops.add(torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()).cpu().numpy()
+    np.testing.assert_array_equal(got, a + b)
+
+
+@pytest.mark.parametrize("left", [False, True])
+@pytest.mark.parametrize("name", ["add", "sub", "mul", "div", "gt", "maximum"])
+def test_binary_scalar_operand(ops, port, name, left):
+    rng = np.random.default_rng(14)
+    a = rng.standard_normal((17, 33), dtype=np.float32)
+    s = np.array(1.25, np.float32)
+    ta = torch.from_numpy(a).cuda()
+    got = to_np(ops.binary(name, 1.25, ta) if left else ops.binary(name, ta, 1.25))
+    want = port.binary(name, s, a, oracle.F32) if left else port.binary(name, a, s, oracle.F32)
+    np.testing.assert_array_equal(got, want)
+    with pytest.raises(ValueError, match="unsupported dtype for scalar op"):
+        ops.add(ta.bfloat16(), 1.0)
+    with pytest.raises(ValueError, match="Half CPU scalars"):
+        ops.add(ta.half(), 1.0)
+
+
+def test_dtype_mismatch_and_shape_errors(ops):
+    a = torch.ones(4, device="cuda")
+    with pytest.raises(ValueError, match="vt::add: dtype mismatch"):
+        ops.add(a, a.bfloat16())
+    with pytest.raises(ValueError, match="shape mismatch"):
+        ops.add(torch.ones(3, device="cuda"), torch.ones(4, device="cuda"), out=torch.ones(4, device="cuda"))
+    with pytest.raises(ValueError, match="25D"):
+        ops.add(torch.ones([1] * 26, device="cuda"), torch.ones([1] * 26, device="cuda"))
+    big = torch.ones([2] + [1] * 24, device="cuda")
+    assert ops.add(big, big).shape == big.shape  # rank 25 is accepted
+
+
+@pytest.mark.parametrize("dtype", FLOATS)
+@pytest.mark.parametrize("name", oracle.TERNARY)
+def test_ternary_bit_exact(ops, port, name, dtype):
+    rng = np.random.default_rng(15)
+    a = rand_storage(rng, (4, 1, 24, 1), dtype)
+    b = rand_storage(rng, (1, 16, 1, 8), dtype)
+    c = rand_storage(rng, (4, 16, 1, 8), dtype)
+    if name == "clamp":
+        b, c = port.binary("minimum", b, c, CODE[dtype]), port.binary("maximum", b, c, CODE[dtype])
+    got = to_np(ops.ternary(name, from_np(a, dtype), from_np(b, dtype), from_np(c, dtype)))
+    want = port.ternary(name, a, b, c, CODE[dtype])
+    if name == "addcdiv":
+        np.testing.assert_allclose(as_f32(got, dtype), as_f32(want, dtype), rtol=1e-6 if dtype == torch.float32 else 1e-2)
+    else:
+        np.testing.assert_array_equal(got, want)
+
+
+def _config3(rng, n0, d1, d2, d3):
+    a = rand_storage(rng, (n0, 1, d2, 1), torch.bfloat16)
+    b = rand_storage(rng, (1, d1, 1, d3), torch.bfloat16)
+    c = rand_storage(rng, (n0, d1, 1, d3), torch.bfloat16)
+    return a, b, c
+
+
+@pytest.mark.parametrize("shape", [(4, 16, 24, 8), (3, 128, 40, 16), (2, 24, 7, 5), (2, 8, 1, 8)])
+def test_config3_chain_into_transposed_output(ops, port, shape):
+    """where(a > 0, a + b*c, 0) in bf16 written into out_base.transpose(1, 3): the fused
+    entry, the four separate ops with out=, and the oracle all agree bit for bit."""
+    n0, d1, d2, d3 = shape
+    rng = np.random.default_rng(1)
+    a, b, c = _config3(rng, *shape)
+    ta, tb, tc = [from_np(v, torch.bfloat16) for v in (a, b, c)]
+    want = port.ternary("where_gt0_addcmul", a, b, c, oracle.BF16)  # [n0,d1,d2,d3]
+    base = torch.full((n0, d3, d2, d1), 7.0, dtype=torch.bfloat16, device="cuda")
+    out = base.transpose(1, 3)
+    ops.where_gt0_addcmul(ta, tb, tc, out=out)
+    np.testing.assert_array_equal(to_np(out), want)
+    # storage really is [n0, d3, d2, d1]
+    np.testing.assert_array_equal(to_np(base), np.ascontiguousarray(want.transpose(0, 3, 2, 1)))
+    # the same as the reference would chain it: mul -> add -> gt -> where
+    t1 = ops.mul(tb, tc)
+    t2 = ops.add(ta, t1)
+    m = ops.gt(ta, torch.zeros(1, dtype=torch.bfloat16, device="cuda"))
+    base2 = torch.zeros_like(base)
+    ops.where(m, t2, torch.zeros(1, dtype=torch.bfloat16, device="cuda"), out=base2.transpose(1, 3))
+    assert torch.equal(base2, base)
+    plan = ops.ti_plan(out, ta, tb, tc)
+    assert plan[0][0] == d1 and plan[1][0][0] == 1  # dim 0 is the dim the output is contiguous in
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int64, torch.bool])
+def test_where_and_masked_fill(ops, port, dtype):
+    rng = np.random.default_rng(16)
+    cond = rng.integers(0, 2, (5, 1, 33)).astype(np.uint8)
+    if dtype == torch.bool:
+        x = rng.integers(0, 2, (5, 4, 33)).astype(np.uint8)
+        y = rng.integers(0, 2, (1, 33)).astype(np.uint8)
+    else:
+        x = rand_storage(rng, (5, 4, 33), dtype)
+        y = rand_storage(rng, (1, 33), dtype)
+    got = to_np(ops.where(from_np(cond, torch.bool), from_np(x, dtype), from_np(y, dtype)))
+    want = port.where(cond, x, y, CODE[dtype])
+    np.testing.assert_array_equal(got, want)
+    with pytest.raises(ValueError, match="bool"):
+        ops.where(torch.ones(4, device="cuda"), torch.ones(4, device="cuda"), torch.ones(4, device="cuda"))
+
+
+def test_strided_inputs_negative_strides_and_offsets(ops, port):
+    rng = np.random.default_rng(17)
+    a_np = rng.standard_normal((9, 14), dtype=np.float32)
+    b_np = rng.standard_normal((9, 14), dtype=np.float32)
+    ta, va = strided_like(a_np, torch.float32, (3, 40), 1024, offset=5)      # transposed-ish, gaps
+    tb = torch.from_numpy(b_np).cuda().flip(1)                               # negative stride
+    got = ops.add(ta, tb).cpu().numpy()
+    np.testing.assert_array_equal(got, port.binary("add", va, b_np[:, ::-1], oracle.F32))
+    # strided (column-major) output
+    out = torch.empty((14, 9), device="cuda").t()
+    ops.mul(ta, tb, out=out)
+    np.testing.assert_array_equal(out.cpu().numpy(), a_np * b_np[:, ::-1])
+    # output walked backwards
+    out2 = torch.zeros((9, 14), device="cuda")
+    ops.sub(ta, tb, out=out2.flip(0))
+    np.testing.assert_array_equal(out2.cpu().numpy()[::-1], a_np - b_np[:, ::-1])
+
+
+def test_exhaustive_small_shapes_vs_oracle(ops, port):
+    """All stride patterns (dense, broadcast 0, gapped, reversed) over small ranks: every
+    offset the kernel computes is checked against the oracle's odometer."""
+    rng = np.random.default_rng(18)
+    sizes = [1, 2, 3, 5, 33]
+    for trial in range(60):
+        nd = int(rng.integers(1, 5))
+        shape = tuple(int(rng.choice(sizes)) for _ in range(nd))
+        bshape = tuple(s if rng.random() < 0.6 else 1 for s in shape)
+        a_np = rng.standard_normal(shape, dtype=np.float32)
+        b_np = rng.standard_normal(bshape, dtype=np.float32)
+        ta = torch.from_numpy(a_np).cuda()
+        if rng.random() < 0.5 and nd >= 2:
+            perm = list(rng.permutation(nd))
+            ta = torch.from_numpy(np.ascontiguousarray(a_np.transpose(perm))).cuda().permute(
+                *np.argsort(perm).tolist())
+        tb = torch.from_numpy(b_np).cuda()
+        got = ops.add(ta, tb).cpu().numpy()
+        np.testing.assert_array_equal(got, a_np + b_np, err_msg=f"{shape} {bshape}")
+
+
+def test_empty_and_scalar(ops):
+    e = torch.empty((0, 4), device="cuda")
+    assert ops.add(e, e).shape == (0, 4)
+    s = torch.tensor(3.0, device="cuda")
+    assert ops.mul(s, s).item() == 9.0
+    assert ops.relu(torch.tensor(-1.0, device="cuda")).item() == 0.0
+
+
+def test_misaligned_and_ragged_flat(ops):
+    x = torch.arange(1003, dtype=torch.float32, device="cuda")
+    for off in (0, 1, 3):
+        v = x[off:]
+        np.testing.assert_array_equal(ops.add(v, v).cpu().numpy(), 2 * v.cpu().numpy())
+    xb = torch.arange(517, dtype=torch.float32, device="cuda").bfloat16()
+    assert torch.equal(ops.add(xb[1:], xb[1:]), xb[1:] + xb[1:])
+
+
+def test_copy_contiguous(ops):
+    x = torch.arange(2 * 3 * 5, dtype=torch.float32, device="cuda").reshape(2, 3, 5).permute(2, 0, 1)
+    assert torch.equal(ops.contiguous(x), x.contiguous())
+    xi = torch.arange(30, dtype=torch.int64, device="cuda").reshape(5, 6).t()
+    assert torch.equal(ops.contiguous(xi), xi.contiguous())
+
+
+def test_overlap_is_rejected(ops):
+    x = torch.zeros(16, device="cuda")
+    with pytest.raises(ValueError, match="overlap"):
+        ops.add(x[:8], x[:8], out=torch.as_strided(x, (8,), (0,)))
+    with pytest.raises(ValueError, match="partially overlaps"):
+        ops.add(x[:8], x[:8], out=x[4:12])
+    ops.add(x[:8], x[:8], out=x[:8])  # exact in-place is fine
+
+
+def test_large_dim_over_2_31_elements_linearity(ops):
+    """> 2^31 output elements in one call (64-bit offsets): a[65536,1] + b[1,32769] in bf16,
+    checked on sampled positions and by a checksum that is linear in the inputs."""
+    n0, n1 = 65536, 32769
+    a = torch.arange(n0, device="cuda", dtype=torch.float32).remainder(7).bfloat16().reshape(n0, 1)
+    b = torch.arange(n1, device="cuda", dtype=torch.float32).remainder(5).bfloat16().reshape(1, n1)
+    out = ops.add(a, b)
+    assert out.numel() > 2 ** 31
+    for (i, j) in [(0, 0), (n0 - 1, n1 - 1), (40000, 32768), (65535, 1), (12345, 23456)]:
+        assert out[i, j].item() == float((i % 7) + (j % 5))
+    # row sums: sum_j (a_i + b_j) = n1*a_i + sum(b); exact in fp32 for these small integers
+    rs = out[::4096].float().sum(1).cpu().numpy()
+    ai = (np.arange(n0)[::4096] % 7).astype(np.float64)
+    np.testing.assert_array_equal(rs, n1 * ai + float((np.arange(n1) % 5).sum()))

@@ -1,0 +1,227 @@
+"""Row gather / scatter(-add) / last-dim index vs the CPU oracle through the C ABI.
+Gather, overwrite-scatter with distinct rows and int64 / int32 scatter-add are bit-exact;
+fp32 scatter-add is compared with 1e-5 * (sum of |updates| per destination element) because
+atomics do not fix the order of additions (neither does the reference's CUDA path)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests.util import from_np, to_np
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_vectors.npz"))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from vibetensor_b200 import ops as o
+    return o
+
+
+@pytest.fixture(scope="module")
+def kernels():
+    from vibetensor_b200 import kernels as k
+    return k
+
+
+def zipf_indices(rng, V, N, s=1.1):
+    """Bounded Zipf(s) over ranks 1..V, ranks scattered over rows by a permutation."""
+    p = np.arange(1, V + 1, dtype=np.float64) ** -s
+    ranks = np.searchsorted(np.cumsum(p / p.sum()), rng.random(N))
+    return rng.permutation(V)[np.minimum(ranks, V - 1)].astype(np.int64)
+
+
+def test_known_answers_from_reference_tests(ops):
+    # tests/cpp/indexing_advanced_cpu_kernel_test.cc:57-96, :149-226
+    base = torch.tensor([[10.], [11.], [12.], [13.], [14.]], device="cuda")
+    out = ops.index_rows(base, torch.tensor([0, 4, 2], device="cuda"))
+    assert out.flatten().tolist() == [10.0, 14.0, 12.0]
+    b = torch.zeros((4, 1), device="cuda")
+    ops.index_put_rows_(b, torch.tensor([1, 3], device="cuda"), torch.tensor([[5.], [7.]], device="cuda"))
+    assert b.flatten().tolist() == [0.0, 5.0, 0.0, 7.0]
+    ops.index_put_rows_(b, torch.tensor([1, 1], device="cuda"), torch.tensor([[1.], [2.]], device="cuda"),
+                        accumulate=True)
+    assert b[1, 0].item() == 8.0
+    # tests/py/test_tensor_index_put_accumulate_cub_env.py:47-80
+    idx = torch.tensor([0, 1, 0, 4], device="cuda")
+    x = torch.zeros((5, 1), device="cuda")
+    ops.index_put_rows_(x, idx, torch.tensor([[1.], [2.], [3.], [4.]], device="cuda"), accumulate=True)
+    assert x.flatten().tolist() == [4.0, 2.0, 0.0, 0.0, 4.0]
+    xi = torch.zeros((5, 1), dtype=torch.int64, device="cuda")
+    ops.index_put_rows_(xi, idx, torch.tensor([[1], [2], [3], [4]], device="cuda"), accumulate=True)
+    assert xi.flatten().tolist() == [4, 2, 0, 0, 4]
+
+
+def test_golden_reference_vectors(ops):
+    table, idx = torch.from_numpy(GOLD["ix_table"]).cuda(), torch.from_numpy(GOLD["ix_idx"]).cuda()
+    np.testing.assert_array_equal(ops.index_rows(table, idx).cpu().numpy(), GOLD["ix_gather"])
+    np.testing.assert_array_equal(ops.embedding(table, idx % 50).cpu().numpy(), GOLD["ix_embedding"])
+    acc = torch.zeros((50, 12), device="cuda")
+    ops.index_put_rows_(acc, idx, torch.from_numpy(GOLD["ix_vals"]).cuda(), accumulate=True)
+    np.testing.assert_allclose(acc.cpu().numpy(), GOLD["ix_put_acc"], rtol=1e-5, atol=1e-5)
+    acci = torch.zeros((50, 12), dtype=torch.int64, device="cuda")
+    ops.index_put_rows_(acci, idx, torch.from_numpy(GOLD["ix_vals_i64"]).cuda(), accumulate=True)
+    np.testing.assert_array_equal(acci.cpu().numpy(), GOLD["ix_put_acc_i64"])
+    t2 = table.clone()
+    ops.index_put_rows_(t2, torch.from_numpy(GOLD["ix_perm"]).cuda(),
+                        torch.from_numpy(GOLD["ix_vals"][:30].copy()).cuda())
+    np.testing.assert_array_equal(t2.cpu().numpy(), GOLD["ix_put_overwrite"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int64, torch.int32, torch.bool])
+@pytest.mark.parametrize("V,D,N", [(1000, 256, 5000), (333, 7, 1000), (64, 4, 300), (50, 1024, 200),
+                                   (10, 2048 + 4, 100), (5, 1, 0)])
+def test_gather_rows_bit_exact(ops, port, dtype, V, D, N):
+    rng = np.random.default_rng(31)
+    if dtype in (torch.float32,):
+        table = rng.standard_normal((V, D), dtype=np.float32)
+    elif dtype == torch.bfloat16:
+        table = rng.integers(0, 2 ** 16, (V, D)).astype(np.uint16)
+    elif dtype == torch.bool:
+        table = rng.integers(0, 2, (V, D)).astype(np.uint8)
+    else:
+        table = rng.integers(-10 ** 6, 10 ** 6, (V, D)).astype(np.int64 if dtype == torch.int64 else np.int32)
+    idx = rng.integers(-V, V, N).astype(np.int64)
+    got = to_np(ops.index_rows(from_np(table, dtype), torch.from_numpy(idx).cuda()))
+    np.testing.assert_array_equal(got.view(table.dtype), port.gather_rows(table, idx))
+
+
+def test_gather_strided_table_and_int32_index(ops, port):
+    rng = np.random.default_rng(32)
+    big = rng.standard_normal((200, 96), dtype=np.float32)
+    tb = torch.from_numpy(big).cuda()
+    idx = rng.integers(0, 200, 777)
+    for view_np, view_t in ((big[:, 8:72], tb[:, 8:72]), (big[::2], tb[::2]), (big.T[:50], tb.t()[:50])):
+        i = idx % view_np.shape[0]
+        got = ops.index_rows(view_t, torch.from_numpy(i.astype(np.int32)).cuda()).cpu().numpy()
+        np.testing.assert_array_equal(got, port.gather_rows(view_np, i))
+    # 2-D index
+    i2 = (idx[:60] % 200).reshape(6, 10)
+    got = ops.index_rows(tb, torch.from_numpy(i2).cuda()).cpu().numpy()
+    np.testing.assert_array_equal(got, port.gather_rows(big, i2))
+
+
+@pytest.mark.parametrize("V,D,N", [(1000, 256, 20000), (97, 64, 5000), (40, 8, 3000), (16, 516, 999),
+                                   (300, 3, 2000)])
+def test_scatter_add_zipf(ops, port, V, D, N):
+    rng = np.random.default_rng(33)
+    idx = zipf_indices(rng, V, N)
+    ti = torch.from_numpy(idx).cuda()
+    # int64: exact whatever the order
+    vi = rng.integers(-1000, 1001, (N, D)).astype(np.int64)
+    acc = torch.zeros((V, D), dtype=torch.int64, device="cuda")
+    ops.index_put_rows_(acc, ti, torch.from_numpy(vi).cuda(), accumulate=True)
+    np.testing.assert_array_equal(acc.cpu().numpy(), port.scatter_rows(np.zeros((V, D), np.int64), idx, vi, oracle.I64))
+    v32 = vi.astype(np.int32)
+    acc32 = torch.zeros((V, D), dtype=torch.int32, device="cuda")
+    ops.index_put_rows_(acc32, ti, torch.from_numpy(v32).cuda(), accumulate=True)
+    np.testing.assert_array_equal(acc32.cpu().numpy(), port.scatter_rows(np.zeros((V, D), np.int32), idx, v32, oracle.I32))
+    # fp32: tolerance relative to the mass added into each element
+    vf = rng.standard_normal((N, D), dtype=np.float32)
+    init = rng.standard_normal((V, D), dtype=np.float32)
+    accf = torch.from_numpy(init.copy()).cuda()
+    ops.index_put_rows_(accf, ti, torch.from_numpy(vf).cuda(), accumulate=True)
+    want = port.scatter_rows(init.copy(), idx, vf, oracle.F32)
+    mass = port.scatter_rows(np.abs(init), idx, np.abs(vf), oracle.F32)
+    err = np.abs(accf.cpu().numpy().astype(np.float64) - want)
+    assert (err <= 1e-5 * mass + 1e-30).all(), err.max()
+
+
+def test_scatter_overwrite_unique_rows_and_negative(ops, port):
+    rng = np.random.default_rng(34)
+    V, D = 500, 64
+    table = rng.standard_normal((V, D), dtype=np.float32)
+    idx = rng.permutation(V)[:300].astype(np.int64)
+    idx[::3] -= V
+    vals = rng.standard_normal((300, D), dtype=np.float32)
+    t = torch.from_numpy(table.copy()).cuda()
+    ops.index_put_rows_(t, torch.from_numpy(idx).cuda(), torch.from_numpy(vals).cuda())
+    np.testing.assert_array_equal(t.cpu().numpy(), port.scatter_rows(table.copy(), idx, vals, oracle.F32, accumulate=False))
+
+
+def test_out_of_range_is_reported_not_faulted(ops):
+    table = torch.arange(12, dtype=torch.float32, device="cuda").reshape(4, 3)
+    for bad in ([1, 4], [-5, 0]):
+        with pytest.raises(IndexError, match="out of range"):
+            ops.index_rows(table, torch.tensor(bad, device="cuda"))
+    with pytest.raises(IndexError, match="vt::embedding"):
+        ops.embedding(table, torch.tensor([-1], device="cuda"))
+    # lazy mode: the good rows are produced, the bad one is zero, the status says so
+    st = ops.IndexStatus("cuda")
+    out = ops.index_rows(table, torch.tensor([3, 9, 0], device="cuda"), status=st)
+    assert out.tolist() == [[9., 10., 11.], [0., 0., 0.], [0., 1., 2.]]
+    with pytest.raises(IndexError):
+        st.check("index", 4)
+    st.check("index", 4)  # cleared after reporting
+    t2 = torch.zeros((4, 3), device="cuda")
+    with pytest.raises(IndexError):
+        ops.index_put_rows_(t2, torch.tensor([0, 7], device="cuda"), torch.ones((2, 3), device="cuda"), accumulate=True)
+    assert t2.tolist()[0] == [1., 1., 1.] and t2.sum().item() == 3.0
+    with pytest.raises(ValueError, match="Int32 and Int64"):
+        ops.index_rows(table, torch.tensor([0.0], device="cuda"))
+
+
+def test_embedding_backward_duplicates_and_padding(ops):
+    # tests/py/test_embedding_backward_cuda.py:31-60 of the reference
+    idx = torch.tensor([0, 2, 2, 2, 1], device="cuda")
+    g = torch.arange(15, dtype=torch.float32, device="cuda").reshape(5, 3)
+    gw = ops.embedding_backward(g, idx, 5, padding_idx=1).cpu().numpy()
+    gn = g.cpu().numpy()
+    exp = np.zeros((5, 3), np.float32)
+    exp[0] += gn[0]
+    exp[2] += gn[1] + gn[2] + gn[3]
+    np.testing.assert_allclose(gw, exp, rtol=1e-6, atol=1e-6)
+
+
+def test_lastdim_index_and_put(ops, port):
+    rng = np.random.default_rng(35)
+    src = rng.standard_normal((37, 50), dtype=np.float32)
+    idx = rng.integers(-50, 50, 123).astype(np.int64)
+    ts = torch.from_numpy(src).cuda()
+    np.testing.assert_array_equal(ops.index_lastdim(ts, torch.from_numpy(idx).cuda()).cpu().numpy(),
+                                  port.index_lastdim(src, idx))
+    np.testing.assert_array_equal(ops.index_lastdim(ts.t(), torch.from_numpy(idx[:20] % 37).cuda()).cpu().numpy(),
+                                  port.index_lastdim(src.T, idx[:20] % 37))
+    vals = rng.integers(-9, 10, (37, 123)).astype(np.int64)
+    self_ = np.zeros((37, 50), np.int64)
+    t = torch.from_numpy(self_.copy()).cuda()
+    ops.index_put_lastdim_(t, torch.from_numpy(idx).cuda(), torch.from_numpy(vals).cuda(), accumulate=True)
+    np.testing.assert_array_equal(t.cpu().numpy(), port.index_put_lastdim(self_.copy(), idx, vals, oracle.I64, True))
+
+
+def test_vibe_kernels_gather_scatter_add_surface(kernels, port):
+    # vibe_kernels/indexing/tests/test_vbt_native.py:45-66 of the reference
+    src = np.arange(32, dtype=np.float32).reshape(4, 8)
+    idx = np.array([1, 3, 0], np.int64)
+    out = kernels.gather(torch.from_numpy(src).cuda(), 0, torch.from_numpy(idx).cuda())
+    np.testing.assert_array_equal(out.cpu().numpy(), src[idx])
+    dst = torch.zeros((4, 8), device="cuda")
+    kernels.scatter_add(dst, 0, torch.tensor([1, 1, 9], device="cuda"), torch.ones((3, 8), device="cuda"))
+    assert dst[1].tolist() == [2.0] * 8 and dst[3].tolist() == [1.0] * 8  # 9 is clamped to row 3
+    with pytest.raises(NotImplementedError):
+        kernels.gather(torch.from_numpy(src).cuda(), 1, torch.from_numpy(idx).cuda())
+    with pytest.raises(TypeError):
+        kernels.gather(torch.from_numpy(src).cuda(), 0, torch.from_numpy(idx.astype(np.int32)).cuda())
+
+
+def test_config2_scale_roundtrip_properties(ops):
+    """Full table shape of the benchmark configuration ([1,048,576 x 256] fp32), reduced
+    index count: gather(idx) of a table whose row r is filled with r returns idx; scatter-add
+    of ones counts occurrences exactly (small integers are exact in fp32)."""
+    V, D, N = 1 << 20, 256, 1 << 18
+    rng = np.random.default_rng(2)
+    idx = zipf_indices(rng, V, N)
+    ti = torch.from_numpy(idx).cuda()
+    table = torch.arange(V, dtype=torch.float32, device="cuda").reshape(V, 1).expand(V, D).contiguous()
+    out = ops.index_rows(table, ti)
+    assert torch.equal(out[:, 0].long(), ti) and torch.equal(out[:, -1].long(), ti)
+    acc = torch.zeros((V, D), device="cuda")
+    ops.index_put_rows_(acc, ti, torch.ones((N, D), device="cuda"), accumulate=True)
+    counts = torch.bincount(ti, minlength=V).float()
+    assert torch.equal(acc[:, 0], counts) and torch.equal(acc[:, 255], counts)
+    acci = torch.zeros((V, D), dtype=torch.int64, device="cuda")
+    ops.index_put_rows_(acci, ti, torch.full((N, D), 3, dtype=torch.int64, device="cuda"), accumulate=True)
+    assert torch.equal(acci[:, 17], 3 * counts.long())

@@ -1,0 +1,306 @@
+// Elementwise kernels over a TiPlan (sm_100a).
+//
+// Two kernels replace the reference's dense / *_ti_strided_kernel family
+// (src/vbt/ops/cuda_elementwise.cu:1409-1663, :2216-2246, :2534-2569, :2645-2662):
+//
+//   ew_flat_kernel   every operand is contiguous or a single broadcast value: 16-byte
+//                    vectors, several per thread in flight.
+//   ew_tiled_kernel  general broadcast / strided case.  Dim 0 is the dim the OUTPUT is
+//                    contiguous in; a thread owns one 16-byte output vector along dim 0 and
+//                    walks dim 1, so stores stay coalesced whatever the inputs look like.
+//                    Offsets of the outer dims are decoded ONCE per block with 32-bit
+//                    multiply-shift division; inside the loop there is only pointer
+//                    stepping.  Operands that do not vary along dim 1 are loaded once and
+//                    stay in registers (a broadcast operand, or a "transposed" operand whose
+//                    rows have to be gathered element-wise, costs nothing per output row).
+//
+// The reference decodes every element's offset with up to 2*ndim 64-bit divisions per
+// operand (include/vbt/core/tensor_iterator/cuda.h:25-42).
+#pragma once
+#include <algorithm>
+
+#include "ti_plan.h"
+
+namespace vb {
+
+constexpr int kMaxOuter = VBT_B200_MAX_NDIM - 2;
+constexpr int kEwThreads = 256;
+constexpr int kEwUnroll = 4;
+
+template <int NOPS>
+struct TiledParams {
+  char* ptr[NOPS];
+  int64_t s0[NOPS];
+  int64_t s1[NOPS];
+  int64_t so[NOPS][kMaxOuter];
+  FastDiv odiv[kMaxOuter];
+  FastDiv div_t0, div_t1;
+  int n_outer;
+  uint32_t n0v;   // vectors along dim 0
+  int64_t size1;
+  int log2_w0;    // threads along dim 0 = 1 << log2_w0
+  int L;          // dim-1 passes per block
+};
+
+template <int NOPS>
+struct FlatParams {
+  char* ptr[NOPS];
+  int s[NOPS];  // 0 or 1
+  int64_t n;    // elements
+};
+
+template <class T, int V>
+__device__ __forceinline__ Vec<T, V> load_vec(const T* p, int64_t s0) {
+  Vec<T, V> r;
+  if constexpr (V == 1) {
+    r.v[0] = *p;
+  } else {
+    if (s0 == 1) {
+      r = *reinterpret_cast<const Vec<T, V>*>(p);
+    } else if (s0 == 0) {
+      const T x = *p;
+#pragma unroll
+      for (int j = 0; j < V; ++j) r.v[j] = x;
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) r.v[j] = p[j * s0];
+    }
+  }
+  return r;
+}
+
+template <class F, class TO, class T1, class T2, class T3, int NIN, int V>
+__device__ __forceinline__ Vec<TO, V> apply_vec(const F& f, const Vec<T1, V>& a,
+                                                const Vec<T2, V>& b, const Vec<T3, V>& c) {
+  Vec<TO, V> o;
+#pragma unroll
+  for (int j = 0; j < V; ++j) o.v[j] = f(a.v[j], b.v[j], c.v[j]);
+  return o;
+}
+
+// INV: bitmask of inputs known at compile time not to vary along dim 1 (bit 0 = first
+// input); -1 = decide at run time from the strides (loads are hoisted, arithmetic is not).
+template <class F, class TO, class T1, class T2, class T3, int NIN, int V, int INV>
+__global__ void __launch_bounds__(kEwThreads)
+ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
+  uint32_t b = blockIdx.x, t0, t1;
+  p.div_t0.divmod(b, b, t0);
+  p.div_t1.divmod(b, b, t1);
+  int64_t base[NIN + 1];
+#pragma unroll
+  for (int k = 0; k <= NIN; ++k) base[k] = 0;
+  for (int d = 0; d < p.n_outer; ++d) {
+    uint32_t c;
+    p.odiv[d].divmod(b, b, c);
+#pragma unroll
+    for (int k = 0; k <= NIN; ++k) base[k] += static_cast<int64_t>(c) * p.so[k][d];
+  }
+  const uint32_t w0 = 1u << p.log2_w0;
+  const uint32_t tx = threadIdx.x & (w0 - 1), ty = threadIdx.x >> p.log2_w0;
+  const int R = kEwThreads >> p.log2_w0;
+  const uint32_t v = t0 * w0 + tx;
+  if (v >= p.n0v) return;
+  const int64_t row0 = static_cast<int64_t>(t1) * (static_cast<int64_t>(R) * p.L) + ty;
+  if (row0 >= p.size1) return;
+  const int64_t rows_left = (p.size1 - row0 + R - 1) / R;
+  const int n = rows_left < p.L ? static_cast<int>(rows_left) : p.L;
+#pragma unroll
+  for (int k = 0; k <= NIN; ++k) base[k] += static_cast<int64_t>(v) * V * p.s0[k] + row0 * p.s1[k];
+
+  TO* po = reinterpret_cast<TO*>(p.ptr[0]) + base[0];
+  const T1* p1 = reinterpret_cast<const T1*>(p.ptr[1]) + base[1];
+  const T2* p2 = NIN >= 2 ? reinterpret_cast<const T2*>(p.ptr[NIN >= 2 ? 2 : 0]) + base[NIN >= 2 ? 2 : 0] : nullptr;
+  const T3* p3 = NIN >= 3 ? reinterpret_cast<const T3*>(p.ptr[NIN >= 3 ? 3 : 0]) + base[NIN >= 3 ? 3 : 0] : nullptr;
+  const int64_t so_ = R * p.s1[0];
+  const int64_t st1 = R * p.s1[1];
+  const int64_t st2 = NIN >= 2 ? R * p.s1[NIN >= 2 ? 2 : 0] : 0;
+  const int64_t st3 = NIN >= 3 ? R * p.s1[NIN >= 3 ? 3 : 0] : 0;
+  const int64_t s01 = p.s0[1];
+  const int64_t s02 = NIN >= 2 ? p.s0[NIN >= 2 ? 2 : 0] : 0;
+  const int64_t s03 = NIN >= 3 ? p.s0[NIN >= 3 ? 3 : 0] : 0;
+  const bool inv1 = INV >= 0 ? ((INV >> 0) & 1) : (st1 == 0);
+  const bool inv2 = NIN >= 2 && (INV >= 0 ? ((INV >> 1) & 1) : (st2 == 0));
+  const bool inv3 = NIN >= 3 && (INV >= 0 ? ((INV >> 2) & 1) : (st3 == 0));
+
+  Vec<T1, V> a0{};
+  Vec<T2, V> b0{};
+  Vec<T3, V> c0{};
+  if (inv1) a0 = load_vec<T1, V>(p1, s01);
+  if constexpr (NIN >= 2) { if (inv2) b0 = load_vec<T2, V>(p2, s02); }
+  if constexpr (NIN >= 3) { if (inv3) c0 = load_vec<T3, V>(p3, s03); }
+
+  int l = 0;
+  for (; l + kEwUnroll <= n; l += kEwUnroll) {
+    Vec<T1, V> a[kEwUnroll];
+    Vec<T2, V> bb[kEwUnroll];
+    Vec<T3, V> c[kEwUnroll];
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; ++u) {
+      a[u] = inv1 ? a0 : load_vec<T1, V>(p1 + (l + u) * st1, s01);
+      if constexpr (NIN >= 2) bb[u] = inv2 ? b0 : load_vec<T2, V>(p2 + (l + u) * st2, s02);
+      else bb[u] = b0;
+      if constexpr (NIN >= 3) c[u] = inv3 ? c0 : load_vec<T3, V>(p3 + (l + u) * st3, s03);
+      else c[u] = c0;
+    }
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; ++u) {
+      const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(f, a[u], bb[u], c[u]);
+      if constexpr (V == 1) po[(l + u) * so_] = o.v[0];
+      else *reinterpret_cast<Vec<TO, V>*>(po + (l + u) * so_) = o;
+    }
+  }
+  for (; l < n; ++l) {
+    const Vec<T1, V> a = inv1 ? a0 : load_vec<T1, V>(p1 + l * st1, s01);
+    Vec<T2, V> bb = b0;
+    Vec<T3, V> c = c0;
+    if constexpr (NIN >= 2) { if (!inv2) bb = load_vec<T2, V>(p2 + l * st2, s02); }
+    if constexpr (NIN >= 3) { if (!inv3) c = load_vec<T3, V>(p3 + l * st3, s03); }
+    const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(f, a, bb, c);
+    if constexpr (V == 1) po[l * so_] = o.v[0];
+    else *reinterpret_cast<Vec<TO, V>*>(po + l * so_) = o;
+  }
+}
+
+template <class F, class TO, class T1, class T2, class T3, int NIN, int V>
+__global__ void __launch_bounds__(kEwThreads)
+ew_flat_kernel(const __grid_constant__ FlatParams<NIN + 1> p, const F f) {
+  const int64_t nvec = p.n / V;
+  TO* po = reinterpret_cast<TO*>(p.ptr[0]);
+  const T1* p1 = reinterpret_cast<const T1*>(p.ptr[1]);
+  const T2* p2 = reinterpret_cast<const T2*>(p.ptr[NIN >= 2 ? 2 : 0]);
+  const T3* p3 = reinterpret_cast<const T3*>(p.ptr[NIN >= 3 ? 3 : 0]);
+  const int s1 = p.s[1], s2 = NIN >= 2 ? p.s[NIN >= 2 ? 2 : 0] : 0, s3 = NIN >= 3 ? p.s[NIN >= 3 ? 3 : 0] : 0;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * (kEwThreads * kEwUnroll) + threadIdx.x;
+  Vec<T1, V> a[kEwUnroll];
+  Vec<T2, V> bb[kEwUnroll];
+  Vec<T3, V> c[kEwUnroll];
+#pragma unroll
+  for (int u = 0; u < kEwUnroll; ++u) {
+    const int64_t i = first + u * kEwThreads;
+    bb[u] = Vec<T2, V>{};
+    c[u] = Vec<T3, V>{};
+    if (i < nvec) {
+      a[u] = load_vec<T1, V>(p1 + i * V * s1, s1);
+      if constexpr (NIN >= 2) bb[u] = load_vec<T2, V>(p2 + i * V * s2, s2);
+      if constexpr (NIN >= 3) c[u] = load_vec<T3, V>(p3 + i * V * s3, s3);
+    } else {
+      a[u] = Vec<T1, V>{};
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kEwUnroll; ++u) {
+    const int64_t i = first + u * kEwThreads;
+    if (i < nvec) {
+      const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(f, a[u], bb[u], c[u]);
+      *reinterpret_cast<Vec<TO, V>*>(po + i * V) = o;
+    }
+  }
+  if constexpr (V > 1) {  // ragged tail, at most V-1 elements
+    if (blockIdx.x == 0) {
+      const int64_t i = nvec * V + threadIdx.x;
+      if (i < p.n) {
+        T2 bv{};
+        T3 cv{};
+        if constexpr (NIN >= 2) bv = p2[i * s2];
+        if constexpr (NIN >= 3) cv = p3[i * s3];
+        po[i] = f(p1[i * s1], bv, cv);
+      }
+    }
+  }
+}
+
+// Host: picks the kernel for the plan and launches it.  INV_SPECIAL >= 0 additionally
+// instantiates the tiled vector kernel for that compile-time invariance mask and uses it
+// when the plan's strides match it.
+template <class F, class TO, class T1, class T2, class T3, int NIN, int INV_SPECIAL = -1>
+vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
+  if (plan.numel == 0) return VBT_B200_OK;
+  constexpr int kMaxEs = static_cast<int>(std::max({sizeof(TO), sizeof(T1), NIN >= 2 ? sizeof(T2) : size_t{1},
+                                                    NIN >= 3 ? sizeof(T3) : size_t{1}}));
+  constexpr int V = 16 / kMaxEs;
+  bool flat_vec = false;
+  const TiKernel kind = choose_ti_kernel(plan, V, &flat_vec);
+  if (kind == kTiFlat) {
+    FlatParams<NIN + 1> fp{};
+    for (int k = 0; k <= NIN; ++k) {
+      fp.ptr[k] = plan.ptr[k];
+      fp.s[k] = static_cast<int>(plan.stride[k][0]);
+    }
+    fp.n = plan.numel;
+    if (flat_vec) {
+      const int64_t nvec = plan.numel / V;
+      const int64_t blocks = std::max<int64_t>(1, (nvec + kEwThreads * kEwUnroll - 1) / (kEwThreads * kEwUnroll));
+      VB_ARG(blocks <= 0x7fffffff, "elementwise: tensor too large for one launch");
+      ew_flat_kernel<F, TO, T1, T2, T3, NIN, V><<<static_cast<unsigned>(blocks), kEwThreads, 0, stream>>>(fp, f);
+    } else {
+      const int64_t blocks = (plan.numel + kEwThreads * kEwUnroll - 1) / (kEwThreads * kEwUnroll);
+      VB_ARG(blocks <= 0x7fffffff, "elementwise: tensor too large for one launch");
+      ew_flat_kernel<F, TO, T1, T2, T3, NIN, 1><<<static_cast<unsigned>(blocks), kEwThreads, 0, stream>>>(fp, f);
+    }
+    VB_LAUNCH_CHECK();
+    return VBT_B200_OK;
+  }
+
+  const bool vec = kind == kTiTiledVec;
+  const int v = vec ? V : 1;
+  TiledParams<NIN + 1> tp{};
+  const int nd = plan.ndim;
+  const int64_t size0 = plan.shape[0];
+  const int64_t size1 = nd >= 2 ? plan.shape[1] : 1;
+  const int64_t n0v = size0 / v;
+  VB_ARG(n0v <= 0x7fffffff && size1 <= (int64_t{1} << 40), "elementwise: dim too large");
+  for (int k = 0; k <= NIN; ++k) {
+    tp.ptr[k] = plan.ptr[k];
+    tp.s0[k] = plan.stride[k][0];
+    tp.s1[k] = nd >= 2 ? plan.stride[k][1] : 0;
+    for (int d = 2; d < nd; ++d) tp.so[k][d - 2] = plan.stride[k][d];
+  }
+  tp.n_outer = std::max(0, nd - 2);
+  int64_t outer = 1;
+  for (int d = 2; d < nd; ++d) {
+    VB_ARG(plan.shape[d] <= 0x7fffffff, "elementwise: dim too large");
+    tp.odiv[d - 2] = FastDiv(static_cast<uint32_t>(plan.shape[d]));
+    outer *= plan.shape[d];
+  }
+  int log2_w0 = 0;
+  while ((int64_t{1} << log2_w0) < n0v && (1 << log2_w0) < kEwThreads) ++log2_w0;
+  const int w0 = 1 << log2_w0;
+  const int R = kEwThreads / w0;
+  const int64_t tiles0 = (n0v + w0 - 1) / w0;
+  // rows per block: long enough to amortise the per-block offset decode and to reuse
+  // hoisted operands, short enough to leave >= ~16 blocks per SM when the tensor allows
+  int L = static_cast<int>(std::min<int64_t>(32, (size1 + R - 1) / R));
+  const int sms = 148;
+  while (L > 4 && tiles0 * ((size1 + int64_t{R} * L - 1) / (int64_t{R} * L)) * outer < int64_t{sms} * 16) L /= 2;
+  L = std::max(L, 1);
+  const int64_t tiles1 = (size1 + int64_t{R} * L - 1) / (int64_t{R} * L);
+  const int64_t blocks = tiles0 * tiles1 * outer;
+  VB_ARG(blocks <= 0x7fffffff && tiles0 <= 0x7fffffff && tiles1 <= 0x7fffffff,
+         "elementwise: tensor too large for one launch");
+  tp.div_t0 = FastDiv(static_cast<uint32_t>(tiles0));
+  tp.div_t1 = FastDiv(static_cast<uint32_t>(tiles1));
+  tp.n0v = static_cast<uint32_t>(n0v);
+  tp.size1 = size1;
+  tp.log2_w0 = log2_w0;
+  tp.L = L;
+  const unsigned g = static_cast<unsigned>(blocks);
+  if (vec) {
+    if constexpr (INV_SPECIAL >= 0) {
+      int mask = 0;
+      for (int k = 1; k <= NIN; ++k)
+        if (tp.s1[k] == 0) mask |= 1 << (k - 1);
+      if (mask == INV_SPECIAL) {
+        ew_tiled_kernel<F, TO, T1, T2, T3, NIN, V, INV_SPECIAL><<<g, kEwThreads, 0, stream>>>(tp, f);
+        VB_LAUNCH_CHECK();
+        return VBT_B200_OK;
+      }
+    }
+    ew_tiled_kernel<F, TO, T1, T2, T3, NIN, V, -1><<<g, kEwThreads, 0, stream>>>(tp, f);
+  } else {
+    ew_tiled_kernel<F, TO, T1, T2, T3, NIN, 1, -1><<<g, kEwThreads, 0, stream>>>(tp, f);
+  }
+  VB_LAUNCH_CHECK();
+  return VBT_B200_OK;
+}
+
+}  // namespace vb

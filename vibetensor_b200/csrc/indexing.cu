@@ -1,0 +1,586 @@
+// Row gather, row scatter / scatter-add, last-dim index / index_put (sm_100a).
+//
+// Replaces embedding_gather_f32_kernel / embedding_backward_accum_f32_kernel (one thread
+// and one 64-bit division per scalar, grid capped at 65 535 blocks;
+// src/vbt/ops/embedding_cuda.cu:47-87), advanced_index_cuda_kernel /
+// advanced_index_put_cuda_kernel (per-element coordinate decode;
+// src/vbt/core/indexing_advanced_cuda.cu:1325-1453) and the Triton gather / scatter_add
+// kernels (vibe_kernels/indexing/kernels.py:13-186).
+//
+//   gather        the output is a flat run of 16-byte chunks; a thread moves four chunks,
+//                 a warp always covers 512 contiguous bytes of one table row.
+//   scatter-add   a block takes 256 updates, sorts their (row, position) keys in shared
+//                 memory, and each warp walks 32 sorted entries: equal rows are summed in
+//                 registers (in update order) and leave the block as ONE vector atomic per
+//                 16-byte chunk (red.global.add.v4.f32 / 64-bit integer atomics).  With
+//                 Zipf-distributed rows this removes most same-address atomic traffic.
+//
+// Bad indices never fault: they are skipped and counted in the caller's status block.
+#include "common.cuh"
+
+namespace vb {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct IndexSrc {
+  const void* idx;
+  int is32;
+  __device__ __forceinline__ int64_t get(int64_t i) const {
+    return is32 ? static_cast<int64_t>(static_cast<const int32_t*>(idx)[i])
+                : static_cast<const int64_t*>(idx)[i];
+  }
+};
+
+// returns false for an index that must be skipped (and records it)
+__device__ __forceinline__ bool normalize(int64_t& v, int64_t V, int policy, unsigned long long* status,
+                                          bool record) {
+  if (policy == VBT_B200_INDEX_CLAMP) {
+    v = v < 0 ? 0 : (v > V - 1 ? V - 1 : v);
+    if (V > 0) return true;
+  } else {
+    const int64_t raw = v;
+    if (policy == VBT_B200_INDEX_WRAP && v < 0) v += V;
+    if (v >= 0 && v < V) return true;
+    v = raw;
+  }
+  if (record && status) {
+    if (atomicAdd(&status[0], 1ull) == 0ull) status[1] = static_cast<unsigned long long>(v);
+  }
+  return false;
+}
+
+struct GatherParams {
+  const char* table;
+  char* out;
+  IndexSrc idx;
+  int64_t N, V;
+  int64_t row_stride_bytes;
+  uint32_t cpr;       // 16-byte chunks per row
+  FastDiv div_cpr;
+  int64_t total;      // N * cpr
+  int policy;
+  unsigned long long* status;
+  int scatter;        // 0: out[i] = table[idx[i]]   1: table[idx[i]] = out[i]
+};
+
+// chunk-flat row copy, both directions
+__global__ void __launch_bounds__(kThreads) rows_copy_kernel(const __grid_constant__ GatherParams p) {
+  constexpr int U = 4;
+  const int64_t g0 = static_cast<int64_t>(blockIdx.x) * (kThreads * U) + threadIdx.x;
+  int4 data[U];
+  int64_t dst_off[U];
+  bool ok[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int64_t g = g0 + u * kThreads;
+    ok[u] = false;
+    data[u] = make_int4(0, 0, 0, 0);
+    if (g < p.total) {
+      // N < 2^31 is guaranteed by the host; the 64-bit division only runs for huge outputs
+      uint32_t row, c;
+      if (p.total <= 0x7fffffff) {
+        p.div_cpr.divmod(static_cast<uint32_t>(g), row, c);
+      } else {
+        row = static_cast<uint32_t>(g / p.cpr);
+        c = static_cast<uint32_t>(g - static_cast<int64_t>(row) * p.cpr);
+      }
+      int64_t v = p.idx.get(row);
+      const bool good = normalize(v, p.V, p.policy, p.status, c == 0);
+      const int64_t toff = v * p.row_stride_bytes + static_cast<int64_t>(c) * 16;
+      if (!p.scatter) {
+        ok[u] = true;
+        dst_off[u] = g * 16;
+        if (good) data[u] = *reinterpret_cast<const int4*>(p.table + toff);
+      } else if (good) {
+        ok[u] = true;
+        dst_off[u] = toff;
+        data[u] = *reinterpret_cast<const int4*>(p.out + g * 16);
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    if (ok[u]) {
+      char* dst = p.scatter ? const_cast<char*>(p.table) : p.out;
+      *reinterpret_cast<int4*>(dst + dst_off[u]) = data[u];
+    }
+  }
+}
+
+// element-wise fallback: any element size, any strides
+struct ElemParams {
+  const char* table;
+  char* out;
+  IndexSrc idx;
+  int64_t N, V, D;
+  int64_t s0, s1;  // table strides, elements
+  int es;
+  int policy;
+  unsigned long long* status;
+  int scatter;
+};
+__global__ void __launch_bounds__(kThreads) rows_copy_elem_kernel(const __grid_constant__ ElemParams p) {
+  const int64_t e = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (e >= p.N * p.D) return;
+  const int64_t row = e / p.D, j = e - row * p.D;
+  int64_t v = p.idx.get(row);
+  const bool good = normalize(v, p.V, p.policy, p.status, j == 0);
+  const char* t = p.table + (v * p.s0 + j * p.s1) * p.es;
+  char* o = p.out + e * p.es;
+  if (!p.scatter) {
+    for (int b = 0; b < p.es; ++b) o[b] = good ? t[b] : 0;
+  } else if (good) {
+    char* tw = const_cast<char*>(t);
+    for (int b = 0; b < p.es; ++b) tw[b] = o[b];
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// scatter-add with in-block duplicate aggregation
+// ------------------------------------------------------------------------------------
+constexpr int kBatch = 256;  // updates per block
+constexpr uint64_t kSkipKey = ~0ull;
+
+struct ScatterParams {
+  char* table;
+  const char* values;
+  IndexSrc idx;
+  int64_t N, V;
+  uint32_t cpr;  // 16-byte chunks per row
+  int policy;
+  unsigned long long* status;
+  int use_padding;
+  int64_t padding_idx;
+};
+
+template <class T> struct AddVec;
+template <> struct AddVec<float> {
+  using acc_t = float4;
+  __device__ static acc_t zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ static void add(acc_t& a, const int4& raw) {
+    a.x += __int_as_float(raw.x); a.y += __int_as_float(raw.y);
+    a.z += __int_as_float(raw.z); a.w += __int_as_float(raw.w);
+  }
+  __device__ static void flush(char* dst, const acc_t& a) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a.x), "f"(a.y),
+                 "f"(a.z), "f"(a.w) : "memory");
+  }
+};
+template <> struct AddVec<int64_t> {
+  struct acc_t { unsigned long long a, b; };
+  __device__ static acc_t zero() { return acc_t{0ull, 0ull}; }
+  __device__ static void add(acc_t& a, const int4& raw) {
+    a.a += (static_cast<unsigned long long>(static_cast<unsigned>(raw.y)) << 32) | static_cast<unsigned>(raw.x);
+    a.b += (static_cast<unsigned long long>(static_cast<unsigned>(raw.w)) << 32) | static_cast<unsigned>(raw.z);
+  }
+  __device__ static void flush(char* dst, const acc_t& a) {
+    atomicAdd(reinterpret_cast<unsigned long long*>(dst), a.a);
+    atomicAdd(reinterpret_cast<unsigned long long*>(dst) + 1, a.b);
+  }
+};
+template <> struct AddVec<int32_t> {
+  using acc_t = uint4;
+  __device__ static acc_t zero() { return make_uint4(0u, 0u, 0u, 0u); }
+  __device__ static void add(acc_t& a, const int4& raw) {
+    a.x += static_cast<unsigned>(raw.x); a.y += static_cast<unsigned>(raw.y);
+    a.z += static_cast<unsigned>(raw.z); a.w += static_cast<unsigned>(raw.w);
+  }
+  __device__ static void flush(char* dst, const acc_t& a) {
+    unsigned* d = reinterpret_cast<unsigned*>(dst);
+    atomicAdd(d, a.x); atomicAdd(d + 1, a.y); atomicAdd(d + 2, a.z); atomicAdd(d + 3, a.w);
+  }
+};
+
+// K = 16-byte chunks a lane keeps in registers per pass over the entries
+template <class T, int K>
+__global__ void __launch_bounds__(kThreads) scatter_add_rows_kernel(const __grid_constant__ ScatterParams p) {
+  using AV = AddVec<T>;
+  using acc_t = typename AV::acc_t;
+  __shared__ uint64_t keys[kBatch];  // (row << 8) | position, sorted
+  const int t = threadIdx.x;
+  const int64_t b0 = static_cast<int64_t>(blockIdx.x) * kBatch;
+  {
+    uint64_t key = kSkipKey;
+    const int64_t i = b0 + t;
+    if (i < p.N) {
+      int64_t v = p.idx.get(i);
+      if (!(p.use_padding && v == p.padding_idx)) {
+        if (normalize(v, p.V, p.policy, p.status, true))
+          key = (static_cast<uint64_t>(v) << 8) | static_cast<uint64_t>(t);
+      }
+    }
+    keys[t] = key;
+  }
+  __syncthreads();
+  // bitonic sort of 256 keys; equal rows end up adjacent and in update order
+  for (int k = 2; k <= kBatch; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      const int ixj = t ^ j;
+      if (ixj > t) {
+        const uint64_t a = keys[t], b = keys[ixj];
+        const bool up = (t & k) == 0;
+        if ((a > b) == up) { keys[t] = b; keys[ixj] = a; }
+      }
+      __syncthreads();
+    }
+  }
+  const int lane = t & 31, w = t >> 5;
+  const int e_begin = w * 32;
+  const int64_t row_bytes = static_cast<int64_t>(p.cpr) * 16;
+  constexpr int U = 4;
+  for (uint32_t cb = 0; cb < p.cpr; cb += 32 * K) {  // column block of 32*K chunks
+    acc_t acc[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) acc[k] = AV::zero();
+    uint64_t cur = kSkipKey;  // current row (key >> 8), kSkipKey = none
+    auto flush = [&](uint64_t row) {
+      char* dst = p.table + static_cast<int64_t>(row) * row_bytes;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const uint32_t c = cb + k * 32 + lane;
+        if (c < p.cpr) AV::flush(dst + static_cast<int64_t>(c) * 16, acc[k]);
+        acc[k] = AV::zero();
+      }
+    };
+    for (int e0 = 0; e0 < 32; e0 += U) {
+      uint64_t key[U];
+      int4 raw[U][K];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        key[u] = keys[e_begin + e0 + u];
+        if (key[u] != kSkipKey) {
+          const char* src = p.values + (b0 + static_cast<int64_t>(key[u] & 0xff)) * row_bytes;
+#pragma unroll
+          for (int k = 0; k < K; ++k) {
+            const uint32_t c = cb + k * 32 + lane;
+            raw[u][k] = c < p.cpr ? *reinterpret_cast<const int4*>(src + static_cast<int64_t>(c) * 16)
+                                  : make_int4(0, 0, 0, 0);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (key[u] == kSkipKey) continue;  // skipped entries sort to the end
+        const uint64_t row = key[u] >> 8;
+        if (row != cur) {
+          if (cur != kSkipKey) flush(cur);
+          cur = row;
+        }
+#pragma unroll
+        for (int k = 0; k < K; ++k) AV::add(acc[k], raw[u][k]);
+      }
+    }
+    if (cur != kSkipKey) flush(cur);
+  }
+}
+
+// element-wise atomic fallback (rows that are not whole aligned 16-byte chunks)
+struct ScatterElemParams {
+  char* table;
+  const char* values;
+  IndexSrc idx;
+  int64_t N, V, D;
+  int policy;
+  unsigned long long* status;
+  int use_padding;
+  int64_t padding_idx;
+};
+template <class T>
+__device__ __forceinline__ void atomic_add_elem(T* dst, T v);
+template <> __device__ __forceinline__ void atomic_add_elem<float>(float* d, float v) { atomicAdd(d, v); }
+template <> __device__ __forceinline__ void atomic_add_elem<int64_t>(int64_t* d, int64_t v) {
+  atomicAdd(reinterpret_cast<unsigned long long*>(d), static_cast<unsigned long long>(v));
+}
+template <> __device__ __forceinline__ void atomic_add_elem<int32_t>(int32_t* d, int32_t v) { atomicAdd(d, v); }
+
+template <class T>
+__global__ void __launch_bounds__(kThreads) scatter_add_elem_kernel(const __grid_constant__ ScatterElemParams p) {
+  const int64_t e = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (e >= p.N * p.D) return;
+  const int64_t row = e / p.D, j = e - row * p.D;
+  int64_t v = p.idx.get(row);
+  if (p.use_padding && v == p.padding_idx) return;
+  if (!normalize(v, p.V, p.policy, p.status, j == 0)) return;
+  atomic_add_elem<T>(reinterpret_cast<T*>(p.table) + v * p.D + j, reinterpret_cast<const T*>(p.values)[e]);
+}
+
+// ------------------------------------------------------------------------------------
+// last-dim index / index_put: out[b, k] = src[b, idx[k]]
+// ------------------------------------------------------------------------------------
+struct LastDimParams {
+  char* self;       // [B, K0] strides (sb, sk) elements
+  char* other;      // dense [B, K]
+  IndexSrc idx;
+  int64_t B, K0, K, sb, sk;
+  int es;
+  int policy;
+  unsigned long long* status;
+  int mode;  // 0 gather, 1 put overwrite, 2 put accumulate
+  int dtype;
+};
+__global__ void __launch_bounds__(kThreads) lastdim_kernel(const __grid_constant__ LastDimParams p) {
+  const int64_t e = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (e >= p.B * p.K) return;
+  const int64_t b = e / p.K, k = e - b * p.K;
+  int64_t v = p.idx.get(k);
+  const bool good = normalize(v, p.K0, p.policy, p.status, b == 0);
+  char* s = p.self + (b * p.sb + v * p.sk) * p.es;
+  char* o = p.other + e * p.es;
+  if (p.mode == 0) {
+    for (int i = 0; i < p.es; ++i) o[i] = good ? s[i] : 0;
+  } else if (good) {
+    if (p.mode == 1) {
+      for (int i = 0; i < p.es; ++i) s[i] = o[i];
+    } else {
+      switch (p.dtype) {
+        case VBT_B200_F32: atomicAdd(reinterpret_cast<float*>(s), *reinterpret_cast<const float*>(o)); break;
+        case VBT_B200_I64:
+          atomicAdd(reinterpret_cast<unsigned long long*>(s), *reinterpret_cast<const unsigned long long*>(o));
+          break;
+        case VBT_B200_I32: atomicAdd(reinterpret_cast<int*>(s), *reinterpret_cast<const int*>(o)); break;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// host
+// ------------------------------------------------------------------------------------
+vbt_b200_status check_idx(const vbt_b200_tensor* idx, const char* name, IndexSrc* src, int64_t* n) {
+  VB_TRY(validate_tensor(idx, name));
+  VB_ARG(idx->dtype == VBT_B200_I64 || idx->dtype == VBT_B200_I32,
+         std::string(name) + ": only Int32 and Int64 index tensors are supported");
+  VB_ARG(is_dense_row_major(*idx), std::string(name) + ": index tensor must be contiguous");
+  *n = numel(*idx);
+  VB_ARG(*n <= 0x7fffffff, std::string(name) + ": too many indices for one call");
+  src->idx = idx->data;
+  src->is32 = idx->dtype == VBT_B200_I32;
+  return VBT_B200_OK;
+}
+
+vbt_b200_status rows_copy(const char* name, const vbt_b200_tensor* dense, const vbt_b200_tensor* table,
+                          const vbt_b200_tensor* idx, int policy, void* status, cudaStream_t s,
+                          int scatter) {
+  VB_TRY(validate_tensor(dense, name));
+  VB_TRY(validate_tensor(table, name));
+  VB_ARG(table->ndim == 2, std::string(name) + ": table must be rank 2");
+  VB_ARG(dense->dtype == table->dtype, std::string(name) + ": dtype mismatch");
+  VB_ARG(policy >= 0 && policy <= 2, std::string(name) + ": unknown index policy");
+  IndexSrc is{};
+  int64_t N = 0;
+  VB_TRY(check_idx(idx, name, &is, &N));
+  const int64_t V = table->sizes[0], D = table->sizes[1];
+  VB_ARG(is_dense_row_major(*dense) && numel(*dense) == N * D,
+         std::string(name) + ": dense operand must be contiguous [N, D]");
+  if (scatter) VB_ARG(table->strides[1] == 1 || D <= 1, std::string(name) + ": table rows must be contiguous");
+  if (N == 0 || D == 0) return VBT_B200_OK;
+  VB_ARG(V > 0 || policy != VBT_B200_INDEX_CLAMP, std::string(name) + ": empty table");
+  const int es = itemsize(table->dtype);
+  const int64_t s0 = table->strides[0], s1 = D > 1 ? table->strides[1] : 1;
+  DeviceScope scope(dense->data);
+  const bool chunked = s1 == 1 && (D * es) % 16 == 0 && (s0 * es) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(table->data) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(dense->data) % 16 == 0 && s0 >= 0 &&
+                       D * es / 16 <= 0x7fffffff;
+  if (chunked) {
+    GatherParams p{};
+    p.table = static_cast<const char*>(table->data);
+    p.out = static_cast<char*>(dense->data);
+    p.idx = is;
+    p.N = N;
+    p.V = V;
+    p.row_stride_bytes = s0 * es;
+    p.cpr = static_cast<uint32_t>(D * es / 16);
+    p.div_cpr = FastDiv(p.cpr);
+    p.total = N * p.cpr;
+    p.policy = policy;
+    p.status = static_cast<unsigned long long*>(status);
+    p.scatter = scatter;
+    const int64_t blocks = (p.total + kThreads * 4 - 1) / (kThreads * 4);
+    VB_ARG(blocks <= 0x7fffffff, std::string(name) + ": too large for one call");
+    rows_copy_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p);
+  } else {
+    ElemParams p{};
+    p.table = static_cast<const char*>(table->data);
+    p.out = static_cast<char*>(dense->data);
+    p.idx = is;
+    p.N = N; p.V = V; p.D = D; p.s0 = s0; p.s1 = s1; p.es = es;
+    p.policy = policy;
+    p.status = static_cast<unsigned long long*>(status);
+    p.scatter = scatter;
+    const int64_t blocks = (N * D + kThreads - 1) / kThreads;
+    VB_ARG(blocks <= 0x7fffffff, std::string(name) + ": too large for one call");
+    rows_copy_elem_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p);
+  }
+  VB_LAUNCH_CHECK();
+  return VBT_B200_OK;
+}
+
+template <class T>
+vbt_b200_status scatter_add_typed(const ScatterParams& p, const ScatterElemParams& pe, bool chunked,
+                                  cudaStream_t s) {
+  if (chunked) {
+    const unsigned g = static_cast<unsigned>((p.N + kBatch - 1) / kBatch);
+    if (p.cpr <= 32) scatter_add_rows_kernel<T, 1><<<g, kThreads, 0, s>>>(p);
+    else if (p.cpr <= 64) scatter_add_rows_kernel<T, 2><<<g, kThreads, 0, s>>>(p);
+    else scatter_add_rows_kernel<T, 4><<<g, kThreads, 0, s>>>(p);
+  } else {
+    const int64_t blocks = (pe.N * pe.D + kThreads - 1) / kThreads;
+    VB_ARG(blocks <= 0x7fffffff, "index_put_: too large for one call");
+    scatter_add_elem_kernel<T><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(pe);
+  }
+  VB_LAUNCH_CHECK();
+  return VBT_B200_OK;
+}
+
+vbt_b200_status scatter_add_rows(const char* name, const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
+                                 const vbt_b200_tensor* values, int policy, void* status, int use_padding,
+                                 int64_t padding_idx, cudaStream_t s) {
+  VB_TRY(validate_tensor(table, name));
+  VB_TRY(validate_tensor(values, name));
+  VB_ARG(table->ndim == 2, std::string(name) + ": table must be rank 2");
+  VB_ARG(values->dtype == table->dtype, std::string(name) + ": dtype mismatch");
+  VB_ARG(policy >= 0 && policy <= 2, std::string(name) + ": unknown index policy");
+  const int dt = table->dtype;
+  VB_ARG(dt == VBT_B200_F32 || dt == VBT_B200_I64 || dt == VBT_B200_I32,
+         std::string(name) + ": accumulate supports float32, int32 and int64");
+  IndexSrc is{};
+  int64_t N = 0;
+  VB_TRY(check_idx(idx, name, &is, &N));
+  const int64_t V = table->sizes[0], D = table->sizes[1];
+  VB_ARG(is_dense_row_major(*table), std::string(name) + ": table must be contiguous");
+  VB_ARG(is_dense_row_major(*values) && numel(*values) == N * D,
+         std::string(name) + ": values must be contiguous [N, D]");
+  if (N == 0 || D == 0) return VBT_B200_OK;
+  const int es = itemsize(dt);
+  DeviceScope scope(table->data);
+  const bool chunked = (D * es) % 16 == 0 && reinterpret_cast<uintptr_t>(table->data) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(values->data) % 16 == 0 && V < (int64_t{1} << 55);
+  ScatterParams p{};
+  p.table = static_cast<char*>(table->data);
+  p.values = static_cast<const char*>(values->data);
+  p.idx = is;
+  p.N = N; p.V = V;
+  p.cpr = static_cast<uint32_t>(D * es / 16);
+  p.policy = policy;
+  p.status = static_cast<unsigned long long*>(status);
+  p.use_padding = use_padding;
+  p.padding_idx = padding_idx;
+  ScatterElemParams pe{};
+  pe.table = p.table; pe.values = p.values; pe.idx = is; pe.N = N; pe.V = V; pe.D = D;
+  pe.policy = policy; pe.status = p.status; pe.use_padding = use_padding; pe.padding_idx = padding_idx;
+  switch (dt) {
+    case VBT_B200_F32: return scatter_add_typed<float>(p, pe, chunked, s);
+    case VBT_B200_I64: return scatter_add_typed<int64_t>(p, pe, chunked, s);
+    default: return scatter_add_typed<int32_t>(p, pe, chunked, s);
+  }
+}
+
+vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt_b200_tensor* idx,
+                        const vbt_b200_tensor* other, int mode, int policy, void* status, cudaStream_t s) {
+  VB_TRY(validate_tensor(self, name));
+  VB_TRY(validate_tensor(other, name));
+  VB_ARG(self->ndim == 2, std::string(name) + ": tensor must be rank 2");
+  VB_ARG(other->dtype == self->dtype, std::string(name) + ": dtype mismatch");
+  IndexSrc is{};
+  int64_t K = 0;
+  VB_TRY(check_idx(idx, name, &is, &K));
+  const int64_t B = self->sizes[0];
+  VB_ARG(is_dense_row_major(*other) && numel(*other) == B * K,
+         std::string(name) + ": dense operand must be contiguous [B, K]");
+  if (mode == 2)
+    VB_ARG(self->dtype == VBT_B200_F32 || self->dtype == VBT_B200_I64 || self->dtype == VBT_B200_I32,
+           std::string(name) + ": accumulate supports float32, int32 and int64");
+  if (B * K == 0) return VBT_B200_OK;
+  DeviceScope scope(other->data);
+  LastDimParams p{};
+  p.self = static_cast<char*>(self->data);
+  p.other = static_cast<char*>(other->data);
+  p.idx = is;
+  p.B = B; p.K0 = self->sizes[1]; p.K = K; p.sb = self->strides[0]; p.sk = self->strides[1];
+  p.es = itemsize(self->dtype);
+  p.policy = policy;
+  p.status = static_cast<unsigned long long*>(status);
+  p.mode = mode;
+  p.dtype = self->dtype;
+  const int64_t blocks = (B * K + kThreads - 1) / kThreads;
+  VB_ARG(blocks <= 0x7fffffff, std::string(name) + ": too large for one call");
+  lastdim_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p);
+  VB_LAUNCH_CHECK();
+  return VBT_B200_OK;
+}
+
+}  // namespace
+}  // namespace vb
+
+extern "C" {
+
+vbt_b200_status vbt_b200_index_rows(const vbt_b200_tensor* out, const vbt_b200_tensor* table,
+                                    const vbt_b200_tensor* idx, int32_t policy, void* index_status,
+                                    void* stream) {
+  return vb::rows_copy("index", out, table, idx, policy, index_status, static_cast<cudaStream_t>(stream), 0);
+}
+
+vbt_b200_status vbt_b200_index_put_rows(const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
+                                        const vbt_b200_tensor* values, int32_t accumulate, int32_t policy,
+                                        void* index_status, void* stream) {
+  if (accumulate)
+    return vb::scatter_add_rows("index_put_", table, idx, values, policy, index_status, 0, 0,
+                                static_cast<cudaStream_t>(stream));
+  return vb::rows_copy("index_put_", values, table, idx, policy, index_status,
+                       static_cast<cudaStream_t>(stream), 1);
+}
+
+vbt_b200_status vbt_b200_index_lastdim(const vbt_b200_tensor* out, const vbt_b200_tensor* src,
+                                       const vbt_b200_tensor* idx, int32_t policy, void* index_status,
+                                       void* stream) {
+  return vb::lastdim("index", src, idx, out, 0, policy, index_status, static_cast<cudaStream_t>(stream));
+}
+
+vbt_b200_status vbt_b200_index_put_lastdim(const vbt_b200_tensor* self, const vbt_b200_tensor* idx,
+                                           const vbt_b200_tensor* values, int32_t accumulate, int32_t policy,
+                                           void* index_status, void* stream) {
+  return vb::lastdim("index_put_", self, idx, values, accumulate ? 2 : 1, policy, index_status,
+                     static_cast<cudaStream_t>(stream));
+}
+
+vbt_b200_status vbt_b200_embedding(const vbt_b200_tensor* out, const vbt_b200_tensor* weight,
+                                   const vbt_b200_tensor* idx, void* index_status, void* stream) {
+  using namespace vb;
+  const char* name = "vt::embedding";
+  VB_ARG(weight && idx && out, std::string(name) + ": null tensor descriptor");
+  VB_ARG(weight->dtype == VBT_B200_F32, std::string(name) + ": weight must be float32");
+  VB_ARG(weight->ndim == 2, std::string(name) + ": weight must be rank 2");
+  VB_ARG(weight->strides[0] >= 0 && weight->strides[1] >= 0,
+         std::string(name) + ": weight strides must be non-negative");
+  VB_ARG(idx->dtype == VBT_B200_I64, std::string(name) + ": indices must be int64");
+  return rows_copy(name, out, weight, idx, VBT_B200_INDEX_STRICT, index_status,
+                   static_cast<cudaStream_t>(stream), 0);
+}
+
+vbt_b200_status vbt_b200_embedding_backward(const vbt_b200_tensor* grad_weight, const vbt_b200_tensor* idx,
+                                            const vbt_b200_tensor* grad_out, int64_t padding_idx,
+                                            void* index_status, void* stream) {
+  return vb::scatter_add_rows("vt::embedding", grad_weight, idx, grad_out, VBT_B200_INDEX_STRICT,
+                              index_status, 1, padding_idx, static_cast<cudaStream_t>(stream));
+}
+
+vbt_b200_status vbt_b200_index_status_check(void* index_status, const char* what, int64_t dim_size,
+                                            void* stream) {
+  using namespace vb;
+  VB_ARG(index_status != nullptr, "index_status_check: null status block");
+  DeviceScope scope(index_status);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned long long h[2] = {0, 0};
+  VB_CUDA(cudaMemcpyAsync(h, index_status, sizeof(h), cudaMemcpyDeviceToHost, s));
+  VB_CUDA(cudaStreamSynchronize(s));
+  if (h[0] == 0) return VBT_B200_OK;
+  VB_CUDA(cudaMemsetAsync(index_status, 0, sizeof(h), s));
+  return fail(VBT_B200_OUT_OF_RANGE,
+              std::string(what ? what : "index") + ": index " + std::to_string(static_cast<long long>(h[1])) +
+                  " is out of range for dimension with size " + std::to_string(dim_size) + " (" +
+                  std::to_string(h[0]) + " bad indices)");
+}
+
+}  // extern "C"

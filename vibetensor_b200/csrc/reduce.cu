@@ -1,0 +1,809 @@
+// Dim reductions: sum / mean / max / min / prod / argmax / argmin (sm_100a).
+//
+// Replaces cuda_reduce_dispatch and the K1 (one atomic per input element), K2 and K3
+// kernels of the reference (src/vbt/ops/cuda_reduction.cu:254-416, :907-2034).  Every
+// reduction is brought to one of three shapes on the host:
+//
+//   ROW      the reduced dims are one run with stride 1: each output owns a contiguous
+//            slice.  Short slices: one warp per output.  Long slices: one block per
+//            (output, chunk); chunk partials go to the workspace and the block that
+//            arrives last folds them in chunk order.
+//   COL      memory is [A, R, B] with B contiguous and R reduced: a warp reads whole
+//            16-byte-per-lane rows (coalesced), the 8 warps of a block split R, blocks
+//            split R further through the same workspace + last-arriver fold.
+//   GENERIC  anything else: one warp per output walks the reduced index space through a
+//            multiply-shift offset decoder.
+//
+// No floating-point atomics anywhere: for a given shape the order of additions is fixed,
+// so results repeat bit for bit from run to run.  There are no spin waits either -- the
+// cross-block fold is done by whichever block draws the last ticket.
+#include <cfloat>
+#include <climits>
+
+#include "common.cuh"
+
+namespace vb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxDims = VBT_B200_MAX_NDIM;
+
+// ------------------------------------------------------------------------------------
+// reducers
+// ------------------------------------------------------------------------------------
+template <class A>
+struct Pair {
+  A v;
+  int64_t i;
+};
+
+template <class A> __device__ __forceinline__ A lowest();
+template <> __device__ __forceinline__ float lowest<float>() { return -INFINITY; }
+template <> __device__ __forceinline__ int64_t lowest<int64_t>() { return LLONG_MIN; }
+template <class A> __device__ __forceinline__ A highest();
+template <> __device__ __forceinline__ float highest<float>() { return INFINITY; }
+template <> __device__ __forceinline__ int64_t highest<int64_t>() { return LLONG_MAX; }
+
+__device__ __forceinline__ float shfl_down(float v, int d) { return __shfl_down_sync(0xffffffffu, v, d); }
+__device__ __forceinline__ int64_t shfl_down(int64_t v, int d) { return __shfl_down_sync(0xffffffffu, v, d); }
+template <class A>
+__device__ __forceinline__ Pair<A> shfl_down(Pair<A> p, int d) {
+  return Pair<A>{shfl_down(p.v, d), shfl_down(p.i, d)};
+}
+
+template <class A>
+struct SumR {
+  using acc_t = A;
+  static constexpr bool kIndexed = false;
+  __device__ static acc_t init() { return A(0); }
+  __device__ static void accum(acc_t& a, A v, int64_t) {
+    if constexpr (sizeof(A) == 8) a = static_cast<A>(static_cast<uint64_t>(a) + static_cast<uint64_t>(v));
+    else a += v;
+  }
+  __device__ static acc_t combine(acc_t a, acc_t b) {
+    if constexpr (sizeof(A) == 8) return static_cast<A>(static_cast<uint64_t>(a) + static_cast<uint64_t>(b));
+    else return a + b;
+  }
+};
+template <class A>
+struct ProdR {
+  using acc_t = A;
+  static constexpr bool kIndexed = false;
+  __device__ static acc_t init() { return A(1); }
+  __device__ static void accum(acc_t& a, A v, int64_t) { a = combine(a, v); }
+  __device__ static acc_t combine(acc_t a, acc_t b) {
+    if constexpr (sizeof(A) == 8) return static_cast<A>(static_cast<uint64_t>(a) * static_cast<uint64_t>(b));
+    else return a * b;
+  }
+};
+// max / min: NaN never wins here (comparisons are false); "NaN at position 0 wins" of the
+// reference's scan (src/vbt/python/tensor_bindings.cc:361-379) is applied at finalize.
+template <class A, bool MAX>
+struct ExtR {
+  using acc_t = A;
+  static constexpr bool kIndexed = false;
+  __device__ static acc_t init() { return MAX ? lowest<A>() : highest<A>(); }
+  __device__ static void accum(acc_t& a, A v, int64_t) { if (MAX ? (v > a) : (v < a)) a = v; }
+  __device__ static acc_t combine(acc_t a, acc_t b) { return (MAX ? (b > a) : (b < a)) ? b : a; }
+};
+// argmax / argmin: first extremum wins (tensor_bindings.cc:630-682)
+template <class A, bool MAX>
+struct ArgR {
+  using acc_t = Pair<A>;
+  static constexpr bool kIndexed = true;
+  __device__ static acc_t init() { return Pair<A>{MAX ? lowest<A>() : highest<A>(), LLONG_MAX}; }
+  __device__ static void accum(acc_t& a, A v, int64_t i) {
+    if ((MAX ? (v > a.v) : (v < a.v)) || (v == a.v && i < a.i)) { a.v = v; a.i = i; }
+  }
+  __device__ static acc_t combine(acc_t a, acc_t b) {
+    return ((MAX ? (b.v > a.v) : (b.v < a.v)) || (b.v == a.v && b.i < a.i)) ? b : a;
+  }
+};
+
+template <class T> struct Widen { using type = float; };
+template <> struct Widen<int64_t> { using type = int64_t; };
+__device__ __forceinline__ float widen(float x) { return x; }
+__device__ __forceinline__ float widen(__half x) { return __half2float(x); }
+__device__ __forceinline__ float widen(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ int64_t widen(int64_t x) { return x; }
+
+__device__ __forceinline__ float ld_cg(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ int64_t ld_cg(const int64_t* p) {
+  return static_cast<int64_t>(__ldcg(reinterpret_cast<const long long*>(p)));
+}
+template <class A>
+__device__ __forceinline__ Pair<A> ld_cg(const Pair<A>* p) {
+  return Pair<A>{ld_cg(&p->v), ld_cg(&p->i)};
+}
+
+template <class R>
+__device__ __forceinline__ typename R::acc_t warp_reduce(typename R::acc_t a) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) a = R::combine(a, shfl_down(a, d));
+  return a;
+}
+// all threads call; result valid in thread 0
+template <class R>
+__device__ __forceinline__ typename R::acc_t block_reduce(typename R::acc_t a, typename R::acc_t* smem) {
+  a = warp_reduce<R>(a);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) smem[w] = a;
+  __syncthreads();
+  if (w == 0) {
+    a = lane < kWarps ? smem[lane] : R::init();
+    a = warp_reduce<R>(a);
+  }
+  return a;
+}
+
+// ------------------------------------------------------------------------------------
+// finalize: acc -> output element(s)
+// ------------------------------------------------------------------------------------
+enum { OP_SUM = 0, OP_MEAN, OP_MAX, OP_MIN, OP_PROD, OP_ARGMAX, OP_ARGMIN };
+
+struct OutSpec {
+  void* out;        // values (may be null for arg ops)
+  int64_t* out_idx; // indices (arg ops)
+  int out_dtype;
+  int op;
+  float inv_count_n;  // reduce count as float, for MEAN
+};
+
+__device__ __forceinline__ void store_value(const OutSpec& o, int64_t i, float v) {
+  switch (o.out_dtype) {
+    case VBT_B200_F32: static_cast<float*>(o.out)[i] = v; break;
+    case VBT_B200_F16: static_cast<__half*>(o.out)[i] = __float2half_rn(v); break;
+    case VBT_B200_BF16: static_cast<__nv_bfloat16*>(o.out)[i] = __float2bfloat16_rn(v); break;
+  }
+}
+__device__ __forceinline__ void store_value(const OutSpec& o, int64_t i, int64_t v) {
+  static_cast<int64_t*>(o.out)[i] = v;
+}
+__device__ __forceinline__ bool is_nan(float v) { return v != v; }
+__device__ __forceinline__ bool is_nan(int64_t) { return false; }
+
+// first: the slice's element 0 (widened), needed for the NaN-at-0 rule
+template <class R, class A>
+__device__ __forceinline__ void finalize(const OutSpec& o, int64_t i, typename R::acc_t acc, A first) {
+  if constexpr (R::kIndexed) {
+    if (is_nan(first)) { acc.v = first; acc.i = 0; }
+    if (o.out) store_value(o, i, acc.v);
+    if (o.out_idx) o.out_idx[i] = acc.i;
+  } else {
+    if (o.op == OP_MAX || o.op == OP_MIN) {
+      if (is_nan(first)) acc = first;
+    }
+    if constexpr (sizeof(A) == 4) {
+      if (o.op == OP_MEAN) acc = acc / o.inv_count_n;
+    }
+    store_value(o, i, acc);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// offset decoding for the kept / reduced dims
+// ------------------------------------------------------------------------------------
+struct DimList {
+  int n;
+  FastDiv div[kMaxDims];
+  int64_t stride[kMaxDims];
+  // linear index (last dim fastest) -> element offset
+  __device__ __forceinline__ int64_t offset(uint32_t lin) const {
+    int64_t off = 0;
+    for (int d = n - 1; d >= 0; --d) {
+      uint32_t c;
+      div[d].divmod(lin, lin, c);
+      off += static_cast<int64_t>(c) * stride[d];
+    }
+    return off;
+  }
+};
+
+// ------------------------------------------------------------------------------------
+// ROW kernels
+// ------------------------------------------------------------------------------------
+template <class T, int V>
+__device__ __forceinline__ void load_widen(const T* p, typename Widen<T>::type (&w)[V]) {
+  if constexpr (V == 1) {
+    w[0] = widen(*p);
+  } else {
+    const Vec<T, V> v = *reinterpret_cast<const Vec<T, V>*>(p);
+#pragma unroll
+    for (int j = 0; j < V; ++j) w[j] = widen(v.v[j]);
+  }
+}
+
+struct RowParams {
+  const void* x;
+  int64_t n;          // slice length
+  int64_t rows;
+  int64_t row_stride; // used when kept.n == 0 is false? (see kept)
+  DimList kept;       // row index -> slice base offset
+  int splits;
+  int64_t chunk;      // elements per split (multiple of the vector width)
+  void* ws_partials;
+  unsigned* ws_counters;
+  OutSpec o;
+};
+
+// one warp per slice; n is small
+template <class T, class R, int V>
+__global__ void __launch_bounds__(kThreads) row_warp_kernel(const __grid_constant__ RowParams p) {
+  using A = typename Widen<T>::type;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  const int lane = threadIdx.x & 31;
+  const T* x = static_cast<const T*>(p.x) + p.kept.offset(static_cast<uint32_t>(row));
+  typename R::acc_t acc = R::init();
+  const int64_t nvec = p.n / V;
+  for (int64_t i = lane; i < nvec; i += 32) {
+    A w[V];
+    load_widen<T, V>(x + i * V, w);
+#pragma unroll
+    for (int j = 0; j < V; ++j) R::accum(acc, w[j], i * V + j);
+  }
+  if constexpr (V > 1) {
+    const int64_t i = nvec * V + lane;
+    if (i < p.n) R::accum(acc, widen(x[i]), i);
+  }
+  acc = warp_reduce<R>(acc);
+  if (lane == 0) finalize<R, A>(p.o, row, acc, widen(x[0]));
+}
+
+// one block per (slice, chunk)
+template <class T, class R, int V>
+__global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_constant__ RowParams p) {
+  using A = typename Widen<T>::type;
+  using acc_t = typename R::acc_t;
+  __shared__ acc_t smem[kWarps];
+  __shared__ bool is_last;
+  const int64_t row = blockIdx.x;
+  const int split = blockIdx.y;
+  const T* x = static_cast<const T*>(p.x) + p.kept.offset(static_cast<uint32_t>(row));
+  const int64_t c0 = static_cast<int64_t>(split) * p.chunk;
+  const int64_t c1 = min(p.n, c0 + p.chunk);
+  constexpr int U = 4;
+  acc_t acc[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) acc[u] = R::init();
+  const int64_t v0 = c0 / V, v1 = c1 / V;  // whole vectors in [c0, c1); c0 is a multiple of V
+  int64_t i = v0 + threadIdx.x;
+  for (; i + (U - 1) * kThreads < v1; i += U * kThreads) {
+    A w[U][V];
+#pragma unroll
+    for (int u = 0; u < U; ++u) load_widen<T, V>(x + (i + u * kThreads) * V, w[u]);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < V; ++j) R::accum(acc[u], w[u][j], (i + u * kThreads) * V + j);
+  }
+  for (; i < v1; i += kThreads) {
+    A w[V];
+    load_widen<T, V>(x + i * V, w);
+#pragma unroll
+    for (int j = 0; j < V; ++j) R::accum(acc[0], w[j], i * V + j);
+  }
+  if constexpr (V > 1) {
+    const int64_t t = v1 * V + threadIdx.x;  // ragged tail, only in the last chunk
+    if (t < c1) R::accum(acc[0], widen(x[t]), t);
+  }
+  acc_t a = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
+  a = block_reduce<R>(a, smem);
+  if (p.splits == 1) {
+    if (threadIdx.x == 0) finalize<R, A>(p.o, row, a, widen(x[0]));
+    return;
+  }
+  acc_t* part = static_cast<acc_t*>(p.ws_partials) + row * p.splits;
+  if (threadIdx.x == 0) {
+    part[split] = a;
+    __threadfence();
+    const unsigned t = atomicAdd(&p.ws_counters[row], 1u);
+    is_last = (t == static_cast<unsigned>(p.splits) - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // fold the chunk partials in chunk order: thread t takes chunks t, t+256, ... in order,
+  // then the fixed shuffle tree -- the same order on every run
+  acc_t f = R::init();
+  for (int s = threadIdx.x; s < p.splits; s += kThreads) f = R::combine(f, ld_cg(part + s));
+  __syncthreads();
+  f = block_reduce<R>(f, smem);
+  if (threadIdx.x == 0) finalize<R, A>(p.o, row, f, widen(x[0]));
+}
+
+// ------------------------------------------------------------------------------------
+// COL kernel: memory [A, Rn, B], B contiguous, reduce Rn
+// ------------------------------------------------------------------------------------
+struct ColParams {
+  const void* x;
+  int64_t B, Rn, S;   // S = stride of the reduced dim (elements)
+  DimList outer;      // a -> base offset
+  int64_t A;
+  int splits;
+  int64_t chunk;      // reduced rows per split
+  void* ws_partials;
+  unsigned* ws_counters;
+  int ctiles;
+  OutSpec o;
+};
+
+template <class T, class R, int V>
+__global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ ColParams p) {
+  using A = typename Widen<T>::type;
+  using acc_t = typename R::acc_t;
+  __shared__ acc_t smem[kWarps][32 * V + 1];
+  __shared__ bool is_last;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int ct = blockIdx.x, split = blockIdx.y;
+  const int64_t a = blockIdx.z;
+  const int64_t col = (static_cast<int64_t>(ct) * 32 + lane) * V;
+  const bool active = col < p.B;  // B % V == 0 in vector mode
+  const T* x = static_cast<const T*>(p.x) + p.outer.offset(static_cast<uint32_t>(a)) + col;
+  const int64_t r0 = static_cast<int64_t>(split) * p.chunk;
+  const int64_t r1 = min(p.Rn, r0 + p.chunk);
+  acc_t acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = R::init();
+  if (active) {
+    constexpr int U = 4;
+    int64_t r = r0 + w;
+    for (; r + (U - 1) * kWarps < r1; r += U * kWarps) {
+      A v[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u) load_widen<T, V>(x + (r + u * kWarps) * p.S, v[u]);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < V; ++j) R::accum(acc[j], v[u][j], r + u * kWarps);
+    }
+    for (; r < r1; r += kWarps) {
+      A v[V];
+      load_widen<T, V>(x + r * p.S, v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) R::accum(acc[j], v[j], r);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) smem[w][lane * V + j] = acc[j];
+  __syncthreads();
+  // threads 0 .. 32V-1 each own one column of the tile: fold the 8 warps in warp order
+  const int ncols = 32 * V;
+  acc_t colacc = R::init();
+  const int c = threadIdx.x;
+  const int64_t gcol = static_cast<int64_t>(ct) * ncols + c;
+  const bool owner = c < ncols && gcol < p.B;
+  if (owner) {
+#pragma unroll
+    for (int ww = 0; ww < kWarps; ++ww) colacc = R::combine(colacc, smem[ww][c]);
+  }
+  const int64_t out_i = a * p.B + gcol;
+  const T* first_p = static_cast<const T*>(p.x) + p.outer.offset(static_cast<uint32_t>(a)) + gcol;
+  if (p.splits == 1) {
+    if (owner) finalize<R, A>(p.o, out_i, colacc, widen(*first_p));
+    return;
+  }
+  acc_t* part = static_cast<acc_t*>(p.ws_partials) +
+                ((a * p.ctiles + ct) * p.splits) * ncols;  // [split][col]
+  if (owner) part[static_cast<int64_t>(split) * ncols + c] = colacc;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned t = atomicAdd(&p.ws_counters[a * p.ctiles + ct], 1u);
+    is_last = (t == static_cast<unsigned>(p.splits) - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (owner) {
+    acc_t f = R::init();
+    for (int s = 0; s < p.splits; ++s)
+      f = R::combine(f, ld_cg(part + static_cast<int64_t>(s) * ncols + c));
+    finalize<R, A>(p.o, out_i, f, widen(*first_p));
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// GENERIC kernel: one warp per output
+// ------------------------------------------------------------------------------------
+struct GenParams {
+  const void* x;
+  DimList kept;
+  DimList red;
+  int64_t nout;
+  uint32_t nred;
+  OutSpec o;
+};
+
+template <class T, class R>
+__global__ void __launch_bounds__(kThreads) generic_kernel(const __grid_constant__ GenParams p) {
+  using A = typename Widen<T>::type;
+  const int64_t oi = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (oi >= p.nout) return;
+  const int lane = threadIdx.x & 31;
+  const T* x = static_cast<const T*>(p.x) + p.kept.offset(static_cast<uint32_t>(oi));
+  typename R::acc_t acc = R::init();
+  for (uint32_t j = lane; j < p.nred; j += 32) R::accum(acc, widen(x[p.red.offset(j)]), j);
+  acc = warp_reduce<R>(acc);
+  if (lane == 0) finalize<R, A>(p.o, oi, acc, widen(x[0]));
+}
+
+// fills an output with a constant (empty reduction domains)
+template <class T>
+__global__ void fill_kernel(T* out, int64_t n, T v) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = v;
+}
+
+// ------------------------------------------------------------------------------------
+// host plan
+// ------------------------------------------------------------------------------------
+enum Shape { kRowWarp, kRowBlock, kCol, kGeneric, kEmptyDomain, kNoOutput };
+
+struct Plan {
+  Shape shape{kGeneric};
+  int64_t nout{1}, nred{1};
+  // kept / reduced dims after dropping size-1 dims and merging, outermost first
+  int nk{0}, nr{0};
+  int64_t ksize[kMaxDims]{}, kstride[kMaxDims]{}, rsize[kMaxDims]{}, rstride[kMaxDims]{};
+  int splits{1};
+  int64_t chunk{0};
+  int ctiles{0};
+  int V{1};
+  size_t ws_partial_bytes{0}, ws_counter_bytes{0};
+  int64_t out_sizes[kMaxDims]{};
+  int out_ndim{0};
+};
+
+const char* op_name(int op) {
+  static const char* const n[] = {"sum", "mean", "amax", "amin", "prod", "argmax", "argmin"};
+  return (op >= 0 && op < VBT_B200_R_COUNT) ? n[op] : "reduce";
+}
+
+vbt_b200_status normalize_dims(const vbt_b200_tensor& self, const int64_t* dims, int ndims,
+                               const char* name, bool* reduced /*[ndim]*/) {
+  const int nd = self.ndim;
+  for (int d = 0; d < nd; ++d) reduced[d] = ndims == 0;
+  for (int i = 0; i < ndims; ++i) {
+    int64_t d = dims[i];
+    if (d < 0) d += nd;
+    VB_ARG(d >= 0 && d < nd, std::string(name) + ": dim out of range");
+    reduced[d] = true;
+  }
+  return VBT_B200_OK;
+}
+
+size_t acc_bytes(int op, int dtype) {
+  const size_t a = dtype == VBT_B200_I64 ? 8 : 4;
+  return (op == OP_ARGMAX || op == OP_ARGMIN) ? 16 : a;
+}
+
+vbt_b200_status make_plan(int op, const vbt_b200_tensor& self, const int64_t* dims, int ndims,
+                          bool keepdim, Plan* pl) {
+  const char* name = op_name(op);
+  VB_ARG(self.ndim <= kMaxDims, std::string(name) + ": rank too large");
+  bool reduced[kMaxDims + 1];
+  VB_TRY(normalize_dims(self, dims, ndims, name, reduced));
+  const int nd = self.ndim;
+  pl->out_ndim = 0;
+  pl->nout = 1;
+  pl->nred = 1;
+  for (int d = 0; d < nd; ++d) {
+    if (reduced[d]) {
+      pl->nred *= self.sizes[d];
+      if (keepdim) pl->out_sizes[pl->out_ndim++] = 1;
+    } else {
+      pl->nout *= self.sizes[d];
+      pl->out_sizes[pl->out_ndim++] = self.sizes[d];
+    }
+  }
+  if (pl->nout == 0) { pl->shape = kNoOutput; return VBT_B200_OK; }
+  if (pl->nred == 0) { pl->shape = kEmptyDomain; return VBT_B200_OK; }
+  // split into kept / reduced lists (outermost first), drop size-1, merge neighbours
+  auto push = [](int& n, int64_t* sz, int64_t* st, int64_t size, int64_t stride) {
+    if (size == 1) return;
+    if (n > 0 && st[n - 1] == stride * size) {  // previous (outer) dim continues this one
+      sz[n - 1] *= size;
+      st[n - 1] = stride;
+      return;
+    }
+    sz[n] = size;
+    st[n] = stride;
+    ++n;
+  };
+  pl->nk = pl->nr = 0;
+  for (int d = 0; d < nd; ++d) {
+    if (reduced[d]) push(pl->nr, pl->rsize, pl->rstride, self.sizes[d], self.strides[d]);
+    else push(pl->nk, pl->ksize, pl->kstride, self.sizes[d], self.strides[d]);
+  }
+  VB_ARG(pl->nout <= 0x7fffffff, std::string(name) + ": too many outputs for one call");
+  const int es = itemsize(self.dtype);
+  const int vmax = 16 / es;
+  const uintptr_t base = reinterpret_cast<uintptr_t>(self.data);
+  auto all_multiple = [&](const int64_t* st, int n, int v) {
+    for (int i = 0; i < n; ++i)
+      if (st[i] % v) return false;
+    return true;
+  };
+  const int sms = 148;
+  const size_t ab = acc_bytes(op, self.dtype);
+  if (pl->nr == 1 && pl->rstride[0] == 1) {
+    // ROW
+    const int64_t n = pl->rsize[0];
+    pl->V = (base % 16 == 0 && all_multiple(pl->kstride, pl->nk, vmax)) ? vmax : 1;
+    if (n * es <= 4096 && pl->nout >= 64) {
+      pl->shape = kRowWarp;
+      return VBT_B200_OK;
+    }
+    pl->shape = kRowBlock;
+    const int64_t per_block_min = int64_t{kThreads} * vmax * 4;  // one unrolled pass
+    int64_t splits = 1;
+    if (pl->nout < 2 * sms) {
+      splits = std::min<int64_t>((n + per_block_min - 1) / per_block_min,
+                                 (int64_t{sms} * 4 + pl->nout - 1) / pl->nout);
+      splits = std::max<int64_t>(splits, 1);
+    }
+    int64_t chunk = (n + splits - 1) / splits;
+    chunk = (chunk + vmax - 1) / vmax * vmax;
+    splits = (n + chunk - 1) / chunk;
+    pl->splits = static_cast<int>(splits);
+    pl->chunk = chunk;
+    if (splits > 1) {
+      pl->ws_partial_bytes = static_cast<size_t>(pl->nout) * splits * ab;
+      pl->ws_counter_bytes = static_cast<size_t>(pl->nout) * 4;
+    }
+    return VBT_B200_OK;
+  }
+  if (pl->nr == 1 && pl->nk >= 1 && pl->kstride[pl->nk - 1] == 1) {
+    // COL: last kept dim contiguous
+    const int64_t B = pl->ksize[pl->nk - 1];
+    const int64_t Rn = pl->rsize[0];
+    int64_t A = 1;
+    for (int i = 0; i + 1 < pl->nk; ++i) A *= pl->ksize[i];
+    if (A <= 65535) {
+      bool vec = base % 16 == 0 && B % vmax == 0 && pl->rstride[0] % vmax == 0 &&
+                 all_multiple(pl->kstride, pl->nk - 1, vmax);
+      pl->V = vec ? vmax : 1;
+      // 16-byte lanes only pay off when a tile of 32 lanes is mostly inside B
+      if (vec && B < 32 * vmax / 2) pl->V = 1;
+      pl->shape = kCol;
+      const int ncols = 32 * pl->V;
+      pl->ctiles = static_cast<int>((B + ncols - 1) / ncols);
+      int64_t want = (int64_t{sms} * 6 + pl->ctiles * A - 1) / (pl->ctiles * A);
+      int64_t splits = std::max<int64_t>(1, std::min<int64_t>(want, (Rn + 31) / 32));
+      splits = std::min<int64_t>(splits, 65535);
+      int64_t chunk = (Rn + splits - 1) / splits;
+      splits = (Rn + chunk - 1) / chunk;
+      pl->splits = static_cast<int>(splits);
+      pl->chunk = chunk;
+      if (splits > 1) {
+        pl->ws_partial_bytes = static_cast<size_t>(A) * pl->ctiles * splits * ncols * ab;
+        pl->ws_counter_bytes = static_cast<size_t>(A) * pl->ctiles * 4;
+      }
+      return VBT_B200_OK;
+    }
+  }
+  pl->shape = kGeneric;
+  VB_ARG(pl->nred <= 0x7fffffff, std::string(name) + ": reduced extent too large for this layout");
+  return VBT_B200_OK;
+}
+
+void fill_dimlist(DimList& dl, const int64_t* sizes, const int64_t* strides, int n) {
+  dl.n = n;
+  for (int i = 0; i < n; ++i) {
+    dl.div[i] = FastDiv(static_cast<uint32_t>(sizes[i]));
+    dl.stride[i] = strides[i];
+  }
+}
+
+template <class T, class R>
+vbt_b200_status launch(const Plan& pl, const vbt_b200_tensor& self, const OutSpec& o, void* ws,
+                       cudaStream_t s) {
+  constexpr int VMAX = 16 / sizeof(T);
+  if (pl.shape == kRowWarp || pl.shape == kRowBlock) {
+    RowParams p{};
+    p.x = self.data;
+    p.n = pl.rsize[0];
+    p.rows = pl.nout;
+    fill_dimlist(p.kept, pl.ksize, pl.kstride, pl.nk);
+    p.splits = pl.splits;
+    p.chunk = pl.chunk;
+    p.o = o;
+    if (pl.shape == kRowWarp) {
+      const unsigned g = static_cast<unsigned>((pl.nout + kWarps - 1) / kWarps);
+      if (pl.V > 1) row_warp_kernel<T, R, VMAX><<<g, kThreads, 0, s>>>(p);
+      else row_warp_kernel<T, R, 1><<<g, kThreads, 0, s>>>(p);
+    } else {
+      if (pl.splits > 1) {
+        p.ws_partials = ws;
+        p.ws_counters = reinterpret_cast<unsigned*>(static_cast<char*>(ws) + pl.ws_partial_bytes);
+        VB_CUDA(cudaMemsetAsync(p.ws_counters, 0, pl.ws_counter_bytes, s));
+      }
+      VB_ARG(pl.splits <= 65535, "reduce: too many chunks");
+      dim3 g(static_cast<unsigned>(pl.nout), static_cast<unsigned>(pl.splits));
+      if (pl.V > 1) row_block_kernel<T, R, VMAX><<<g, kThreads, 0, s>>>(p);
+      else row_block_kernel<T, R, 1><<<g, kThreads, 0, s>>>(p);
+    }
+    VB_LAUNCH_CHECK();
+    return VBT_B200_OK;
+  }
+  if (pl.shape == kCol) {
+    ColParams p{};
+    p.x = self.data;
+    p.B = pl.ksize[pl.nk - 1];
+    p.Rn = pl.rsize[0];
+    p.S = pl.rstride[0];
+    fill_dimlist(p.outer, pl.ksize, pl.kstride, pl.nk - 1);
+    p.A = pl.nout / p.B;
+    p.splits = pl.splits;
+    p.chunk = pl.chunk;
+    p.ctiles = pl.ctiles;
+    p.o = o;
+    if (pl.splits > 1) {
+      p.ws_partials = ws;
+      p.ws_counters = reinterpret_cast<unsigned*>(static_cast<char*>(ws) + pl.ws_partial_bytes);
+      VB_CUDA(cudaMemsetAsync(p.ws_counters, 0, pl.ws_counter_bytes, s));
+    }
+    dim3 g(static_cast<unsigned>(pl.ctiles), static_cast<unsigned>(pl.splits), static_cast<unsigned>(p.A));
+    if (pl.V > 1) col_kernel<T, R, VMAX><<<g, kThreads, 0, s>>>(p);
+    else col_kernel<T, R, 1><<<g, kThreads, 0, s>>>(p);
+    VB_LAUNCH_CHECK();
+    return VBT_B200_OK;
+  }
+  GenParams p{};
+  p.x = self.data;
+  fill_dimlist(p.kept, pl.ksize, pl.kstride, pl.nk);
+  fill_dimlist(p.red, pl.rsize, pl.rstride, pl.nr);
+  p.nout = pl.nout;
+  p.nred = static_cast<uint32_t>(pl.nred);
+  p.o = o;
+  const unsigned g = static_cast<unsigned>((pl.nout + kWarps - 1) / kWarps);
+  generic_kernel<T, R><<<g, kThreads, 0, s>>>(p);
+  VB_LAUNCH_CHECK();
+  return VBT_B200_OK;
+}
+
+template <class T>
+vbt_b200_status launch_op(int op, const Plan& pl, const vbt_b200_tensor& self, const OutSpec& o,
+                          void* ws, cudaStream_t s) {
+  using A = typename Widen<T>::type;
+  switch (op) {
+    case OP_SUM:
+    case OP_MEAN: return launch<T, SumR<A>>(pl, self, o, ws, s);
+    case OP_PROD: return launch<T, ProdR<A>>(pl, self, o, ws, s);
+    case OP_MAX: return launch<T, ExtR<A, true>>(pl, self, o, ws, s);
+    case OP_MIN: return launch<T, ExtR<A, false>>(pl, self, o, ws, s);
+    case OP_ARGMAX: return launch<T, ArgR<A, true>>(pl, self, o, ws, s);
+    case OP_ARGMIN: return launch<T, ArgR<A, false>>(pl, self, o, ws, s);
+  }
+  return fail(VBT_B200_INVALID_ARGUMENT, "reduce: unknown op code");
+}
+
+vbt_b200_status check_dtypes(int op, const vbt_b200_tensor& self, const vbt_b200_tensor* out,
+                             const vbt_b200_tensor* out_index) {
+  const char* name = op_name(op);
+  const int dt = self.dtype;
+  if (op == OP_MEAN)
+    VB_ARG(is_float_dtype(dt), "mean: expected dtype=float32");
+  else
+    VB_ARG(dt == VBT_B200_I64 || is_float_dtype(dt), std::string(name) + ": unsupported dtype");
+  const bool arg = op == OP_ARGMAX || op == OP_ARGMIN;
+  if (arg) VB_ARG(out_index && out_index->dtype == VBT_B200_I64, std::string(name) + ": index output must be int64");
+  else VB_ARG(out != nullptr, std::string(name) + ": null output");
+  if (out)
+    VB_ARG(out->dtype == dt || (out->dtype == VBT_B200_F32 && is_float_dtype(dt)),
+           std::string(name) + ": output dtype mismatch");
+  return VBT_B200_OK;
+}
+
+vbt_b200_status check_out_shape(const Plan& pl, const vbt_b200_tensor* t, const char* name) {
+  if (!t) return VBT_B200_OK;
+  bool ok = t->ndim == pl.out_ndim;
+  for (int d = 0; ok && d < pl.out_ndim; ++d) ok = t->sizes[d] == pl.out_sizes[d];
+  VB_ARG(ok, std::string(name) + ": output has the wrong shape");
+  VB_ARG(is_dense_row_major(*t), std::string(name) + ": output must be dense");
+  return VBT_B200_OK;
+}
+
+}  // namespace
+}  // namespace vb
+
+extern "C" {
+
+size_t vbt_b200_reduce_workspace_bytes(int32_t op, const vbt_b200_tensor* self, const int64_t* dims,
+                                       int32_t ndims) {
+  using namespace vb;
+  if (!self || validate_tensor(self, "reduce") != VBT_B200_OK) return 0;
+  Plan pl;
+  if (make_plan(op, *self, dims, ndims, false, &pl) != VBT_B200_OK) return 0;
+  const size_t partial = (pl.ws_partial_bytes + 15) / 16 * 16;
+  return partial + pl.ws_counter_bytes;
+}
+
+vbt_b200_status vbt_b200_reduce_shape(const vbt_b200_tensor* self, const int64_t* dims, int32_t ndims,
+                                      int32_t keepdim, int64_t* out_sizes, int32_t* out_ndim) {
+  using namespace vb;
+  VB_TRY(validate_tensor(self, "reduce"));
+  VB_ARG(self->ndim <= kMaxDims, "reduce: rank too large");
+  bool reduced[kMaxDims + 1];
+  VB_TRY(normalize_dims(*self, dims, ndims, "reduce", reduced));
+  int n = 0;
+  for (int d = 0; d < self->ndim; ++d) {
+    if (!reduced[d]) out_sizes[n++] = self->sizes[d];
+    else if (keepdim) out_sizes[n++] = 1;
+  }
+  *out_ndim = n;
+  return VBT_B200_OK;
+}
+
+vbt_b200_status vbt_b200_reduce(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* out_index,
+                                const vbt_b200_tensor* self, const int64_t* dims, int32_t ndims,
+                                int32_t keepdim, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace vb;
+  VB_ARG(op >= 0 && op < VBT_B200_R_COUNT, "reduce: unknown op code");
+  const char* name = op_name(op);
+  VB_TRY(validate_tensor(self, name));
+  if (out) VB_TRY(validate_tensor(out, name));
+  if (out_index) VB_TRY(validate_tensor(out_index, name));
+  VB_TRY(check_dtypes(op, *self, out, out_index));
+  Plan pl;
+  VB_TRY(make_plan(op, *self, dims, ndims, keepdim != 0, &pl));
+  VB_TRY(check_out_shape(pl, out, name));
+  VB_TRY(check_out_shape(pl, out_index, name));
+  if (pl.shape == kNoOutput) return VBT_B200_OK;
+  DeviceScope scope(out ? out->data : out_index->data);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pl.shape == kEmptyDomain) {
+    // cuda_reduction.cu:1176-1216
+    if (op == OP_MAX || op == OP_ARGMAX) return fail(VBT_B200_RUNTIME_ERROR, "amax: empty");
+    if (op == OP_MIN || op == OP_ARGMIN) return fail(VBT_B200_RUNTIME_ERROR, "amin: empty");
+    const double v = op == OP_SUM ? 0.0 : (op == OP_PROD ? 1.0 : NAN);
+    const unsigned g = static_cast<unsigned>((pl.nout + 255) / 256);
+    switch (out->dtype) {
+      case VBT_B200_F32: fill_kernel<float><<<g, 256, 0, s>>>(static_cast<float*>(out->data), pl.nout, static_cast<float>(v)); break;
+      case VBT_B200_F16: fill_kernel<__half><<<g, 256, 0, s>>>(static_cast<__half*>(out->data), pl.nout, __float2half_rn(static_cast<float>(v))); break;
+      case VBT_B200_BF16: fill_kernel<__nv_bfloat16><<<g, 256, 0, s>>>(static_cast<__nv_bfloat16*>(out->data), pl.nout, __float2bfloat16_rn(static_cast<float>(v))); break;
+      case VBT_B200_I64: fill_kernel<int64_t><<<g, 256, 0, s>>>(static_cast<int64_t*>(out->data), pl.nout, static_cast<int64_t>(op == OP_PROD ? 1 : 0)); break;
+    }
+    VB_LAUNCH_CHECK();
+    return VBT_B200_OK;
+  }
+  const size_t partial = (pl.ws_partial_bytes + 15) / 16 * 16;
+  Plan run = pl;
+  run.ws_partial_bytes = partial;
+  if (partial + pl.ws_counter_bytes > 0) {
+    VB_ARG(workspace != nullptr && workspace_bytes >= partial + pl.ws_counter_bytes,
+           std::string(name) + ": workspace too small (see vbt_b200_reduce_workspace_bytes)");
+    VB_ARG(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, std::string(name) + ": workspace must be 16-byte aligned");
+  }
+  OutSpec o{};
+  o.out = out ? out->data : nullptr;
+  o.out_idx = out_index ? static_cast<int64_t*>(out_index->data) : nullptr;
+  o.out_dtype = out ? out->dtype : self->dtype;
+  o.op = op;
+  o.inv_count_n = static_cast<float>(pl.nred);
+  switch (self->dtype) {
+    case VBT_B200_F32: return launch_op<float>(op, run, *self, o, workspace, s);
+    case VBT_B200_F16: return launch_op<__half>(op, run, *self, o, workspace, s);
+    case VBT_B200_BF16: return launch_op<__nv_bfloat16>(op, run, *self, o, workspace, s);
+    case VBT_B200_I64: return launch_op<int64_t>(op, run, *self, o, workspace, s);
+  }
+  return fail(VBT_B200_INVALID_ARGUMENT, std::string(name) + ": unsupported dtype");
+}
+
+vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_tensor* partial,
+                                        const vbt_b200_tensor* shard, const int64_t* dims, int32_t ndims,
+                                        int32_t keepdim, void* workspace, size_t workspace_bytes,
+                                        void* stream) {
+  using namespace vb;
+  VB_ARG(op == VBT_B200_R_SUM || op == VBT_B200_R_MAX || op == VBT_B200_R_MIN,
+         "reduce_partial: only sum / max / min combine across shards");
+  VB_ARG(partial && shard, "reduce_partial: null tensor descriptor");
+  VB_ARG(partial->dtype == VBT_B200_F32 || partial->dtype == VBT_B200_I64,
+         "reduce_partial: partials are float32 or int64");
+  return vbt_b200_reduce(op, partial, nullptr, shard, dims, ndims, keepdim, workspace, workspace_bytes,
+                         stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,282 @@
+"""Fabric: row-sharded tensors across the GPUs of one box, one process per GPU.
+
+The reference's Fabric (python/vibetensor/fabric.py:206-533, :811-877) is a single process
+that holds one shard per mesh device and loops over them; it has elementwise add / mul only
+and no reductions.  Here each rank (``torch.distributed``, NCCL over NVLink) owns one shard
+of a ``sharded_1d_row`` tensor -- rows ``[shard_offsets[r], shard_offsets[r+1])`` of the
+global tensor -- and
+
+* elementwise ops between tensors of the same placement are purely local kernel launches
+  (no communication), as ``fabric.add`` / ``fabric.mul`` are in the reference;
+* a reduction over the sharded dim is a local partial (FP32 or INT64, computed by
+  ``vbt_b200_reduce_partial``) followed by ONE all-reduce of the partial on the same stream:
+  4 bytes for a full sum / amax, ``4 * columns`` bytes for ``mean(dim=0)``;
+* a reduction over a non-sharded dim is local and yields a tensor sharded the same way.
+
+``FabricPlacement`` keeps the reference's invariants (kinds, offsets = prefix sums of rows,
+``global_shape = (sum rows,) + tail``).
+
+The compute backend is ``vibetensor_b200.ops`` (CUDA only).  ``local_ops=`` exists so the
+multi-rank bookkeeping can be exercised by CPU ``gloo`` tests with a stand-in; nothing in
+this module falls back to it on its own.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+class FabricError(RuntimeError):
+    def __init__(self, msg: str):
+        super().__init__("[Fabric] " + msg)
+
+
+@dataclasses.dataclass(frozen=True)
+class FabricMesh:
+    """The ranks taking part (one CUDA device each); ``devices[r]`` is rank r's device index."""
+
+    devices: Tuple[int, ...]
+    group: Optional[object] = None  # torch.distributed process group, None = default
+
+    def __post_init__(self):
+        devs = tuple(int(d) for d in self.devices)
+        if not devs:
+            raise FabricError("FabricMesh.devices must not be empty")
+        if any(d < 0 for d in devs):
+            raise FabricError("FabricMesh.devices must be non-negative")
+        object.__setattr__(self, "devices", devs)
+
+    @property
+    def world_size(self) -> int:
+        return len(self.devices)
+
+    @property
+    def rank(self) -> int:
+        return dist.get_rank(self.group) if dist.is_initialized() else 0
+
+    @staticmethod
+    def from_world(group=None) -> "FabricMesh":
+        """One mesh slot per rank of the process group; device index = local rank slot."""
+        ws = dist.get_world_size(group) if dist.is_initialized() else 1
+        return FabricMesh(tuple(range(ws)), group)
+
+
+@dataclasses.dataclass(frozen=True)
+class FabricPlacement:
+    kind: str
+    mesh: FabricMesh
+    global_shape: Tuple[int, ...]
+    shard_offsets: Tuple[int, ...]
+
+    def __post_init__(self):
+        if self.kind not in ("replicated", "sharded_1d_row"):
+            raise FabricError(f"Invalid FabricPlacement.kind: {self.kind!r}")
+        gs = tuple(int(s) for s in self.global_shape)
+        so = tuple(int(s) for s in self.shard_offsets)
+        if len(so) != self.mesh.world_size:
+            raise FabricError("FabricPlacement.shard_offsets must have the same length as mesh.devices")
+        if self.kind == "replicated":
+            if any(o != 0 for o in so):
+                raise FabricError("FabricPlacement(replicated) requires shard_offsets to be all zeros")
+        else:
+            if len(gs) < 1:
+                raise FabricError("FabricPlacement(sharded_1d_row) requires global_shape to have rank >= 1")
+            if so[0] != 0:
+                raise FabricError("FabricPlacement(sharded_1d_row) requires shard_offsets[0] == 0")
+            if any(c < p for p, c in zip(so, so[1:])):
+                raise FabricError("FabricPlacement(sharded_1d_row) requires shard_offsets to be non-decreasing")
+            if so[-1] > gs[0]:
+                raise FabricError("FabricPlacement(sharded_1d_row) offsets exceed the global row count")
+        object.__setattr__(self, "global_shape", gs)
+        object.__setattr__(self, "shard_offsets", so)
+
+    def rows_of(self, rank: int) -> int:
+        if self.kind == "replicated":
+            return self.global_shape[0] if self.global_shape else 1
+        end = self.shard_offsets[rank + 1] if rank + 1 < len(self.shard_offsets) else self.global_shape[0]
+        return end - self.shard_offsets[rank]
+
+
+def _backend(local_ops):
+    if local_ops is not None:
+        return local_ops
+    from . import ops
+    return ops
+
+
+class FabricTensor:
+    """This rank's shard plus the placement that says where it sits in the global tensor."""
+
+    __vbt_fabric_tensor__ = True
+
+    def __init__(self, placement: FabricPlacement, shard: torch.Tensor):
+        if not isinstance(placement, FabricPlacement):
+            raise FabricError("FabricTensor.placement must be a FabricPlacement")
+        r = placement.mesh.rank
+        if placement.kind == "sharded_1d_row":
+            if shard.dim() < 1:
+                raise FabricError("sharded_1d_row shards must have rank >= 1")
+            if tuple(shard.shape[1:]) != tuple(placement.global_shape[1:]):
+                raise FabricError("shard tail dims must match the global shape")
+            if shard.shape[0] != placement.rows_of(r):
+                raise FabricError("shard row count does not match the placement offsets")
+        elif tuple(shard.shape) != tuple(placement.global_shape):
+            raise FabricError("replicated shards must have the global shape")
+        self.placement = placement
+        self.shard = shard
+
+    # ---- constructors (FabricTensor.replicated / sharded_1d_row of the reference) ----
+    @staticmethod
+    def replicated(mesh: FabricMesh, tensor: torch.Tensor) -> "FabricTensor":
+        return FabricTensor(FabricPlacement("replicated", mesh, tuple(tensor.shape),
+                                            (0,) * mesh.world_size), tensor)
+
+    @staticmethod
+    def sharded_1d_row(mesh: FabricMesh, local_shard: torch.Tensor) -> "FabricTensor":
+        """Builds the placement from every rank's row count (one small all-gather on the host
+        side of construction, not on the data path)."""
+        rows = int(local_shard.shape[0]) if local_shard.dim() >= 1 else None
+        if rows is None:
+            raise FabricError("sharded_1d_row shards must have rank >= 1")
+        ws = mesh.world_size
+        if ws > 1:
+            counts = [None] * ws
+            dist.all_gather_object(counts, (rows, tuple(local_shard.shape[1:]), str(local_shard.dtype)),
+                                   group=mesh.group)
+            tails = {c[1] for c in counts}
+            dts = {c[2] for c in counts}
+            if len(tails) != 1:
+                raise FabricError("sharded_1d_row shards must share their tail dims")
+            if len(dts) != 1:
+                raise FabricError("sharded_1d_row shards must share their dtype")
+            row_counts = [c[0] for c in counts]
+        else:
+            row_counts = [rows]
+        offs, acc = [], 0
+        for c in row_counts:
+            offs.append(acc)
+            acc += c
+        pl = FabricPlacement("sharded_1d_row", mesh, (acc,) + tuple(local_shard.shape[1:]), tuple(offs))
+        return FabricTensor(pl, local_shard)
+
+    @property
+    def global_shape(self):
+        return self.placement.global_shape
+
+    @property
+    def dtype(self):
+        return self.shard.dtype
+
+    def to_local_shard(self) -> torch.Tensor:
+        return self.shard
+
+
+def _same_placement(a: FabricTensor, b: FabricTensor, what: str):
+    if a.placement.mesh.devices != b.placement.mesh.devices or a.placement.kind != b.placement.kind \
+            or a.placement.shard_offsets != b.placement.shard_offsets \
+            or a.placement.global_shape != b.placement.global_shape:
+        raise FabricError(f"{what}: operands must share mesh and placement")
+    if a.shard.dtype != b.shard.dtype:
+        raise FabricError(f"{what}: dtype mismatch")
+
+
+def _elementwise(name: str, a: FabricTensor, b: FabricTensor, local_ops=None) -> FabricTensor:
+    _same_placement(a, b, "fabric." + name)
+    out = _backend(local_ops).binary(name, a.shard, b.shard)
+    return FabricTensor(a.placement, out)
+
+
+def add(a: FabricTensor, b: FabricTensor, local_ops=None) -> FabricTensor:
+    """fabric.add: per-shard vt::add, no communication (python/vibetensor/fabric.py:843-859)."""
+    return _elementwise("add", a, b, local_ops)
+
+
+def mul(a: FabricTensor, b: FabricTensor, local_ops=None) -> FabricTensor:
+    return _elementwise("mul", a, b, local_ops)
+
+
+_REDUCE_OP = {"sum": dist.ReduceOp.SUM, "mean": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX,
+              "min": dist.ReduceOp.MIN}
+
+
+def _all_reduce(t: torch.Tensor, name: str, mesh: FabricMesh):
+    if mesh.world_size > 1:
+        dist.all_reduce(t, op=_REDUCE_OP[name], group=mesh.group)
+    return t
+
+
+def reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False, local_ops=None):
+    """sum / mean / max / min of a FabricTensor.
+
+    * the reduced dims include dim 0 of a sharded_1d_row tensor: local partial, all-reduce,
+      (mean: scale by 1 / global count, cast to the input dtype) -> a plain tensor, identical
+      on every rank;
+    * otherwise: local reduction -> FabricTensor sharded the same way.
+    """
+    if name not in _REDUCE_OP:
+        raise FabricError(f"fabric.reduce: unsupported reduction {name!r}")
+    be = _backend(local_ops)
+    x = ft.shard
+    nd = x.dim()
+    dims = list(range(nd)) if dim is None else ([dim] if isinstance(dim, int) else list(dim))
+    dims = sorted({d + nd if d < 0 else d for d in dims})
+    if any(d < 0 or d >= nd for d in dims):
+        raise ValueError(f"{name}: dim out of range")
+    crosses = ft.placement.kind == "sharded_1d_row" and 0 in dims
+    if not crosses:
+        out = be.reduce(name, x, dims, keepdim)
+        if ft.placement.kind == "replicated":
+            return out
+        pl = FabricPlacement("sharded_1d_row", ft.placement.mesh,
+                             (ft.placement.global_shape[0],) + tuple(out.shape[1:]),
+                             ft.placement.shard_offsets)
+        return FabricTensor(pl, out)
+    local = "sum" if name == "mean" else name
+    if x.shape[0] == 0:
+        # an empty shard contributes the identity
+        oshape = [1 if i in dims else s for i, s in enumerate(x.shape) if keepdim or i not in dims]
+        pdt = torch.int64 if x.dtype == torch.int64 else torch.float32
+        ident = {"sum": 0, "max": float("-inf") if pdt.is_floating_point else torch.iinfo(pdt).min,
+                 "min": float("inf") if pdt.is_floating_point else torch.iinfo(pdt).max}[local]
+        partial = torch.full(oshape, ident, dtype=pdt, device=x.device)
+    else:
+        partial = be.reduce(local, x, dims, keepdim, partial=True)
+    _all_reduce(partial, name, ft.placement.mesh)
+    if name == "mean":
+        count = 1
+        for d in dims:
+            count *= ft.placement.global_shape[d]
+        return be.scale_cast(partial, 1.0 / count if count else float("nan"), x.dtype)
+    if partial.dtype != x.dtype:
+        return be.scale_cast(partial, 1.0, x.dtype)
+    return partial
+
+
+def sum(ft, dim=None, keepdim=False, local_ops=None):  # noqa: A001
+    return reduce("sum", ft, dim, keepdim, local_ops)
+
+
+def mean(ft, dim=None, keepdim=False, local_ops=None):
+    return reduce("mean", ft, dim, keepdim, local_ops)
+
+
+def amax(ft, dim=None, keepdim=False, local_ops=None):
+    return reduce("max", ft, dim, keepdim, local_ops)
+
+
+def amin(ft, dim=None, keepdim=False, local_ops=None):
+    return reduce("min", ft, dim, keepdim, local_ops)
+
+
+def split_rows(total_rows: int, world_size: int) -> Sequence[Tuple[int, int]]:
+    """(offset, rows) per rank for an even row split, remainder to the leading ranks."""
+    base, rem = divmod(total_rows, world_size)
+    out, off = [], 0
+    for r in range(world_size):
+        n = base + (1 if r < rem else 0)
+        out.append((off, n))
+        off += n
+    return out

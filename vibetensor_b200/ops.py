@@ -1,0 +1,398 @@
+"""vt:: ops on CUDA tensors, served by libvbt_b200.so.
+
+Mirrors the operator surface of the reference for this path -- ``vibetensor.torch.ops.vt.*``
+(python/vibetensor/torch/ops.py:36-80) and the ``Tensor`` reduction / indexing methods
+(src/vbt/python/tensor_bindings.cc:2219-2573) -- with the same argument meaning, dtype
+rules and error classes.  Tensors are ``torch.Tensor`` objects on a CUDA device: torch
+provides memory and the current stream, nothing else.  Every function launches on the
+current stream and returns without synchronising, except where stated.
+
+Each elementwise op also takes ``out=``: any strided view of the broadcast shape (the
+reference allocates a dense result for every op, src/vbt/ops/cuda_elementwise.cu:96-110).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import check, desc, i64_array, lib, stream_ptr
+
+UNARY = ["relu", "neg", "abs", "square", "exp", "log", "sqrt", "rsqrt", "sin", "cos", "tanh",
+         "sigmoid", "silu", "gelu", "reciprocal", "sign", "floor", "ceil", "trunc", "round",
+         "expm1", "log1p", "softplus", "relu6", "hardtanh"]
+BINARY = ["add", "sub", "mul", "div", "maximum", "minimum", "fmax", "fmin", "eq", "ne", "lt", "gt",
+          "le", "ge"]
+TERNARY = ["clamp", "lerp", "threshold", "addcmul", "addcdiv", "where_gt0_addcmul"]
+REDUCE = ["sum", "mean", "max", "min", "prod", "argmax", "argmin"]
+INDEX_WRAP, INDEX_STRICT, INDEX_CLAMP = 0, 1, 2
+
+
+def _require_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise ValueError("vibetensor_b200 ops take CUDA tensors (there is no CPU path)")
+
+
+def _alloc_out(out, shape, dtype, like):
+    if out is None:
+        return torch.empty(tuple(shape), dtype=dtype, device=like.device)
+    if tuple(out.shape) != tuple(shape):
+        raise ValueError("out= has the wrong shape for the broadcast result")
+    return out
+
+
+def _bshape(*ts):
+    return torch.broadcast_shapes(*[tuple(t.shape) for t in ts])
+
+
+# --------------------------------------------------------------------------------------
+# elementwise
+# --------------------------------------------------------------------------------------
+def unary(name: str, a: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(a)
+    o = _alloc_out(out, a.shape, a.dtype, a)
+    do, da = desc(o), desc(a)
+    check(lib().vbt_b200_unary(UNARY.index(name), do.ref, da.ref, stream_ptr(a)))
+    return o
+
+
+def binary(name: str, a, b, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a, b: CUDA tensors of one dtype, or one of them a Python number (the reference's CPU
+    0-d scalar operand, float32 / int64 tensors only)."""
+    op = BINARY.index(name)
+    cmp_ = op >= BINARY.index("eq")
+    a_t, b_t = isinstance(a, torch.Tensor), isinstance(b, torch.Tensor)
+    if a_t and b_t:
+        _require_cuda(a, b)
+        o = _alloc_out(out, _bshape(a, b), torch.bool if cmp_ else a.dtype, a)
+        do, da, db = desc(o), desc(a), desc(b)
+        check(lib().vbt_b200_binary(op, do.ref, da.ref, db.ref, stream_ptr(a)))
+        return o
+    t, s, left = (a, b, False) if a_t else (b, a, True)
+    _require_cuda(t)
+    o = _alloc_out(out, t.shape, torch.bool if cmp_ else t.dtype, t)
+    if t.dtype == torch.float32:
+        sv = ctypes.c_float(float(s))
+    elif t.dtype == torch.int64:
+        sv = ctypes.c_int64(int(s))
+    elif t.dtype == torch.float16:
+        raise ValueError(f"vt::{name}: Half CPU scalars not supported yet")
+    else:
+        raise ValueError(f"vt::{name}: unsupported dtype for scalar op")
+    do, dt_ = desc(o), desc(t)
+    check(lib().vbt_b200_binary_scalar(op, do.ref, dt_.ref, ctypes.byref(sv), int(left), stream_ptr(t)))
+    return o
+
+
+def ternary(name: str, a, b, c, out=None) -> torch.Tensor:
+    _require_cuda(a, b, c)
+    o = _alloc_out(out, _bshape(a, b, c), a.dtype, a)
+    do, da, db, dc = desc(o), desc(a), desc(b), desc(c)
+    check(lib().vbt_b200_ternary(TERNARY.index(name), do.ref, da.ref, db.ref, dc.ref, stream_ptr(a)))
+    return o
+
+
+def where(cond, x, y, out=None) -> torch.Tensor:
+    _require_cuda(cond, x, y)
+    o = _alloc_out(out, _bshape(cond, x, y), x.dtype, x)
+    do, dc, dx, dy = desc(o), desc(cond), desc(x), desc(y)
+    check(lib().vbt_b200_where(do.ref, dc.ref, dx.ref, dy.ref, stream_ptr(x)))
+    return o
+
+
+def masked_fill(self_, mask, value, out=None):
+    """vt::masked_fill = where(mask, value, self) (cuda_elementwise.cu:3924-3926)."""
+    return where(mask, value, self_, out=out)
+
+
+def copy_(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """Strided copy (src broadcast to dst)."""
+    _require_cuda(dst, src)
+    dd, ds = desc(dst), desc(src)
+    check(lib().vbt_b200_copy(dd.ref, ds.ref, stream_ptr(dst)))
+    return dst
+
+
+def contiguous(a: torch.Tensor) -> torch.Tensor:
+    """clone_cuda: dense row-major copy of a strided view."""
+    return copy_(torch.empty(a.shape, dtype=a.dtype, device=a.device), a)
+
+
+def _mk_unary(n):
+    def f(a, out=None):
+        return unary(n, a, out=out)
+    f.__name__ = n
+    f.__doc__ = f"vt::{n}"
+    return f
+
+
+def _mk_binary(n):
+    def f(a, b, out=None):
+        return binary(n, a, b, out=out)
+    f.__name__ = n
+    f.__doc__ = f"vt::{n}"
+    return f
+
+
+def _mk_ternary(n):
+    def f(a, b, c, out=None):
+        return ternary(n, a, b, c, out=out)
+    f.__name__ = n
+    f.__doc__ = f"vt::{n}"
+    return f
+
+
+for _n in UNARY:
+    globals()[_n if _n != "round" else "round_"] = _mk_unary(_n)
+for _n in BINARY:
+    globals()[_n] = _mk_binary(_n)
+for _n in TERNARY:
+    globals()[_n] = _mk_ternary(_n)
+clamp_min = globals()["maximum"]   # cuda_elementwise.cu:3912-3917
+clamp_max = globals()["minimum"]
+clip = globals()["clamp"]
+
+
+def ti_plan(out: torch.Tensor, *inputs: torch.Tensor):
+    """The iteration plan the library builds for (out, inputs): (shape, strides-per-operand,
+    kernel kind, pieces), dims innermost first.  Host-only; works on any device's tensors."""
+    ds = [desc(out)] + [desc(t) for t in inputs]
+    arr = (ctypes.POINTER(_lib.VbtTensor) * len(ds))(*[ctypes.pointer(d.struct) for d in ds])
+    shape = (ctypes.c_int64 * _lib.MAX_NDIM)()
+    strides = (ctypes.c_int64 * (_lib.MAX_NDIM * len(ds)))()
+    nd, kern, pieces = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+    check(lib().vbt_b200_ti_plan(arr, len(ds), shape, strides, ctypes.byref(nd), ctypes.byref(kern),
+                                 ctypes.byref(pieces)))
+    n = nd.value
+    return (list(shape[:n]),
+            [list(strides[k * _lib.MAX_NDIM:k * _lib.MAX_NDIM + n]) for k in range(len(ds))],
+            kern.value, pieces.value)
+
+
+# --------------------------------------------------------------------------------------
+# reductions
+# --------------------------------------------------------------------------------------
+def _norm_dims(dim) -> list:
+    if dim is None:
+        return []
+    if isinstance(dim, int):
+        return [dim]
+    return list(dim)
+
+
+def reduce_shape(x: torch.Tensor, dims: Sequence[int], keepdim: bool):
+    dx = desc(x)
+    out = (ctypes.c_int64 * _lib.MAX_NDIM)()
+    nd = ctypes.c_int32()
+    check(lib().vbt_b200_reduce_shape(dx.ref, i64_array(dims), len(dims), int(keepdim), out,
+                                      ctypes.byref(nd)))
+    return tuple(out[:nd.value])
+
+
+_ws_cache: dict = {}
+
+
+def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
+    """Scratch for split reductions.  One buffer per (device, stream), grown on demand and
+    reused: work on one stream is ordered, so successive calls cannot overlap."""
+    if nbytes == 0:
+        return None
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _ws_cache.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _ws_cache[key] = ws
+    return ws
+
+
+def reduce(name: str, x: torch.Tensor, dim=None, keepdim: bool = False,
+           out_dtype: Optional[torch.dtype] = None, partial: bool = False):
+    """sum / mean / max / min / prod -> values; argmax / argmin -> (values, int64 indices).
+    partial=True is the per-shard step of a sharded reduction (FP32 / INT64 partials)."""
+    _require_cuda(x)
+    op = REDUCE.index(name)
+    dims = _norm_dims(dim)
+    oshape = reduce_shape(x, dims, keepdim)
+    if out_dtype is None:
+        out_dtype = x.dtype
+        if partial and x.dtype in (torch.float16, torch.bfloat16):
+            out_dtype = torch.float32
+    o = torch.empty(oshape, dtype=out_dtype, device=x.device)
+    oi = torch.empty(oshape, dtype=torch.int64, device=x.device) if op >= 5 else None
+    dx, do = desc(x), desc(o)
+    di = desc(oi) if oi is not None else None
+    da = i64_array(dims)
+    nbytes = lib().vbt_b200_reduce_workspace_bytes(op, dx.ref, da, len(dims))
+    ws = _workspace(nbytes, x.device)
+    wp = ctypes.c_void_p(ws.data_ptr()) if ws is not None else None
+    if partial:
+        check(lib().vbt_b200_reduce_partial(op, do.ref, dx.ref, da, len(dims), int(keepdim), wp,
+                                            nbytes, stream_ptr(x)))
+    else:
+        check(lib().vbt_b200_reduce(op, do.ref, di.ref if di else None, dx.ref, da, len(dims),
+                                    int(keepdim), wp, nbytes, stream_ptr(x)))
+    return (o, oi) if oi is not None else o
+
+
+def sum(x, dim=None, keepdim=False):  # noqa: A001 - mirrors Tensor.sum
+    return reduce("sum", x, dim, keepdim)
+
+
+def mean(x, dim=None, keepdim=False):
+    return reduce("mean", x, dim, keepdim)
+
+
+def amax(x, dim=None, keepdim=False):
+    return reduce("max", x, dim, keepdim)
+
+
+def amin(x, dim=None, keepdim=False):
+    return reduce("min", x, dim, keepdim)
+
+
+def prod(x, dim=None, keepdim=False):
+    return reduce("prod", x, dim, keepdim)
+
+
+def argmax(x, dim=None, keepdim=False):
+    return reduce("argmax", x, dim, keepdim)[1]
+
+
+def argmin(x, dim=None, keepdim=False):
+    return reduce("argmin", x, dim, keepdim)[1]
+
+
+def max_dim(x, dim, keepdim=False):
+    """Tensor.max(dim) -> (values, indices) (tensor_bindings.cc:2538-2573)."""
+    return reduce("argmax", x, dim, keepdim)
+
+
+def min_dim(x, dim, keepdim=False):
+    return reduce("argmin", x, dim, keepdim)
+
+
+# --------------------------------------------------------------------------------------
+# indexing
+# --------------------------------------------------------------------------------------
+class IndexStatus:
+    """Device-side record of out-of-range indices: {count, first bad value}.  Kernels skip a
+    bad index and note it here; ``check`` synchronises and raises IndexError."""
+
+    def __init__(self, device):
+        self.buf = torch.zeros(2, dtype=torch.int64, device=device)
+
+    @property
+    def ptr(self):
+        return ctypes.c_void_p(self.buf.data_ptr())
+
+    def check(self, what: str, dim_size: int) -> None:
+        check(lib().vbt_b200_index_status_check(self.ptr, what.encode(), int(dim_size),
+                                                stream_ptr(self.buf)))
+
+
+def _status(status, eager, device):
+    if status is not None:
+        return status, False
+    return (IndexStatus(device), True) if eager else (None, False)
+
+
+def index_rows(table: torch.Tensor, idx: torch.Tensor, policy: int = INDEX_WRAP,
+               status: Optional[IndexStatus] = None, eager_check: bool = True,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``table[idx]`` for a 2-D table: out[..., :] = table[idx[...], :].  eager_check=True
+    reproduces the reference's immediate IndexError (which costs a stream sync, as its own
+    bounds check does, src/vbt/ops/embedding_cuda.cu:282-299); pass a shared ``status``
+    and check it later to stay asynchronous."""
+    _require_cuda(table, idx)
+    st, own = _status(status, eager_check, table.device)
+    o = _alloc_out(out, tuple(idx.shape) + (table.shape[1],), table.dtype, table)
+    do, dt_, di = desc(o), desc(table), desc(idx.contiguous())
+    check(lib().vbt_b200_index_rows(do.ref, dt_.ref, di.ref, policy, st.ptr if st else None,
+                                    stream_ptr(table)))
+    if own:
+        st.check("index", table.shape[0])
+    return o
+
+
+def index_put_rows_(table: torch.Tensor, idx: torch.Tensor, values: torch.Tensor,
+                    accumulate: bool = False, policy: int = INDEX_WRAP,
+                    status: Optional[IndexStatus] = None, eager_check: bool = True) -> torch.Tensor:
+    """``table.index_put_((idx,), values, accumulate)`` for a 2-D table and [N, D] values."""
+    _require_cuda(table, idx, values)
+    st, own = _status(status, eager_check, table.device)
+    dt_, di, dv = desc(table), desc(idx.contiguous()), desc(values)
+    check(lib().vbt_b200_index_put_rows(dt_.ref, di.ref, dv.ref, int(accumulate), policy,
+                                        st.ptr if st else None, stream_ptr(table)))
+    if own:
+        st.check("index_put_", table.shape[0])
+    return table
+
+
+def index_lastdim(src: torch.Tensor, idx: torch.Tensor, status=None, eager_check=True):
+    """The reference's CUDA advanced-index form ``src[..., idx]`` for 2-D src."""
+    _require_cuda(src, idx)
+    st, own = _status(status, eager_check, src.device)
+    o = torch.empty((src.shape[0], idx.numel()), dtype=src.dtype, device=src.device)
+    do, ds, di = desc(o), desc(src), desc(idx.contiguous())
+    check(lib().vbt_b200_index_lastdim(do.ref, ds.ref, di.ref, INDEX_WRAP, st.ptr if st else None,
+                                       stream_ptr(src)))
+    if own:
+        st.check("index", src.shape[1])
+    return o
+
+
+def index_put_lastdim_(self_: torch.Tensor, idx, values, accumulate=False, status=None,
+                       eager_check=True):
+    _require_cuda(self_, idx, values)
+    st, own = _status(status, eager_check, self_.device)
+    ds, di, dv = desc(self_), desc(idx.contiguous()), desc(values)
+    check(lib().vbt_b200_index_put_lastdim(ds.ref, di.ref, dv.ref, int(accumulate), INDEX_WRAP,
+                                           st.ptr if st else None, stream_ptr(self_)))
+    if own:
+        st.check("index_put_", self_.shape[1])
+    return self_
+
+
+def embedding(weight: torch.Tensor, indices: torch.Tensor, status=None, eager_check=True):
+    """vt::embedding forward (src/vbt/ops/embedding_dispatch.cc:536-709)."""
+    _require_cuda(weight, indices)
+    st, own = _status(status, eager_check, weight.device)
+    o = torch.empty(tuple(indices.shape) + (weight.shape[1],), dtype=weight.dtype, device=weight.device)
+    do, dw, di = desc(o), desc(weight), desc(indices)
+    check(lib().vbt_b200_embedding(do.ref, dw.ref, di.ref, st.ptr if st else None, stream_ptr(weight)))
+    if own:
+        st.check("vt::embedding", weight.shape[0])
+    return o
+
+
+def embedding_backward(grad_out: torch.Tensor, indices: torch.Tensor, num_weights: int,
+                       padding_idx: int = -1, status=None, eager_check=True) -> torch.Tensor:
+    """Dense weight gradient: gw[idx[i], :] += grad_out[i, :], padding_idx rows skipped."""
+    _require_cuda(grad_out, indices)
+    st, own = _status(status, eager_check, grad_out.device)
+    D = grad_out.shape[-1]
+    gw = torch.zeros((num_weights, D), dtype=grad_out.dtype, device=grad_out.device)
+    dg, di, do = desc(gw), desc(indices), desc(grad_out.reshape(-1, D))
+    check(lib().vbt_b200_embedding_backward(dg.ref, di.ref, do.ref, int(padding_idx),
+                                            st.ptr if st else None, stream_ptr(gw)))
+    if own:
+        st.check("vt::embedding", num_weights)
+    return gw
+
+
+def scale_cast(partial: torch.Tensor, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """out = cast(partial * scale): the last step of a sharded mean (float32 partials)."""
+    _require_cuda(partial)
+    if partial.dtype != torch.float32:
+        if scale == 1.0 and partial.dtype == out_dtype:
+            return partial
+        raise ValueError("scale_cast: partial must be float32")
+    p = partial.contiguous()
+    o = torch.empty(p.shape, dtype=out_dtype, device=p.device)
+    check(lib().vbt_b200_scale_cast(ctypes.c_void_p(o.data_ptr()), _lib.dtype_code(out_dtype),
+                                    ctypes.c_void_p(p.data_ptr()), p.numel(), float(scale),
+                                    stream_ptr(p)))
+    return o
