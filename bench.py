@@ -1,0 +1,480 @@
+#!/usr/bin/env python
+"""Benchmark of the vt:: data-parallel op path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-suite]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+Headline line (one JSON object on stdout, printed by rank 0):
+
+  workload  the sharded fp32 sum over a [2^32] tensor (16 GiB, N(0,1)), split along dim 0
+            across the N ranks: every rank reduces its shard to an fp32 partial with one
+            kernel launch, and (N > 1) one 4-byte NCCL all-reduce on the same stream combines
+            the partials.  Total work is fixed ("strong" scaling); value = 2^32 elements /
+            step time, whole job, max over ranks, timed with CUDA events.  Shards are
+            >= 2 GiB, far above the 126 MB L2, so no flush is needed between iterations.
+  roofline  the local reduce kernel: algorithmic bytes (4 B per element of the shard) per
+            launch / mean CUDA-event duration of that launch, against the measured HBM copy
+            bandwidth in MEASURED_PEAKS.json.
+  e2e       the same sum with the input in PINNED HOST memory: every step copies the shard
+            host->device in chunks (copy stream) overlapped with per-chunk partial sums
+            (compute stream), combines, and reads the 4-byte result back.
+  ops       (N = 1 only) the per-op table the metric asks for: every named vt:: op at the
+            shapes of the other benchmark configurations, each with ms, GB/s and the fraction
+            of the measured HBM bandwidth and of the nominal 8 TB/s.
+  cpu_baseline  (N = 1 only) the reference's own single-threaded CPU sum
+            (vbt_default_sum_impl compiled from its sources) on a bounded sample.
+
+--impl reference times the reference's CPU implementation of the headline workload on the
+host cores (bounded sample per step) and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TOTAL_ELEMS = 1 << 32
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per launch of the local reduce kernel for a 2 GiB shard, from the ncu capture
+# summarised in profiles/ (filled in once the capture has been taken; None = not captured).
+REDUCE_TRAFFIC_BYTES_PER_ELEM = None
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms during a timed region."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.tmp.flush()
+        rows = []
+        with open(self.tmp.name) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) >= 8:
+                    rows.append(parts)
+        os.unlink(self.tmp.name)
+        if not rows:
+            return out
+        sm = sorted(float(r[1]) for r in rows if r[1].replace(".", "").isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for k, n in enumerate(names) if any(r[4 + k].lower().startswith("active") for r in rows)]
+        out.update(sm_mhz=sm[len(sm) // 2] if sm else None,
+                   sm_max_mhz=float(rows[0][2]) if rows[0][2].replace(".", "").isdigit() else None,
+                   power_w_max=max(float(r[3]) for r in rows if r[3].replace(".", "").isdigit()),
+                   reasons=reasons, samples=len(rows))
+        return out
+
+
+def env_ranks():
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")),
+            int(os.environ.get("WORLD_SIZE", "1")))
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU sum on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_reference_sum(sample_elems: int, reps: int):
+    """Times vbt_default_sum_impl (reference CPU code, single-threaded by design:
+    include/vbt/core/tensor_iterator/core.h:210) when oracle/_ref is present, else the C
+    restatement, on `sample_elems` fp32 N(0,1) values; returns (elements/s, kind)."""
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal(sample_elems, dtype=np.float32)
+    if oracle.have_ref():
+        fn, kind = (lambda: oracle.ref().sum(x, oracle.F32, [])), "reference"
+    else:
+        fn, kind = (lambda: oracle.port().reduce("sum", x, oracle.F32)), "port"
+    fn()
+    best = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fn()
+        best.append(time.perf_counter() - t0)
+    return sample_elems / (sum(best) / len(best)), kind, sum(best)
+
+
+def run_reference(args):
+    rank, _, world = env_ranks()
+    if rank != 0:
+        return
+    sample = 1 << 27  # 512 MiB of the 16 GiB tensor per step
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal(sample, dtype=np.float32)
+    if oracle.have_ref():
+        fn, kind = (lambda: oracle.ref().sum(x, oracle.F32, [])), "reference"
+    else:
+        fn, kind = (lambda: oracle.port().reduce("sum", x, oracle.F32)), "port"
+    for _ in range(max(1, min(args.warmup, 3))):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = sample / dt
+    sample_desc = f"{sample} of {TOTAL_ELEMS} fp32 elements per step (contiguous slice), 1 thread"
+    line = {
+        "impl": "reference", "metric": "sharded fp32 sum throughput (elements/s; HBM GB/s in roofline)",
+        "value": value, "unit": "elements/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "elements/s", "cores": 1, "kind": kind, "sample": sample_desc},
+        "e2e": {"value": value, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "host_cores": os.cpu_count(),
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n):
+    return {"workload": "c5_sharded_sum_f32_2p32", "tensor": "[4294967296] fp32 N(0,1), seed 4",
+            "sharding": f"sharded_1d_row over {n} rank(s), {TOTAL_ELEMS // n} elements per rank",
+            "collective": "none" if n == 1 else "ncclAllReduce(sum, 4 bytes) after the local kernel",
+            "l2_policy": "inputs larger than L2 (>= 2 GiB per rank); no flush needed"}
+
+
+# ------------------------------------------------------------------------------------------
+# per-op suite (N = 1): every named op at the benchmark configurations' shapes
+# ------------------------------------------------------------------------------------------
+def time_op(torch, fn, iters, warm=3):
+    for _ in range(warm):
+        fn(0)
+    torch.cuda.synchronize()
+    s = torch.cuda.Event(enable_timing=True)
+    e = torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(iters):
+        fn(i)
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def op_suite(torch, peak_gbs):
+    """Returns a list of {op, config, bytes, elements, ms, gbs, frac_measured, frac_8tbs}.
+    Inputs smaller than L2 are rotated over enough distinct buffers to exceed it."""
+    import numpy as np
+    from vibetensor_b200 import kernels, ops
+    dev = "cuda"
+    res = []
+
+    def add(op, config, nbytes, nelem, ms, launches=1, note=None):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        r = {"op": op, "config": config, "bytes": int(nbytes), "elements": int(nelem), "ms": round(ms, 5),
+             "gbs": round(gbs, 1), "frac_measured": round(gbs / peak_gbs, 4),
+             "frac_8tbs": round(gbs / NOMINAL_HBM_GBS, 4), "elements_per_s": nelem / (ms * 1e-3),
+             "launches": launches}
+        if note:
+            r["note"] = note
+        res.append(r)
+
+    g = torch.Generator(device=dev)
+    # ---- C1: [4096,4096] fp32 reductions, contiguous and transposed view; 4 buffers = 256 MiB > L2
+    g.manual_seed(0)
+    xs = [torch.randn((4096, 4096), device=dev, generator=g) for _ in range(4)]
+    for name, fn, dim, outb in (("sum", ops.sum, -1, 4), ("mean", ops.mean, 0, 4), ("amax", ops.amax, -1, 4),
+                                ("argmax", ops.argmax, -1, 8)):
+        for label, view in (("contig", lambda t: t), ("transposed", lambda t: t.t())):
+            ms = time_op(torch, lambda i: fn(view(xs[i % 4]), dim), 40)
+            add(f"{name}(dim={dim})", f"C1 [4096,4096] fp32 {label}", 4096 * 4096 * 4 + 4096 * outb,
+                4096 * 4096, ms, note="rotating 4 inputs (256 MiB) to defeat L2")
+    del xs
+    # ---- C4: row ops
+    for shape in ((32768, 4096), (262144, 128)):
+        for dt, es in ((torch.float32, 4), (torch.bfloat16, 2)):
+            g.manual_seed(3)
+            nbuf = max(1, int(np.ceil(300e6 / (shape[0] * shape[1] * es))))
+            xs = [(3 * torch.randn(shape, device=dev, generator=g)).to(dt) for _ in range(nbuf)]
+            gamma = 1 + 0.02 * torch.randn(shape[1], device=dev, generator=g)
+            n = shape[0] * shape[1]
+            ms = time_op(torch, lambda i: kernels.softmax(xs[i % nbuf]), 20)
+            add("softmax", f"C4 {list(shape)} {str(dt)[6:]}", 2 * n * es, n, ms)
+            ms = time_op(torch, lambda i: kernels.rmsnorm(xs[i % nbuf], gamma, 1e-6), 20)
+            add("rmsnorm", f"C4 {list(shape)} {str(dt)[6:]}", 2 * n * es + shape[1] * 4 + shape[0] * 4, n, ms)
+            del xs
+    # ---- C2: gather / scatter_add on a [1,048,576 x 256] table with 4,194,304 indices
+    V, D, N = 1 << 20, 256, 1 << 22
+    rng = np.random.default_rng(2)
+    table = torch.randn((V, D), device=dev)
+    idx_u = torch.from_numpy(rng.integers(0, V, N).astype(np.int64)).to(dev)
+    p = np.arange(1, V + 1, dtype=np.float64) ** -1.1
+    ranks = np.searchsorted(np.cumsum(p / p.sum()), rng.random(N))
+    idx_z = torch.from_numpy(rng.permutation(V)[np.minimum(ranks, V - 1)].astype(np.int64)).to(dev)
+    U = int(torch.unique(idx_z).numel())
+    out = torch.empty((N, D), device=dev)
+    st = ops.IndexStatus(dev)
+    ms = time_op(torch, lambda i: ops.index_rows(table, idx_u, status=st, out=out), 5)
+    add("index_rows/gather", "C2 table [1048576,256] fp32, 4194304 uniform int64 indices", 2 * N * D * 4 + N * 8,
+        N * D, ms)
+    upd = torch.randn((N, D), device=dev)
+    acc = torch.zeros((V, D), device=dev)
+    ms = time_op(torch, lambda i: ops.index_put_rows_(acc, idx_z, upd, accumulate=True, status=st), 5)
+    add("index_put_(accumulate)/scatter_add fp32", f"C2 Zipf(1.1) indices, {U} distinct rows",
+        N * D * 4 + N * 8 + 2 * U * D * 4, N * D, ms)
+    del upd, acc, out, table
+    updi = torch.randint(-1000, 1001, (N, D), device=dev, dtype=torch.int64)
+    acci = torch.zeros((V, D), device=dev, dtype=torch.int64)
+    ms = time_op(torch, lambda i: ops.index_put_rows_(acci, idx_z, updi, accumulate=True, status=st), 5)
+    add("index_put_(accumulate)/scatter_add int64", f"C2 Zipf(1.1) indices, {U} distinct rows",
+        N * D * 8 + N * 8 + 2 * U * D * 8, N * D, ms)
+    st.check("bench", V)
+    del updi, acci
+    # ---- C3: bf16 broadcast chain into a transposed output view
+    g.manual_seed(1)
+    a = torch.randn((64, 1, 512, 1), device=dev, generator=g).bfloat16()
+    b = torch.randn((1, 128, 1, 1024), device=dev, generator=g).bfloat16()
+    c = torch.randn((64, 128, 1, 1024), device=dev, generator=g).bfloat16()
+    base = torch.empty((64, 1024, 512, 128), device=dev, dtype=torch.bfloat16)
+    outv = base.transpose(1, 3)
+    n = outv.numel()
+    ms = time_op(torch, lambda i: ops.where_gt0_addcmul(a, b, c, out=outv), 5)
+    add("where(a>0, a+b*c, 0) fused", "C3 bf16 a[64,1,512,1] b[1,128,1,1024] c[64,128,1,1024] -> transpose(1,3) view",
+        n * 2 + (a.numel() + b.numel() + c.numel()) * 2, n, ms)
+    del base, outv
+    torch.cuda.empty_cache()
+    return res
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank, local_rank, world = env_ranks()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    n = world
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if n > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    from vibetensor_b200 import fabric, ops
+
+    peak_gbs, peak_kind = measured_peak()
+    shard_elems = TOTAL_ELEMS // n
+    # per-rank stream of the seed: shards are reproducible without one host holding 16 GiB
+    g = torch.Generator(device=dev)
+    g.manual_seed(4 * 1000 + rank)
+    shard = torch.empty(shard_elems, device=dev, dtype=torch.float32)
+    step_fill = 1 << 28
+    for o in range(0, shard_elems, step_fill):
+        shard[o:o + step_fill].normal_(generator=g)
+    mesh = fabric.FabricMesh.from_world()
+    ft = fabric.FabricTensor.sharded_1d_row(mesh, shard)
+    assert ft.global_shape == (TOTAL_ELEMS,)
+
+    def barrier():
+        if n > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    result = None
+    for _ in range(max(args.warmup, 3)):
+        result = fabric.sum(ft)
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    kern_events = []
+    barrier()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for _ in range(args.steps):
+        k0 = torch.cuda.Event(enable_timing=True)
+        k1 = torch.cuda.Event(enable_timing=True)
+        k0.record()
+        partial = ops.reduce("sum", shard, None, False, partial=True)   # the local kernel
+        k1.record()
+        kern_events.append((k0, k1))
+        if n > 1:
+            dist.all_reduce(partial)                                     # 4-byte combine
+        result = partial
+    t_end.record()
+    barrier()
+    ms_total = t_start.elapsed_time(t_end)
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if n > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    kern_ms = sum(a.elapsed_time(b) for a, b in kern_events) / len(kern_events)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # correctness of what was timed: against an fp64 fold of the same shards
+    truth = shard.double().sum()
+    scale = shard.abs().double().sum()
+    if n > 1:
+        dist.all_reduce(truth)
+        dist.all_reduce(scale)
+    rel = abs(result.double().item() - truth.item()) / scale.item()
+    assert rel <= 1e-5, f"sharded sum off by {rel:.3e} of sum|x|"
+
+    # ---- e2e: the shard starts in pinned host memory every step
+    e2e = None
+    try:
+        e2e = run_e2e(torch, dist, ops, shard, n, args)
+    except Exception as ex:  # host memory for the pinned copy may be unavailable
+        e2e = {"value": None, "unit": "elements/s", "error": str(ex)[:200]}
+
+    suite = None
+    cpu = None
+    if n == 1 and rank == 0:
+        del shard, ft
+        torch.cuda.empty_cache()
+        if not args.no_suite:
+            suite = op_suite(torch, peak_gbs)
+        v, kind, secs = cpu_reference_sum(1 << 28, 8)
+        cpu = {"value": v, "unit": "elements/s", "cores": 1, "kind": kind,
+               "sample": f"8 passes over {1 << 28} of {TOTAL_ELEMS} fp32 elements ({secs:.1f} s), single thread "
+                         f"(the reference CPU path is single-threaded); host has {os.cpu_count()} cores"}
+
+    if rank == 0:
+        shard_bytes = shard_elems * 4
+        achieved = shard_bytes / (kern_ms * 1e-3) / 1e9
+        line = {
+            "metric": "sharded fp32 sum throughput (elements/s; HBM GB/s in roofline)",
+            "value": TOTAL_ELEMS / (ms_step * 1e-3), "unit": "elements/s", "n_gpus": n, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(n),
+            "gb_per_s_whole_job": TOTAL_ELEMS * 4 / (ms_step * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak_gbs, "unit": "GB/s",
+                         "frac": round(achieved / peak_gbs, 4), "peak_source": peak_kind,
+                         "frac_of_nominal_8tbs": round(achieved / NOMINAL_HBM_GBS, 4),
+                         "kernel": "row_block_kernel<float, SumR<float>, 4>",
+                         "bytes_per_launch": shard_bytes, "ms_per_launch": kern_ms,
+                         "traffic": (REDUCE_TRAFFIC_BYTES_PER_ELEM * shard_elems
+                                     if REDUCE_TRAFFIC_BYTES_PER_ELEM is not None else None)},
+            "e2e": e2e, "gpu_launches": args.steps * n, "clocks": clocks,
+            "parity": {"rel_err_vs_fp64_over_sum_abs": rel},
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        if suite is not None:
+            line["ops"] = suite
+        print(json.dumps(line), flush=True)
+    if n > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(torch, dist, ops, shard, n, args):
+    """Host-resident input: per step, H2D of the whole shard from pinned memory in 256 MiB
+    chunks on a copy stream, per-chunk partial sums on the compute stream behind events,
+    one combine, all-reduce, and a D2H read of the 4-byte result."""
+    dev = shard.device
+    steps = max(1, min(args.steps, 3))
+    chunk = 1 << 26  # elements (256 MiB)
+    nchunks = (shard.numel() + chunk - 1) // chunk
+    host = torch.empty(shard.numel(), dtype=torch.float32, pin_memory=True)
+    host.copy_(shard)  # the synthetic shard, now host-resident
+    torch.cuda.synchronize()
+    stage = [torch.empty(chunk, device=dev, dtype=torch.float32) for _ in range(2)]
+    free_ev = [torch.cuda.Event() for _ in range(2)]
+    copy_stream = torch.cuda.Stream(device=dev)
+    partials = torch.empty(nchunks, device=dev, dtype=torch.float32)
+    out_host = torch.empty(1, dtype=torch.float32, pin_memory=True)
+    compute = torch.cuda.current_stream(dev)
+
+    def one_step():
+        for c in range(nchunks):
+            lo, hi = c * chunk, min((c + 1) * chunk, shard.numel())
+            buf = stage[c % 2][: hi - lo]
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(free_ev[c % 2])
+                buf.copy_(host[lo:hi], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(copy_stream)
+            compute.wait_event(ready)
+            p = ops.reduce("sum", buf, None, False, partial=True)
+            partials[c:c + 1].copy_(p.reshape(1))
+            free_ev[c % 2].record(compute)
+        total = ops.reduce("sum", partials, None, False, partial=True)
+        if n > 1:
+            dist.all_reduce(total)
+        out_host.copy_(total.reshape(1), non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        return float(out_host[0])
+
+    for ev in free_ev:
+        ev.record(compute)
+    one_step()
+    if n > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        val = one_step()
+    torch.cuda.synchronize()
+    dt = torch.tensor([(time.perf_counter() - t0) / steps], device=dev, dtype=torch.float64)
+    if n > 1:
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    del host
+    return {"value": TOTAL_ELEMS / dt.item(), "unit": "elements/s", "ms_per_step": dt.item() * 1e3,
+            "h2d_bytes_per_step": shard.numel() * 4 * n, "d2h_bytes_per_step": 4 * n, "steps": steps,
+            "launches_per_step": (nchunks + 1) * n, "result": val}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-suite", action="store_true", help="skip the per-op table (N = 1)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -433,19 +433,42 @@ int vbo_index_put_lastdim(int dtype, int64_t B, int64_t K0, void* self, const in
 }
 
 /* ---- row ops ---- */
-/* Triton softmax_kernel (vibe_kernels/softmax/vbt_native.py:59-97): fp32 math,
+/* Both Triton kernels reduce a row block by block: tl.sum over a block of BLOCK lanes (a
+ * halving tree), block results accumulated in order.  The restatement keeps that shape so
+ * that long rows see the same kind of rounding; the order inside tl.sum is Triton's own and
+ * is not pinned by the reference, which is why these paths are tolerance-checked. */
+static float block_tree_sum(const float* vals, int64_t n, int64_t block, float* tmp) {
+  float acc = 0.f;
+  for (int64_t start = 0; start < n; start += block) {
+    for (int64_t i = 0; i < block; ++i) tmp[i] = (start + i < n) ? vals[start + i] : 0.f;
+    for (int64_t s = block / 2; s > 0; s /= 2)
+      for (int64_t i = 0; i < s; ++i) tmp[i] += tmp[i + s];
+    acc += tmp[0];
+  }
+  return acc;
+}
+static int64_t next_pow2(int64_t v) { int64_t p = 1; while (p < v) p <<= 1; return p; }
+
+/* Triton softmax_kernel (vibe_kernels/softmax/vbt_native.py:39-97): fp32 math,
  * m = max x; s = sum exp(x - m); s = max(s, 1e-20); y = exp(x - (log s + m));
- * log_softmax: y = x - (log s + m) (:262-328). */
+ * log_softmax: y = x - (log s + m).  BLOCK_SIZE = clamp(round_up(cols, 128), 128, 1024)
+ * (:240-252). */
 int vbo_softmax(int dtype, int64_t rows, int64_t cols, const void* x, int64_t row_stride,
                 void* out, int log_softmax) {
   const int es = itemsize(dtype);
+  int64_t block = (cols + 127) / 128 * 128;
+  if (block < 128) block = 128;
+  if (block > 1024) block = 1024;
+  block = next_pow2(block); /* tl.arange needs a power of two; 128..1024 */
+  float* e = (float*)malloc(sizeof(float) * (size_t)(cols > 0 ? cols : 1));
+  float* tmp = (float*)malloc(sizeof(float) * (size_t)block);
   for (int64_t r = 0; r < rows; ++r) {
     const char* px = (const char*)x + r * row_stride * es;
     char* po = (char*)out + r * cols * es;
     float m = -INFINITY;
     for (int64_t j = 0; j < cols; ++j) { float v = load_f(px + j * es, dtype); m = fmaxf(m, v); }
-    float s = 0.f;
-    for (int64_t j = 0; j < cols; ++j) s += expf(load_f(px + j * es, dtype) - m);
+    for (int64_t j = 0; j < cols; ++j) e[j] = expf(load_f(px + j * es, dtype) - m);
+    float s = block_tree_sum(e, cols, block, tmp);
     s = fmaxf(s, 1e-20f);
     const float lse = logf(s) + m;
     for (int64_t j = 0; j < cols; ++j) {
@@ -453,19 +476,26 @@ int vbo_softmax(int dtype, int64_t rows, int64_t cols, const void* x, int64_t ro
       store_f(po + j * es, dtype, log_softmax ? v : expf(v));
     }
   }
+  free(e);
+  free(tmp);
   return 0;
 }
-/* Triton _rmsnorm_fwd_kernel (vibe_kernels/rmsnorm/vbt_native.py:75-103):
+/* Triton _rmsnorm_fwd_kernel (vibe_kernels/rmsnorm/vbt_native.py:55-103):
  * inv_rms = rsqrt(sum x^2 / cols + eps); y = x * inv_rms * gamma; output cast to the
- * input dtype (vibe_kernels/rmsnorm/impl/triton_impl.py:99-104). */
+ * input dtype (vibe_kernels/rmsnorm/impl/triton_impl.py:99-104).
+ * BLOCK = min(256, next_pow2(hidden)) (:378-380). */
 int vbo_rmsnorm(int dtype, int64_t rows, int64_t cols, const void* x, int64_t row_stride,
                 const float* gamma, float eps, void* out, float* inv_rms) {
   const int es = itemsize(dtype);
+  int64_t block = next_pow2(cols);
+  if (block > 256) block = 256;
+  float* sq = (float*)malloc(sizeof(float) * (size_t)(cols > 0 ? cols : 1));
+  float* tmp = (float*)malloc(sizeof(float) * (size_t)block);
   for (int64_t r = 0; r < rows; ++r) {
     const char* px = (const char*)x + r * row_stride * es;
     char* po = (char*)out + r * cols * es;
-    float ss = 0.f;
-    for (int64_t j = 0; j < cols; ++j) { float v = load_f(px + j * es, dtype); ss += v * v; }
+    for (int64_t j = 0; j < cols; ++j) { float v = load_f(px + j * es, dtype); sq[j] = v * v; }
+    const float ss = block_tree_sum(sq, cols, block, tmp);
     const float inv = (float)(1.0 / sqrt((double)(ss / (float)cols + eps)));
     if (inv_rms) inv_rms[r] = inv;
     for (int64_t j = 0; j < cols; ++j) {
@@ -474,6 +504,8 @@ int vbo_rmsnorm(int dtype, int64_t rows, int64_t cols, const void* x, int64_t ro
       store_f(po + j * es, dtype, v);
     }
   }
+  free(sq);
+  free(tmp);
   return 0;
 }
 

@@ -205,22 +205,43 @@ def test_where_and_masked_fill(ops, port, dtype):
         ops.where(torch.ones(4, device="cuda"), torch.ones(4, device="cuda"), torch.ones(4, device="cuda"))
 
 
-def test_strided_inputs_negative_strides_and_offsets(ops, port):
+def test_strided_inputs_and_outputs(ops, port):
     rng = np.random.default_rng(17)
     a_np = rng.standard_normal((9, 14), dtype=np.float32)
     b_np = rng.standard_normal((9, 14), dtype=np.float32)
     ta, va = strided_like(a_np, torch.float32, (3, 40), 1024, offset=5)      # transposed-ish, gaps
-    tb = torch.from_numpy(b_np).cuda().flip(1)                               # negative stride
+    tb = torch.from_numpy(b_np).cuda()
     got = ops.add(ta, tb).cpu().numpy()
-    np.testing.assert_array_equal(got, port.binary("add", va, b_np[:, ::-1], oracle.F32))
-    # strided (column-major) output
-    out = torch.empty((14, 9), device="cuda").t()
+    np.testing.assert_array_equal(got, port.binary("add", va, b_np, oracle.F32))
+    out = torch.empty((14, 9), device="cuda").t()                            # column-major output
     ops.mul(ta, tb, out=out)
-    np.testing.assert_array_equal(out.cpu().numpy(), a_np * b_np[:, ::-1])
-    # output walked backwards
-    out2 = torch.zeros((9, 14), device="cuda")
-    ops.sub(ta, tb, out=out2.flip(0))
-    np.testing.assert_array_equal(out2.cpu().numpy()[::-1], a_np - b_np[:, ::-1])
+    np.testing.assert_array_equal(out.cpu().numpy(), a_np * b_np)
+
+
+def test_negative_strides_through_the_c_abi(port):
+    """torch has no negative strides, VibeTensor views do: build the descriptors by hand."""
+    import ctypes
+    from vibetensor_b200 import _lib
+    L = _lib.lib()
+    rng = np.random.default_rng(19)
+    a_np = rng.standard_normal((6, 10), dtype=np.float32)
+    b_np = rng.standard_normal((6, 10), dtype=np.float32)
+    ta, tb = torch.from_numpy(a_np).cuda(), torch.from_numpy(b_np).cuda()
+    out = torch.zeros((6, 10), device="cuda")
+
+    def d(t, shape, strides, off):
+        keep = ((ctypes.c_int64 * 2)(*shape), (ctypes.c_int64 * 2)(*strides))
+        s = _lib.VbtTensor(t.data_ptr() + 4 * off, _lib.F32, 2, keep[0], keep[1])
+        s._keep = keep
+        return s
+    # b read reversed along both dims, out written with rows reversed
+    db = d(tb, (6, 10), (-10, -1), 59)
+    da = d(ta, (6, 10), (10, 1), 0)
+    do = d(out, (6, 10), (-10, 1), 50)
+    _lib.check(L.vbt_b200_binary(0, ctypes.byref(do), ctypes.byref(da), ctypes.byref(db),
+                                 _lib.stream_ptr(out)))
+    want = a_np + b_np[::-1, ::-1]
+    np.testing.assert_array_equal(out.cpu().numpy()[::-1], want)
 
 
 def test_exhaustive_small_shapes_vs_oracle(ops, port):

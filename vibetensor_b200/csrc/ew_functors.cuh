@@ -37,8 +37,8 @@ __device__ __forceinline__ float unary_math(float a) {
     if (a > 20.f) return a;
     if (a < -20.f) return expf(a);
     return log1pf(expf(a));
-  } else if constexpr (OP == VBT_B200_U_RELU6) return a != a ? a : fminf(fmaxf(a, 0.f), 6.f);
-  else if constexpr (OP == VBT_B200_U_HARDTANH) return a != a ? a : fminf(fmaxf(a, -1.f), 1.f);
+  } else if constexpr (OP == VBT_B200_U_RELU6) return a < 0.f ? 0.f : (a > 6.f ? 6.f : a);
+  else if constexpr (OP == VBT_B200_U_HARDTANH) return a < -1.f ? -1.f : (a > 1.f ? 1.f : a);
   else return a;
 }
 

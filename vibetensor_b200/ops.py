@@ -45,7 +45,10 @@ def _alloc_out(out, shape, dtype, like):
 
 
 def _bshape(*ts):
-    return torch.broadcast_shapes(*[tuple(t.shape) for t in ts])
+    try:
+        return torch.broadcast_shapes(*[tuple(t.shape) for t in ts])
+    except RuntimeError:
+        raise ValueError("shape mismatch: operands cannot be broadcast together") from None
 
 
 # --------------------------------------------------------------------------------------
