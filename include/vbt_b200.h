@@ -233,6 +233,22 @@ VBT_B200_API vbt_b200_status vbt_b200_reduce(int32_t op, const vbt_b200_tensor* 
                                 const vbt_b200_tensor* out_index, const vbt_b200_tensor* self,
                                 const int64_t* dims, int32_t ndims, int32_t keepdim,
                                 void* workspace, size_t workspace_bytes, void* stream);
+/* The same reduction for callers that cannot supply scratch memory (no counterpart in the
+ * reference, whose kernels take their temporaries from its caching allocator).  Meant for
+ * hosts that cannot allocate at call time -- a plugin whose host API only creates "dense
+ * like" outputs, code running under an allocator lock, an embedder that bans cudaMalloc after
+ * start-up.  The partials and ticket counters live in a fixed device array of
+ * VBT_B200_NOALLOC_SCRATCH_BYTES inside the library (held by every GPU that loads it);
+ * shapes that need more are rejected with INVALID_ARGUMENT.  No cudaMalloc / cudaFree or
+ * other allocating call is made.  The first call on a device looks up the array's device
+ * address (cudaGetSymbolAddress, cached): make that call before any stream capture.  Every
+ * call on a device shares the array: calls that may overlap on the GPU race and must be
+ * ordered by the caller.  Results are bit-identical to vbt_b200_reduce. */
+#define VBT_B200_NOALLOC_SCRATCH_BYTES (2u << 20)
+VBT_B200_API vbt_b200_status vbt_b200_reduce_noalloc(int32_t op, const vbt_b200_tensor* out,
+                                        const vbt_b200_tensor* out_index,
+                                        const vbt_b200_tensor* self, const int64_t* dims,
+                                        int32_t ndims, int32_t keepdim, void* stream);
 /* Reduced shape for (self, dims, keepdim): cuda_reduction.cu:749-810.  INVALID_ARGUMENT
  * "<op>: dim out of range" on a bad dim. */
 VBT_B200_API vbt_b200_status vbt_b200_reduce_shape(const vbt_b200_tensor* self, const int64_t* dims,

@@ -55,6 +55,7 @@ SIGNATURES = {
     "vbt_b200_ti_plan": (_i32, [ctypes.POINTER(_P), _i32, _i64p, _i64p, _i32p, _i32p, _i32p]),
     "vbt_b200_reduce_workspace_bytes": (ctypes.c_size_t, [_i32, _P, _i64p, _i32]),
     "vbt_b200_reduce": (_i32, [_i32, _P, _P, _P, _i64p, _i32, _i32, _vp, ctypes.c_size_t, _vp]),
+    "vbt_b200_reduce_noalloc": (_i32, [_i32, _P, _P, _P, _i64p, _i32, _i32, _vp]),
     "vbt_b200_reduce_shape": (_i32, [_P, _i64p, _i32, _i32, _i64p, _i32p]),
     "vbt_b200_index_rows": (_i32, [_P, _P, _P, _i32, _vp, _vp]),
     "vbt_b200_index_put_rows": (_i32, [_P, _P, _P, _i32, _i32, _vp, _vp]),

@@ -19,6 +19,7 @@
 // cross-block fold is done by whichever block draws the last ticket.
 #include <cfloat>
 #include <climits>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -807,3 +808,75 @@ vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_tensor* parti
 }
 
 }  // extern "C"
+
+// =====================================================================================
+// vbt_b200_reduce_noalloc: the same reduction for callers that cannot hand over scratch.
+//
+// Some hosts of this library have no way to obtain device memory at call time: a plugin
+// kernel running under a host whose allocator API only hands out "dense like" outputs, a
+// callback that runs while the allocator's lock is held, or an embedder that forbids
+// cudaMalloc after start-up.  For them the split reductions' scratch (chunk partials and
+// ticket counters) lives in the fixed device array below instead of a caller workspace.
+//
+//  * The array is part of the loaded module: every GPU that loads the library holds
+//    VBT_B200_NOALLOC_SCRATCH_BYTES of it until the process exits.
+//  * Host code must not pass the array's name to a kernel -- in host code that name is only
+//    a stand-in for the symbol, not a device address.  The device address is looked up with
+//    cudaGetSymbolAddress once per device, with that device current, and cached.  That
+//    look-up happens on the FIRST call on a device, so make that first call outside any
+//    stream capture.
+//  * Nothing is allocated or freed here, by this library or by anything it calls.
+//  * All calls on a device share the one array, and it keeps whatever the previous call
+//    left in it.  The only part that has to start at zero -- the ticket counters -- is
+//    cleared on the stream at the start of every call.  Two calls whose kernels can overlap
+//    on the GPU (different streams, no dependency) would race on the array: callers must
+//    order them.
+//  * Shapes whose scratch need exceeds the array are rejected with INVALID_ARGUMENT.
+// =====================================================================================
+static __device__ __align__(256) unsigned char vb_noalloc_scratch[VBT_B200_NOALLOC_SCRATCH_BYTES];
+
+namespace vb {
+namespace {
+// device address of vb_noalloc_scratch per device ordinal; looked up under the mutex
+vbt_b200_status noalloc_scratch_ptr(int device, void** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* cached[kMaxDevices] = {};
+  VB_ARG(device >= 0 && device < kMaxDevices, "reduce_noalloc: device ordinal out of range");
+  std::lock_guard<std::mutex> lk(mu);
+  if (cached[device] == nullptr) {
+    void* p = nullptr;
+    // `device` is current here (DeviceScope in the caller), so this resolves that device's copy
+    VB_CUDA(cudaGetSymbolAddress(&p, vb_noalloc_scratch));
+    VB_REQUIRE(p != nullptr, VBT_B200_CUDA_ERROR, "reduce_noalloc: symbol address is null");
+    cached[device] = p;
+  }
+  *out = cached[device];
+  return VBT_B200_OK;
+}
+}  // namespace
+}  // namespace vb
+
+extern "C" vbt_b200_status vbt_b200_reduce_noalloc(int32_t op, const vbt_b200_tensor* out,
+                                                   const vbt_b200_tensor* out_index,
+                                                   const vbt_b200_tensor* self, const int64_t* dims,
+                                                   int32_t ndims, int32_t keepdim, void* stream) {
+  using namespace vb;
+  VB_ARG(op >= 0 && op < VBT_B200_R_COUNT, "reduce_noalloc: unknown op code");
+  VB_TRY(validate_tensor(self, "reduce_noalloc"));
+  VB_ARG(out != nullptr || out_index != nullptr, "reduce_noalloc: null output");
+  const size_t need = vbt_b200_reduce_workspace_bytes(op, self, dims, ndims);
+  if (need > VBT_B200_NOALLOC_SCRATCH_BYTES)
+    return fail(VBT_B200_INVALID_ARGUMENT,
+                std::string(op_name(op)) + ": this shape needs " + std::to_string(need) +
+                    " bytes of scratch, more than the fixed " +
+                    std::to_string(static_cast<size_t>(VBT_B200_NOALLOC_SCRATCH_BYTES)) +
+                    " bytes of vbt_b200_reduce_noalloc; use vbt_b200_reduce with a workspace");
+  void* scratch = nullptr;
+  if (need > 0) {
+    const void* anchor = out ? out->data : out_index->data;
+    DeviceScope scope(anchor);
+    VB_TRY(noalloc_scratch_ptr(scope.device(), &scratch));
+  }
+  return vbt_b200_reduce(op, out, out_index, self, dims, ndims, keepdim, scratch, need, stream);
+}
