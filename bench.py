@@ -171,7 +171,8 @@ def run_reference(args):
 
 
 def workload_config(n):
-    return {"workload": "c5_sharded_sum_f32_2p32", "tensor": "[4294967296] fp32 N(0,1), seed 4",
+    return {"workload": "c5_sharded_sum_f32_2p32" if TOTAL_ELEMS == 1 << 32 else "c5_sharded_sum_f32_reduced",
+            "tensor": f"[{TOTAL_ELEMS}] fp32 N(0,1), seed 4",
             "sharding": f"sharded_1d_row over {n} rank(s), {TOTAL_ELEMS // n} elements per rank",
             "collective": "none" if n == 1 else "ncclAllReduce(sum, 4 bytes) after the local kernel",
             "l2_policy": "inputs larger than L2 (>= 2 GiB per rank); no flush needed"}
@@ -180,21 +181,43 @@ def workload_config(n):
 # ------------------------------------------------------------------------------------------
 # per-op suite (N = 1): every named op at the benchmark configurations' shapes
 # ------------------------------------------------------------------------------------------
-def time_op(torch, fn, iters, warm=3):
+def time_op(torch, fn, iters, warm=3, graph=True):
+    """Mean device time of fn(i) in ms.  The calls are captured once into a CUDA graph and the
+    graph is replayed, so that host-side launch cost (Python, ctypes) does not sit between
+    kernels of a few microseconds; falls back to an eager loop if capture is refused."""
     for _ in range(warm):
         fn(0)
     torch.cuda.synchronize()
     s = torch.cuda.Event(enable_timing=True)
     e = torch.cuda.Event(enable_timing=True)
+    if graph:
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(iters):
+                    fn(i)
+            g.replay()
+            torch.cuda.synchronize()
+            reps = 3
+            s.record()
+            for _ in range(reps):
+                g.replay()
+            e.record()
+            torch.cuda.synchronize()
+            ms = s.elapsed_time(e) / (iters * reps)
+            del g
+            return ms, "cuda-graph replay"
+        except Exception:
+            torch.cuda.synchronize()
     s.record()
     for i in range(iters):
         fn(i)
     e.record()
     torch.cuda.synchronize()
-    return s.elapsed_time(e) / iters
+    return s.elapsed_time(e) / iters, "eager loop"
 
 
-def op_suite(torch, peak_gbs):
+def op_suite(torch, peak_gbs, scale="full"):
     """Returns a list of {op, config, bytes, elements, ms, gbs, frac_measured, frac_8tbs}.
     Inputs smaller than L2 are rotated over enough distinct buffers to exceed it."""
     import numpy as np
@@ -202,12 +225,15 @@ def op_suite(torch, peak_gbs):
     dev = "cuda"
     res = []
 
-    def add(op, config, nbytes, nelem, ms, launches=1, note=None):
+    small = scale == "small"
+
+    def add(op, config, nbytes, nelem, timed, launches=1, note=None):
+        ms, how = timed
         gbs = nbytes / (ms * 1e-3) / 1e9
         r = {"op": op, "config": config, "bytes": int(nbytes), "elements": int(nelem), "ms": round(ms, 5),
              "gbs": round(gbs, 1), "frac_measured": round(gbs / peak_gbs, 4),
              "frac_8tbs": round(gbs / NOMINAL_HBM_GBS, 4), "elements_per_s": nelem / (ms * 1e-3),
-             "launches": launches}
+             "launches": launches, "timing": how}
         if note:
             r["note"] = note
         res.append(r)
@@ -224,7 +250,7 @@ def op_suite(torch, peak_gbs):
                 4096 * 4096, ms, note="rotating 4 inputs (256 MiB) to defeat L2")
     del xs
     # ---- C4: row ops
-    for shape in ((32768, 4096), (262144, 128)):
+    for shape in (((4096, 4096), (32768, 128)) if small else ((32768, 4096), (262144, 128))):
         for dt, es in ((torch.float32, 4), (torch.bfloat16, 2)):
             g.manual_seed(3)
             nbuf = max(1, int(np.ceil(300e6 / (shape[0] * shape[1] * es))))
@@ -237,7 +263,7 @@ def op_suite(torch, peak_gbs):
             add("rmsnorm", f"C4 {list(shape)} {str(dt)[6:]}", 2 * n * es + shape[1] * 4 + shape[0] * 4, n, ms)
             del xs
     # ---- C2: gather / scatter_add on a [1,048,576 x 256] table with 4,194,304 indices
-    V, D, N = 1 << 20, 256, 1 << 22
+    V, D, N = 1 << 20, 256, (1 << 19 if small else 1 << 22)
     rng = np.random.default_rng(2)
     table = torch.randn((V, D), device=dev)
     idx_u = torch.from_numpy(rng.integers(0, V, N).astype(np.int64)).to(dev)
@@ -248,7 +274,7 @@ def op_suite(torch, peak_gbs):
     out = torch.empty((N, D), device=dev)
     st = ops.IndexStatus(dev)
     ms = time_op(torch, lambda i: ops.index_rows(table, idx_u, status=st, out=out), 5)
-    add("index_rows/gather", "C2 table [1048576,256] fp32, 4194304 uniform int64 indices", 2 * N * D * 4 + N * 8,
+    add("index_rows/gather", f"C2 table [1048576,256] fp32, {N} uniform int64 indices", 2 * N * D * 4 + N * 8,
         N * D, ms)
     upd = torch.randn((N, D), device=dev)
     acc = torch.zeros((V, D), device=dev)
@@ -265,14 +291,15 @@ def op_suite(torch, peak_gbs):
     del updi, acci
     # ---- C3: bf16 broadcast chain into a transposed output view
     g.manual_seed(1)
-    a = torch.randn((64, 1, 512, 1), device=dev, generator=g).bfloat16()
+    n0 = 8 if small else 64
+    a = torch.randn((n0, 1, 512, 1), device=dev, generator=g).bfloat16()
     b = torch.randn((1, 128, 1, 1024), device=dev, generator=g).bfloat16()
-    c = torch.randn((64, 128, 1, 1024), device=dev, generator=g).bfloat16()
-    base = torch.empty((64, 1024, 512, 128), device=dev, dtype=torch.bfloat16)
+    c = torch.randn((n0, 128, 1, 1024), device=dev, generator=g).bfloat16()
+    base = torch.empty((n0, 1024, 512, 128), device=dev, dtype=torch.bfloat16)
     outv = base.transpose(1, 3)
     n = outv.numel()
     ms = time_op(torch, lambda i: ops.where_gt0_addcmul(a, b, c, out=outv), 5)
-    add("where(a>0, a+b*c, 0) fused", "C3 bf16 a[64,1,512,1] b[1,128,1,1024] c[64,128,1,1024] -> transpose(1,3) view",
+    add("where(a>0, a+b*c, 0) fused", f"C3 bf16 a[{n0},1,512,1] b[1,128,1,1024] c[{n0},128,1,1024] -> transpose(1,3) view",
         n * 2 + (a.numel() + b.numel() + c.numel()) * 2, n, ms)
     del base, outv
     torch.cuda.empty_cache()
@@ -299,6 +326,12 @@ def run_ours(args):
     from vibetensor_b200 import fabric, ops
 
     peak_gbs, peak_kind = measured_peak()
+    if args.suite_only:
+        if rank == 0:
+            suite = op_suite(torch, peak_gbs, args.suite_scale)
+            print(json.dumps({"metric": "per-op HBM GB/s", "n_gpus": 1, "suite_scale": args.suite_scale,
+                              "peak_gbs": peak_gbs, "peak_source": peak_kind, "ops": suite}), flush=True)
+        return
     shard_elems = TOTAL_ELEMS // n
     # per-rank stream of the seed: shards are reproducible without one host holding 16 GiB
     g = torch.Generator(device=dev)
@@ -360,10 +393,11 @@ def run_ours(args):
 
     # ---- e2e: the shard starts in pinned host memory every step
     e2e = None
-    try:
-        e2e = run_e2e(torch, dist, ops, shard, n, args)
-    except Exception as ex:  # host memory for the pinned copy may be unavailable
-        e2e = {"value": None, "unit": "elements/s", "error": str(ex)[:200]}
+    if not args.no_e2e:
+        try:
+            e2e = run_e2e(torch, dist, ops, shard, n, args)
+        except Exception as ex:  # host memory for the pinned copy may be unavailable
+            e2e = {"value": None, "unit": "elements/s", "error": str(ex)[:200]}
 
     suite = None
     cpu = None
@@ -371,7 +405,8 @@ def run_ours(args):
         del shard, ft
         torch.cuda.empty_cache()
         if not args.no_suite:
-            suite = op_suite(torch, peak_gbs)
+            suite = op_suite(torch, peak_gbs, args.suite_scale)
+    if n == 1 and rank == 0 and not args.no_cpu:
         v, kind, secs = cpu_reference_sum(1 << 28, 8)
         cpu = {"value": v, "unit": "elements/s", "cores": 1, "kind": kind,
                "sample": f"8 passes over {1 << 28} of {TOTAL_ELEMS} fp32 elements ({secs:.1f} s), single thread "
@@ -469,7 +504,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-suite", action="store_true", help="skip the per-op table (N = 1)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-resident end-to-end leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--suite-only", action="store_true", help="run only the per-op table")
+    ap.add_argument("--suite-scale", default="full", choices=["full", "small"],
+                    help="small: reduced C2/C3/C4 shapes (a few GB on the device) for profiler captures")
+    ap.add_argument("--elems", type=int, default=TOTAL_ELEMS,
+                    help="elements of the headline tensor (default 2^32; smaller only for profiler captures)")
     args = ap.parse_args()
+    global TOTAL_ELEMS
+    TOTAL_ELEMS = args.elems
     if args.impl == "reference":
         run_reference(args)
     else:

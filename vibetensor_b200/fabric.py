@@ -100,9 +100,12 @@ class FabricPlacement:
         return end - self.shard_offsets[rank]
 
 
-def _backend(local_ops):
+def _backend(local_ops, *tensors):
     if local_ops is not None:
         return local_ops
+    for t in tensors:
+        if not t.is_cuda:  # checked on every rank before any collective is entered
+            raise ValueError("vibetensor_b200 ops take CUDA tensors (there is no CPU path)")
     from . import ops
     return ops
 
@@ -185,7 +188,7 @@ def _same_placement(a: FabricTensor, b: FabricTensor, what: str):
 
 def _elementwise(name: str, a: FabricTensor, b: FabricTensor, local_ops=None) -> FabricTensor:
     _same_placement(a, b, "fabric." + name)
-    out = _backend(local_ops).binary(name, a.shard, b.shard)
+    out = _backend(local_ops, a.shard, b.shard).binary(name, a.shard, b.shard)
     return FabricTensor(a.placement, out)
 
 
@@ -218,8 +221,8 @@ def reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False, local_o
     """
     if name not in _REDUCE_OP:
         raise FabricError(f"fabric.reduce: unsupported reduction {name!r}")
-    be = _backend(local_ops)
     x = ft.shard
+    be = _backend(local_ops, x)
     nd = x.dim()
     dims = list(range(nd)) if dim is None else ([dim] if isinstance(dim, int) else list(dim))
     dims = sorted({d + nd if d < 0 else d for d in dims})
