@@ -217,7 +217,7 @@ def time_op(torch, fn, iters, warm=3, graph=True):
     return s.elapsed_time(e) / iters, "eager loop"
 
 
-def op_suite(torch, peak_gbs, scale="full"):
+def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4")):
     """Returns a list of {op, config, bytes, elements, ms, gbs, frac_measured, frac_8tbs}.
     Inputs smaller than L2 are rotated over enough distinct buffers to exceed it."""
     import numpy as np
@@ -241,16 +241,16 @@ def op_suite(torch, peak_gbs, scale="full"):
     g = torch.Generator(device=dev)
     # ---- C1: [4096,4096] fp32 reductions, contiguous and transposed view; 4 buffers = 256 MiB > L2
     g.manual_seed(0)
-    xs = [torch.randn((4096, 4096), device=dev, generator=g) for _ in range(4)]
+    xs = [torch.randn((4096, 4096), device=dev, generator=g) for _ in range(4 if "c1" in which else 0)]
     for name, fn, dim, outb in (("sum", ops.sum, -1, 4), ("mean", ops.mean, 0, 4), ("amax", ops.amax, -1, 4),
                                 ("argmax", ops.argmax, -1, 8)):
-        for label, view in (("contig", lambda t: t), ("transposed", lambda t: t.t())):
+        for label, view in ((("contig", lambda t: t), ("transposed", lambda t: t.t())) if "c1" in which else ()):
             ms = time_op(torch, lambda i: fn(view(xs[i % 4]), dim), 40)
             add(f"{name}(dim={dim})", f"C1 [4096,4096] fp32 {label}", 4096 * 4096 * 4 + 4096 * outb,
                 4096 * 4096, ms, note="rotating 4 inputs (256 MiB) to defeat L2")
     del xs
     # ---- C4: row ops
-    for shape in (((4096, 4096), (32768, 128)) if small else ((32768, 4096), (262144, 128))):
+    for shape in (() if "c4" not in which else ((4096, 4096), (32768, 128)) if small else ((32768, 4096), (262144, 128))):
         for dt, es in ((torch.float32, 4), (torch.bfloat16, 2)):
             g.manual_seed(3)
             nbuf = max(1, int(np.ceil(300e6 / (shape[0] * shape[1] * es))))
@@ -262,46 +262,48 @@ def op_suite(torch, peak_gbs, scale="full"):
             ms = time_op(torch, lambda i: kernels.rmsnorm(xs[i % nbuf], gamma, 1e-6), 20)
             add("rmsnorm", f"C4 {list(shape)} {str(dt)[6:]}", 2 * n * es + shape[1] * 4 + shape[0] * 4, n, ms)
             del xs
-    # ---- C2: gather / scatter_add on a [1,048,576 x 256] table with 4,194,304 indices
-    V, D, N = 1 << 20, 256, (1 << 19 if small else 1 << 22)
-    rng = np.random.default_rng(2)
-    table = torch.randn((V, D), device=dev)
-    idx_u = torch.from_numpy(rng.integers(0, V, N).astype(np.int64)).to(dev)
-    p = np.arange(1, V + 1, dtype=np.float64) ** -1.1
-    ranks = np.searchsorted(np.cumsum(p / p.sum()), rng.random(N))
-    idx_z = torch.from_numpy(rng.permutation(V)[np.minimum(ranks, V - 1)].astype(np.int64)).to(dev)
-    U = int(torch.unique(idx_z).numel())
-    out = torch.empty((N, D), device=dev)
-    st = ops.IndexStatus(dev)
-    ms = time_op(torch, lambda i: ops.index_rows(table, idx_u, status=st, out=out), 5)
-    add("index_rows/gather", f"C2 table [1048576,256] fp32, {N} uniform int64 indices", 2 * N * D * 4 + N * 8,
-        N * D, ms)
-    upd = torch.randn((N, D), device=dev)
-    acc = torch.zeros((V, D), device=dev)
-    ms = time_op(torch, lambda i: ops.index_put_rows_(acc, idx_z, upd, accumulate=True, status=st), 5)
-    add("index_put_(accumulate)/scatter_add fp32", f"C2 Zipf(1.1) indices, {U} distinct rows",
-        N * D * 4 + N * 8 + 2 * U * D * 4, N * D, ms)
-    del upd, acc, out, table
-    updi = torch.randint(-1000, 1001, (N, D), device=dev, dtype=torch.int64)
-    acci = torch.zeros((V, D), device=dev, dtype=torch.int64)
-    ms = time_op(torch, lambda i: ops.index_put_rows_(acci, idx_z, updi, accumulate=True, status=st), 5)
-    add("index_put_(accumulate)/scatter_add int64", f"C2 Zipf(1.1) indices, {U} distinct rows",
-        N * D * 8 + N * 8 + 2 * U * D * 8, N * D, ms)
-    st.check("bench", V)
-    del updi, acci
-    # ---- C3: bf16 broadcast chain into a transposed output view
-    g.manual_seed(1)
-    n0 = 8 if small else 64
-    a = torch.randn((n0, 1, 512, 1), device=dev, generator=g).bfloat16()
-    b = torch.randn((1, 128, 1, 1024), device=dev, generator=g).bfloat16()
-    c = torch.randn((n0, 128, 1, 1024), device=dev, generator=g).bfloat16()
-    base = torch.empty((n0, 1024, 512, 128), device=dev, dtype=torch.bfloat16)
-    outv = base.transpose(1, 3)
-    n = outv.numel()
-    ms = time_op(torch, lambda i: ops.where_gt0_addcmul(a, b, c, out=outv), 5)
-    add("where(a>0, a+b*c, 0) fused", f"C3 bf16 a[{n0},1,512,1] b[1,128,1,1024] c[{n0},128,1,1024] -> transpose(1,3) view",
-        n * 2 + (a.numel() + b.numel() + c.numel()) * 2, n, ms)
-    del base, outv
+    if "c2" in which:
+        # ---- C2: gather / scatter_add on a [1,048,576 x 256] table with 4,194,304 indices
+        V, D, N = 1 << 20, 256, (1 << 19 if small else 1 << 22)
+        rng = np.random.default_rng(2)
+        table = torch.randn((V, D), device=dev)
+        idx_u = torch.from_numpy(rng.integers(0, V, N).astype(np.int64)).to(dev)
+        p = np.arange(1, V + 1, dtype=np.float64) ** -1.1
+        ranks = np.searchsorted(np.cumsum(p / p.sum()), rng.random(N))
+        idx_z = torch.from_numpy(rng.permutation(V)[np.minimum(ranks, V - 1)].astype(np.int64)).to(dev)
+        U = int(torch.unique(idx_z).numel())
+        out = torch.empty((N, D), device=dev)
+        st = ops.IndexStatus(dev)
+        ms = time_op(torch, lambda i: ops.index_rows(table, idx_u, status=st, out=out), 5)
+        add("index_rows/gather", f"C2 table [1048576,256] fp32, {N} uniform int64 indices", 2 * N * D * 4 + N * 8,
+            N * D, ms)
+        upd = torch.randn((N, D), device=dev)
+        acc = torch.zeros((V, D), device=dev)
+        ms = time_op(torch, lambda i: ops.index_put_rows_(acc, idx_z, upd, accumulate=True, status=st), 5)
+        add("index_put_(accumulate)/scatter_add fp32", f"C2 Zipf(1.1) indices, {U} distinct rows",
+            N * D * 4 + N * 8 + 2 * U * D * 4, N * D, ms)
+        del upd, acc, out, table
+        updi = torch.randint(-1000, 1001, (N, D), device=dev, dtype=torch.int64)
+        acci = torch.zeros((V, D), device=dev, dtype=torch.int64)
+        ms = time_op(torch, lambda i: ops.index_put_rows_(acci, idx_z, updi, accumulate=True, status=st), 5)
+        add("index_put_(accumulate)/scatter_add int64", f"C2 Zipf(1.1) indices, {U} distinct rows",
+            N * D * 8 + N * 8 + 2 * U * D * 8, N * D, ms)
+        st.check("bench", V)
+        del updi, acci
+    if "c3" in which:
+        # ---- C3: bf16 broadcast chain into a transposed output view
+        g.manual_seed(1)
+        n0 = 8 if small else 64
+        a = torch.randn((n0, 1, 512, 1), device=dev, generator=g).bfloat16()
+        b = torch.randn((1, 128, 1, 1024), device=dev, generator=g).bfloat16()
+        c = torch.randn((n0, 128, 1, 1024), device=dev, generator=g).bfloat16()
+        base = torch.empty((n0, 1024, 512, 128), device=dev, dtype=torch.bfloat16)
+        outv = base.transpose(1, 3)
+        n = outv.numel()
+        ms = time_op(torch, lambda i: ops.where_gt0_addcmul(a, b, c, out=outv), 5)
+        add("where(a>0, a+b*c, 0) fused", f"C3 bf16 a[{n0},1,512,1] b[1,128,1,1024] c[{n0},128,1,1024] -> transpose(1,3) view",
+            n * 2 + (a.numel() + b.numel() + c.numel()) * 2, n, ms)
+        del base, outv
     torch.cuda.empty_cache()
     return res
 
@@ -328,7 +330,7 @@ def run_ours(args):
     peak_gbs, peak_kind = measured_peak()
     if args.suite_only:
         if rank == 0:
-            suite = op_suite(torch, peak_gbs, args.suite_scale)
+            suite = op_suite(torch, peak_gbs, args.suite_scale, tuple(args.suite_ops.split(',')))
             print(json.dumps({"metric": "per-op HBM GB/s", "n_gpus": 1, "suite_scale": args.suite_scale,
                               "peak_gbs": peak_gbs, "peak_source": peak_kind, "ops": suite}), flush=True)
         return
@@ -405,7 +407,7 @@ def run_ours(args):
         del shard, ft
         torch.cuda.empty_cache()
         if not args.no_suite:
-            suite = op_suite(torch, peak_gbs, args.suite_scale)
+            suite = op_suite(torch, peak_gbs, args.suite_scale, tuple(args.suite_ops.split(',')))
     if n == 1 and rank == 0 and not args.no_cpu:
         v, kind, secs = cpu_reference_sum(1 << 28, 8)
         cpu = {"value": v, "unit": "elements/s", "cores": 1, "kind": kind,
@@ -498,6 +500,7 @@ def run_e2e(torch, dist, ops, shard, n, args):
 
 
 def main():
+    global TOTAL_ELEMS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -509,10 +512,10 @@ def main():
     ap.add_argument("--suite-only", action="store_true", help="run only the per-op table")
     ap.add_argument("--suite-scale", default="full", choices=["full", "small"],
                     help="small: reduced C2/C3/C4 shapes (a few GB on the device) for profiler captures")
+    ap.add_argument("--suite-ops", default="c1,c2,c3,c4", help="which configurations the per-op table runs")
     ap.add_argument("--elems", type=int, default=TOTAL_ELEMS,
                     help="elements of the headline tensor (default 2^32; smaller only for profiler captures)")
     args = ap.parse_args()
-    global TOTAL_ELEMS
     TOTAL_ELEMS = args.elems
     if args.impl == "reference":
         run_reference(args)
