@@ -61,6 +61,8 @@ __device__ __forceinline__ int64_t unary_int(int64_t a) {
 
 template <int OP, class T>
 struct UnaryF {
+  static constexpr bool kFloatMath = is_float_storage<T>::value;
+  __device__ __forceinline__ float fn(float a, float, float) const { return unary_math<OP>(a); }
   __device__ __forceinline__ T operator()(T a, T, T) const {
     if constexpr (is_float_storage<T>::value) return from_f<T>(unary_math<OP>(to_f(a)));
     else return static_cast<T>(unary_int<OP>(static_cast<int64_t>(a)));
@@ -99,6 +101,8 @@ __device__ __forceinline__ bool compare(X a, X b) {
 
 template <int OP, class T>
 struct BinaryF {
+  static constexpr bool kFloatMath = is_float_storage<T>::value;
+  __device__ __forceinline__ float fn(float a, float b, float) const { return binary_math<OP>(a, b); }
   __device__ __forceinline__ T operator()(T a, T b, T) const {
     if constexpr (is_float_storage<T>::value) return from_f<T>(binary_math<OP>(to_f(a), to_f(b)));
     else return static_cast<T>(binary_int<OP>(a, b));
@@ -123,25 +127,30 @@ struct ScalarF {
   }
 };
 
+// float in, float out; the caller rounds the result to T once.  Intermediates of the fused
+// chains are rounded to T here, exactly where the reference's separate launches round.
 template <int OP, class T>
 struct TernaryF {
-  __device__ __forceinline__ T operator()(T ta, T tb, T tc) const {
-    const float a = to_f(ta), b = to_f(tb), c = to_f(tc);
+  static constexpr bool kFloatMath = true;
+  __device__ __forceinline__ float fn(float a, float b, float c) const {
     if constexpr (OP == VBT_B200_T_CLAMP) {
-      if (b != b || c != c) return from_f<T>(__int_as_float(0x7fc00000));
-      return from_f<T>(a < b ? b : (a > c ? c : a));
+      if (b != b || c != c) return __int_as_float(0x7fc00000);
+      return a < b ? b : (a > c ? c : a);
     } else if constexpr (OP == VBT_B200_T_LERP) {
-      return from_f<T>(fmaf(c, b - a, a));
+      return fmaf(c, b - a, a);
     } else if constexpr (OP == VBT_B200_T_THRESHOLD) {
-      return from_f<T>(a > b ? a : c);
+      return a > b ? a : c;
     } else if constexpr (OP == VBT_B200_T_ADDCMUL) {
-      return from_f<T>(a + to_f(from_f<T>(__fmul_rn(b, c))));
+      return __fadd_rn(a, to_f(from_f<T>(__fmul_rn(b, c))));
     } else if constexpr (OP == VBT_B200_T_ADDCDIV) {
-      return from_f<T>(a + to_f(from_f<T>(__fdiv_rn(b, c))));
-    } else {  // where(a > 0, a + b*c, 0), every intermediate rounded like the 4-op chain
-      const T t2 = from_f<T>(a + to_f(from_f<T>(__fmul_rn(b, c))));
-      return a > 0.f ? t2 : from_f<T>(0.f);
+      return __fadd_rn(a, to_f(from_f<T>(__fdiv_rn(b, c))));
+    } else {  // where(a > 0, a + b*c, 0): mul, add, gt, where of the reference, fused
+      const float t2 = __fadd_rn(a, to_f(from_f<T>(__fmul_rn(b, c))));
+      return a > 0.f ? t2 : 0.f;
     }
+  }
+  __device__ __forceinline__ T operator()(T ta, T tb, T tc) const {
+    return from_f<T>(fn(to_f(ta), to_f(tb), to_f(tc)));
   }
 };
 

@@ -18,6 +18,7 @@
 // operand (include/vbt/core/tensor_iterator/cuda.h:25-42).
 #pragma once
 #include <algorithm>
+#include <type_traits>
 
 #include "ti_plan.h"
 
@@ -49,11 +50,18 @@ struct FlatParams {
   int64_t n;    // elements
 };
 
-template <class T, int V>
+// SPLAT: the operand is known at compile time to be broadcast along dim 0 (stride 0): one
+// scalar load, and every lane of the vector is the SAME value to the compiler, so per-lane
+// work on it (conversion, comparison) is done once.
+template <class T, int V, bool SPLAT = false>
 __device__ __forceinline__ Vec<T, V> load_vec(const T* p, int64_t s0) {
   Vec<T, V> r;
   if constexpr (V == 1) {
     r.v[0] = *p;
+  } else if constexpr (SPLAT) {
+    const T x = *p;
+#pragma unroll
+    for (int j = 0; j < V; ++j) r.v[j] = x;
   } else {
     if (s0 == 1) {
       r = *reinterpret_cast<const Vec<T, V>*>(p);
@@ -69,18 +77,46 @@ __device__ __forceinline__ Vec<T, V> load_vec(const T* p, int64_t s0) {
   return r;
 }
 
+// two floats -> two 16-bit storage values with ONE conversion instruction
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, __nv_bfloat16) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, __half) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <class F, class = void>
+struct has_float_fn : std::false_type {};
+template <class F>
+struct has_float_fn<F, std::void_t<decltype(F::kFloatMath)>> : std::bool_constant<F::kFloatMath> {};
+
 template <class F, class TO, class T1, class T2, class T3, int NIN, int V>
 __device__ __forceinline__ Vec<TO, V> apply_vec(const F& f, const Vec<T1, V>& a,
                                                 const Vec<T2, V>& b, const Vec<T3, V>& c) {
   Vec<TO, V> o;
+  if constexpr (has_float_fn<F>::value && sizeof(TO) == 2 && V % 2 == 0) {
+    // 16-bit float outputs: compute in float, round and pack two lanes per instruction
+    uint32_t* w = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-  for (int j = 0; j < V; ++j) o.v[j] = f(a.v[j], b.v[j], c.v[j]);
+    for (int j = 0; j < V; j += 2) {
+      const float lo = f.fn(to_f(a.v[j]), to_f(b.v[j]), to_f(c.v[j]));
+      const float hi = f.fn(to_f(a.v[j + 1]), to_f(b.v[j + 1]), to_f(c.v[j + 1]));
+      w[j / 2] = pack2(lo, hi, TO{});
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j) o.v[j] = f(a.v[j], b.v[j], c.v[j]);
+  }
   return o;
 }
 
 // INV: bitmask of inputs known at compile time not to vary along dim 1 (bit 0 = first
 // input); -1 = decide at run time from the strides (loads are hoisted, arithmetic is not).
-template <class F, class TO, class T1, class T2, class T3, int NIN, int V, int INV>
+// BC0: bitmask of inputs known at compile time to be broadcast along dim 0 (only used
+// together with INV >= 0).
+template <class F, class TO, class T1, class T2, class T3, int NIN, int V, int INV, int BC0 = 0>
 __global__ void __launch_bounds__(kEwThreads)
 ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
   uint32_t b = blockIdx.x, t0, t1;
@@ -125,9 +161,10 @@ ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
   Vec<T1, V> a0{};
   Vec<T2, V> b0{};
   Vec<T3, V> c0{};
-  if (inv1) a0 = load_vec<T1, V>(p1, s01);
-  if constexpr (NIN >= 2) { if (inv2) b0 = load_vec<T2, V>(p2, s02); }
-  if constexpr (NIN >= 3) { if (inv3) c0 = load_vec<T3, V>(p3, s03); }
+  constexpr bool sp1 = INV >= 0 && (BC0 & 1), sp2 = INV >= 0 && (BC0 & 2), sp3 = INV >= 0 && (BC0 & 4);
+  if (inv1) a0 = load_vec<T1, V, sp1>(p1, s01);
+  if constexpr (NIN >= 2) { if (inv2) b0 = load_vec<T2, V, sp2>(p2, s02); }
+  if constexpr (NIN >= 3) { if (inv3) c0 = load_vec<T3, V, sp3>(p3, s03); }
 
   int l = 0;
   for (; l + kEwUnroll <= n; l += kEwUnroll) {
@@ -136,10 +173,10 @@ ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
     Vec<T3, V> c[kEwUnroll];
 #pragma unroll
     for (int u = 0; u < kEwUnroll; ++u) {
-      a[u] = inv1 ? a0 : load_vec<T1, V>(p1 + (l + u) * st1, s01);
-      if constexpr (NIN >= 2) bb[u] = inv2 ? b0 : load_vec<T2, V>(p2 + (l + u) * st2, s02);
+      a[u] = inv1 ? a0 : load_vec<T1, V, sp1>(p1 + (l + u) * st1, s01);
+      if constexpr (NIN >= 2) bb[u] = inv2 ? b0 : load_vec<T2, V, sp2>(p2 + (l + u) * st2, s02);
       else bb[u] = b0;
-      if constexpr (NIN >= 3) c[u] = inv3 ? c0 : load_vec<T3, V>(p3 + (l + u) * st3, s03);
+      if constexpr (NIN >= 3) c[u] = inv3 ? c0 : load_vec<T3, V, sp3>(p3 + (l + u) * st3, s03);
       else c[u] = c0;
     }
 #pragma unroll
@@ -150,11 +187,11 @@ ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
     }
   }
   for (; l < n; ++l) {
-    const Vec<T1, V> a = inv1 ? a0 : load_vec<T1, V>(p1 + l * st1, s01);
+    const Vec<T1, V> a = inv1 ? a0 : load_vec<T1, V, sp1>(p1 + l * st1, s01);
     Vec<T2, V> bb = b0;
     Vec<T3, V> c = c0;
-    if constexpr (NIN >= 2) { if (!inv2) bb = load_vec<T2, V>(p2 + l * st2, s02); }
-    if constexpr (NIN >= 3) { if (!inv3) c = load_vec<T3, V>(p3 + l * st3, s03); }
+    if constexpr (NIN >= 2) { if (!inv2) bb = load_vec<T2, V, sp2>(p2 + l * st2, s02); }
+    if constexpr (NIN >= 3) { if (!inv3) c = load_vec<T3, V, sp3>(p3 + l * st3, s03); }
     const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(f, a, bb, c);
     if constexpr (V == 1) po[l * so_] = o.v[0];
     else *reinterpret_cast<Vec<TO, V>*>(po + l * so_) = o;
@@ -212,7 +249,7 @@ ew_flat_kernel(const __grid_constant__ FlatParams<NIN + 1> p, const F f) {
 // Host: picks the kernel for the plan and launches it.  INV_SPECIAL >= 0 additionally
 // instantiates the tiled vector kernel for that compile-time invariance mask and uses it
 // when the plan's strides match it.
-template <class F, class TO, class T1, class T2, class T3, int NIN, int INV_SPECIAL = -1>
+template <class F, class TO, class T1, class T2, class T3, int NIN, int INV_SPECIAL = -1, int BC0_SPECIAL = 0>
 vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
   if (plan.numel == 0) return VBT_B200_OK;
   constexpr int kMaxEs = static_cast<int>(std::max({sizeof(TO), sizeof(T1), NIN >= 2 ? sizeof(T2) : size_t{1},
@@ -290,6 +327,16 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
       for (int k = 1; k <= NIN; ++k)
         if (tp.s1[k] == 0) mask |= 1 << (k - 1);
       if (mask == INV_SPECIAL) {
+        if constexpr (BC0_SPECIAL != 0) {
+          int bc = 0;
+          for (int k = 1; k <= NIN; ++k)
+            if (tp.s0[k] == 0) bc |= 1 << (k - 1);
+          if (bc == BC0_SPECIAL) {
+            ew_tiled_kernel<F, TO, T1, T2, T3, NIN, V, INV_SPECIAL, BC0_SPECIAL><<<g, kEwThreads, 0, stream>>>(tp, f);
+            VB_LAUNCH_CHECK();
+            return VBT_B200_OK;
+          }
+        }
         ew_tiled_kernel<F, TO, T1, T2, T3, NIN, V, INV_SPECIAL><<<g, kEwThreads, 0, stream>>>(tp, f);
         VB_LAUNCH_CHECK();
         return VBT_B200_OK;

@@ -28,8 +28,12 @@ extern "C" vbt_b200_status vbt_b200_ternary(int32_t op, const vbt_b200_tensor* o
     constexpr int OP = decltype(opc)::value;
     // The fused chains also get a build where inputs 2 and 3 are known not to vary along
     // dim 1, so that their product is computed once per thread and reused for every row.
+    // ... and where the first input is also a per-row scalar (broadcast along the output's
+    // inner dim), which is the layout of a[n,1,h,1] + b[1,c,1,w] * c[n,c,1,w] written
+    // channels-last: the per-element work shrinks to one add and one select.
     constexpr int INV = OP >= VBT_B200_T_ADDCMUL ? 6 : -1;
-    VB_DISPATCH_FLOAT(dt, T, (st = launch_ew<TernaryF<OP, T>, T, T, T, T, 3, INV>(plan, {}, s)));
+    constexpr int BC0 = OP >= VBT_B200_T_ADDCMUL ? 1 : 0;
+    VB_DISPATCH_FLOAT(dt, T, (st = launch_ew<TernaryF<OP, T>, T, T, T, T, 3, INV, BC0>(plan, {}, s)));
   });
   return st;
 }

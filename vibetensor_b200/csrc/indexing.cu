@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(kThreads) scatter_add_rows_kernel(const __grid
   const int lane = t & 31, w = t >> 5;
   const int e_begin = w * 32;
   const int64_t row_bytes = static_cast<int64_t>(p.cpr) * 16;
-  constexpr int U = 4;
+  constexpr int U = K >= 4 ? 2 : 4;  // entries in flight per warp; bounded by registers
   for (uint32_t cb = 0; cb < p.cpr; cb += 32 * K) {  // column block of 32*K chunks
     acc_t acc[K];
 #pragma unroll

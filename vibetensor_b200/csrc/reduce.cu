@@ -33,10 +33,10 @@ constexpr int kMaxDims = VBT_B200_MAX_NDIM;
 // ------------------------------------------------------------------------------------
 // reducers
 // ------------------------------------------------------------------------------------
-template <class A>
+template <class A, class I>
 struct Pair {
   A v;
-  int64_t i;
+  I i;
 };
 
 template <class A> __device__ __forceinline__ A lowest();
@@ -48,17 +48,19 @@ template <> __device__ __forceinline__ int64_t highest<int64_t>() { return LLONG
 
 __device__ __forceinline__ float shfl_down(float v, int d) { return __shfl_down_sync(0xffffffffu, v, d); }
 __device__ __forceinline__ int64_t shfl_down(int64_t v, int d) { return __shfl_down_sync(0xffffffffu, v, d); }
-template <class A>
-__device__ __forceinline__ Pair<A> shfl_down(Pair<A> p, int d) {
-  return Pair<A>{shfl_down(p.v, d), shfl_down(p.i, d)};
+__device__ __forceinline__ int32_t shfl_down(int32_t v, int d) { return __shfl_down_sync(0xffffffffu, v, d); }
+template <class A, class I>
+__device__ __forceinline__ Pair<A, I> shfl_down(Pair<A, I> p, int d) {
+  return Pair<A, I>{shfl_down(p.v, d), shfl_down(p.i, d)};
 }
 
 template <class A>
 struct SumR {
   using acc_t = A;
+  using idx_t = int32_t;  // unused
   static constexpr bool kIndexed = false;
   __device__ static acc_t init() { return A(0); }
-  __device__ static void accum(acc_t& a, A v, int64_t) {
+  __device__ static void accum(acc_t& a, A v, idx_t) {
     if constexpr (sizeof(A) == 8) a = static_cast<A>(static_cast<uint64_t>(a) + static_cast<uint64_t>(v));
     else a += v;
   }
@@ -70,9 +72,10 @@ struct SumR {
 template <class A>
 struct ProdR {
   using acc_t = A;
+  using idx_t = int32_t;  // unused
   static constexpr bool kIndexed = false;
   __device__ static acc_t init() { return A(1); }
-  __device__ static void accum(acc_t& a, A v, int64_t) { a = combine(a, v); }
+  __device__ static void accum(acc_t& a, A v, idx_t) { a = combine(a, v); }
   __device__ static acc_t combine(acc_t a, acc_t b) {
     if constexpr (sizeof(A) == 8) return static_cast<A>(static_cast<uint64_t>(a) * static_cast<uint64_t>(b));
     else return a * b;
@@ -83,18 +86,23 @@ struct ProdR {
 template <class A, bool MAX>
 struct ExtR {
   using acc_t = A;
+  using idx_t = int32_t;  // unused
   static constexpr bool kIndexed = false;
   __device__ static acc_t init() { return MAX ? lowest<A>() : highest<A>(); }
-  __device__ static void accum(acc_t& a, A v, int64_t) { if (MAX ? (v > a) : (v < a)) a = v; }
+  __device__ static void accum(acc_t& a, A v, idx_t) { if (MAX ? (v > a) : (v < a)) a = v; }
   __device__ static acc_t combine(acc_t a, acc_t b) { return (MAX ? (b > a) : (b < a)) ? b : a; }
 };
-// argmax / argmin: first extremum wins (tensor_bindings.cc:630-682)
-template <class A, bool MAX>
+// argmax / argmin: first extremum wins (tensor_bindings.cc:630-682).  I is the index type
+// carried through the reduction: 32-bit whenever the reduced extent allows it (index
+// arithmetic, selects and shuffles are then half the work).
+template <class A, bool MAX, class I>
 struct ArgR {
-  using acc_t = Pair<A>;
+  using acc_t = Pair<A, I>;
+  using idx_t = I;
   static constexpr bool kIndexed = true;
-  __device__ static acc_t init() { return Pair<A>{MAX ? lowest<A>() : highest<A>(), LLONG_MAX}; }
-  __device__ static void accum(acc_t& a, A v, int64_t i) {
+  static constexpr I kNone = sizeof(I) == 4 ? static_cast<I>(INT_MAX) : static_cast<I>(LLONG_MAX);
+  __device__ static acc_t init() { return acc_t{MAX ? lowest<A>() : highest<A>(), kNone}; }
+  __device__ static void accum(acc_t& a, A v, idx_t i) {
     if ((MAX ? (v > a.v) : (v < a.v)) || (v == a.v && i < a.i)) { a.v = v; a.i = i; }
   }
   __device__ static acc_t combine(acc_t a, acc_t b) {
@@ -113,9 +121,10 @@ __device__ __forceinline__ float ld_cg(const float* p) { return __ldcg(p); }
 __device__ __forceinline__ int64_t ld_cg(const int64_t* p) {
   return static_cast<int64_t>(__ldcg(reinterpret_cast<const long long*>(p)));
 }
-template <class A>
-__device__ __forceinline__ Pair<A> ld_cg(const Pair<A>* p) {
-  return Pair<A>{ld_cg(&p->v), ld_cg(&p->i)};
+__device__ __forceinline__ int32_t ld_cg(const int32_t* p) { return __ldcg(p); }
+template <class A, class I>
+__device__ __forceinline__ Pair<A, I> ld_cg(const Pair<A, I>* p) {
+  return Pair<A, I>{ld_cg(&p->v), ld_cg(&p->i)};
 }
 
 template <class R>
@@ -170,7 +179,7 @@ __device__ __forceinline__ void finalize(const OutSpec& o, int64_t i, typename R
   if constexpr (R::kIndexed) {
     if (is_nan(first)) { acc.v = first; acc.i = 0; }
     if (o.out) store_value(o, i, acc.v);
-    if (o.out_idx) o.out_idx[i] = acc.i;
+    if (o.out_idx) o.out_idx[i] = static_cast<int64_t>(acc.i);
   } else {
     if (o.op == OP_MAX || o.op == OP_MIN) {
       if (is_nan(first)) acc = first;
@@ -238,15 +247,17 @@ __global__ void __launch_bounds__(kThreads) row_warp_kernel(const __grid_constan
   const T* x = static_cast<const T*>(p.x) + p.kept.offset(static_cast<uint32_t>(row));
   typename R::acc_t acc = R::init();
   const int64_t nvec = p.n / V;
+  using idx_t = typename R::idx_t;
   for (int64_t i = lane; i < nvec; i += 32) {
     A w[V];
     load_widen<T, V>(x + i * V, w);
+    const idx_t base = static_cast<idx_t>(i) * V;
 #pragma unroll
-    for (int j = 0; j < V; ++j) R::accum(acc, w[j], i * V + j);
+    for (int j = 0; j < V; ++j) R::accum(acc, w[j], base + j);
   }
   if constexpr (V > 1) {
     const int64_t i = nvec * V + lane;
-    if (i < p.n) R::accum(acc, widen(x[i]), i);
+    if (i < p.n) R::accum(acc, widen(x[i]), static_cast<idx_t>(i));
   }
   acc = warp_reduce<R>(acc);
   if (lane == 0) finalize<R, A>(p.o, row, acc, widen(x[0]));
@@ -257,6 +268,7 @@ template <class T, class R, int V>
 __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_constant__ RowParams p) {
   using A = typename Widen<T>::type;
   using acc_t = typename R::acc_t;
+  using idx_t = typename R::idx_t;
   __shared__ acc_t smem[kWarps];
   __shared__ bool is_last;
   const int64_t row = blockIdx.x;
@@ -275,19 +287,22 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
 #pragma unroll
     for (int u = 0; u < U; ++u) load_widen<T, V>(x + (i + u * kThreads) * V, w[u]);
 #pragma unroll
-    for (int u = 0; u < U; ++u)
+    for (int u = 0; u < U; ++u) {
+      const idx_t base = static_cast<idx_t>(i + u * kThreads) * V;
 #pragma unroll
-      for (int j = 0; j < V; ++j) R::accum(acc[u], w[u][j], (i + u * kThreads) * V + j);
+      for (int j = 0; j < V; ++j) R::accum(acc[u], w[u][j], base + j);
+    }
   }
   for (; i < v1; i += kThreads) {
     A w[V];
     load_widen<T, V>(x + i * V, w);
+    const idx_t base = static_cast<idx_t>(i) * V;
 #pragma unroll
-    for (int j = 0; j < V; ++j) R::accum(acc[0], w[j], i * V + j);
+    for (int j = 0; j < V; ++j) R::accum(acc[0], w[j], base + j);
   }
   if constexpr (V > 1) {
     const int64_t t = v1 * V + threadIdx.x;  // ragged tail, only in the last chunk
-    if (t < c1) R::accum(acc[0], widen(x[t]), t);
+    if (t < c1) R::accum(acc[0], widen(x[t]), static_cast<idx_t>(t));
   }
   acc_t a = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
   a = block_reduce<R>(a, smem);
@@ -357,13 +372,13 @@ __global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ C
 #pragma unroll
       for (int u = 0; u < U; ++u)
 #pragma unroll
-        for (int j = 0; j < V; ++j) R::accum(acc[j], v[u][j], r + u * kWarps);
+        for (int j = 0; j < V; ++j) R::accum(acc[j], v[u][j], static_cast<typename R::idx_t>(r + u * kWarps));
     }
     for (; r < r1; r += kWarps) {
       A v[V];
       load_widen<T, V>(x + r * p.S, v);
 #pragma unroll
-      for (int j = 0; j < V; ++j) R::accum(acc[j], v[j], r);
+      for (int j = 0; j < V; ++j) R::accum(acc[j], v[j], static_cast<typename R::idx_t>(r));
     }
   }
 #pragma unroll
@@ -425,7 +440,8 @@ __global__ void __launch_bounds__(kThreads) generic_kernel(const __grid_constant
   const int lane = threadIdx.x & 31;
   const T* x = static_cast<const T*>(p.x) + p.kept.offset(static_cast<uint32_t>(oi));
   typename R::acc_t acc = R::init();
-  for (uint32_t j = lane; j < p.nred; j += 32) R::accum(acc, widen(x[p.red.offset(j)]), j);
+  for (uint32_t j = lane; j < p.nred; j += 32)
+    R::accum(acc, widen(x[p.red.offset(j)]), static_cast<typename R::idx_t>(j));
   acc = warp_reduce<R>(acc);
   if (lane == 0) finalize<R, A>(p.o, oi, acc, widen(x[0]));
 }
@@ -571,7 +587,8 @@ vbt_b200_status make_plan(int op, const vbt_b200_tensor& self, const int64_t* di
       pl->shape = kCol;
       const int ncols = 32 * pl->V;
       pl->ctiles = static_cast<int>((B + ncols - 1) / ncols);
-      int64_t want = (int64_t{sms} * 6 + pl->ctiles * A - 1) / (pl->ctiles * A);
+      // about one resident wave of blocks (4 per SM): a second, partial wave only adds a tail
+      int64_t want = (int64_t{sms} * 4) / (pl->ctiles * A);
       int64_t splits = std::max<int64_t>(1, std::min<int64_t>(want, (Rn + 31) / 32));
       splits = std::min<int64_t>(splits, 65535);
       int64_t chunk = (Rn + splits - 1) / splits;
@@ -675,8 +692,12 @@ vbt_b200_status launch_op(int op, const Plan& pl, const vbt_b200_tensor& self, c
     case OP_PROD: return launch<T, ProdR<A>>(pl, self, o, ws, s);
     case OP_MAX: return launch<T, ExtR<A, true>>(pl, self, o, ws, s);
     case OP_MIN: return launch<T, ExtR<A, false>>(pl, self, o, ws, s);
-    case OP_ARGMAX: return launch<T, ArgR<A, true>>(pl, self, o, ws, s);
-    case OP_ARGMIN: return launch<T, ArgR<A, false>>(pl, self, o, ws, s);
+    case OP_ARGMAX:
+      return pl.nred < 0x7fffffff ? launch<T, ArgR<A, true, int32_t>>(pl, self, o, ws, s)
+                                  : launch<T, ArgR<A, true, int64_t>>(pl, self, o, ws, s);
+    case OP_ARGMIN:
+      return pl.nred < 0x7fffffff ? launch<T, ArgR<A, false, int32_t>>(pl, self, o, ws, s)
+                                  : launch<T, ArgR<A, false, int64_t>>(pl, self, o, ws, s);
   }
   return fail(VBT_B200_INVALID_ARGUMENT, "reduce: unknown op code");
 }

@@ -166,32 +166,43 @@ __device__ __forceinline__ void load_gamma(const float* gamma, int first_vec, in
   }
 }
 
-// G lanes per row, 256 / G rows per block pass, persistent over rows
-template <class T, int KIND, int G, int VPL>
+// G lanes per row; a warp keeps RPG rows per group in flight (RPG * 32 / G rows per warp
+// iteration) so that short rows still put enough bytes on the wire; persistent over rows
+template <class T, int KIND, int G, int VPL, int RPG>
 __global__ void __launch_bounds__(256) rowop_group_kernel(const __grid_constant__ RowParams p) {
   constexpr int V = 16 / sizeof(T);
-  constexpr int kGroups = 256 / G;
+  constexpr int kGroupsPerWarp = 32 / G;
+  constexpr int kRowsPerWarp = kGroupsPerWarp * RPG;
+  constexpr int kRowsPerBlock = 8 * kRowsPerWarp;
   const int lane = threadIdx.x % G;
-  const int grp = threadIdx.x / G;
+  const int gw = (threadIdx.x % 32) / G;  // group within the warp
   const int nvec = static_cast<int>(p.cols / V);
   float g[VPL][V];
   load_gamma<T, VPL>(KIND == K_RMSNORM ? p.gamma : nullptr, lane, G, nvec, g);
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * kGroups;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kRowsPerBlock;
   // every lane of a warp runs the same number of iterations (shuffles are warp-wide)
-  const int64_t base_row = static_cast<int64_t>(blockIdx.x) * kGroups + (threadIdx.x / 32) * (32 / G);
+  const int64_t base_row = static_cast<int64_t>(blockIdx.x) * kRowsPerBlock + (threadIdx.x / 32) * kRowsPerWarp;
   for (int64_t r0 = base_row; r0 < p.rows; r0 += stride) {
-    const int64_t row = r0 + (grp % (32 / G));
-    const bool live = row < p.rows;
-    float v[VPL][V];
-    bool valid[VPL];
-    const T* xr = static_cast<const T*>(p.x) + (live ? row : 0) * p.x_row_stride;
-    load_row<T, VPL>(xr, lane, G, live ? nvec : 0, v, valid);
-    float inv = 0.f;
-    row_math<T, KIND, VPL>(v, valid, g, p, [](float a) { return group_max<G>(a); },
-                           [](float a) { return group_sum<G>(a); }, &inv);
-    if (live) {
-      store_row<T, VPL>(static_cast<T*>(p.out) + row * p.cols, lane, G, v, valid);
-      if (KIND == K_RMSNORM && p.inv_rms && lane == 0) p.inv_rms[row] = inv;
+    float v[RPG][VPL][V];
+    bool valid[RPG][VPL];
+    bool live[RPG];
+#pragma unroll
+    for (int r = 0; r < RPG; ++r) {
+      const int64_t row = r0 + r * kGroupsPerWarp + gw;
+      live[r] = row < p.rows;
+      const T* xr = static_cast<const T*>(p.x) + (live[r] ? row : 0) * p.x_row_stride;
+      load_row<T, VPL>(xr, lane, G, live[r] ? nvec : 0, v[r], valid[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < RPG; ++r) {
+      const int64_t row = r0 + r * kGroupsPerWarp + gw;
+      float inv = 0.f;
+      row_math<T, KIND, VPL>(v[r], valid[r], g, p, [](float a) { return group_max<G>(a); },
+                             [](float a) { return group_sum<G>(a); }, &inv);
+      if (live[r]) {
+        store_row<T, VPL>(static_cast<T*>(p.out) + row * p.cols, lane, G, v[r], valid[r]);
+        if (KIND == K_RMSNORM && p.inv_rms && lane == 0) p.inv_rms[row] = inv;
+      }
     }
   }
 }
@@ -296,14 +307,15 @@ vbt_b200_status launch_rowop(const RowParams& p, cudaStream_t s, int device) {
   auto grid = [&](int64_t units, int per_sm) {
     return static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(units, int64_t{sms} * per_sm)));
   };
-#define VB_GROUP(G, VPL)                                                                      \
-  rowop_group_kernel<T, KIND, G, VPL><<<grid((p.rows + 256 / G - 1) / (256 / G), 8), 256, 0, s>>>(p)
+#define VB_GROUP(G, VPL, RPG)                                                                 \
+  rowop_group_kernel<T, KIND, G, VPL, RPG>                                                    \
+      <<<grid((p.rows + (256 / G) * RPG - 1) / ((256 / G) * RPG), 8), 256, 0, s>>>(p)
 #define VB_BLOCK(TH, VPL, PER_SM) rowop_block_kernel<T, KIND, TH, VPL><<<grid(p.rows, PER_SM), TH, 0, s>>>(p)
-  if (nvec <= 8) VB_GROUP(8, 1);
-  else if (nvec <= 16) VB_GROUP(16, 1);
-  else if (nvec <= 32) VB_GROUP(32, 1);
-  else if (nvec <= 64) VB_GROUP(32, 2);
-  else if (nvec <= 128) VB_GROUP(32, 4);
+  if (nvec <= 8) VB_GROUP(8, 1, 4);
+  else if (nvec <= 16) VB_GROUP(16, 1, 4);
+  else if (nvec <= 32) VB_GROUP(32, 1, 4);
+  else if (nvec <= 64) VB_GROUP(32, 2, 2);
+  else if (nvec <= 128) VB_GROUP(32, 4, 1);
   else if (nvec <= 256) VB_BLOCK(128, 2, 16);
   else if (nvec <= 512) VB_BLOCK(128, 4, 16);
   else if (nvec <= 1024) VB_BLOCK(256, 4, 8);
