@@ -44,9 +44,10 @@ if ROOT not in sys.path:
 TOTAL_ELEMS = 1 << 32
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per launch of the local reduce kernel for a 2 GiB shard, from the ncu capture
-# summarised in profiles/ (filled in once the capture has been taken; None = not captured).
-REDUCE_TRAFFIC_BYTES_PER_ELEM = None
+# DRAM bytes per element moved by one launch of the local reduce kernel, from the ncu capture
+# of a 2 GiB shard summarised in profiles/ncu_row_block_kernel_sum_f32_2GiB_shard.md
+# (dram__bytes_read.sum + dram__bytes_write.sum; traffic grows in proportion to the shard).
+REDUCE_TRAFFIC_BYTES_PER_ELEM = 2151534080 / (1 << 29)  # 2 147 509 504 B read + 4 024 576 B written for 2^29 elements
 
 
 def measured_peak():
@@ -167,7 +168,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "host_cores": os.cpu_count(),
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(n):
@@ -331,8 +332,8 @@ def run_ours(args):
     if args.suite_only:
         if rank == 0:
             suite = op_suite(torch, peak_gbs, args.suite_scale, tuple(args.suite_ops.split(',')))
-            print(json.dumps({"metric": "per-op HBM GB/s", "n_gpus": 1, "suite_scale": args.suite_scale,
-                              "peak_gbs": peak_gbs, "peak_source": peak_kind, "ops": suite}), flush=True)
+            emit({"metric": "per-op HBM GB/s", "n_gpus": 1, "suite_scale": args.suite_scale,
+                  "peak_gbs": peak_gbs, "peak_source": peak_kind, "ops": suite})
         return
     shard_elems = TOTAL_ELEMS // n
     # per-rank stream of the seed: shards are reproducible without one host holding 16 GiB
@@ -437,7 +438,7 @@ def run_ours(args):
             line["cpu_baseline"] = cpu
         if suite is not None:
             line["ops"] = suite
-        print(json.dumps(line), flush=True)
+        emit(line)
     if n > 1:
         dist.destroy_process_group()
 
@@ -499,8 +500,21 @@ def run_e2e(torch, dist, ops, shard, n, args):
             "launches_per_step": (nchunks + 1) * n, "result": val}
 
 
+_JSON_OUT = sys.stdout
+
+
+def emit(line: dict) -> None:
+    """The one JSON line, on the process's original stdout."""
+    print(json.dumps(line), file=_JSON_OUT, flush=True)
+
+
 def main():
-    global TOTAL_ELEMS
+    global TOTAL_ELEMS, _JSON_OUT
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1.  Keep the real
+    # stdout for the JSON line only and send everything else to stderr.
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
