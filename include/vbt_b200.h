@@ -297,6 +297,24 @@ VBT_B200_API vbt_b200_status vbt_b200_index_rows(const vbt_b200_tensor* out, con
 VBT_B200_API vbt_b200_status vbt_b200_index_put_rows(const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
                                         const vbt_b200_tensor* values, int32_t accumulate,
                                         int32_t policy, void* index_status, void* stream);
+/* table[idx[i], :] += values[i, :] by SORTING the updates by destination row first: the
+ * deterministic counterpart of the accumulate path above, and the fast one for 64-bit
+ * integers and for heavily repeated rows.  It does what the reference's opt-in sort +
+ * reduce-by-key path does (advanced_index_put_make_kv_cuda_kernel + CUB SortPairs +
+ * ReduceByKey + scatter, src/vbt/core/indexing_advanced_cuda.cu:1460-1557, :2888-3055) with
+ * an LSD radix sort written here.  Each destination row is summed in update order by one
+ * warp and written with a plain read-add-write; only rows with more updates than one warp's
+ * slice (32) see atomics.  INT64 / INT32 exact; F32 bit-identical to a sequential loop for
+ * every row updated from one slice when the row starts at zero.  `workspace` (16-byte
+ * aligned, vbt_b200_index_put_rows_sorted_workspace_bytes(N) bytes, about 16 bytes per
+ * index) needs no initialisation.  Shapes the sorted kernels do not take (rows that are not
+ * whole 16-byte chunks) are served by the atomic path with the same result. */
+VBT_B200_API size_t vbt_b200_index_put_rows_sorted_workspace_bytes(int64_t num_indices);
+VBT_B200_API vbt_b200_status vbt_b200_index_put_rows_sorted(const vbt_b200_tensor* table,
+                                               const vbt_b200_tensor* idx,
+                                               const vbt_b200_tensor* values, int32_t policy,
+                                               void* index_status, void* workspace,
+                                               size_t workspace_bytes, void* stream);
 /* The reference's CUDA advanced-index pattern: one index tensor applied to the LAST dim
  * (indexing_advanced_cuda.cu:2139-2177): out[b, k] = src[b, idx[k]]; src [B, K0] strided. */
 VBT_B200_API vbt_b200_status vbt_b200_index_lastdim(const vbt_b200_tensor* out, const vbt_b200_tensor* src,

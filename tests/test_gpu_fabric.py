@@ -93,3 +93,36 @@ def test_two_rank_nccl_sharded_ops():
             errs.append((-1, "rank still alive after 300 s"))
     assert not errs, "\n".join(f"rank {r}:\n{t}" for r, t in errs)
     assert all(p.exitcode == 0 for p in procs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_elementwise_with_one_operand_in_peer_memory():
+    """The reference's vt::fabric_add / fabric_mul shape (src/vbt/cuda/fabric_elementwise.cu:
+    820-1042): compute on the primary GPU, read one operand straight from a peer GPU's memory
+    (plain loads over NVLink), write the result locally."""
+    import oracle
+    from vibetensor_b200 import ops
+    if not torch.cuda.can_device_access_peer(0, 1):
+        pytest.skip("no peer access between GPU 0 and GPU 1")
+    rng = np.random.default_rng(5)
+    a_np = rng.standard_normal((512, 300), dtype=np.float32)
+    b_np = rng.standard_normal((512, 300), dtype=np.float32)
+    a = torch.from_numpy(a_np).to("cuda:0")
+    b = torch.from_numpy(b_np).to("cuda:1")
+    a.add_(b.to("cuda:0") * 0)            # a device-to-device copy makes torch enable peer access
+    torch.cuda.synchronize(0)
+    torch.cuda.synchronize(1)
+    port = oracle.port()
+    with torch.cuda.device(0):
+        for name in ("add", "mul"):
+            out = torch.empty_like(a)
+            ops.binary(name, a, b, out=out)   # b lives on GPU 1
+            torch.cuda.synchronize(0)
+            np.testing.assert_array_equal(out.cpu().numpy(), port.binary(name, a_np, b_np, oracle.F32))
+        # bf16 with a broadcast remote operand
+        ab = a.bfloat16()
+        bb = b[:1].bfloat16()
+        out = ops.binary("add", ab, bb)
+        torch.cuda.synchronize(0)
+        assert out.device.index == 0
+        assert torch.equal(out, ab + bb.to("cuda:0"))

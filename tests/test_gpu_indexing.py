@@ -225,3 +225,66 @@ def test_config2_scale_roundtrip_properties(ops):
     acci = torch.zeros((V, D), dtype=torch.int64, device="cuda")
     ops.index_put_rows_(acci, ti, torch.full((N, D), 3, dtype=torch.int64, device="cuda"), accumulate=True)
     assert torch.equal(acci[:, 17], 3 * counts.long())
+
+
+@pytest.mark.parametrize("V,D,N", [(1000, 256, 20000), (97, 64, 5000), (5000, 8, 4097), (16, 516, 999),
+                                   (300, 4, 31), (70000, 4, 300000), (3, 4, 1)])
+def test_sorted_scatter_add(ops, port, V, D, N):
+    """The sort-based accumulate engine: exact for integers, within tolerance for fp32, and
+    exact for fp32 too when no row is updated twice."""
+    rng = np.random.default_rng(36)
+    idx = zipf_indices(rng, V, N)
+    idx[::7] -= V                                   # negative indices wrap
+    ti = torch.from_numpy(idx).cuda()
+    vi = rng.integers(-1000, 1001, (N, D)).astype(np.int64)
+    init = rng.integers(-5, 6, (V, D)).astype(np.int64)
+    acc = torch.from_numpy(init.copy()).cuda()
+    ops.index_put_rows_(acc, ti, torch.from_numpy(vi).cuda(), accumulate=True, deterministic=True)
+    np.testing.assert_array_equal(acc.cpu().numpy(), port.scatter_rows(init.copy(), idx, vi, oracle.I64))
+    v32 = vi.astype(np.int32)
+    acc32 = torch.zeros((V, D), dtype=torch.int32, device="cuda")
+    ops.index_put_rows_(acc32, ti, torch.from_numpy(v32).cuda(), accumulate=True, deterministic=True)
+    np.testing.assert_array_equal(acc32.cpu().numpy(),
+                                  port.scatter_rows(np.zeros((V, D), np.int32), idx, v32, oracle.I32))
+    vf = rng.standard_normal((N, D), dtype=np.float32)
+    initf = rng.standard_normal((V, D), dtype=np.float32)
+    accf = torch.from_numpy(initf.copy()).cuda()
+    ops.index_put_rows_(accf, ti, torch.from_numpy(vf).cuda(), accumulate=True, deterministic=True)
+    want = port.scatter_rows(initf.copy(), idx, vf, oracle.F32)
+    mass = port.scatter_rows(np.abs(initf), idx, np.abs(vf), oracle.F32)
+    err = np.abs(accf.cpu().numpy().astype(np.float64) - want)
+    assert (err <= 1e-5 * mass + 1e-30).all(), err.max()
+
+
+def test_sorted_scatter_add_unique_rows_is_bit_exact_and_flags_bad_indices(ops, port):
+    rng = np.random.default_rng(37)
+    V, D, N = 4000, 64, 3000
+    idx = rng.permutation(V)[:N].astype(np.int64)
+    vf = rng.standard_normal((N, D), dtype=np.float32)
+    init = rng.standard_normal((V, D), dtype=np.float32)
+    acc = torch.from_numpy(init.copy()).cuda()
+    ops.index_put_rows_(acc, torch.from_numpy(idx).cuda(), torch.from_numpy(vf).cuda(), accumulate=True,
+                        deterministic=True)
+    np.testing.assert_array_equal(acc.cpu().numpy(), port.scatter_rows(init.copy(), idx, vf, oracle.F32))
+    # zero-initialised destination, duplicates: every row summed from one slice is the
+    # sequential sum; compare all rows with few updates bit for bit
+    idx2 = rng.integers(0, V, 6000).astype(np.int64)
+    v2 = rng.standard_normal((6000, D), dtype=np.float32)
+    a2 = torch.zeros((V, D), device="cuda")
+    ops.index_put_rows_(a2, torch.from_numpy(idx2).cuda(), torch.from_numpy(v2).cuda(), accumulate=True,
+                        deterministic=True)
+    want = port.scatter_rows(np.zeros((V, D), np.float32), idx2, v2, oracle.F32)
+    got = a2.cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+    assert (got == want).all(axis=1).mean() > 0.9
+    # out-of-range updates are dropped and reported
+    bad = idx.copy()
+    bad[5] = V + 3
+    acc3 = torch.zeros((V, D), device="cuda")
+    with pytest.raises(IndexError):
+        ops.index_put_rows_(acc3, torch.from_numpy(bad).cuda(), torch.from_numpy(vf).cuda(), accumulate=True,
+                            deterministic=True)
+    keep = np.ones(N, bool)
+    keep[5] = False
+    np.testing.assert_array_equal(
+        acc3.cpu().numpy(), port.scatter_rows(np.zeros((V, D), np.float32), idx[keep], vf[keep], oracle.F32))

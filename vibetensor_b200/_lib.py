@@ -59,6 +59,8 @@ SIGNATURES = {
     "vbt_b200_reduce_shape": (_i32, [_P, _i64p, _i32, _i32, _i64p, _i32p]),
     "vbt_b200_index_rows": (_i32, [_P, _P, _P, _i32, _vp, _vp]),
     "vbt_b200_index_put_rows": (_i32, [_P, _P, _P, _i32, _i32, _vp, _vp]),
+    "vbt_b200_index_put_rows_sorted_workspace_bytes": (ctypes.c_size_t, [_i64]),
+    "vbt_b200_index_put_rows_sorted": (_i32, [_P, _P, _P, _i32, _vp, _vp, ctypes.c_size_t, _vp]),
     "vbt_b200_index_lastdim": (_i32, [_P, _P, _P, _i32, _vp, _vp]),
     "vbt_b200_index_put_lastdim": (_i32, [_P, _P, _P, _i32, _i32, _vp, _vp]),
     "vbt_b200_embedding": (_i32, [_P, _P, _P, _vp, _vp]),

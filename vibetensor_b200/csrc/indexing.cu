@@ -306,6 +306,270 @@ __global__ void __launch_bounds__(kThreads) scatter_add_elem_kernel(const __grid
 }
 
 // ------------------------------------------------------------------------------------
+// sorted scatter-add: radix-sort (row, position) pairs, then accumulate runs
+//
+// The block-local aggregation above still sends one atomic per distinct row PER BLOCK; with
+// 64-bit integer rows (256 scalar atomics per 2 KiB row) the L2 atomic units, not HBM, set
+// the pace.  Sorting ALL updates by destination row first makes every row one contiguous
+// run: a warp walks 32 sorted entries, sums each run in update order in registers, and a
+// run that lies wholly inside the warp's slice is the ONLY writer of its row, so it is
+// finished with a plain read-add-write.  Only runs that cross a slice boundary (rows with
+// more updates than a slice holds) use atomics.  Results are exact for integers; for fp32
+// every row updated from a single slice is summed in update order -- bit-identical to a
+// sequential loop when the destination starts at zero -- and independent of scheduling.
+//
+// Sort: LSD radix, 8 bits per pass over just the bits the row range needs; per pass a
+// block histogram, one exclusive scan, and a stable scatter (ranks from __match_any_sync).
+// ------------------------------------------------------------------------------------
+constexpr int kSortThreads = 256;
+constexpr int kSortItems = 16;                            // per thread
+constexpr int kSortTile = kSortThreads * kSortItems;      // 4096 items per block
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr int kWarpChunk = kSortTile / kSortWarps;        // 512 consecutive items per warp
+
+struct KeyParams {
+  IndexSrc idx;
+  int64_t N, V;
+  int policy;
+  unsigned long long* status;
+  int use_padding;
+  int64_t padding_idx;
+  uint32_t* keys;
+  uint32_t* vals;
+};
+// key = destination row, or V for an update that must be skipped (sorts last)
+__global__ void __launch_bounds__(256) make_keys_kernel(const __grid_constant__ KeyParams p) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= p.N) return;
+  int64_t v = p.idx.get(i);
+  uint32_t key = static_cast<uint32_t>(p.V);
+  if (!(p.use_padding && v == p.padding_idx)) {
+    if (normalize(v, p.V, p.policy, p.status, true)) key = static_cast<uint32_t>(v);
+  }
+  p.keys[i] = key;
+  p.vals[i] = static_cast<uint32_t>(i);
+}
+
+// hist[d * nblocks + b] = number of items of block b whose digit is d
+// and totals[d] += the same counts (totals is zero on entry)
+__global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(const uint32_t* keys, int64_t n, int shift,
+                                                                  uint32_t* hist, int nblocks, uint32_t* totals) {
+  __shared__ uint32_t h[256];
+  h[threadIdx.x] = 0;
+  __syncthreads();
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kSortTile;
+#pragma unroll
+  for (int k = 0; k < kSortItems; ++k) {
+    const int64_t i = base + k * kSortThreads + threadIdx.x;
+    if (i < n) atomicAdd(&h[(keys[i] >> shift) & 0xff], 1u);
+  }
+  __syncthreads();
+  hist[static_cast<int64_t>(threadIdx.x) * nblocks + blockIdx.x] = h[threadIdx.x];
+  if (h[threadIdx.x]) atomicAdd(&totals[threadIdx.x], h[threadIdx.x]);
+}
+
+// block d turns row d of hist ([256][nblocks], counts) into output start offsets:
+// (items with a smaller digit) + (items with digit d in earlier blocks)
+__global__ void __launch_bounds__(1024) radix_scan_kernel(uint32_t* hist, int nblocks, const uint32_t* totals) {
+  __shared__ uint32_t warp_sums[32];
+  __shared__ uint32_t base_s;
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  const int d = blockIdx.x;
+  auto block_inclusive = [&](uint32_t v) {  // inclusive scan over the 1024 threads
+#pragma unroll
+    for (int k = 1; k < 32; k <<= 1) {
+      const uint32_t y = __shfl_up_sync(0xffffffffu, v, k);
+      if (lane >= k) v += y;
+    }
+    __syncthreads();  // warp_sums may still be read from the previous use
+    if (lane == 31) warp_sums[w] = v;
+    __syncthreads();
+    if (w == 0) {
+      uint32_t s = warp_sums[lane], si = s;
+#pragma unroll
+      for (int k = 1; k < 32; k <<= 1) {
+        const uint32_t y = __shfl_up_sync(0xffffffffu, si, k);
+        if (lane >= k) si += y;
+      }
+      warp_sums[lane] = si - s;
+    }
+    __syncthreads();
+    return v + warp_sums[w];
+  };
+  const uint32_t below = block_inclusive(t < d ? totals[t] : 0u);  // thread 1023 holds the full sum
+  if (t == 1023) base_s = below;
+  __syncthreads();
+  uint32_t carry = base_s;
+  uint32_t* row = hist + static_cast<int64_t>(d) * nblocks;
+  for (int b0 = 0; b0 < nblocks; b0 += 1024) {
+    const int b = b0 + t;
+    const uint32_t c = b < nblocks ? row[b] : 0u;
+    const uint32_t incl = block_inclusive(c);
+    if (b < nblocks) row[b] = carry + incl - c;
+    __syncthreads();
+    if (t == 1023) base_s = carry + incl;
+    __syncthreads();
+    carry = base_s;
+  }
+}
+
+// stable scatter of one 4096-item tile by the current digit
+__global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(const uint32_t* keys_in, const uint32_t* vals_in,
+                                                                     uint32_t* keys_out, uint32_t* vals_out,
+                                                                     int64_t n, int shift, const uint32_t* hist,
+                                                                     int nblocks) {
+  __shared__ uint32_t cnt[kSortWarps][256];
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  for (int i = t; i < kSortWarps * 256; i += kSortThreads) (&cnt[0][0])[i] = 0;
+  __syncthreads();
+  // a warp owns 512 CONSECUTIVE items and takes them 32 at a time, so "earlier in the
+  // array" == (earlier warp) or (same warp, earlier round) or (same round, lower lane)
+  const int64_t wbase = static_cast<int64_t>(blockIdx.x) * kSortTile + w * kWarpChunk;
+  uint32_t key[kSortItems], val[kSortItems], rank[kSortItems];
+#pragma unroll
+  for (int r = 0; r < kSortItems; ++r) {
+    const int64_t i = wbase + r * 32 + lane;
+    const bool valid = i < n;
+    key[r] = valid ? keys_in[i] : 0u;
+    val[r] = valid ? vals_in[i] : 0u;
+  }
+#pragma unroll
+  for (int r = 0; r < kSortItems; ++r) {
+    const int64_t i = wbase + r * 32 + lane;
+    const bool valid = i < n;
+    const uint32_t d = (key[r] >> shift) & 0xff;
+    const unsigned peers = __match_any_sync(0xffffffffu, valid ? d : 256u + lane);
+    const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+    rank[r] = valid ? cnt[w][d] + before : 0u;
+    __syncwarp();
+    if (valid && before == 0) cnt[w][d] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+  {
+    // thread d: turn the per-warp counts of digit d into start offsets in the output
+    uint32_t off = hist[static_cast<int64_t>(t) * nblocks + blockIdx.x];
+#pragma unroll
+    for (int ww = 0; ww < kSortWarps; ++ww) {
+      const uint32_t c = cnt[ww][t];
+      cnt[ww][t] = off;
+      off += c;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < kSortItems; ++r) {
+    const int64_t i = wbase + r * 32 + lane;
+    if (i < n) {
+      const uint32_t dst = cnt[w][(key[r] >> shift) & 0xff] + rank[r];
+      keys_out[dst] = key[r];
+      vals_out[dst] = val[r];
+    }
+  }
+}
+
+struct SortedScatterParams {
+  char* table;
+  const char* values;
+  const uint32_t* keys;   // sorted rows; V = skip
+  const uint32_t* vals;   // original update positions
+  int64_t N, V;
+  uint32_t cpr;
+};
+
+template <class T> struct PlainAdd;
+template <> struct PlainAdd<float> {
+  __device__ static void rmw(char* dst, const float4& a) {
+    float4 t = *reinterpret_cast<const float4*>(dst);
+    t.x += a.x; t.y += a.y; t.z += a.z; t.w += a.w;
+    *reinterpret_cast<float4*>(dst) = t;
+  }
+};
+template <> struct PlainAdd<int64_t> {
+  __device__ static void rmw(char* dst, const AddVec<int64_t>::acc_t& a) {
+    ulonglong2 t = *reinterpret_cast<const ulonglong2*>(dst);
+    t.x += a.a; t.y += a.b;
+    *reinterpret_cast<ulonglong2*>(dst) = t;
+  }
+};
+template <> struct PlainAdd<int32_t> {
+  __device__ static void rmw(char* dst, const uint4& a) {
+    uint4 t = *reinterpret_cast<const uint4*>(dst);
+    t.x += a.x; t.y += a.y; t.z += a.z; t.w += a.w;
+    *reinterpret_cast<uint4*>(dst) = t;
+  }
+};
+
+// one warp per slice of 32 sorted entries
+template <class T, int K>
+__global__ void __launch_bounds__(kThreads) scatter_add_sorted_kernel(const __grid_constant__ SortedScatterParams p) {
+  using AV = AddVec<T>;
+  using acc_t = typename AV::acc_t;
+  const int lane = threadIdx.x & 31;
+  const int64_t slice = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+  const int64_t s0 = slice * 32;
+  if (s0 >= p.N) return;
+  const uint32_t skip = static_cast<uint32_t>(p.V);
+  const int64_t me = s0 + lane;
+  const uint32_t my_key = me < p.N ? p.keys[me] : skip;
+  const uint32_t my_pos = me < p.N ? p.vals[me] : 0u;
+  // does the slice's first run continue the previous slice's last one / its last run go on?
+  const uint32_t prev_last = s0 > 0 ? p.keys[s0 - 1] : 0xffffffffu;
+  const uint32_t next_first = s0 + 32 < p.N ? p.keys[s0 + 32] : 0xffffffffu;
+  const int64_t row_bytes = static_cast<int64_t>(p.cpr) * 16;
+  constexpr int U = K >= 4 ? 2 : 4;
+  for (uint32_t cb = 0; cb < p.cpr; cb += 32 * K) {
+    acc_t acc[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) acc[k] = AV::zero();
+    uint32_t cur = skip;      // row of the open run (skip = none)
+    bool cur_shared = false;  // the open run started in an earlier slice
+    auto flush = [&](uint32_t row, bool shared) {
+      char* dst = p.table + static_cast<int64_t>(row) * row_bytes;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const uint32_t c = cb + k * 32 + lane;
+        if (c < p.cpr) {
+          if (shared) AV::flush(dst + static_cast<int64_t>(c) * 16, acc[k]);
+          else PlainAdd<T>::rmw(dst + static_cast<int64_t>(c) * 16, acc[k]);
+        }
+        acc[k] = AV::zero();
+      }
+    };
+    for (int e0 = 0; e0 < 32; e0 += U) {
+      uint32_t key[U];
+      int4 raw[U][K];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        key[u] = __shfl_sync(0xffffffffu, my_key, e0 + u);
+        const uint32_t pos = __shfl_sync(0xffffffffu, my_pos, e0 + u);
+        if (key[u] != skip) {
+          const char* src = p.values + static_cast<int64_t>(pos) * row_bytes;
+#pragma unroll
+          for (int k = 0; k < K; ++k) {
+            const uint32_t c = cb + k * 32 + lane;
+            raw[u][k] = c < p.cpr ? *reinterpret_cast<const int4*>(src + static_cast<int64_t>(c) * 16)
+                                  : make_int4(0, 0, 0, 0);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (key[u] == skip) continue;  // skipped updates sort to the very end
+        if (key[u] != cur) {
+          if (cur != skip) flush(cur, cur_shared);
+          cur = key[u];
+          cur_shared = (e0 + u == 0) && (cur == prev_last);
+        }
+#pragma unroll
+        for (int k = 0; k < K; ++k) AV::add(acc[k], raw[u][k]);
+      }
+    }
+    if (cur != skip) flush(cur, cur_shared || cur == next_first);
+  }
+}
+
+// ------------------------------------------------------------------------------------
 // last-dim index / index_put: out[b, k] = src[b, idx[k]]
 // ------------------------------------------------------------------------------------
 struct LastDimParams {
@@ -477,6 +741,90 @@ vbt_b200_status scatter_add_rows(const char* name, const vbt_b200_tensor* table,
   }
 }
 
+size_t sorted_workspace_bytes(int64_t n) {
+  if (n <= 0) return 0;
+  const int64_t nblocks = (n + kSortTile - 1) / kSortTile;
+  const size_t arrays = 4 * ((static_cast<size_t>(n) * 4 + 255) / 256 * 256);
+  return arrays + static_cast<size_t>(nblocks) * 256 * 4 + 4 * 256 * 4;  // + per-pass digit totals
+}
+
+template <class T>
+void launch_sorted(const SortedScatterParams& p, cudaStream_t s) {
+  const int64_t slices = (p.N + 31) / 32;
+  const unsigned g = static_cast<unsigned>((slices + kThreads / 32 - 1) / (kThreads / 32));
+  if (p.cpr <= 32) scatter_add_sorted_kernel<T, 1><<<g, kThreads, 0, s>>>(p);
+  else if (p.cpr <= 64) scatter_add_sorted_kernel<T, 2><<<g, kThreads, 0, s>>>(p);
+  else scatter_add_sorted_kernel<T, 4><<<g, kThreads, 0, s>>>(p);
+}
+
+vbt_b200_status scatter_add_rows_sorted(const char* name, const vbt_b200_tensor* table,
+                                        const vbt_b200_tensor* idx, const vbt_b200_tensor* values, int policy,
+                                        void* status, int use_padding, int64_t padding_idx, void* ws,
+                                        size_t ws_bytes, cudaStream_t s) {
+  VB_TRY(validate_tensor(table, name));
+  VB_TRY(validate_tensor(values, name));
+  VB_ARG(table->ndim == 2, std::string(name) + ": table must be rank 2");
+  const int dt = table->dtype;
+  const int64_t V = table->sizes[0], D = table->sizes[1];
+  const int es = itemsize(dt);
+  IndexSrc is{};
+  int64_t N = 0;
+  VB_TRY(check_idx(idx, name, &is, &N));
+  const bool chunked = (D * es) % 16 == 0 && D > 0 && reinterpret_cast<uintptr_t>(table->data) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(values->data) % 16 == 0 && V < (int64_t{1} << 31);
+  const bool typed = dt == VBT_B200_F32 || dt == VBT_B200_I64 || dt == VBT_B200_I32;
+  if (!chunked || !typed || N == 0)  // shapes the sorted kernels do not take: same result, atomic path
+    return scatter_add_rows(name, table, idx, values, policy, status, use_padding, padding_idx, s);
+  VB_ARG(values->dtype == dt, std::string(name) + ": dtype mismatch");
+  VB_ARG(policy >= 0 && policy <= 2, std::string(name) + ": unknown index policy");
+  VB_ARG(is_dense_row_major(*table), std::string(name) + ": table must be contiguous");
+  VB_ARG(is_dense_row_major(*values) && numel(*values) == N * D,
+         std::string(name) + ": values must be contiguous [N, D]");
+  const size_t need = sorted_workspace_bytes(N);
+  VB_ARG(ws != nullptr && ws_bytes >= need,
+         std::string(name) + ": workspace too small (see vbt_b200_index_put_rows_sorted_workspace_bytes)");
+  VB_ARG(reinterpret_cast<uintptr_t>(ws) % 16 == 0, std::string(name) + ": workspace must be 16-byte aligned");
+  DeviceScope scope(table->data);
+  const size_t arr = (static_cast<size_t>(N) * 4 + 255) / 256 * 256;
+  char* w = static_cast<char*>(ws);
+  uint32_t* keys[2] = {reinterpret_cast<uint32_t*>(w), reinterpret_cast<uint32_t*>(w + 2 * arr)};
+  uint32_t* vals[2] = {reinterpret_cast<uint32_t*>(w + arr), reinterpret_cast<uint32_t*>(w + 3 * arr)};
+  uint32_t* hist = reinterpret_cast<uint32_t*>(w + 4 * arr);
+  const int nblocks = static_cast<int>((N + kSortTile - 1) / kSortTile);
+  uint32_t* totals = hist + static_cast<size_t>(nblocks) * 256;  // [4 passes][256]
+  VB_CUDA(cudaMemsetAsync(totals, 0, 4 * 256 * 4, s));
+  KeyParams kp{};
+  kp.idx = is; kp.N = N; kp.V = V; kp.policy = policy;
+  kp.status = static_cast<unsigned long long*>(status);
+  kp.use_padding = use_padding; kp.padding_idx = padding_idx;
+  kp.keys = keys[0]; kp.vals = vals[0];
+  make_keys_kernel<<<static_cast<unsigned>((N + 255) / 256), 256, 0, s>>>(kp);
+  int bits = 0;
+  while ((int64_t{1} << bits) <= V) ++bits;  // keys run 0..V (V = skip)
+  int cur = 0;
+  for (int shift = 0; shift < bits; shift += 8) {
+    uint32_t* tot = totals + (shift / 8) * 256;
+    radix_hist_kernel<<<nblocks, kSortThreads, 0, s>>>(keys[cur], N, shift, hist, nblocks, tot);
+    radix_scan_kernel<<<256, 1024, 0, s>>>(hist, nblocks, tot);
+    radix_scatter_kernel<<<nblocks, kSortThreads, 0, s>>>(keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], N,
+                                                          shift, hist, nblocks);
+    cur ^= 1;
+  }
+  SortedScatterParams sp{};
+  sp.table = static_cast<char*>(table->data);
+  sp.values = static_cast<const char*>(values->data);
+  sp.keys = keys[cur]; sp.vals = vals[cur];
+  sp.N = N; sp.V = V;
+  sp.cpr = static_cast<uint32_t>(D * es / 16);
+  switch (dt) {
+    case VBT_B200_F32: launch_sorted<float>(sp, s); break;
+    case VBT_B200_I64: launch_sorted<int64_t>(sp, s); break;
+    default: launch_sorted<int32_t>(sp, s); break;
+  }
+  VB_LAUNCH_CHECK();
+  return VBT_B200_OK;
+}
+
 vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt_b200_tensor* idx,
                         const vbt_b200_tensor* other, int mode, int policy, void* status, cudaStream_t s) {
   VB_TRY(validate_tensor(self, name));
@@ -530,6 +878,17 @@ vbt_b200_status vbt_b200_index_put_rows(const vbt_b200_tensor* table, const vbt_
                                 static_cast<cudaStream_t>(stream));
   return vb::rows_copy("index_put_", values, table, idx, policy, index_status,
                        static_cast<cudaStream_t>(stream), 1);
+}
+
+size_t vbt_b200_index_put_rows_sorted_workspace_bytes(int64_t num_indices) {
+  return vb::sorted_workspace_bytes(num_indices);
+}
+
+vbt_b200_status vbt_b200_index_put_rows_sorted(const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
+                                               const vbt_b200_tensor* values, int32_t policy, void* index_status,
+                                               void* workspace, size_t workspace_bytes, void* stream) {
+  return vb::scatter_add_rows_sorted("index_put_", table, idx, values, policy, index_status, 0, 0, workspace,
+                                     workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 vbt_b200_status vbt_b200_index_lastdim(const vbt_b200_tensor* out, const vbt_b200_tensor* src,

@@ -413,9 +413,17 @@ __global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ C
   if (!is_last) return;
   __threadfence();
   if (owner) {
+    // chunk order, eight independent loads in flight at a time (a loop of load-then-combine
+    // would pay one L2 round trip per chunk)
     acc_t f = R::init();
-    for (int s = 0; s < p.splits; ++s)
-      f = R::combine(f, ld_cg(part + static_cast<int64_t>(s) * ncols + c));
+    for (int s0 = 0; s0 < p.splits; s0 += 8) {
+      acc_t t[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        t[u] = s0 + u < p.splits ? ld_cg(part + static_cast<int64_t>(s0 + u) * ncols + c) : R::init();
+#pragma unroll
+      for (int u = 0; u < 8; ++u) f = R::combine(f, t[u]);
+    }
     finalize<R, A>(p.o, out_i, f, widen(*first_p));
   }
 }

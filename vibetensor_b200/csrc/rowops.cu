@@ -207,7 +207,8 @@ __global__ void __launch_bounds__(256) rowop_group_kernel(const __grid_constant_
   }
 }
 
-// THREADS threads per row, persistent over rows
+// THREADS threads per row, persistent over rows.  gamma is re-read per row (it stays in L1)
+// rather than pinned in registers: with 32 values per thread it would halve the occupancy.
 template <class T, int KIND, int THREADS, int VPL>
 __global__ void __launch_bounds__(THREADS) rowop_block_kernel(const __grid_constant__ RowParams p) {
   constexpr int V = 16 / sizeof(T);
@@ -215,8 +216,11 @@ __global__ void __launch_bounds__(THREADS) rowop_block_kernel(const __grid_const
   __shared__ float red[2][kWarps];
   const int t = threadIdx.x;
   const int nvec = static_cast<int>(p.cols / V);
-  float g[VPL][V];
-  load_gamma<T, VPL>(KIND == K_RMSNORM ? p.gamma : nullptr, t, THREADS, nvec, g);
+  float ones[VPL][V];
+#pragma unroll
+  for (int k = 0; k < VPL; ++k)
+#pragma unroll
+    for (int e = 0; e < V; ++e) ones[k][e] = 1.0f;
   int phase = 0;
   auto block_fold = [&](float a, bool is_max) {
     a = is_max ? group_max<32>(a) : group_sum<32>(a);
@@ -233,8 +237,23 @@ __global__ void __launch_bounds__(THREADS) rowop_block_kernel(const __grid_const
     bool valid[VPL];
     load_row<T, VPL>(static_cast<const T*>(p.x) + row * p.x_row_stride, t, THREADS, nvec, v, valid);
     float inv = 0.f;
-    row_math<T, KIND, VPL>(v, valid, g, p, [&](float a) { return block_fold(a, true); },
+    row_math<T, KIND, VPL>(v, valid, ones, p, [&](float a) { return block_fold(a, true); },
                            [&](float a) { return block_fold(a, false); }, &inv);
+    if constexpr (KIND == K_RMSNORM) {
+      if (p.gamma) {
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) {
+          if (!valid[k]) continue;
+          const float4* gp = reinterpret_cast<const float4*>(p.gamma + static_cast<int64_t>(t + k * THREADS) * V);
+#pragma unroll
+          for (int q = 0; q < V / 4; ++q) {
+            const float4 gq = __ldg(gp + q);
+            v[k][4 * q + 0] *= gq.x; v[k][4 * q + 1] *= gq.y;
+            v[k][4 * q + 2] *= gq.z; v[k][4 * q + 3] *= gq.w;
+          }
+        }
+      }
+    }
     store_row<T, VPL>(static_cast<T*>(p.out) + row * p.cols, t, THREADS, v, valid);
     if (KIND == K_RMSNORM && p.inv_rms && t == 0) p.inv_rms[row] = inv;
   }
@@ -302,7 +321,7 @@ vbt_b200_status launch_rowop(const RowParams& p, cudaStream_t s, int device) {
   const bool aligned = p.cols % V == 0 && (p.x_row_stride * sizeof(T)) % 16 == 0 &&
                        reinterpret_cast<uintptr_t>(p.x) % 16 == 0 &&
                        reinterpret_cast<uintptr_t>(p.out) % 16 == 0 &&
-                       (KIND != K_RMSNORM || p.gamma == nullptr || reinterpret_cast<uintptr_t>(p.gamma) % 4 == 0);
+                       (KIND != K_RMSNORM || p.gamma == nullptr || reinterpret_cast<uintptr_t>(p.gamma) % 16 == 0);
   const int64_t nvec = aligned ? p.cols / V : (int64_t{1} << 40);
   auto grid = [&](int64_t units, int per_sm) {
     return static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(units, int64_t{sms} * per_sm)));
@@ -311,13 +330,14 @@ vbt_b200_status launch_rowop(const RowParams& p, cudaStream_t s, int device) {
   rowop_group_kernel<T, KIND, G, VPL, RPG>                                                    \
       <<<grid((p.rows + (256 / G) * RPG - 1) / ((256 / G) * RPG), 8), 256, 0, s>>>(p)
 #define VB_BLOCK(TH, VPL, PER_SM) rowop_block_kernel<T, KIND, TH, VPL><<<grid(p.rows, PER_SM), TH, 0, s>>>(p)
-  if (nvec <= 8) VB_GROUP(8, 1, 4);
-  else if (nvec <= 16) VB_GROUP(16, 1, 4);
-  else if (nvec <= 32) VB_GROUP(32, 1, 4);
-  else if (nvec <= 64) VB_GROUP(32, 2, 2);
+  // short rows: few lanes per row and several vectors per lane keep the shuffle trees short
+  if (nvec <= 8) VB_GROUP(2, 4, 2);
+  else if (nvec <= 16) VB_GROUP(4, 4, 2);
+  else if (nvec <= 32) VB_GROUP(8, 4, 2);
+  else if (nvec <= 64) VB_GROUP(16, 4, 2);
   else if (nvec <= 128) VB_GROUP(32, 4, 1);
   else if (nvec <= 256) VB_BLOCK(128, 2, 16);
-  else if (nvec <= 512) VB_BLOCK(128, 4, 16);
+  else if (nvec <= 512) VB_BLOCK(256, 2, 8);
   else if (nvec <= 1024) VB_BLOCK(256, 4, 8);
   else if (nvec <= 2048) VB_BLOCK(256, 8, 8);
   else rowop_stream_kernel<T, KIND><<<grid(p.rows, 8), 256, 0, s>>>(p);

@@ -322,13 +322,28 @@ def index_rows(table: torch.Tensor, idx: torch.Tensor, policy: int = INDEX_WRAP,
 
 def index_put_rows_(table: torch.Tensor, idx: torch.Tensor, values: torch.Tensor,
                     accumulate: bool = False, policy: int = INDEX_WRAP,
-                    status: Optional[IndexStatus] = None, eager_check: bool = True) -> torch.Tensor:
-    """``table.index_put_((idx,), values, accumulate)`` for a 2-D table and [N, D] values."""
+                    status: Optional[IndexStatus] = None, eager_check: bool = True,
+                    deterministic: Optional[bool] = None) -> torch.Tensor:
+    """``table.index_put_((idx,), values, accumulate)`` for a 2-D table and [N, D] values.
+
+    accumulate=True has two engines: block-local aggregation + atomics (no scratch), and
+    sort-by-row + per-row sums (scratch of ~16 bytes per index, order-independent results).
+    ``deterministic=None`` picks the sorted engine for integer tables with many updates,
+    where it is also the faster one; True / False force the choice."""
     _require_cuda(table, idx, values)
     st, own = _status(status, eager_check, table.device)
     dt_, di, dv = desc(table), desc(idx.contiguous()), desc(values)
-    check(lib().vbt_b200_index_put_rows(dt_.ref, di.ref, dv.ref, int(accumulate), policy,
-                                        st.ptr if st else None, stream_ptr(table)))
+    if deterministic is None:
+        deterministic = accumulate and table.dtype in (torch.int64, torch.int32) and idx.numel() >= (1 << 16)
+    if accumulate and deterministic:
+        nbytes = lib().vbt_b200_index_put_rows_sorted_workspace_bytes(idx.numel())
+        ws = _workspace(nbytes, table.device)
+        check(lib().vbt_b200_index_put_rows_sorted(dt_.ref, di.ref, dv.ref, policy, st.ptr if st else None,
+                                                   ctypes.c_void_p(ws.data_ptr()) if ws is not None else None,
+                                                   nbytes, stream_ptr(table)))
+    else:
+        check(lib().vbt_b200_index_put_rows(dt_.ref, di.ref, dv.ref, int(accumulate), policy,
+                                            st.ptr if st else None, stream_ptr(table)))
     if own:
         st.check("index_put_", table.shape[0])
     return table
