@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(kThreads) scatter_add_rows_kernel(const __grid
   const int lane = t & 31, w = t >> 5;
   const int e_begin = w * 32;
   const int64_t row_bytes = static_cast<int64_t>(p.cpr) * 16;
-  constexpr int U = K >= 4 ? 2 : 4;  // entries in flight per warp; bounded by registers
+  constexpr int U = 4;  // entries in flight per warp
   for (uint32_t cb = 0; cb < p.cpr; cb += 32 * K) {  // column block of 32*K chunks
     acc_t acc[K];
 #pragma unroll
@@ -753,8 +753,7 @@ void launch_sorted(const SortedScatterParams& p, cudaStream_t s) {
   const int64_t slices = (p.N + 31) / 32;
   const unsigned g = static_cast<unsigned>((slices + kThreads / 32 - 1) / (kThreads / 32));
   if (p.cpr <= 32) scatter_add_sorted_kernel<T, 1><<<g, kThreads, 0, s>>>(p);
-  else if (p.cpr <= 64) scatter_add_sorted_kernel<T, 2><<<g, kThreads, 0, s>>>(p);
-  else scatter_add_sorted_kernel<T, 4><<<g, kThreads, 0, s>>>(p);
+  else scatter_add_sorted_kernel<T, 2><<<g, kThreads, 0, s>>>(p);
 }
 
 vbt_b200_status scatter_add_rows_sorted(const char* name, const vbt_b200_tensor* table,

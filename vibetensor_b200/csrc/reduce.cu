@@ -17,6 +17,8 @@
 // No floating-point atomics anywhere: for a given shape the order of additions is fixed,
 // so results repeat bit for bit from run to run.  There are no spin waits either -- the
 // cross-block fold is done by whichever block draws the last ticket.
+#include <cooperative_groups.h>
+
 #include <cfloat>
 #include <climits>
 #include <mutex>
@@ -428,6 +430,74 @@ __global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ C
   }
 }
 
+// COL through a thread-block cluster: the blocks that split R for one column tile form a
+// cluster (2..16 blocks along grid.y) and fold their partials through distributed shared
+// memory -- no workspace, no ticket, no memset in front of the kernel.  Used for small
+// problems, where those few microseconds are a large part of the run time.
+template <class T, class R, int V>
+__global__ void __launch_bounds__(kThreads) col_cluster_kernel(const __grid_constant__ ColParams p) {
+  namespace cg = cooperative_groups;
+  using A = typename Widen<T>::type;
+  using acc_t = typename R::acc_t;
+  __shared__ acc_t smem[kWarps][32 * V + 1];
+  __shared__ acc_t part_s[32 * V];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int ct = blockIdx.x, split = blockIdx.y;
+  const int64_t a = blockIdx.z;
+  const int64_t col = (static_cast<int64_t>(ct) * 32 + lane) * V;
+  const bool active = col < p.B;
+  const T* x = static_cast<const T*>(p.x) + p.outer.offset(static_cast<uint32_t>(a)) + col;
+  const int64_t r0 = static_cast<int64_t>(split) * p.chunk;
+  const int64_t r1 = min(p.Rn, r0 + p.chunk);
+  acc_t acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = R::init();
+  if (active) {
+    constexpr int U = 8;
+    int64_t r = r0 + w;
+    for (; r + (U - 1) * kWarps < r1; r += U * kWarps) {
+      A v[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u) load_widen<T, V>(x + (r + u * kWarps) * p.S, v[u]);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < V; ++j) R::accum(acc[j], v[u][j], static_cast<typename R::idx_t>(r + u * kWarps));
+    }
+    for (; r < r1; r += kWarps) {
+      A v[V];
+      load_widen<T, V>(x + r * p.S, v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) R::accum(acc[j], v[j], static_cast<typename R::idx_t>(r));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) smem[w][lane * V + j] = acc[j];
+  __syncthreads();
+  const int ncols = 32 * V;
+  const int c = threadIdx.x;
+  const int64_t gcol = static_cast<int64_t>(ct) * ncols + c;
+  const bool owner = c < ncols && gcol < p.B;
+  if (c < ncols) {
+    acc_t colacc = R::init();
+    if (owner) {
+#pragma unroll
+      for (int ww = 0; ww < kWarps; ++ww) colacc = R::combine(colacc, smem[ww][c]);
+    }
+    part_s[c] = colacc;
+  }
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();  // every block's part_s is complete and visible cluster-wide
+  if (cluster.block_rank() == 0 && owner) {
+    acc_t f = R::init();
+    const unsigned nb = cluster.num_blocks();
+    for (unsigned r = 0; r < nb; ++r) f = R::combine(f, cluster.map_shared_rank(part_s, r)[c]);  // chunk order
+    const T* first_p = static_cast<const T*>(p.x) + p.outer.offset(static_cast<uint32_t>(a)) + gcol;
+    finalize<R, A>(p.o, a * p.B + gcol, f, widen(*first_p));
+  }
+  cluster.sync();  // nobody leaves while block 0 may still read its shared memory
+}
+
 // ------------------------------------------------------------------------------------
 // GENERIC kernel: one warp per output
 // ------------------------------------------------------------------------------------
@@ -475,6 +545,7 @@ struct Plan {
   int splits{1};
   int64_t chunk{0};
   int ctiles{0};
+  int cluster{0};  // COL: > 1 = fold R-chunks inside a thread-block cluster of this many blocks
   int V{1};
   size_t ws_partial_bytes{0}, ws_counter_bytes{0};
   int64_t out_sizes[kMaxDims]{};
@@ -606,6 +677,14 @@ vbt_b200_status make_plan(int op, const vbt_b200_tensor& self, const int64_t* di
       if (splits > 1) {
         pl->ws_partial_bytes = static_cast<size_t>(A) * pl->ctiles * splits * ncols * ab;
         pl->ws_counter_bytes = static_cast<size_t>(A) * pl->ctiles * 4;
+        // up to 256 MiB of input and enough column tiles to fill the GPU with clusters of
+        // <= 16 blocks: take the cluster path (the workspace stays sized as the fallback)
+        const int64_t bytes = pl->nout * Rn * es;
+        if (bytes <= (int64_t{256} << 20) && Rn >= 512) {
+          int cl = 16;
+          while (cl > 2 && static_cast<int64_t>(pl->ctiles) * A * cl > int64_t{sms} * 5) cl >>= 1;
+          if (static_cast<int64_t>(pl->ctiles) * A * cl >= sms) pl->cluster = cl;
+        }
       }
       return VBT_B200_OK;
     }
@@ -666,6 +745,35 @@ vbt_b200_status launch(const Plan& pl, const vbt_b200_tensor& self, const OutSpe
     p.chunk = pl.chunk;
     p.ctiles = pl.ctiles;
     p.o = o;
+    if (pl.cluster > 1) {
+      // small problem: fold the R-chunks inside a cluster instead of through the workspace
+      p.splits = pl.cluster;
+      p.chunk = (p.Rn + pl.cluster - 1) / pl.cluster;
+      auto kern = pl.V > 1 ? col_cluster_kernel<T, R, VMAX> : col_cluster_kernel<T, R, 1>;
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(static_cast<unsigned>(pl.ctiles), static_cast<unsigned>(pl.cluster), static_cast<unsigned>(p.A));
+      cfg.blockDim = dim3(kThreads);
+      cfg.stream = s;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = static_cast<unsigned>(pl.cluster);
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      bool ok = true;
+      if (pl.cluster > 8)
+        ok = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+      int max_clusters = 0;
+      ok = ok && cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) == cudaSuccess && max_clusters > 0;
+      if (ok) {
+        VB_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+        return VBT_B200_OK;
+      }
+      cudaGetLastError();  // this device cannot co-schedule such a cluster: use the workspace path
+      p.splits = pl.splits;
+      p.chunk = pl.chunk;
+    }
     if (pl.splits > 1) {
       p.ws_partials = ws;
       p.ws_counters = reinterpret_cast<unsigned*>(static_cast<char*>(ws) + pl.ws_partial_bytes);

@@ -36,6 +36,7 @@ struct RowParams {
   int64_t cols;
   int64_t x_row_stride;  // elements
   float eps;
+  int gamma_smem;  // block kernel: gamma staged in dynamic shared memory (cols floats)
 };
 
 template <class T> __device__ __forceinline__ float fast_exp(float x) {
@@ -207,15 +208,21 @@ __global__ void __launch_bounds__(256) rowop_group_kernel(const __grid_constant_
   }
 }
 
-// THREADS threads per row, persistent over rows.  gamma is re-read per row (it stays in L1)
-// rather than pinned in registers: with 32 values per thread it would halve the occupancy.
+// THREADS threads per row, persistent over rows.  gamma is staged once per block in shared
+// memory (pinned in registers, 32 values per thread would halve the occupancy; re-read from
+// L1/L2 per row it puts a global-load latency into every row's epilogue).
 template <class T, int KIND, int THREADS, int VPL>
 __global__ void __launch_bounds__(THREADS) rowop_block_kernel(const __grid_constant__ RowParams p) {
   constexpr int V = 16 / sizeof(T);
   constexpr int kWarps = THREADS / 32;
   __shared__ float red[2][kWarps];
+  extern __shared__ __align__(16) float gamma_s[];
   const int t = threadIdx.x;
   const int nvec = static_cast<int>(p.cols / V);
+  if (KIND == K_RMSNORM && p.gamma_smem) {
+    for (int64_t j = t; j < p.cols; j += THREADS) gamma_s[j] = p.gamma[j];
+    __syncthreads();
+  }
   float ones[VPL][V];
 #pragma unroll
   for (int k = 0; k < VPL; ++k)
@@ -241,13 +248,14 @@ __global__ void __launch_bounds__(THREADS) rowop_block_kernel(const __grid_const
                            [&](float a) { return block_fold(a, false); }, &inv);
     if constexpr (KIND == K_RMSNORM) {
       if (p.gamma) {
+        const float* gsrc = p.gamma_smem ? gamma_s : p.gamma;
 #pragma unroll
         for (int k = 0; k < VPL; ++k) {
           if (!valid[k]) continue;
-          const float4* gp = reinterpret_cast<const float4*>(p.gamma + static_cast<int64_t>(t + k * THREADS) * V);
+          const float4* gp = reinterpret_cast<const float4*>(gsrc + static_cast<int64_t>(t + k * THREADS) * V);
 #pragma unroll
           for (int q = 0; q < V / 4; ++q) {
-            const float4 gq = __ldg(gp + q);
+            const float4 gq = gp[q];
             v[k][4 * q + 0] *= gq.x; v[k][4 * q + 1] *= gq.y;
             v[k][4 * q + 2] *= gq.z; v[k][4 * q + 3] *= gq.w;
           }
@@ -329,15 +337,32 @@ vbt_b200_status launch_rowop(const RowParams& p, cudaStream_t s, int device) {
 #define VB_GROUP(G, VPL, RPG)                                                                 \
   rowop_group_kernel<T, KIND, G, VPL, RPG>                                                    \
       <<<grid((p.rows + (256 / G) * RPG - 1) / ((256 / G) * RPG), 8), 256, 0, s>>>(p)
-#define VB_BLOCK(TH, VPL, PER_SM) rowop_block_kernel<T, KIND, TH, VPL><<<grid(p.rows, PER_SM), TH, 0, s>>>(p)
-  // short rows: few lanes per row and several vectors per lane keep the shuffle trees short
-  if (nvec <= 8) VB_GROUP(2, 4, 2);
-  else if (nvec <= 16) VB_GROUP(4, 4, 2);
-  else if (nvec <= 32) VB_GROUP(8, 4, 2);
-  else if (nvec <= 64) VB_GROUP(16, 4, 2);
-  else if (nvec <= 128) VB_GROUP(32, 4, 1);
-  else if (nvec <= 256) VB_BLOCK(128, 2, 16);
-  else if (nvec <= 512) VB_BLOCK(256, 2, 8);
+#define VB_BLOCK(TH, VPL, PER_SM) rowop_block_kernel<T, KIND, TH, VPL><<<grid(p.rows, PER_SM), TH, gsmem, s>>>(pp)
+  // rmsnorm's gamma goes to shared memory in the block kernels when it fits the default 48 KB
+  RowParams pp = p;
+  size_t gsmem = 0;
+  if (KIND == K_RMSNORM && p.gamma != nullptr && p.cols * 4 <= 40 * 1024) {
+    pp.gamma_smem = 1;
+    gsmem = static_cast<size_t>(p.cols) * 4;
+  }
+  // short rows: a few lanes per row with several vectors each keep the shuffle trees short;
+  // the register budget (vectors per lane x rows in flight) is set per element width
+  if constexpr (V == 4) {
+    if (nvec <= 8) VB_GROUP(2, 4, 2);
+    else if (nvec <= 16) VB_GROUP(4, 4, 2);
+    else if (nvec <= 32) VB_GROUP(8, 4, 2);
+    else if (nvec <= 64) VB_GROUP(16, 4, 2);
+    else if (nvec <= 128) VB_GROUP(32, 4, 1);
+  } else {
+    if (nvec <= 8) VB_GROUP(4, 2, 2);
+    else if (nvec <= 16) VB_GROUP(8, 2, 2);
+    else if (nvec <= 32) VB_GROUP(16, 2, 2);
+    else if (nvec <= 64) VB_GROUP(32, 2, 2);
+    else if (nvec <= 128) VB_GROUP(32, 4, 1);
+  }
+  if (nvec <= 128) {
+  } else if (nvec <= 256) VB_BLOCK(128, 2, 16);
+  else if (nvec <= 512) VB_BLOCK(128, 4, 16);
   else if (nvec <= 1024) VB_BLOCK(256, 4, 8);
   else if (nvec <= 2048) VB_BLOCK(256, 8, 8);
   else rowop_stream_kernel<T, KIND><<<grid(p.rows, 8), 256, 0, s>>>(p);
