@@ -218,7 +218,7 @@ def time_op(torch, fn, iters, warm=3, graph=True):
     return s.elapsed_time(e) / iters, "eager loop"
 
 
-def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4")):
+def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4", "ew")):
     """Returns a list of {op, config, bytes, elements, ms, gbs, frac_measured, frac_8tbs}.
     Inputs smaller than L2 are rotated over enough distinct buffers to exceed it."""
     import numpy as np
@@ -315,7 +315,50 @@ def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4")):
         ms = time_op(torch, lambda i: ops.where_gt0_addcmul(a, b, c, out=outv), 5)
         add("where(a>0, a+b*c, 0) fused", f"C3 bf16 a[{n0},1,512,1] b[1,128,1,1024] c[{n0},128,1,1024] -> transpose(1,3) view",
             n * 2 + (a.numel() + b.numel() + c.numel()) * 2, n, ms)
+        # the same expression as the reference has to run it: four launches with dense
+        # temporaries (b*c is [n0,128,1,1024]; a + t1, a > 0 and the result are full size)
+        if not small:
+            zero = torch.zeros(1, device=dev, dtype=torch.bfloat16)
+            shp = (n0, 128, 512, 1024)
+            t1 = torch.empty((n0, 128, 1, 1024), device=dev, dtype=torch.bfloat16)
+            t2 = torch.empty(shp, device=dev, dtype=torch.bfloat16)
+            m = torch.empty((n0, 1, 512, 1), device=dev, dtype=torch.bool)
+
+            def chain(i):
+                ops.mul(b, c, out=t1)
+                ops.add(a, t1, out=t2)
+                ops.gt(a, zero, out=m)
+                ops.where(m, t2, zero, out=outv)
+            ms = time_op(torch, chain, 3)
+            moved = 2 * t1.numel() * 2 + 3 * n * 2   # t1 written + read, t2 written + read, out written
+            add("mul -> add -> gt -> where (4 launches)", "C3 bf16, same inputs, one launch per vt:: op",
+                moved, n, ms, launches=4,
+                note="bytes = traffic of the four launches (t2 written, t2 read, out written); same result as the fused op")
+            del t1, t2, m
         del base, outv
+    if "ew" in which:
+        nE = 1 << 28
+        x = torch.randn(nE, device=dev)
+        y = torch.randn(nE, device=dev)
+        o = torch.empty_like(x)
+        for name, fn, nb in (("add fp32 dense", lambda i: ops.add(x, y, out=o), 12 * nE),
+                             ("relu fp32 dense", lambda i: ops.relu(x, out=o), 8 * nE),
+                             ("gelu fp32 dense", lambda i: ops.gelu(x, out=o), 8 * nE),
+                             ("add fp32, host scalar operand", lambda i: ops.add(x, 1.5, out=o), 8 * nE)):
+            ms = time_op(torch, fn, 10)
+            add(name, f"[{nE}] contiguous", nb, nE, ms)
+        xb, yb = x.bfloat16(), y[: 1 << 14].bfloat16()
+        ob = torch.empty_like(xb)
+        ms = time_op(torch, lambda i: ops.mul(xb.view(-1, 1 << 14), yb, out=ob.view(-1, 1 << 14)), 10)
+        add("mul bf16, row-broadcast operand", f"[{nE >> 14},16384] * [16384]", 4 * nE, nE, ms)
+        cm = x > 0
+        ms = time_op(torch, lambda i: ops.where(cm, x, y, out=o), 10)
+        add("where fp32 dense", f"[{nE}] contiguous, bool condition", 13 * nE, nE, ms)
+        xt = x.view(1 << 14, 1 << 14)
+        ot = torch.empty_like(xt)
+        ms = time_op(torch, lambda i: ops.copy_(ot, xt.t()), 10)
+        add("contiguous() of a transposed view", "[16384,16384] fp32 transpose -> dense", 8 * nE, nE, ms)
+        del x, y, o, xb, yb, ob, cm, xt, ot
     torch.cuda.empty_cache()
     return res
 
@@ -405,6 +448,53 @@ def run_ours(args):
     rel = abs(result.double().item() - truth.item()) / scale.item()
     assert rel <= 1e-5, f"sharded sum off by {rel:.3e} of sum|x|"
 
+    # ---- the other sharded reductions of the configuration: amax over the same tensor and
+    # mean(dim=0) over a [1,048,576 x 4096] bf16 tensor split by rows (fp32 column partials,
+    # one 16 KiB all-reduce, divide by the global row count, cast)
+    sharded = []
+
+    def timed(fn, steps):
+        for _ in range(3):
+            fn()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        tt = torch.tensor([a.elapsed_time(b) / steps], device=dev, dtype=torch.float64)
+        if n > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return tt.item()
+
+    if not args.no_sharded_extras:
+        k = max(1, min(args.steps, 10))
+        ms = timed(lambda: fabric.amax(ft), k)
+        gmax = shard.max()
+        if n > 1:
+            dist.all_reduce(gmax, op=dist.ReduceOp.MAX)
+        assert fabric.amax(ft).item() == gmax.item(), "sharded amax mismatch"
+        sharded.append({"op": "amax", "tensor": f"[{TOTAL_ELEMS}] fp32", "ms_per_step": ms,
+                        "elements_per_s": TOTAL_ELEMS / (ms * 1e-3), "gb_per_s_whole_job": TOTAL_ELEMS * 4 / (ms * 1e-3) / 1e9})
+        rows_total, cols = (1 << 20) * TOTAL_ELEMS // (1 << 32), 4096
+        rows = rows_total // n
+        xb = torch.empty((rows, cols), device=dev, dtype=torch.bfloat16)
+        for o in range(0, rows, 1 << 14):
+            xb[o:o + (1 << 14)].normal_(generator=g)
+        fb = fabric.FabricTensor.sharded_1d_row(mesh, xb)
+        ms = timed(lambda: fabric.mean(fb, dim=0), k)
+        mcol = fabric.mean(fb, dim=0)
+        ref_col = xb.float().sum(0)
+        if n > 1:
+            dist.all_reduce(ref_col)
+        ref_col = ref_col / (rows * n)
+        assert torch.allclose(mcol.float(), ref_col, rtol=1e-2, atol=1e-2), "sharded bf16 mean(dim=0) off"
+        ne = rows * n * cols
+        sharded.append({"op": "mean(dim=0)", "tensor": f"[{rows * n},{cols}] bf16", "ms_per_step": ms,
+                        "elements_per_s": ne / (ms * 1e-3), "gb_per_s_whole_job": ne * 2 / (ms * 1e-3) / 1e9})
+        del xb, fb
+
     # ---- e2e: the shard starts in pinned host memory every step
     e2e = None
     if not args.no_e2e:
@@ -444,6 +534,7 @@ def run_ours(args):
                                      if REDUCE_TRAFFIC_BYTES_PER_ELEM is not None else None)},
             "e2e": e2e, "gpu_launches": args.steps * n, "clocks": clocks,
             "parity": {"rel_err_vs_fp64_over_sum_abs": rel},
+            "sharded_ops": sharded,
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
@@ -534,10 +625,11 @@ def main():
     ap.add_argument("--no-suite", action="store_true", help="skip the per-op table (N = 1)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-resident end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-sharded-extras", action="store_true", help="skip the sharded amax / bf16 mean(dim=0) legs")
     ap.add_argument("--suite-only", action="store_true", help="run only the per-op table")
     ap.add_argument("--suite-scale", default="full", choices=["full", "small"],
                     help="small: reduced C2/C3/C4 shapes (a few GB on the device) for profiler captures")
-    ap.add_argument("--suite-ops", default="c1,c2,c3,c4", help="which configurations the per-op table runs")
+    ap.add_argument("--suite-ops", default="c1,c2,c3,c4,ew", help="which configurations the per-op table runs")
     ap.add_argument("--elems", type=int, default=TOTAL_ELEMS,
                     help="elements of the headline tensor (default 2^32; smaller only for profiler captures)")
     args = ap.parse_args()
