@@ -190,7 +190,8 @@ VBT_B200_API vbt_b200_status vbt_b200_relu(const vbt_b200_tensor* out, const vbt
  * (innermost first) and, per operand (out first), the element strides in that order.
  * `strides` has room for noperands*VBT_B200_MAX_NDIM entries, row per operand.
  * *kernel: 0 = flat vector kernel, 1 = tiled kernel (vector along dim 0), 2 = tiled
- * scalar kernel.  *pieces: number of 32-bit-safe launches the call is split into. */
+ * scalar kernel, 3 = shared-memory transposing kernel (an input is contiguous along another
+ * dim than the output).  *pieces: number of 32-bit-safe launches the call is split into. */
 VBT_B200_API vbt_b200_status vbt_b200_ti_plan(const vbt_b200_tensor* const* operands, int32_t noperands,
                                  int64_t* shape, int64_t* strides, int32_t* ndim,
                                  int32_t* kernel, int32_t* pieces);

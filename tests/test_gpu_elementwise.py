@@ -312,3 +312,31 @@ def test_large_dim_over_2_31_elements_linearity(ops):
     rs = out[::4096].float().sum(1).cpu().numpy()
     ai = (np.arange(n0)[::4096] % 7).astype(np.float64)
     np.testing.assert_array_equal(rs, n1 * ai + float((np.arange(n1) % 5).sum()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int64, torch.bool])
+@pytest.mark.parametrize("shape", [(100, 70), (33, 1000), (16, 16), (4, 50, 37), (3, 2, 64, 48)])
+def test_transposed_operands_use_the_tiled_transpose_path(ops, port, dtype, shape):
+    """contiguous() of a transposed view, an op between a tensor and its transpose, where()
+    into a transposed output: inputs contiguous along another dim than the output."""
+    rng = np.random.default_rng(41)
+    if dtype == torch.bool:
+        x = rng.integers(0, 2, shape).astype(np.uint8)
+    else:
+        x = rand_storage(rng, shape, dtype)
+    t = from_np(x, dtype)
+    xt = np.swapaxes(x, -1, -2)
+    tt = t.transpose(-1, -2)
+    got = to_np(ops.contiguous(tt))
+    np.testing.assert_array_equal(got, np.ascontiguousarray(xt))
+    if dtype in (torch.float32, torch.bfloat16, torch.int64):
+        y = rand_storage(rng, xt.shape, dtype)
+        ty = from_np(y, dtype)
+        got = to_np(ops.add(ty, tt))                       # dense + transposed
+        np.testing.assert_array_equal(got, port.binary("add", y, xt, CODE[dtype]))
+        out = torch.empty(shape, dtype=dtype, device="cuda").transpose(-1, -2)
+        cond = rng.integers(0, 2, xt.shape).astype(np.uint8)
+        ops.where(from_np(cond, torch.bool), ty, tt, out=out)   # transposed output and operand
+        np.testing.assert_array_equal(to_np(out), port.where(cond, y, xt, CODE[dtype]))
+    if len(shape) == 2 and min(shape) >= 16:
+        assert ops.ti_plan(torch.empty(xt.shape, dtype=dtype, device="cuda"), tt)[2] == 3

@@ -246,6 +246,91 @@ ew_flat_kernel(const __grid_constant__ FlatParams<NIN + 1> p, const F f) {
   }
 }
 
+// Transposing variant: some inputs are contiguous along ANOTHER iteration dim than the output
+// (a transposed view copied to dense, an op between a tensor and its transpose, ...).  Read
+// straight from global memory they cost one 32-byte sector per element.  Here a block owns a
+// (32P x 32P) tile over (dim 0, dim 1 := the inputs' contiguous dim): up to two such inputs
+// are loaded along THEIR contiguous dim, P elements per lane, into shared memory; the block
+// synchronises; every warp then reads the tile transposed while it writes 32P consecutive
+// outputs along dim 0, P per lane.  P = 2 when every staged operand and the output allow
+// aligned element pairs, else 1.  Inputs not in `tmask` are read directly with their strides.
+constexpr int kTrMaxStaged = 2;
+template <class F, class TO, class T1, class T2, class T3, int NIN, int P>
+__global__ void __launch_bounds__(kEwThreads)
+ew_transpose_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, const int tmask) {
+  constexpr int TILE = 32 * P;
+  constexpr int PITCH = TILE + 2;  // even, so element pairs stay aligned
+  constexpr int kMaxEs = sizeof(T1) > sizeof(T2) ? (sizeof(T1) > sizeof(T3) ? sizeof(T1) : sizeof(T3))
+                                                 : (sizeof(T2) > sizeof(T3) ? sizeof(T2) : sizeof(T3));
+  __shared__ __align__(16) unsigned char sm[kTrMaxStaged][TILE * PITCH * kMaxEs];
+  uint32_t b = blockIdx.x, t0, t1;
+  p.div_t0.divmod(b, b, t0);
+  p.div_t1.divmod(b, b, t1);
+  int64_t base[NIN + 1];
+#pragma unroll
+  for (int k = 0; k <= NIN; ++k) base[k] = 0;
+  for (int d = 0; d < p.n_outer; ++d) {
+    uint32_t c;
+    p.odiv[d].divmod(b, b, c);
+#pragma unroll
+    for (int k = 0; k <= NIN; ++k) base[k] += static_cast<int64_t>(c) * p.so[k][d];
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int64_t i0 = static_cast<int64_t>(t0) * TILE, j0 = static_cast<int64_t>(t1) * TILE;
+  const int64_t size0 = p.n0v;  // elements along dim 0
+  // shared-memory slot of each staged input (first staged -> slot 0, second -> slot 1)
+  const int slot1 = 0, slot2 = (tmask & 1) ? 1 : 0, slot3 = ((tmask & 1) ? 1 : 0) + ((tmask & 2) ? 1 : 0);
+  T1* s1 = reinterpret_cast<T1*>(sm[slot1]);
+  T2* s2 = reinterpret_cast<T2*>(sm[slot2 < kTrMaxStaged ? slot2 : 0]);
+  T3* s3 = reinterpret_cast<T3*>(sm[slot3 < kTrMaxStaged ? slot3 : 0]);
+  const T1* g1 = reinterpret_cast<const T1*>(p.ptr[1]) + base[1];
+  const T2* g2 = reinterpret_cast<const T2*>(p.ptr[NIN >= 2 ? 2 : 0]) + base[NIN >= 2 ? 2 : 0];
+  const T3* g3 = reinterpret_cast<const T3*>(p.ptr[NIN >= 3 ? 3 : 0]) + base[NIN >= 3 ? 3 : 0];
+  const int64_t a0 = p.s0[1], a1 = p.s1[1];
+  const int64_t b0 = p.s0[NIN >= 2 ? 2 : 0], b1 = p.s1[NIN >= 2 ? 2 : 0];
+  const int64_t c0 = p.s0[NIN >= 3 ? 3 : 0], c1 = p.s1[NIN >= 3 ? 3 : 0];
+  // stage: a warp reads 32P consecutive elements along dim 1 (stride 1 for staged inputs)
+#pragma unroll
+  for (int r = 0; r < TILE / 8; ++r) {
+    const int il = w + 8 * r;
+    const int64_t i = i0 + il, j = j0 + lane * P;
+    if (i < size0 && j < p.size1) {  // size1 % P == 0 when P == 2
+      if (tmask & 1)
+        *reinterpret_cast<Vec<T1, P>*>(s1 + il * PITCH + lane * P) = *reinterpret_cast<const Vec<T1, P>*>(g1 + i * a0 + j);
+      if constexpr (NIN >= 2) {
+        if (tmask & 2)
+          *reinterpret_cast<Vec<T2, P>*>(s2 + il * PITCH + lane * P) = *reinterpret_cast<const Vec<T2, P>*>(g2 + i * b0 + j);
+      }
+      if constexpr (NIN >= 3) {
+        if (tmask & 4)
+          *reinterpret_cast<Vec<T3, P>*>(s3 + il * PITCH + lane * P) = *reinterpret_cast<const Vec<T3, P>*>(g3 + i * c0 + j);
+      }
+    }
+  }
+  __syncthreads();
+  // compute and store: a warp writes 32P consecutive elements along dim 0, P per lane
+  TO* go = reinterpret_cast<TO*>(p.ptr[0]) + base[0];
+#pragma unroll
+  for (int r = 0; r < TILE / 8; ++r) {
+    const int jl = w + 8 * r;
+    const int64_t i = i0 + lane * P, j = j0 + jl;
+    if (i < size0 && j < p.size1) {  // size0 % P == 0 when P == 2
+      Vec<TO, P> o;
+#pragma unroll
+      for (int e = 0; e < P; ++e) {
+        const int il = lane * P + e;
+        const T1 a = (tmask & 1) ? s1[il * PITCH + jl] : g1[(i + e) * a0 + j * a1];
+        T2 bb{};
+        T3 c{};
+        if constexpr (NIN >= 2) bb = (tmask & 2) ? s2[il * PITCH + jl] : g2[(i + e) * b0 + j * b1];
+        if constexpr (NIN >= 3) c = (tmask & 4) ? s3[il * PITCH + jl] : g3[(i + e) * c0 + j * c1];
+        o.v[e] = f(a, bb, c);
+      }
+      *reinterpret_cast<Vec<TO, P>*>(go + i * p.s0[0] + j * p.s1[0]) = o;  // s0[0] == 1 when P == 2
+    }
+  }
+}
+
 // Host: picks the kernel for the plan and launches it.  INV_SPECIAL >= 0 additionally
 // instantiates the tiled vector kernel for that compile-time invariance mask and uses it
 // when the plan's strides match it.
@@ -278,6 +363,77 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
     return VBT_B200_OK;
   }
 
+  {
+    int dimj = -1;
+    const int tmask = transpose_candidates(plan, &dimj);
+    if (tmask != 0) {
+      TiPlan tpl = plan;  // make the partner dim dim 1
+      if (dimj != 1) {
+        std::swap(tpl.shape[1], tpl.shape[dimj]);
+        for (int k = 0; k <= NIN; ++k) std::swap(tpl.stride[k][1], tpl.stride[k][dimj]);
+      }
+      TiledParams<NIN + 1> tp{};
+      const int nd = tpl.ndim;
+      int64_t outer = 1;
+      for (int k = 0; k <= NIN; ++k) {
+        tp.ptr[k] = tpl.ptr[k];
+        tp.s0[k] = tpl.stride[k][0];
+        tp.s1[k] = tpl.stride[k][1];
+        for (int d = 2; d < nd; ++d) tp.so[k][d - 2] = tpl.stride[k][d];
+      }
+      tp.n_outer = nd - 2;
+      for (int d = 2; d < nd; ++d) {
+        VB_ARG(tpl.shape[d] <= 0x7fffffff, "elementwise: dim too large");
+        tp.odiv[d - 2] = FastDiv(static_cast<uint32_t>(tpl.shape[d]));
+        outer *= tpl.shape[d];
+      }
+      // element pairs: every staged input and the output must keep pairs aligned
+      auto pair_ok = [&](int k, bool along1) {
+        const int es = tpl.esize[k];
+        if (es > 4) return false;
+        if (reinterpret_cast<uintptr_t>(tpl.ptr[k]) % (2 * es)) return false;
+        for (int d = 0; d < nd; ++d) {
+          const bool unit = along1 ? d == 1 : d == 0;
+          if (unit ? tpl.stride[k][d] != 1 : (tpl.stride[k][d] % 2 != 0)) return false;
+        }
+        return true;
+      };
+      bool pairs = sizeof(TO) <= 4 && sizeof(T1) <= 4 && (NIN < 2 || sizeof(T2) <= 4) && (NIN < 3 || sizeof(T3) <= 4) &&
+                   tpl.shape[0] % 2 == 0 && tpl.shape[1] % 2 == 0 && pair_ok(0, false);
+      int staged = 0, use_mask = 0;
+      for (int k = 1; k <= NIN; ++k)
+        if ((tmask >> (k - 1)) & 1) {
+          if (staged == kTrMaxStaged) continue;  // a third transposed input is read directly
+          ++staged;
+          use_mask |= 1 << (k - 1);
+          pairs = pairs && pair_ok(k, true);
+        }
+      const int tile = pairs ? 64 : 32;
+      const int64_t tiles0 = (tpl.shape[0] + tile - 1) / tile;
+      const int64_t tiles1 = (tpl.shape[1] + tile - 1) / tile;
+      const int64_t blocks = tiles0 * tiles1 * outer;
+      if (blocks <= 0x7fffffff && tpl.shape[0] <= 0x7fffffff) {
+        constexpr bool kPairTypes = sizeof(TO) <= 4 && sizeof(T1) <= 4 && (NIN < 2 || sizeof(T2) <= 4) &&
+                                    (NIN < 3 || sizeof(T3) <= 4);
+        if constexpr (kPairTypes) if (pairs) {
+          tp.div_t0 = FastDiv(static_cast<uint32_t>(tiles0));
+          tp.div_t1 = FastDiv(static_cast<uint32_t>(tiles1));
+          tp.n0v = static_cast<uint32_t>(tpl.shape[0]);
+          tp.size1 = tpl.shape[1];
+          ew_transpose_kernel<F, TO, T1, T2, T3, NIN, 2><<<static_cast<unsigned>(blocks), kEwThreads, 0, stream>>>(tp, f, use_mask);
+          VB_LAUNCH_CHECK();
+          return VBT_B200_OK;
+        }
+        tp.div_t0 = FastDiv(static_cast<uint32_t>(tiles0));
+        tp.div_t1 = FastDiv(static_cast<uint32_t>(tiles1));
+        tp.n0v = static_cast<uint32_t>(tpl.shape[0]);
+        tp.size1 = tpl.shape[1];
+        ew_transpose_kernel<F, TO, T1, T2, T3, NIN, 1><<<static_cast<unsigned>(blocks), kEwThreads, 0, stream>>>(tp, f, use_mask);
+        VB_LAUNCH_CHECK();
+        return VBT_B200_OK;
+      }
+    }
+  }
   const bool vec = kind == kTiTiledVec;
   const int v = vec ? V : 1;
   TiledParams<NIN + 1> tp{};

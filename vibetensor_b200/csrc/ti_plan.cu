@@ -215,6 +215,32 @@ TiKernel choose_ti_kernel(const TiPlan& plan, int V, bool* flat_vec_ok) {
   return vec ? kTiTiledVec : kTiTiledScalar;
 }
 
+// Which inputs should go through the transposing kernel, and along which dim: an input
+// qualifies when it would have to be gathered along dim 0, is contiguous along one other
+// dim j, both extents are at least 16, and it really varies over the tensor (an input that is
+// broadcast along a long dim is better served by the register-hoisting kernel above).
+// Returns the mask (0 = none) and sets *dimj.
+int transpose_candidates(const TiPlan& plan, int* dimj) {
+  int mask = 0, jsel = -1;
+  if (plan.ndim < 2 || plan.shape[0] < 16) return 0;
+  for (int k = 1; k < plan.nops; ++k) {
+    const int64_t s0 = plan.stride[k][0];
+    if (s0 == 0 || s0 == 1 || s0 == -1) continue;
+    int j = -1;
+    bool broadcast_long = false;
+    for (int d = 1; d < plan.ndim; ++d) {
+      if (plan.stride[k][d] == 1 && plan.shape[d] >= 16 && j < 0) j = d;
+      if (plan.stride[k][d] == 0 && plan.shape[d] >= 16) broadcast_long = true;
+    }
+    if (j < 0 || broadcast_long) continue;
+    if (jsel >= 0 && j != jsel) continue;  // one partner dim per launch
+    jsel = j;
+    mask |= 1 << (k - 1);
+  }
+  *dimj = jsel;
+  return mask;
+}
+
 }  // namespace vb
 
 extern "C" {
@@ -246,6 +272,8 @@ vbt_b200_status vbt_b200_ti_plan(const vbt_b200_tensor* const* operands, int32_t
   bool flat_vec = false;
   const int V = plan.esize[0] > 0 ? 16 / std::max(plan.esize[0], plan.nops > 1 ? plan.esize[1] : 1) : 1;
   *kernel = plan.numel == 0 ? 0 : static_cast<int>(vb::choose_ti_kernel(plan, V, &flat_vec));
+  int dimj = -1;
+  if (*kernel != 0 && vb::transpose_candidates(plan, &dimj) != 0) *kernel = 3;
   *pieces = 1;
   return VBT_B200_OK;
 }

@@ -37,4 +37,8 @@ enum TiKernel { kTiFlat = 0, kTiTiledVec = 1, kTiTiledScalar = 2 };
 // vec_bytes[k] = bytes one vector of operand k spans (V * esize[k]).
 TiKernel choose_ti_kernel(const TiPlan& plan, int V, bool* flat_vec_ok);
 
+// Inputs (bit k-1 = input k) that the shared-memory transposing kernel should stage, and the
+// iteration dim they are contiguous in; 0 = use the kernels above.
+int transpose_candidates(const TiPlan& plan, int* dimj);
+
 }  // namespace vb
