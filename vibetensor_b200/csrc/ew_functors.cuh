@@ -99,9 +99,41 @@ __device__ __forceinline__ bool compare(X a, X b) {
   else return a >= b;
 }
 
+// Packed 16-bit arithmetic for add / sub / mul: one HADD2 / HMUL2 per two elements instead of
+// widen-compute-round per element.  The result is the same bits as the float route: the
+// float sum (product) of two 16-bit values is exact unless the exponents differ by more than
+// the float significand allows, and in that case both routes return the larger operand, so a
+// single rounding to 16 bits and "round to float, then to 16 bits" cannot disagree.
+template <int OP>
+__device__ __forceinline__ __nv_bfloat162 packed_math(__nv_bfloat162 a, __nv_bfloat162 b) {
+  if constexpr (OP == VBT_B200_B_ADD) return __hadd2_rn(a, b);
+  else if constexpr (OP == VBT_B200_B_SUB) return __hsub2_rn(a, b);
+  else return __hmul2_rn(a, b);
+}
+template <int OP>
+__device__ __forceinline__ __half2 packed_math(__half2 a, __half2 b) {
+  if constexpr (OP == VBT_B200_B_ADD) return __hadd2_rn(a, b);
+  else if constexpr (OP == VBT_B200_B_SUB) return __hsub2_rn(a, b);
+  else return __hmul2_rn(a, b);
+}
+template <class T> struct Packed2 { using type = void; };
+template <> struct Packed2<__nv_bfloat16> { using type = __nv_bfloat162; };
+template <> struct Packed2<__half> { using type = __half2; };
+
 template <int OP, class T>
 struct BinaryF {
   static constexpr bool kFloatMath = is_float_storage<T>::value;
+  static constexpr bool kPacked2 = sizeof(T) == 2 && is_float_storage<T>::value &&
+                                   (OP == VBT_B200_B_ADD || OP == VBT_B200_B_SUB || OP == VBT_B200_B_MUL);
+  __device__ __forceinline__ uint32_t pair(uint32_t a, uint32_t b) const {
+    using P = typename Packed2<T>::type;
+    if constexpr (kPacked2) {
+      const P r = packed_math<OP>(*reinterpret_cast<const P*>(&a), *reinterpret_cast<const P*>(&b));
+      return *reinterpret_cast<const uint32_t*>(&r);
+    } else {
+      return 0u;
+    }
+  }
   __device__ __forceinline__ float fn(float a, float b, float) const { return binary_math<OP>(a, b); }
   __device__ __forceinline__ T operator()(T a, T b, T) const {
     if constexpr (is_float_storage<T>::value) return from_f<T>(binary_math<OP>(to_f(a), to_f(b)));
@@ -151,6 +183,18 @@ struct TernaryF {
   }
   __device__ __forceinline__ T operator()(T ta, T tb, T tc) const {
     return from_f<T>(fn(to_f(ta), to_f(tb), to_f(tc)));
+  }
+  // Split form of the fused chains, fn(a, b, c) == fin(a, pre(b, c)): the kernel evaluates
+  // pre once per thread when b and c do not change along the rows it walks.
+  static constexpr bool kSplit = OP >= VBT_B200_T_ADDCMUL;
+  __device__ __forceinline__ float pre(float b, float c) const {
+    if constexpr (OP == VBT_B200_T_ADDCDIV) return to_f(from_f<T>(__fdiv_rn(b, c)));
+    else return to_f(from_f<T>(__fmul_rn(b, c)));
+  }
+  __device__ __forceinline__ float fin(float a, float t) const {
+    const float r = __fadd_rn(a, t);
+    if constexpr (OP == VBT_B200_T_WHERE_GT0_ADDCMUL) return a > 0.f ? r : 0.f;
+    else return r;
   }
 };
 

@@ -88,6 +88,16 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, __half) {
 }
 
 template <class F, class = void>
+struct has_split : std::false_type {};
+template <class F>
+struct has_split<F, std::void_t<decltype(F::kSplit)>> : std::bool_constant<F::kSplit> {};
+
+template <class F, class = void>
+struct has_packed2 : std::false_type {};
+template <class F>
+struct has_packed2<F, std::void_t<decltype(F::kPacked2)>> : std::bool_constant<F::kPacked2> {};
+
+template <class F, class = void>
 struct has_float_fn : std::false_type {};
 template <class F>
 struct has_float_fn<F, std::void_t<decltype(F::kFloatMath)>> : std::bool_constant<F::kFloatMath> {};
@@ -96,7 +106,13 @@ template <class F, class TO, class T1, class T2, class T3, int NIN, int V>
 __device__ __forceinline__ Vec<TO, V> apply_vec(const F& f, const Vec<T1, V>& a,
                                                 const Vec<T2, V>& b, const Vec<T3, V>& c) {
   Vec<TO, V> o;
-  if constexpr (has_float_fn<F>::value && sizeof(TO) == 2 && V % 2 == 0) {
+  if constexpr (has_packed2<F>::value && sizeof(TO) == 2 && sizeof(T1) == 2 && sizeof(T2) == 2 && V % 2 == 0) {
+    const uint32_t* wa = reinterpret_cast<const uint32_t*>(&a);
+    const uint32_t* wb = reinterpret_cast<const uint32_t*>(&b);
+    uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < V / 2; ++j) w[j] = f.pair(wa[j], wb[j]);
+  } else if constexpr (has_float_fn<F>::value && sizeof(TO) == 2 && V % 2 == 0) {
     // 16-bit float outputs: compute in float, round and pack two lanes per instruction
     uint32_t* w = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
@@ -116,9 +132,14 @@ __device__ __forceinline__ Vec<TO, V> apply_vec(const F& f, const Vec<T1, V>& a,
 // input); -1 = decide at run time from the strides (loads are hoisted, arithmetic is not).
 // BC0: bitmask of inputs known at compile time to be broadcast along dim 0 (only used
 // together with INV >= 0).
+// Register budget: 4 resident blocks per SM for one- and two-input ops (64 registers); below
+// that the kernel cannot cover HBM latency.  Three-input ops are left to the compiler (the
+// write-dominated fused chains run best with the registers they ask for).
 template <class F, class TO, class T1, class T2, class T3, int NIN, int V, int INV, int BC0 = 0>
-__global__ void __launch_bounds__(kEwThreads)
+__global__ void __launch_bounds__(kEwThreads, NIN >= 3 ? 1 : 4)
 ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
+  // rows in flight per thread: fewer for three-input ops and wide vectors (register budget)
+  constexpr int UNR = (NIN >= 3 && V >= 8 && INV < 0) ? 2 : kEwUnroll;
   uint32_t b = blockIdx.x, t0, t1;
   p.div_t0.divmod(b, b, t0);
   p.div_t1.divmod(b, b, t1);
@@ -166,22 +187,47 @@ ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
   if constexpr (NIN >= 2) { if (inv2) b0 = load_vec<T2, V, sp2>(p2, s02); }
   if constexpr (NIN >= 3) { if (inv3) c0 = load_vec<T3, V, sp3>(p3, s03); }
 
-  int l = 0;
-  for (; l + kEwUnroll <= n; l += kEwUnroll) {
-    Vec<T1, V> a[kEwUnroll];
-    Vec<T2, V> bb[kEwUnroll];
-    Vec<T3, V> c[kEwUnroll];
+  if constexpr (INV == 6 && NIN == 3 && has_split<F>::value && sizeof(TO) == 2 && V % 2 == 0) {
+    // inputs 2 and 3 are constant along the rows: their part of the expression is computed
+    // once, the loop only loads input 1, finishes the expression, rounds in pairs and stores
+    float t[V];
 #pragma unroll
-    for (int u = 0; u < kEwUnroll; ++u) {
-      a[u] = inv1 ? a0 : load_vec<T1, V, sp1>(p1 + (l + u) * st1, s01);
-      if constexpr (NIN >= 2) bb[u] = inv2 ? b0 : load_vec<T2, V, sp2>(p2 + (l + u) * st2, s02);
-      else bb[u] = b0;
-      if constexpr (NIN >= 3) c[u] = inv3 ? c0 : load_vec<T3, V, sp3>(p3 + (l + u) * st3, s03);
-      else c[u] = c0;
+    for (int j = 0; j < V; ++j) t[j] = f.pre(to_f(b0.v[j]), to_f(c0.v[j]));
+    auto finish = [&](const Vec<T1, V>& av, int l) {
+      Vec<TO, V> o;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < V; j += 2)
+        w[j / 2] = pack2(f.fin(to_f(av.v[j]), t[j]), f.fin(to_f(av.v[j + 1]), t[j + 1]), TO{});
+      *reinterpret_cast<Vec<TO, V>*>(po + l * so_) = o;
+    };
+    int l = 0;
+    for (; l + 8 <= n; l += 8) {  // eight rows' loads in flight, then eight stores
+      Vec<T1, V> av[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) av[u] = load_vec<T1, V, sp1>(p1 + (l + u) * st1, s01);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) finish(av[u], l + u);
+    }
+    for (; l < n; ++l) finish(load_vec<T1, V, sp1>(p1 + l * st1, s01), l);
+    return;
+  }
+  int l = 0;
+  for (; l + UNR <= n; l += UNR) {
+    Vec<T1, V> a[UNR];
+    Vec<T2, V> bb[NIN >= 2 ? UNR : 1];
+    Vec<T3, V> c[NIN >= 3 ? UNR : 1];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      if (!inv1) a[u] = load_vec<T1, V, sp1>(p1 + (l + u) * st1, s01);
+      if constexpr (NIN >= 2) { if (!inv2) bb[u] = load_vec<T2, V, sp2>(p2 + (l + u) * st2, s02); }
+      if constexpr (NIN >= 3) { if (!inv3) c[u] = load_vec<T3, V, sp3>(p3 + (l + u) * st3, s03); }
     }
 #pragma unroll
-    for (int u = 0; u < kEwUnroll; ++u) {
-      const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(f, a[u], bb[u], c[u]);
+    for (int u = 0; u < UNR; ++u) {
+      const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(
+          f, inv1 ? a0 : a[u], (NIN >= 2 && !inv2) ? bb[NIN >= 2 ? u : 0] : b0,
+          (NIN >= 3 && !inv3) ? c[NIN >= 3 ? u : 0] : c0);
       if constexpr (V == 1) po[(l + u) * so_] = o.v[0];
       else *reinterpret_cast<Vec<TO, V>*>(po + (l + u) * so_) = o;
     }
@@ -339,7 +385,7 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
   if (plan.numel == 0) return VBT_B200_OK;
   constexpr int kMaxEs = static_cast<int>(std::max({sizeof(TO), sizeof(T1), NIN >= 2 ? sizeof(T2) : size_t{1},
                                                     NIN >= 3 ? sizeof(T3) : size_t{1}}));
-  constexpr int V = 16 / kMaxEs;
+  constexpr int V = 16 / kMaxEs > 8 ? 8 : 16 / kMaxEs;  // 1-byte types: 8 lanes keep the register count sane
   bool flat_vec = false;
   const TiKernel kind = choose_ti_kernel(plan, V, &flat_vec);
   if (kind == kTiFlat) {
@@ -462,7 +508,14 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
   const int64_t tiles0 = (n0v + w0 - 1) / w0;
   // rows per block: long enough to amortise the per-block offset decode and to reuse
   // hoisted operands, short enough to leave >= ~16 blocks per SM when the tensor allows
-  int L = static_cast<int>(std::min<int64_t>(32, (size1 + R - 1) / R));
+  // rows per thread.  Long walks (32) pay when an operand that has to be GATHERED along dim 0
+  // is constant along dim 1: it is fetched once and reused for every row.  Otherwise one
+  // unrolled batch per thread is best: blocks retire quickly and the next ones start with
+  // all their loads in flight, as in the flat kernel.
+  bool reuse_gather = false;
+  for (int k = 1; k <= NIN; ++k)
+    reuse_gather = reuse_gather || (tp.s1[k] == 0 && tp.s0[k] != 0 && tp.s0[k] != 1);
+  int L = static_cast<int>(std::min<int64_t>(reuse_gather ? 32 : 8, (size1 + R - 1) / R));
   const int sms = 148;
   while (L > 4 && tiles0 * ((size1 + int64_t{R} * L - 1) / (int64_t{R} * L)) * outer < int64_t{sms} * 16) L /= 2;
   L = std::max(L, 1);
