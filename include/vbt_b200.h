@@ -367,6 +367,13 @@ VBT_B200_API vbt_b200_status vbt_b200_rmsnorm(void* out, float* inv_rms, const v
  *    INPUTS (plain loads over NVLink, as the reference's Fabric kernel does); outputs
  *    must be local.
  * ===================================================================================== */
+/* Lets kernels launched on `compute_device` load from `peer_device` memory: the step the
+ * reference performs before a cross-device fabric op (enable_peer_access_or_throw,
+ * src/vbt/cuda/fabric_elementwise.cu:255-279).  Idempotent.  RUNTIME_ERROR when the two
+ * devices have no P2P path.  Passing a peer pointer to an elementwise entry WITHOUT this
+ * (or the host framework's equivalent) is an invalid-address fault, so bindings must call it
+ * first. */
+VBT_B200_API vbt_b200_status vbt_b200_enable_peer_access(int32_t compute_device, int32_t peer_device);
 /* partial (F32/I64, dense, reduced shape) = local SUM/MAX/MIN of the shard; BF16/F16
  * shards accumulate and emit FP32.  Same workspace contract as vbt_b200_reduce. */
 VBT_B200_API vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_tensor* partial,

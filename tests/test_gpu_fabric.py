@@ -109,7 +109,10 @@ def test_elementwise_with_one_operand_in_peer_memory():
     b_np = rng.standard_normal((512, 300), dtype=np.float32)
     a = torch.from_numpy(a_np).to("cuda:0")
     b = torch.from_numpy(b_np).to("cuda:1")
-    a.add_(b.to("cuda:0") * 0)            # a device-to-device copy makes torch enable peer access
+    with pytest.raises(ValueError, match="enable_peer_access"):
+        ops.binary("add", a, b)           # refused on the host: nothing has opened GPU 1's memory yet
+    ops.enable_peer_access(0, 1)
+    ops.enable_peer_access(0, 1)          # idempotent
     torch.cuda.synchronize(0)
     torch.cuda.synchronize(1)
     port = oracle.port()

@@ -249,6 +249,32 @@ const char* vbt_b200_last_error(void) { return vb::last_error_ref().c_str(); }
 int32_t vbt_b200_version(void) { return 1000; }
 int32_t vbt_b200_compiled_arch(void) { return 100; }
 
+vbt_b200_status vbt_b200_enable_peer_access(int32_t compute_device, int32_t peer_device) {
+  using namespace vb;
+  int n = 0;
+  VB_CUDA(cudaGetDeviceCount(&n));
+  VB_ARG(compute_device >= 0 && compute_device < n && peer_device >= 0 && peer_device < n,
+         "[Fabric] enable_peer_access: device index out of range");
+  if (compute_device == peer_device) return VBT_B200_OK;
+  int can = 0;
+  VB_CUDA(cudaDeviceCanAccessPeer(&can, compute_device, peer_device));
+  VB_REQUIRE(can != 0, VBT_B200_RUNTIME_ERROR,
+             "[Fabric] device " + std::to_string(compute_device) + " cannot access device " +
+                 std::to_string(peer_device) + " memory (no P2P path)");
+  int prev = 0;
+  VB_CUDA(cudaGetDevice(&prev));
+  VB_CUDA(cudaSetDevice(compute_device));
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();  // not an error: somebody (the host framework) enabled it before
+    e = cudaSuccess;
+  }
+  cudaSetDevice(prev);
+  if (e != cudaSuccess)
+    return fail(VBT_B200_CUDA_ERROR, std::string("cudaDeviceEnablePeerAccess: ") + cudaGetErrorString(e));
+  return VBT_B200_OK;
+}
+
 vbt_b200_status vbt_b200_broadcast_shape(const vbt_b200_tensor* const* operands, int32_t n,
                                          int64_t* out_sizes, int32_t* out_ndim) {
   VB_ARG(operands && out_sizes && out_ndim && n >= 1, "broadcast_shape: null argument");

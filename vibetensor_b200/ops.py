@@ -30,10 +30,29 @@ REDUCE = ["sum", "mean", "max", "min", "prod", "argmax", "argmin"]
 INDEX_WRAP, INDEX_STRICT, INDEX_CLAMP = 0, 1, 2
 
 
+_peer_enabled: set = set()  # (compute device index, peer device index) pairs opened so far
+
+
+def enable_peer_access(compute_device: int, peer_device: int) -> None:
+    """Allow kernels on ``compute_device`` to read ``peer_device`` memory (needed before an
+    elementwise op takes an INPUT that lives on another GPU)."""
+    check(lib().vbt_b200_enable_peer_access(int(compute_device), int(peer_device)))
+    _peer_enabled.add((int(compute_device), int(peer_device)))
+
+
 def _require_cuda(*ts: torch.Tensor) -> None:
+    """All tensors on CUDA; the first one (the output, or the tensor the output is allocated
+    like) fixes the compute device, and every other tensor must live there or on a device
+    whose memory has been opened with enable_peer_access."""
+    dev0 = None
     for t in ts:
         if not isinstance(t, torch.Tensor) or not t.is_cuda:
             raise ValueError("vibetensor_b200 ops take CUDA tensors (there is no CPU path)")
+        if dev0 is None:
+            dev0 = t.device.index
+        elif t.device.index != dev0 and (dev0, t.device.index) not in _peer_enabled:
+            raise ValueError(f"operand on cuda:{t.device.index} but the op computes on cuda:{dev0}: "
+                             "call ops.enable_peer_access(compute_device, peer_device) first")
 
 
 def _alloc_out(out, shape, dtype, like):
@@ -55,7 +74,7 @@ def _bshape(*ts):
 # elementwise
 # --------------------------------------------------------------------------------------
 def unary(name: str, a: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    _require_cuda(a)
+    _require_cuda(*([out] if out is not None else []), a)
     o = _alloc_out(out, a.shape, a.dtype, a)
     do, da = desc(o), desc(a)
     check(lib().vbt_b200_unary(UNARY.index(name), do.ref, da.ref, stream_ptr(a)))
@@ -69,7 +88,7 @@ def binary(name: str, a, b, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     cmp_ = op >= BINARY.index("eq")
     a_t, b_t = isinstance(a, torch.Tensor), isinstance(b, torch.Tensor)
     if a_t and b_t:
-        _require_cuda(a, b)
+        _require_cuda(*([out] if out is not None else []), a, b)
         o = _alloc_out(out, _bshape(a, b), torch.bool if cmp_ else a.dtype, a)
         do, da, db = desc(o), desc(a), desc(b)
         check(lib().vbt_b200_binary(op, do.ref, da.ref, db.ref, stream_ptr(a)))
@@ -91,7 +110,7 @@ def binary(name: str, a, b, out: Optional[torch.Tensor] = None) -> torch.Tensor:
 
 
 def ternary(name: str, a, b, c, out=None) -> torch.Tensor:
-    _require_cuda(a, b, c)
+    _require_cuda(*([out] if out is not None else []), a, b, c)
     o = _alloc_out(out, _bshape(a, b, c), a.dtype, a)
     do, da, db, dc = desc(o), desc(a), desc(b), desc(c)
     check(lib().vbt_b200_ternary(TERNARY.index(name), do.ref, da.ref, db.ref, dc.ref, stream_ptr(a)))
@@ -99,7 +118,7 @@ def ternary(name: str, a, b, c, out=None) -> torch.Tensor:
 
 
 def where(cond, x, y, out=None) -> torch.Tensor:
-    _require_cuda(cond, x, y)
+    _require_cuda(*([out] if out is not None else []), x, cond, y)
     o = _alloc_out(out, _bshape(cond, x, y), x.dtype, x)
     do, dc, dx, dy = desc(o), desc(cond), desc(x), desc(y)
     check(lib().vbt_b200_where(do.ref, dc.ref, dx.ref, dy.ref, stream_ptr(x)))
