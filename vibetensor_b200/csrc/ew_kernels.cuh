@@ -18,6 +18,7 @@
 // operand (include/vbt/core/tensor_iterator/cuda.h:25-42).
 #pragma once
 #include <algorithm>
+#include <cstdlib>
 #include <type_traits>
 
 #include "ti_plan.h"
@@ -72,6 +73,24 @@ __device__ __forceinline__ Vec<T, V> load_vec(const T* p, int64_t s0) {
     } else {
 #pragma unroll
       for (int j = 0; j < V; ++j) r.v[j] = p[j * s0];
+    }
+  }
+  return r;
+}
+
+// stride 0 or 1 only (no gather): the form the deep-unrolled loops use
+template <class T, int V>
+__device__ __forceinline__ Vec<T, V> load_vec01(const T* p, bool unit) {
+  Vec<T, V> r;
+  if constexpr (V == 1) {
+    r.v[0] = *p;
+  } else {
+    if (unit) {
+      r = *reinterpret_cast<const Vec<T, V>*>(p);
+    } else {
+      const T x = *p;
+#pragma unroll
+      for (int j = 0; j < V; ++j) r.v[j] = x;
     }
   }
   return r;
@@ -211,6 +230,44 @@ ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
     }
     for (; l < n; ++l) finish(load_vec<T1, V, sp1>(p1 + l * st1, s01), l);
     return;
+  }
+  if constexpr (NIN <= 2 && INV < 0) {
+    // exactly one input varies along the rows (a unary op, or a binary op whose other operand
+    // is constant along them): eight rows in flight per thread.  Two separate loops so that
+    // only one eight-deep buffer is live at a time.
+    auto emit = [&](const Vec<T1, V>& av, const Vec<T2, V>& bv, int l) {
+      const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(f, av, bv, c0);
+      if constexpr (V == 1) po[l * so_] = o.v[0];
+      else *reinterpret_cast<Vec<TO, V>*>(po + l * so_) = o;
+    };
+    if (!inv1 && (NIN == 1 || inv2) && (V == 1 || s01 == 0 || s01 == 1)) {
+      const bool unit = s01 == 1;
+      int l = 0;
+      for (; l + 8 <= n; l += 8) {
+        Vec<T1, V> av[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) av[u] = load_vec01<T1, V>(p1 + (l + u) * st1, unit);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) emit(av[u], b0, l + u);
+      }
+      for (; l < n; ++l) emit(load_vec01<T1, V>(p1 + l * st1, unit), b0, l);
+      return;
+    }
+    if constexpr (NIN == 2) {
+      if (inv1 && !inv2 && (V == 1 || s02 == 0 || s02 == 1)) {
+        const bool unit = s02 == 1;
+        int l = 0;
+        for (; l + 8 <= n; l += 8) {
+          Vec<T2, V> bv[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) bv[u] = load_vec01<T2, V>(p2 + (l + u) * st2, unit);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) emit(a0, bv[u], l + u);
+        }
+        for (; l < n; ++l) emit(a0, load_vec01<T2, V>(p2 + l * st2, unit), l);
+        return;
+      }
+    }
   }
   int l = 0;
   for (; l + UNR <= n; l += UNR) {
@@ -515,7 +572,13 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
   bool reuse_gather = false;
   for (int k = 1; k <= NIN; ++k)
     reuse_gather = reuse_gather || (tp.s1[k] == 0 && tp.s0[k] != 0 && tp.s0[k] != 1);
-  int L = static_cast<int>(std::min<int64_t>(reuse_gather ? 32 : 8, (size1 + R - 1) / R));
+  int want_rows = 32;
+  (void)reuse_gather;
+  if (const char* e = std::getenv("VBT_B200_EW_ROWS_PER_THREAD")) {  // tuning knob, like the reference's VBT_* flags
+    const int v = std::atoi(e);
+    if (v >= 1 && v <= 1024) want_rows = v;
+  }
+  int L = static_cast<int>(std::min<int64_t>(want_rows, (size1 + R - 1) / R));
   const int sms = 148;
   while (L > 4 && tiles0 * ((size1 + int64_t{R} * L - 1) / (int64_t{R} * L)) * outer < int64_t{sms} * 16) L /= 2;
   L = std::max(L, 1);
