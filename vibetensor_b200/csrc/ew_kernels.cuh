@@ -411,6 +411,17 @@ ew_transpose_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, c
     }
   }
   __syncthreads();
+  // direct inputs that are constant over the whole tile (a broadcast mask, a scalar) are
+  // read once per thread instead of once per element
+  const bool k1 = !(tmask & 1) && a0 == 0 && a1 == 0;
+  const bool k2 = NIN >= 2 && !(tmask & 2) && b0 == 0 && b1 == 0;
+  const bool k3 = NIN >= 3 && !(tmask & 4) && c0 == 0 && c1 == 0;
+  T1 ka{};
+  T2 kb{};
+  T3 kc{};
+  if (k1) ka = g1[0];
+  if constexpr (NIN >= 2) { if (k2) kb = g2[0]; }
+  if constexpr (NIN >= 3) { if (k3) kc = g3[0]; }
   // compute and store: a warp writes 32P consecutive elements along dim 0, P per lane
   TO* go = reinterpret_cast<TO*>(p.ptr[0]) + base[0];
 #pragma unroll
@@ -422,11 +433,11 @@ ew_transpose_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, c
 #pragma unroll
       for (int e = 0; e < P; ++e) {
         const int il = lane * P + e;
-        const T1 a = (tmask & 1) ? s1[il * PITCH + jl] : g1[(i + e) * a0 + j * a1];
+        const T1 a = (tmask & 1) ? s1[il * PITCH + jl] : (k1 ? ka : g1[(i + e) * a0 + j * a1]);
         T2 bb{};
         T3 c{};
-        if constexpr (NIN >= 2) bb = (tmask & 2) ? s2[il * PITCH + jl] : g2[(i + e) * b0 + j * b1];
-        if constexpr (NIN >= 3) c = (tmask & 4) ? s3[il * PITCH + jl] : g3[(i + e) * c0 + j * c1];
+        if constexpr (NIN >= 2) bb = (tmask & 2) ? s2[il * PITCH + jl] : (k2 ? kb : g2[(i + e) * b0 + j * b1]);
+        if constexpr (NIN >= 3) c = (tmask & 4) ? s3[il * PITCH + jl] : (k3 ? kc : g3[(i + e) * c0 + j * c1]);
         o.v[e] = f(a, bb, c);
       }
       *reinterpret_cast<Vec<TO, P>*>(go + i * p.s0[0] + j * p.s1[0]) = o;  // s0[0] == 1 when P == 2
