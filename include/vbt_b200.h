@@ -80,7 +80,8 @@ typedef struct vbt_b200_tensor {
  *    `out` is written in place and may be ANY strided view whose shape equals the
  *    broadcast of the inputs (the reference always allocates a dense output,
  *    cuda_elementwise.cu:96-110; a binding passes that allocation here).  Inputs must all
- *    have out's dtype, except: comparison ops write BOOL, `where` takes a BOOL condition.
+ *    have out's dtype, except: comparison, logical and predicate ops write BOOL, `where` takes
+ *    a BOOL condition.
  *    No type promotion, as in the reference (:2887).
  * ===================================================================================== */
 
@@ -115,6 +116,27 @@ enum vbt_b200_unary_op {
   VBT_B200_U_SOFTPLUS,   /* thresholds +-20 (:892-900)                                    */
   VBT_B200_U_RELU6,
   VBT_B200_U_HARDTANH,
+  /* the rest of the reference's unary table (:808-1252, :1279-1287); floating inputs only
+   * unless noted, computed in fp32 where the reference writes fp64                        */
+  VBT_B200_U_EXP2, VBT_B200_U_LOG2, VBT_B200_U_LOG10, VBT_B200_U_SINH, VBT_B200_U_COSH,
+  VBT_B200_U_ASINH, VBT_B200_U_ACOSH, VBT_B200_U_ATANH, VBT_B200_U_TAN, VBT_B200_U_ASIN,
+  VBT_B200_U_ACOS, VBT_B200_U_ATAN, VBT_B200_U_ERF, VBT_B200_U_ERFC, VBT_B200_U_LGAMMA,
+  VBT_B200_U_SINC,       /* sin(pi x)/(pi x), sinc(0)=1 (:817-824)                         */
+  VBT_B200_U_FRAC,       /* modf fraction, keeps the sign of x (:808-815)                  */
+  VBT_B200_U_DEG2RAD, VBT_B200_U_RAD2DEG,
+  VBT_B200_U_MISH,       /* x*tanh(softplus(x)), threshold 20 (:901-908)                   */
+  VBT_B200_U_SELU, VBT_B200_U_ELU,   /* alpha = 1; vt::celu is the same functor (:909-930) */
+  VBT_B200_U_HARDSIGMOID,            /* clamp(x/6 + 0.5, 0, 1)                             */
+  VBT_B200_U_HARDSHRINK, VBT_B200_U_SOFTSHRINK,  /* lambda = 0.5 (:931-948)                */
+  VBT_B200_U_LOGIT,      /* log(x/(1-x)) (:1279-1287)                                      */
+  VBT_B200_U_ANGLE,      /* NaN -> NaN, x<0 -> pi, else 0 (:843-850)                       */
+  VBT_B200_U_POSITIVE,   /* identity; also INT64 (vt::conj_physical is the same)           */
+  VBT_B200_U_SGN,        /* sign with sgn(NaN)=0; also INT64 (:832-838)                    */
+  VBT_B200_U_NAN_TO_NUM, /* F32 only: NaN->0, +-inf->+-FLT_MAX (:1556-1572)                */
+  /* predicates: out dtype BOOL; input F32/F16/BF16/I64/BOOL (:1043-1149, :1995-2100)      */
+  VBT_B200_U_ISFINITE, VBT_B200_U_ISINF, VBT_B200_U_ISNAN, VBT_B200_U_ISNEGINF,
+  VBT_B200_U_ISPOSINF, VBT_B200_U_SIGNBIT, VBT_B200_U_LOGICAL_NOT,
+  VBT_B200_U_BITWISE_NOT, /* I64/I32: ~a; BOOL: logical not (:3498-3506)                   */
   VBT_B200_U_COUNT
 };
 
@@ -133,6 +155,27 @@ enum vbt_b200_binary_op {
   VBT_B200_B_GT,
   VBT_B200_B_LE,
   VBT_B200_B_GE,
+  /* floating dtypes only unless noted (:307-589, :851-876, :1253-1258, :3526-3640)        */
+  VBT_B200_B_POW,        /* powf; vt::float_power is the same functor                      */
+  VBT_B200_B_FMOD,       /* also INT64: b==0 -> 0, INT64_MIN % -1 -> 0 (:307-334)          */
+  VBT_B200_B_REMAINDER,  /* sign of the divisor; also INT64 (:336-377)                     */
+  VBT_B200_B_ATAN2, VBT_B200_B_COPYSIGN, VBT_B200_B_HYPOT,
+  VBT_B200_B_XLOGY, VBT_B200_B_XLOG1PY,  /* x == 0 -> 0 even for NaN y                     */
+  VBT_B200_B_LOGADDEXP, VBT_B200_B_LOGADDEXP2, VBT_B200_B_NEXTAFTER,
+  VBT_B200_B_HEAVISIDE,  /* also INT64                                                     */
+  VBT_B200_B_RSUB,       /* b - a; also INT64 (:3379-3384)                                 */
+  VBT_B200_B_TANH_BACKWARD,    /* (grad, out): grad*(1-out^2)                              */
+  VBT_B200_B_SIGMOID_BACKWARD, /* (grad, out): grad*out*(1-out)                            */
+  VBT_B200_B_SILU_BACKWARD,    /* (grad, x)                                                */
+  VBT_B200_B_LOGIT_BACKWARD,   /* (grad, x): grad/(x*(1-x))                                */
+  VBT_B200_B_MSE_LOSS,   /* (a-b)^2, no reduction (:1365-1370)                             */
+  VBT_B200_B_LDEXP,      /* a * 2^int(b), exponent clamped as :463-478                     */
+  /* integer ops: dtype BOOL/I32/I64 for and/or/xor, I32/I64 for shifts, I64 for gcd/lcm;
+   * a shift count outside [0, bits) gives 0 (right shift of a negative: -1) (:191-243)    */
+  VBT_B200_B_BITWISE_AND, VBT_B200_B_BITWISE_OR, VBT_B200_B_BITWISE_XOR,
+  VBT_B200_B_LSHIFT, VBT_B200_B_RSHIFT, VBT_B200_B_GCD, VBT_B200_B_LCM,
+  /* out dtype BOOL; inputs F32/F16/BF16/I64/BOOL (:194-196, :3510-3512)                   */
+  VBT_B200_B_LOGICAL_AND, VBT_B200_B_LOGICAL_OR, VBT_B200_B_LOGICAL_XOR,
   VBT_B200_B_COUNT
 };
 
@@ -147,6 +190,8 @@ enum vbt_b200_ternary_op {
   VBT_B200_T_WHERE_GT0_ADDCMUL, /* where(a > 0, a + b*c, 0) in one launch: the chain
                             mul -> add -> gt -> where of four reference ops with the same
                             per-op rounding, so results are bit-identical to the chain   */
+  VBT_B200_T_HUBER_LOSS,     /* (input, target, delta), elementwise (:1385-1395)         */
+  VBT_B200_T_SMOOTH_L1_LOSS, /* (input, target, beta) (:1397-1407)                       */
   VBT_B200_T_COUNT
 };
 

@@ -31,10 +31,21 @@ NP_STORAGE = {BOOL: np.uint8, I32: np.int32, I64: np.int64, F32: np.float32, F16
 
 UNARY = ["relu", "neg", "abs", "square", "exp", "log", "sqrt", "rsqrt", "sin", "cos", "tanh",
          "sigmoid", "silu", "gelu", "reciprocal", "sign", "floor", "ceil", "trunc", "round",
-         "expm1", "log1p", "softplus", "relu6", "hardtanh"]
+         "expm1", "log1p", "softplus", "relu6", "hardtanh",
+         "exp2", "log2", "log10", "sinh", "cosh", "asinh", "acosh", "atanh", "tan", "asin", "acos",
+         "atan", "erf", "erfc", "lgamma", "sinc", "frac", "deg2rad", "rad2deg", "mish", "selu", "elu",
+         "hardsigmoid", "hardshrink", "softshrink", "logit", "angle", "positive", "sgn", "nan_to_num",
+         "isfinite", "isinf", "isnan", "isneginf", "isposinf", "signbit", "logical_not", "bitwise_not"]
+UNARY_TO_BOOL = {"isfinite", "isinf", "isnan", "isneginf", "isposinf", "signbit", "logical_not"}
 BINARY = ["add", "sub", "mul", "div", "maximum", "minimum", "fmax", "fmin", "eq", "ne", "lt",
-          "gt", "le", "ge"]
-TERNARY = ["clamp", "lerp", "threshold", "addcmul", "addcdiv", "where_gt0_addcmul"]
+          "gt", "le", "ge",
+          "pow", "fmod", "remainder", "atan2", "copysign", "hypot", "xlogy", "xlog1py", "logaddexp",
+          "logaddexp2", "nextafter", "heaviside", "rsub", "tanh_backward", "sigmoid_backward",
+          "silu_backward", "logit_backward", "mse_loss", "ldexp", "bitwise_and", "bitwise_or",
+          "bitwise_xor", "lshift", "rshift", "gcd", "lcm", "logical_and", "logical_or", "logical_xor"]
+BINARY_TO_BOOL = {"eq", "ne", "lt", "gt", "le", "ge", "logical_and", "logical_or", "logical_xor"}
+TERNARY = ["clamp", "lerp", "threshold", "addcmul", "addcdiv", "where_gt0_addcmul", "huber_loss",
+           "smooth_l1_loss"]
 REDUCE = ["sum", "mean", "max", "min", "prod", "argmax", "argmin"]
 WRAP, STRICT, CLAMP = 0, 1, 2
 
@@ -145,12 +156,12 @@ class Port:
         return out
 
     def unary(self, name, a, dtype, out=None):
-        out = self._out_like(dtype, [a], out)
+        out = self._out_like(dtype, [a], out, BOOL if name in UNARY_TO_BOOL else None)
         return self._ew(0, UNARY.index(name), dtype, out, [a])
 
     def binary(self, name, a, b, dtype, out=None):
         op = BINARY.index(name)
-        out = self._out_like(dtype, [a, b], out, BOOL if op >= BINARY.index("eq") else None)
+        out = self._out_like(dtype, [a, b], out, BOOL if name in BINARY_TO_BOOL else None)
         return self._ew(1, op, dtype, out, [a, b])
 
     def ternary(self, name, a, b, c, dtype, out=None):

@@ -85,13 +85,24 @@ static float round_to(int dt, float v) {
 enum {
   U_RELU, U_NEG, U_ABS, U_SQUARE, U_EXP, U_LOG, U_SQRT, U_RSQRT, U_SIN, U_COS, U_TANH,
   U_SIGMOID, U_SILU, U_GELU, U_RECIPROCAL, U_SIGN, U_FLOOR, U_CEIL, U_TRUNC, U_ROUND,
-  U_EXPM1, U_LOG1P, U_SOFTPLUS, U_RELU6, U_HARDTANH, U_COUNT
+  U_EXPM1, U_LOG1P, U_SOFTPLUS, U_RELU6, U_HARDTANH,
+  U_EXP2, U_LOG2, U_LOG10, U_SINH, U_COSH, U_ASINH, U_ACOSH, U_ATANH, U_TAN, U_ASIN, U_ACOS,
+  U_ATAN, U_ERF, U_ERFC, U_LGAMMA, U_SINC, U_FRAC, U_DEG2RAD, U_RAD2DEG, U_MISH, U_SELU, U_ELU,
+  U_HARDSIGMOID, U_HARDSHRINK, U_SOFTSHRINK, U_LOGIT, U_ANGLE, U_POSITIVE, U_SGN, U_NAN_TO_NUM,
+  U_ISFINITE, U_ISINF, U_ISNAN, U_ISNEGINF, U_ISPOSINF, U_SIGNBIT, U_LOGICAL_NOT, U_BITWISE_NOT,
+  U_COUNT
 };
 enum {
   B_ADD, B_SUB, B_MUL, B_DIV, B_MAXIMUM, B_MINIMUM, B_FMAX, B_FMIN,
-  B_EQ, B_NE, B_LT, B_GT, B_LE, B_GE, B_COUNT
+  B_EQ, B_NE, B_LT, B_GT, B_LE, B_GE,
+  B_POW, B_FMOD, B_REMAINDER, B_ATAN2, B_COPYSIGN, B_HYPOT, B_XLOGY, B_XLOG1PY, B_LOGADDEXP,
+  B_LOGADDEXP2, B_NEXTAFTER, B_HEAVISIDE, B_RSUB, B_TANH_BACKWARD, B_SIGMOID_BACKWARD,
+  B_SILU_BACKWARD, B_LOGIT_BACKWARD, B_MSE_LOSS, B_LDEXP,
+  B_BITWISE_AND, B_BITWISE_OR, B_BITWISE_XOR, B_LSHIFT, B_RSHIFT, B_GCD, B_LCM,
+  B_LOGICAL_AND, B_LOGICAL_OR, B_LOGICAL_XOR, B_COUNT
 };
-enum { T_CLAMP, T_LERP, T_THRESHOLD, T_ADDCMUL, T_ADDCDIV, T_WHERE_GT0_ADDCMUL, T_COUNT };
+enum { T_CLAMP, T_LERP, T_THRESHOLD, T_ADDCMUL, T_ADDCDIV, T_WHERE_GT0_ADDCMUL, T_HUBER_LOSS,
+       T_SMOOTH_L1_LOSS, T_COUNT };
 
 /* Functors on float: src/vbt/ops/cuda_elementwise.cu:590-900, :1622-1630.  Several are
  * written in double there (Silu, Gelu, Reciprocal, Sign, Softplus, Relu6, Hardtanh). */
@@ -127,8 +138,68 @@ static float unary_f(int op, float a) {
     }
     case U_RELU6: { double x = a; if (x < 0.0) x = 0.0; if (x > 6.0) x = 6.0; return (float)x; }
     case U_HARDTANH: { double x = a; if (x < -1.0) x = -1.0; if (x > 1.0) x = 1.0; return (float)x; }
+    /* :1151-1252: float math for T = float */
+    case U_EXP2: return exp2f(a);
+    case U_LOG2: return log2f(a);
+    case U_LOG10: return log10f(a);
+    case U_SINH: return sinhf(a);
+    case U_COSH: return coshf(a);
+    case U_ASINH: return asinhf(a);
+    case U_ACOSH: return acoshf(a);
+    case U_ATANH: return atanhf(a);
+    case U_TAN: return tanf(a);
+    case U_ASIN: return asinf(a);
+    case U_ACOS: return acosf(a);
+    case U_ATAN: return atanf(a);
+    case U_ERF: return erff(a);
+    case U_ERFC: return erfcf(a);
+    case U_LGAMMA: return lgammaf(a);
+    /* :808-850, :901-948: written in double */
+    case U_SINC: { double x = a; if (x == 0.0) return 1.f; double pix = 3.14159265358979323846 * x; return (float)(sin(pix) / pix); }
+    case U_FRAC: { double ip; return (float)modf((double)a, &ip); }
+    case U_DEG2RAD: return (float)((double)a * (3.14159265358979323846 / 180.0));
+    case U_RAD2DEG: return (float)((double)a * (180.0 / 3.14159265358979323846));
+    case U_MISH: { double x = a; double sp = x > 20.0 ? x : log1p(exp(x)); return (float)(x * tanh(sp)); }
+    case U_SELU: {
+      double x = a;
+      double y = x > 0.0 ? x : 1.6732632423543772848170429916717 * expm1(x);
+      return (float)(1.0507009873554804934193349852946 * y);
+    }
+    case U_ELU: { double x = a; return (float)(x > 0.0 ? x : expm1(x)); }
+    case U_HARDSIGMOID: { double y = (double)a / 6.0 + 0.5; if (y < 0.0) y = 0.0; if (y > 1.0) y = 1.0; return (float)y; }
+    case U_HARDSHRINK: { double x = a; return (x > 0.5 || x < -0.5) ? (float)x : 0.f; }
+    case U_SOFTSHRINK: { double x = a; if (x > 0.5) return (float)(x - 0.5); if (x < -0.5) return (float)(x + 0.5); return 0.f; }
+    case U_LOGIT: return logf(a / (1.0f - a)); /* :1279-1287 */
+    case U_ANGLE: { double x = a; if (x != x) return a; if (x == 0.0) return 0.f; return (float)(x < 0.0 ? 3.14159265358979323846 : 0.0); }
+    case U_POSITIVE: return a;
+    case U_SGN: { double x = a; if (x != x) return 0.f; return (float)((x > 0) - (x < 0)); }
+    case U_NAN_TO_NUM: /* :1556-1572 */
+      if (a != a) return 0.f;
+      if (isinf(a)) return a > 0.f ? 3.402823466e+38F : -3.402823466e+38F;
+      return a;
   }
   return 0.f;
+}
+/* Predicates -> bool: :1043-1149 */
+static int pred_f(int op, float x) {
+  switch (op) {
+    case U_ISFINITE: return isfinite(x) != 0;
+    case U_ISINF: return isinf(x) != 0;
+    case U_ISNAN: return x != x;
+    case U_ISNEGINF: return isinf(x) && x < 0.f;
+    case U_ISPOSINF: return isinf(x) && x > 0.f;
+    case U_SIGNBIT: return signbit(x) != 0;
+    case U_LOGICAL_NOT: return !(x != 0.f);
+  }
+  return 0;
+}
+static int pred_i(int op, int64_t a, int is_signed) {
+  switch (op) {
+    case U_ISFINITE: return 1;
+    case U_SIGNBIT: return is_signed ? a < 0 : 0;
+    case U_LOGICAL_NOT: return a == 0;
+  }
+  return 0;
 }
 static int64_t unary_i64(int op, int64_t a, int* ok) {
   uint64_t ua = (uint64_t)a;
@@ -138,7 +209,8 @@ static int64_t unary_i64(int op, int64_t a, int* ok) {
     case U_ABS: return a < 0 ? (int64_t)(0u - ua) : a;
     case U_SQUARE: return (int64_t)(ua * ua);
     case U_SIGN: return (a > 0) - (a < 0);
-    case U_FLOOR: case U_CEIL: case U_TRUNC: case U_ROUND: return a;
+    case U_FLOOR: case U_CEIL: case U_TRUNC: case U_ROUND: case U_POSITIVE: return a;
+    case U_SGN: return (a > 0) - (a < 0);
   }
   *ok = 0; /* transcendental ops reject integral inputs (:121-125) */
   return 0;
@@ -153,6 +225,33 @@ static float binary_f(int op, float a, float b) {
     case B_MINIMUM: if (a != a) return a; if (b != b) return b; return fminf(a, b);
     case B_FMAX: return fmaxf(a, b);
     case B_FMIN: return fminf(a, b);
+    /* :307-589 (float branches), :851-876 and the backward forms in double, :1253-1258 */
+    case B_POW: return powf(a, b);
+    case B_FMOD: return fmodf(a, b);
+    case B_REMAINDER: { float r = fmodf(a, b); if (r != 0.0f && ((r < 0.0f) != (b < 0.0f))) r += b; return r; }
+    case B_ATAN2: return atan2f(a, b);
+    case B_COPYSIGN: return copysignf(a, b);
+    case B_HYPOT: return hypotf(a, b);
+    case B_XLOGY: return a == 0.f ? 0.f : a * logf(b);
+    case B_XLOG1PY: return a == 0.f ? 0.f : a * log1pf(b);
+    case B_LOGADDEXP: { float m = a > b ? a : b; if (isinf(m)) return m; return m + log1pf(expf(-fabsf(a - b))); }
+    case B_LOGADDEXP2: { float m = a > b ? a : b; if (isinf(m)) return m; return m + log2f(1.0f + exp2f(-fabsf(a - b))); }
+    case B_NEXTAFTER: return nextafterf(a, b);
+    case B_HEAVISIDE: if (a < 0.f) return 0.f; if (a > 0.f) return 1.f; return b;
+    case B_RSUB: return b - a;
+    case B_TANH_BACKWARD: { double g = a, o = b; return (float)(g * (1.0 - o * o)); }
+    case B_SIGMOID_BACKWARD: { double g = a, o = b; return (float)(g * o * (1.0 - o)); }
+    case B_SILU_BACKWARD: { double g = a, x = b; double s = 1.0 / (1.0 + exp(-x)); return (float)(g * (s * (1.0 + x * (1.0 - s)))); }
+    case B_LOGIT_BACKWARD: { double g = a, x = b; return (float)(g / (x * (1.0 - x))); }
+    case B_MSE_LOSS: { float d = a - b; return d * d; }
+    case B_LDEXP: { /* :463-478; the device cast of 2^31 saturates to INT_MAX */
+      int e;
+      if (b != b) e = 0;
+      else if (b >= 2147483648.0f) e = 2147483647;
+      else if (b < -2147483648.0f) e = -2147483647 - 1;
+      else e = (int)b;
+      return ldexpf(a, e);
+    }
   }
   return 0.f;
 }
@@ -174,8 +273,58 @@ static int64_t binary_i64(int op, int64_t a, int64_t b) {
     case B_MUL: return (int64_t)((uint64_t)a * (uint64_t)b);
     case B_MAXIMUM: case B_FMAX: return a > b ? a : b;
     case B_MINIMUM: case B_FMIN: return a < b ? a : b;
+    case B_FMOD: case B_REMAINDER: { /* :322-330, :355-366 */
+      if (b == 0) return 0;
+      if (a == INT64_MIN && b == -1) return 0;
+      int64_t r = a % b;
+      if (op == B_REMAINDER && r != 0 && ((r < 0) != (b < 0))) r += b;
+      return r;
+    }
+    case B_HEAVISIDE: if (a < 0) return 0; if (a > 0) return 1; return b;
+    case B_RSUB: return (int64_t)((uint64_t)b - (uint64_t)a);
   }
   return 0;
+}
+/* bitwise / shift / gcd / lcm on a `bits`-wide signed integer held in int64 (:191-243,
+ * :537-588); bits == 1 is BOOL (and/or/xor only). */
+static int64_t intop(int op, int64_t a, int64_t b, int bits) {
+  if (bits == 1) {
+    int x = a != 0, y = b != 0;
+    return op == B_BITWISE_AND ? (x && y) : op == B_BITWISE_OR ? (x || y) : (x != y);
+  }
+  switch (op) {
+    case B_BITWISE_AND: return a & b;
+    case B_BITWISE_OR: return a | b;
+    case B_BITWISE_XOR: return a ^ b;
+    case B_LSHIFT: {
+      if (b < 0 || b >= bits) return 0;
+      uint64_t r = (uint64_t)a << (int)b;
+      return bits == 32 ? (int64_t)(int32_t)(uint32_t)r : (int64_t)r;
+    }
+    case B_RSHIFT: {
+      if (b < 0 || b >= bits) return a < 0 ? -1 : 0;
+      /* logical shift of the two's-complement pattern, then sign fill */
+      uint64_t ua = bits == 32 ? (uint64_t)(uint32_t)(int32_t)a : (uint64_t)a;
+      uint64_t r = ua >> (int)b;
+      if (a < 0 && b > 0) {
+        uint64_t all = bits == 32 ? 0xffffffffull : ~0ull;
+        r |= (all << (bits - (int)b)) & all;
+      }
+      return bits == 32 ? (int64_t)(int32_t)(uint32_t)r : (int64_t)r;
+    }
+    case B_GCD: case B_LCM: {
+      uint64_t ua = a < 0 ? 0ull - (uint64_t)a : (uint64_t)a;
+      uint64_t ub = b < 0 ? 0ull - (uint64_t)b : (uint64_t)b;
+      if (op == B_LCM && (a == 0 || b == 0)) return 0;
+      uint64_t x = ua, y = ub;
+      while (y != 0) { uint64_t t = y; y = x % y; x = t; }
+      return op == B_GCD ? (int64_t)x : (int64_t)((ua / x) * ub);
+    }
+  }
+  return 0;
+}
+static int logical(int op, int x, int y) {
+  return op == B_LOGICAL_AND ? (x && y) : op == B_LOGICAL_OR ? (x || y) : (x != y);
 }
 static int compare_i64(int op, int64_t a, int64_t b) {
   switch (op) {
@@ -200,6 +349,14 @@ static float ternary_f(int op, int dt, float a, float b, float c) {
     case T_WHERE_GT0_ADDCMUL: {
       float t2 = round_to(dt, a + round_to(dt, b * c));
       return a > 0.f ? t2 : 0.f;
+    }
+    case T_HUBER_LOSS: { /* (input, target, delta) :1385-1395 */
+      float d = a - b, ad = fabsf(d);
+      return ad < c ? 0.5f * d * d : c * (ad - 0.5f * c);
+    }
+    case T_SMOOTH_L1_LOSS: { /* (input, target, beta) :1397-1407 */
+      float d = a - b, ad = fabsf(d);
+      return ad < c ? 0.5f * d * d / c : ad - 0.5f * c;
     }
   }
   return 0.f;
@@ -241,8 +398,11 @@ int vbo_elementwise(int kind, int op, int dtype, int ndim, const int64_t* sizes,
   if (ndim > MAXD) return 1;
   const int64_t n = numel_of(ndim, sizes);
   const int es = itemsize(dtype);
-  const int is_cmp = (kind == 1 && op >= B_EQ);
-  const int oes = is_cmp ? 1 : es;
+  const int is_cmp = (kind == 1 && op >= B_EQ && op <= B_GE);
+  const int is_logical = (kind == 1 && op >= B_LOGICAL_AND && op <= B_LOGICAL_XOR);
+  const int is_intop = (kind == 1 && op >= B_BITWISE_AND && op <= B_LCM);
+  const int is_pred = (kind == 0 && op >= U_ISFINITE && op <= U_LOGICAL_NOT);
+  const int oes = (is_cmp || is_logical || is_pred) ? 1 : es;
   odo_t o;
   odo_init(&o, ndim, sizes);
   for (int64_t i = 0; i < n; ++i, odo_next(&o)) {
@@ -258,16 +418,42 @@ int vbo_elementwise(int kind, int op, int dtype, int ndim, const int64_t* sizes,
     if (kind == 4) { memcpy(po, pa, es); continue; }
     const char* pb = b ? (const char*)b + odo_off(&o, bs) * es : 0;
     const char* pc = c ? (const char*)c + odo_off(&o, cs) * es : 0;
-    if (dtype == DT_I64) {
+    if (is_intop || (kind == 0 && op == U_BITWISE_NOT)) {
+      const int bits = dtype == DT_I64 ? 64 : dtype == DT_I32 ? 32 : dtype == DT_BOOL ? 1 : 0;
+      if (bits == 0) return 1;
+      if (bits == 1 && (op == B_LSHIFT || op == B_RSHIFT)) return 1;
+      if (bits != 64 && (op == B_GCD || op == B_LCM) && kind == 1) return 1;
+      int64_t av = bits == 64 ? *(const int64_t*)pa : bits == 32 ? *(const int32_t*)pa : *(const uint8_t*)pa;
+      int64_t r;
+      if (kind == 0) r = bits == 1 ? (av == 0) : ~av;
+      else {
+        int64_t bv = bits == 64 ? *(const int64_t*)pb : bits == 32 ? *(const int32_t*)pb : *(const uint8_t*)pb;
+        r = intop(op, av, bv, bits);
+      }
+      if (bits == 64) *(int64_t*)po = r;
+      else if (bits == 32) *(int32_t*)po = (int32_t)r;
+      else *(uint8_t*)po = (uint8_t)r;
+    } else if (dtype == DT_BOOL) { /* predicates and logical ops on BOOL bytes */
+      const int av = *(const uint8_t*)pa;
+      if (is_pred) *(uint8_t*)po = (uint8_t)pred_i(op, av, 0);
+      else if (is_logical) *(uint8_t*)po = (uint8_t)logical(op, av != 0, *(const uint8_t*)pb != 0);
+      else return 1;
+    } else if (dtype == DT_I64) {
       int64_t av = *(const int64_t*)pa;
-      if (kind == 0) {
+      if (is_pred) {
+        *(uint8_t*)po = (uint8_t)pred_i(op, av, 1);
+      } else if (is_logical) {
+        *(uint8_t*)po = (uint8_t)logical(op, av != 0, *(const int64_t*)pb != 0);
+      } else if (kind == 0) {
         int ok = 1;
         int64_t r = unary_i64(op, av, &ok);
         if (!ok) return 1;
         *(int64_t*)po = r;
       } else if (kind == 1) {
         int64_t bv = *(const int64_t*)pb;
-        if (op == B_DIV) return 1;
+        if (op == B_DIV || (op >= B_POW && op != B_FMOD && op != B_REMAINDER && op != B_HEAVISIDE &&
+                            op != B_RSUB))
+          return 1;
         if (is_cmp) *(uint8_t*)po = (uint8_t)compare_i64(op, av, bv);
         else *(int64_t*)po = binary_i64(op, av, bv);
       } else {
@@ -275,10 +461,14 @@ int vbo_elementwise(int kind, int op, int dtype, int ndim, const int64_t* sizes,
       }
     } else if (dtype == DT_F32 || dtype == DT_F16 || dtype == DT_BF16) {
       float av = load_f(pa, dtype);
-      if (kind == 0) store_f(po, dtype, unary_f(op, av));
-      else if (kind == 1) {
+      if (is_pred) *(uint8_t*)po = (uint8_t)pred_f(op, av);
+      else if (kind == 0) {
+        if (op == U_NAN_TO_NUM && dtype != DT_F32) return 1;
+        store_f(po, dtype, unary_f(op, av));
+      } else if (kind == 1) {
         float bv = load_f(pb, dtype);
-        if (is_cmp) *(uint8_t*)po = (uint8_t)compare_f(op, av, bv);
+        if (is_logical) *(uint8_t*)po = (uint8_t)logical(op, av != 0.f, bv != 0.f);
+        else if (is_cmp) *(uint8_t*)po = (uint8_t)compare_f(op, av, bv);
         else store_f(po, dtype, binary_f(op, av, bv));
       } else {
         store_f(po, dtype, ternary_f(op, dtype, av, load_f(pb, dtype), load_f(pc, dtype)));

@@ -22,7 +22,12 @@ def ops():
 
 
 EXACT_UNARY = ["relu", "neg", "abs", "square", "sign", "floor", "ceil", "trunc", "round", "relu6",
-               "hardtanh", "sqrt"]
+               "hardtanh", "sqrt", "frac", "hardshrink", "softshrink", "angle", "positive", "sgn",
+               "nan_to_num"]
+FLOAT_UNARY = [n for n in oracle.UNARY if n not in oracle.UNARY_TO_BOOL and n != "bitwise_not"]
+CORE_BINARY = oracle.BINARY[:oracle.BINARY.index("pow")]
+TAIL_FLOAT_BINARY = oracle.BINARY[oracle.BINARY.index("pow"):oracle.BINARY.index("bitwise_and")]
+EXACT_TAIL_BINARY = {"fmod", "remainder", "copysign", "nextafter", "heaviside", "rsub", "mse_loss", "ldexp"}
 
 
 def _check_unary(ops, port, name, x_np, dtype):
@@ -40,17 +45,69 @@ def _check_unary(ops, port, name, x_np, dtype):
 
 
 @pytest.mark.parametrize("dtype", FLOATS)
-@pytest.mark.parametrize("name", oracle.UNARY)
+@pytest.mark.parametrize("name", FLOAT_UNARY)
 def test_unary_float(ops, port, name, dtype):
     rng = np.random.default_rng(11)
     x = 4 * rng.standard_normal((37, 129), dtype=np.float32)
-    if name in ("log", "sqrt", "rsqrt", "log1p", "reciprocal"):
+    if name in ("log", "sqrt", "rsqrt", "log1p", "reciprocal", "log2", "log10", "lgamma"):
         x = np.abs(x) + 0.05
+    elif name == "acosh":
+        x = np.abs(x) + 1.0
+    elif name in ("atanh", "asin", "acos"):
+        x = 0.99 * np.tanh(x)
+    elif name == "logit":
+        x = 0.01 + 0.98 / (1.0 + np.exp(-x))
     x.flat[:6] = [0.0, -0.0, 25.0, -25.0, 0.5, 2.5]
+    x.flat[6:9] = [np.inf, -np.inf, np.nan]
+    if name == "nan_to_num" and dtype != torch.float32:
+        with pytest.raises(ValueError, match="float32 tensor expected"):
+            ops.nan_to_num(from_np(oracle.to_storage(x, CODE[dtype]), dtype))
+        return
     _check_unary(ops, port, name, oracle.to_storage(x, CODE[dtype]), dtype)
 
 
-@pytest.mark.parametrize("name", ["relu", "neg", "abs", "square", "sign", "floor", "round"])
+@pytest.mark.parametrize("dtype", FLOATS + [torch.int64, torch.bool])
+@pytest.mark.parametrize("name", sorted(oracle.UNARY_TO_BOOL))
+def test_predicates_write_bool(ops, port, name, dtype):
+    rng = np.random.default_rng(21)
+    if dtype == torch.bool:
+        x = rng.integers(0, 2, (9, 70)).astype(np.uint8)
+    elif dtype == torch.int64:
+        x = rng.integers(-3, 4, (9, 70)).astype(np.int64)
+        x.flat[:2] = [np.iinfo(np.int64).min, np.iinfo(np.int64).max]
+    else:
+        v = rng.standard_normal((9, 70), dtype=np.float32)
+        v.flat[:8] = [0.0, -0.0, np.inf, -np.inf, np.nan, 1e-40, -1e-40, 65536.0 * 65536.0]
+        v.flat[8::7] = 0.0
+        x = oracle.to_storage(v, CODE[dtype])
+    got = ops.unary(name, from_np(x, dtype))
+    assert got.dtype == torch.bool
+    want = port.unary(name, x, CODE[dtype])
+    if name == "signbit" and dtype != torch.bool and dtype != torch.int64:
+        keep = ~np.isnan(as_f32(x, dtype))          # the sign of a NaN is payload, not semantics
+        np.testing.assert_array_equal(to_np(got)[keep], want[keep])
+    else:
+        np.testing.assert_array_equal(to_np(got), want)
+    # into a strided bool view
+    base = torch.zeros((70, 9), dtype=torch.bool, device="cuda")
+    ops.unary(name, from_np(x, dtype), out=base.t())
+    assert torch.equal(base.t(), got)
+
+
+@pytest.mark.parametrize("dtype", [torch.int64, torch.int32, torch.bool])
+def test_bitwise_not(ops, port, dtype):
+    rng = np.random.default_rng(22)
+    if dtype == torch.bool:
+        x = rng.integers(0, 2, (5, 333)).astype(np.uint8)
+    else:
+        npdt = np.int64 if dtype == torch.int64 else np.int32
+        x = rng.integers(np.iinfo(npdt).min, np.iinfo(npdt).max, (5, 333), dtype=npdt)
+    np.testing.assert_array_equal(to_np(ops.bitwise_not(from_np(x, dtype))), port.unary("bitwise_not", x, CODE[dtype]))
+    with pytest.raises(ValueError, match="integral or bool tensor expected"):
+        ops.bitwise_not(torch.ones(4, device="cuda"))
+
+
+@pytest.mark.parametrize("name", ["relu", "neg", "abs", "square", "sign", "floor", "round", "positive", "sgn"])
 def test_unary_int64(ops, port, name):
     rng = np.random.default_rng(12)
     x = rng.integers(-2 ** 62, 2 ** 62, (33, 65)).astype(np.int64)
@@ -64,7 +121,7 @@ def test_unary_rejects_integral_for_transcendental(ops):
 
 
 @pytest.mark.parametrize("dtype", FLOATS + [torch.int64])
-@pytest.mark.parametrize("name", oracle.BINARY)
+@pytest.mark.parametrize("name", CORE_BINARY)
 def test_binary_broadcast_bit_exact(ops, port, name, dtype):
     if dtype == torch.int64 and name == "div":
         with pytest.raises(ValueError):
@@ -85,6 +142,139 @@ def test_binary_broadcast_bit_exact(ops, port, name, dtype):
         g, w = as_f32(got, dtype), as_f32(want, dtype)
         np.testing.assert_array_equal(np.isnan(g), np.isnan(w))
         np.testing.assert_array_equal(g[~np.isnan(g)], w[~np.isnan(w)])
+
+
+def _tail_inputs(rng, name, dtype):
+    a = 3 * rng.standard_normal((6, 1, 40), dtype=np.float32)
+    b = 3 * rng.standard_normal((5, 40), dtype=np.float32)
+    if name == "pow":
+        a = np.abs(a) + 0.1
+    elif name in ("xlogy", "xlog1py"):
+        b = np.abs(b) + 0.1
+        a.flat[3:6] = 0.0
+    elif name in ("tanh_backward", "sigmoid_backward", "logit_backward"):
+        b = 0.01 + 0.98 / (1.0 + np.exp(-b))
+    elif name == "ldexp":
+        b = np.round(4 * b)
+    elif name == "heaviside":
+        a.flat[3:9] = [0.0, -0.0, 0.0, 1.0, -1.0, np.nan]
+    elif name in ("fmod", "remainder"):
+        a.flat[3:9] = [5.5, -5.5, 5.5, -5.5, 0.0, np.inf]
+        b.flat[3:9] = [2.0, 2.0, -2.0, -2.0, 3.0, 2.0]
+    a.flat[0] = np.nan
+    b.flat[1] = np.nan
+    return oracle.to_storage(a, CODE[dtype]), oracle.to_storage(b, CODE[dtype])
+
+
+@pytest.mark.parametrize("dtype", FLOATS)
+@pytest.mark.parametrize("name", TAIL_FLOAT_BINARY)
+def test_binary_tail_float(ops, port, name, dtype):
+    rng = np.random.default_rng(23)
+    a, b = _tail_inputs(rng, name, dtype)
+    got = to_np(ops.binary(name, from_np(a, dtype), from_np(b, dtype)))
+    want = port.binary(name, a, b, CODE[dtype])
+    g, w = as_f32(got, dtype), as_f32(want, dtype)
+    np.testing.assert_array_equal(np.isnan(g), np.isnan(w), err_msg=name)
+    if name in EXACT_TAIL_BINARY:
+        np.testing.assert_array_equal(got[~np.isnan(w)], want[~np.isnan(w)], err_msg=name)
+    else:
+        fin = np.isfinite(w)
+        np.testing.assert_array_equal(g[~fin & ~np.isnan(w)], w[~fin & ~np.isnan(w)], err_msg=name)
+        tol = 2e-5 if dtype == torch.float32 else 1e-2
+        np.testing.assert_allclose(g[fin], w[fin], rtol=tol, atol=1e-6 if dtype == torch.float32 else tol,
+                                   err_msg=name)
+
+
+@pytest.mark.parametrize("name", ["fmod", "remainder", "heaviside", "rsub"])
+def test_binary_tail_int64(ops, port, name):
+    rng = np.random.default_rng(24)
+    a = rng.integers(-2 ** 62, 2 ** 62, (7, 1, 33)).astype(np.int64)
+    b = rng.integers(-9, 10, (5, 33)).astype(np.int64)          # includes zeros
+    a.flat[:3] = [np.iinfo(np.int64).min, 0, np.iinfo(np.int64).max]
+    b.flat[:3] = [-1, 0, -1]
+    got = to_np(ops.binary(name, from_np(a, torch.int64), from_np(b, torch.int64)))
+    np.testing.assert_array_equal(got, port.binary(name, a, b, oracle.I64))
+    for bad in ("pow", "atan2", "hypot", "ldexp"):
+        with pytest.raises(ValueError, match="floating tensor expected"):
+            ops.binary(bad, from_np(a, torch.int64), from_np(b, torch.int64))
+    with pytest.raises(ValueError, match="boolean not supported"):
+        ops.fmod(torch.ones(3, dtype=torch.bool, device="cuda"), torch.ones(3, dtype=torch.bool, device="cuda"))
+
+
+@pytest.mark.parametrize("left", [False, True])
+def test_binary_tail_scalar_operand(ops, port, left):
+    rng = np.random.default_rng(25)
+    a = np.abs(rng.standard_normal((19, 31), dtype=np.float32)) + 0.25
+    ta = torch.from_numpy(a).cuda()
+    s = np.array(2.5, np.float32)
+    for name in ("pow", "fmod", "remainder", "atan2", "rsub", "mse_loss"):
+        got = to_np(ops.binary(name, 2.5, ta) if left else ops.binary(name, ta, 2.5))
+        want = port.binary(name, s, a, oracle.F32) if left else port.binary(name, a, s, oracle.F32)
+        if name in EXACT_TAIL_BINARY:
+            np.testing.assert_array_equal(got, want, err_msg=name)
+        else:
+            np.testing.assert_allclose(got, want, rtol=2e-5, err_msg=name)
+    ai = rng.integers(-1000, 1000, (19, 31)).astype(np.int64)
+    ti = torch.from_numpy(ai).cuda()
+    si = np.array(7, np.int64)
+    for name in ("remainder", "fmod", "rsub"):
+        got = to_np(ops.binary(name, 7, ti) if left else ops.binary(name, ti, 7))
+        want = port.binary(name, si, ai, oracle.I64) if left else port.binary(name, ai, si, oracle.I64)
+        np.testing.assert_array_equal(got, want, err_msg=name)
+    with pytest.raises(ValueError, match="no scalar form"):
+        ops.binary("bitwise_and", ti, 1)
+
+
+def _int_storage(rng, shape, dtype, lo=None, hi=None):
+    if dtype == torch.bool:
+        return rng.integers(0, 2, shape).astype(np.uint8)
+    npdt = np.int64 if dtype == torch.int64 else np.int32
+    info = np.iinfo(npdt)
+    return rng.integers(info.min if lo is None else lo, info.max if hi is None else hi, shape, dtype=npdt)
+
+
+@pytest.mark.parametrize("dtype", [torch.int64, torch.int32, torch.bool])
+@pytest.mark.parametrize("name", ["bitwise_and", "bitwise_or", "bitwise_xor", "lshift", "rshift", "gcd", "lcm"])
+def test_integer_binary_ops(ops, port, name, dtype):
+    rng = np.random.default_rng(26)
+    shift = name in ("lshift", "rshift")
+    gl = name in ("gcd", "lcm")
+    ta1 = torch.ones(3, dtype=dtype, device="cuda")
+    if (shift and dtype == torch.bool) or (gl and dtype != torch.int64):
+        with pytest.raises(ValueError, match="expected Int"):
+            ops.binary(name, ta1, ta1)
+        return
+    a = _int_storage(rng, (6, 1, 70), dtype)
+    if shift:
+        b = _int_storage(rng, (4, 70), dtype, -4, 70)      # counts below 0 and beyond the width too
+    elif gl:
+        a = _int_storage(rng, (6, 1, 70), dtype, -5000, 5000)
+        b = _int_storage(rng, (4, 70), dtype, -60, 60)
+        a.flat[:2] = [0, np.iinfo(np.int64).min]
+        b.flat[:2] = [0, 6]
+    else:
+        b = _int_storage(rng, (4, 70), dtype)
+    got = to_np(ops.binary(name, from_np(a, dtype), from_np(b, dtype)))
+    np.testing.assert_array_equal(got, port.binary(name, a, b, CODE[dtype]))
+    with pytest.raises(ValueError):
+        ops.binary(name, torch.ones(3, device="cuda"), torch.ones(3, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", FLOATS + [torch.int64, torch.bool])
+@pytest.mark.parametrize("name", ["logical_and", "logical_or", "logical_xor"])
+def test_logical_ops_write_bool(ops, port, name, dtype):
+    rng = np.random.default_rng(27)
+    if dtype in (torch.int64, torch.bool):
+        a = _int_storage(rng, (8, 1, 50), dtype, -1, 2)
+        b = _int_storage(rng, (3, 50), dtype, -1, 2)
+    else:
+        va = rng.integers(-1, 2, (8, 1, 50)).astype(np.float32)
+        vb = rng.integers(-1, 2, (3, 50)).astype(np.float32)
+        va.flat[:3] = [np.nan, -0.0, 1e-40]
+        a, b = oracle.to_storage(va, CODE[dtype]), oracle.to_storage(vb, CODE[dtype])
+    got = ops.binary(name, from_np(a, dtype), from_np(b, dtype))
+    assert got.dtype == torch.bool
+    np.testing.assert_array_equal(to_np(got), port.binary(name, a, b, CODE[dtype]))
 
 
 def test_binary_golden_reference_vectors(ops):
@@ -147,9 +337,11 @@ def test_ternary_bit_exact(ops, port, name, dtype):
     c = rand_storage(rng, (4, 16, 1, 8), dtype)
     if name == "clamp":
         b, c = port.binary("minimum", b, c, CODE[dtype]), port.binary("maximum", b, c, CODE[dtype])
+    if name in ("huber_loss", "smooth_l1_loss"):
+        c = port.unary("abs", c, CODE[dtype])
     got = to_np(ops.ternary(name, from_np(a, dtype), from_np(b, dtype), from_np(c, dtype)))
     want = port.ternary(name, a, b, c, CODE[dtype])
-    if name == "addcdiv":
+    if name in ("addcdiv", "huber_loss", "smooth_l1_loss"):
         np.testing.assert_allclose(as_f32(got, dtype), as_f32(want, dtype), rtol=1e-6 if dtype == torch.float32 else 1e-2)
     else:
         np.testing.assert_array_equal(got, want)

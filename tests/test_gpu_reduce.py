@@ -144,6 +144,27 @@ def test_nan_and_inf_rules(ops):
     assert ops.argmax(t([-inf, -inf, -inf])).item() == 0
 
 
+@pytest.mark.parametrize("shape,dim", [((3, 70000), 1), ((700, 300), 0), ((5, 64, 33), 1), ((40, 9), 1)])
+def test_arg_ops_when_nothing_beats_the_identity(ops, port, shape, dim):
+    """Slices that hold only -inf / NaN (argmax), +inf (argmin) or INT64_MIN: index 0, as the
+    CPU scan that starts from element 0; plus ties, where the first position wins."""
+    x = np.full(shape, -np.inf, np.float32)
+    x[0] = np.nan if dim != 0 else -np.inf
+    x.flat[5::7] = np.nan
+    x[-1] = 3.0                                   # a slice (or part of each) with ties everywhere
+    for name, arr in (("argmax", x), ("argmin", -x)):
+        v, i = ops.reduce(name, torch.from_numpy(arr).cuda(), dim)
+        wv, wi = port.reduce(name, arr, oracle.F32, dim=dim)
+        np.testing.assert_array_equal(i.cpu().numpy(), wi)
+        np.testing.assert_array_equal(v.cpu().numpy(), wv)
+    xi = np.full(shape, np.iinfo(np.int64).min, np.int64)
+    xi[-1] = 4
+    v, i = ops.reduce("argmax", torch.from_numpy(xi).cuda(), dim)
+    wv, wi = port.reduce("argmax", xi, oracle.I64, dim=dim)
+    np.testing.assert_array_equal(i.cpu().numpy(), wi)
+    np.testing.assert_array_equal(v.cpu().numpy(), wv)
+
+
 def test_empty_semantics_and_errors(ops):
     x = torch.zeros((3, 0), device="cuda")
     assert ops.sum(x, 1).tolist() == [0.0, 0.0, 0.0]

@@ -290,7 +290,149 @@ def test_unary_float_ops_vs_torch(port):
         "softplus": (x, torch.nn.functional.softplus(t)),
         "relu6": (x, torch.nn.functional.relu6(t)), "hardtanh": (x, torch.nn.functional.hardtanh(t)),
     }
-    assert set(cases) == set(oracle.UNARY)
+    unit = np.clip(x / 16, -0.99, 0.99).astype(np.float32)
+    tu = torch.from_numpy(unit)
+    p01 = (np.abs(unit) * 0.98 + 0.01).astype(np.float32)
+    tp01 = torch.from_numpy(p01)
+    F = torch.nn.functional
+    cases.update({
+        "exp2": (x, t.exp2()), "log2": (pos, tp.log2()), "log10": (pos, tp.log10()), "sinh": (x, t.sinh()),
+        "cosh": (x, t.cosh()), "asinh": (x, t.asinh()), "acosh": (pos + 1, (tp + 1).acosh()),
+        "atanh": (unit, tu.atanh()), "tan": (unit, tu.tan()), "asin": (unit, tu.asin()),
+        "acos": (unit, tu.acos()), "atan": (x, t.atan()), "erf": (x, t.erf()), "erfc": (x, t.erfc()),
+        "lgamma": (pos, tp.lgamma()), "sinc": (x, t.sinc()), "frac": (x, t.frac()),
+        "deg2rad": (x, t.deg2rad()), "rad2deg": (x, t.rad2deg()), "mish": (x, F.mish(t)),
+        "selu": (x, F.selu(t)), "elu": (x, F.elu(t)), "hardsigmoid": (x, F.hardsigmoid(t)),
+        "hardshrink": (x, F.hardshrink(t)), "softshrink": (x, F.softshrink(t)),
+        "logit": (p01, tp01.logit()), "angle": (x, t.angle()), "positive": (x, t.positive()),
+        "sgn": (x, t.sgn()), "nan_to_num": (x, t.nan_to_num()),
+    })
+    assert set(cases) == set(oracle.UNARY) - oracle.UNARY_TO_BOOL - {"bitwise_not"}
     for name, (inp, want) in cases.items():
         got = port.unary(name, inp, F32)
         np.testing.assert_allclose(got, want.numpy(), rtol=1e-5, atol=1e-6, err_msg=name)
+
+
+def test_predicates_and_bitwise_not_vs_torch(port):
+    x = np.array([0.0, -0.0, 1.5, -2.0, np.inf, -np.inf, np.nan, 1e-40], np.float32)
+    t = torch.from_numpy(x)
+    want = {"isfinite": t.isfinite(), "isinf": t.isinf(), "isnan": t.isnan(), "isneginf": t.isneginf(),
+            "isposinf": t.isposinf(), "signbit": t.signbit(), "logical_not": t.logical_not()}
+    assert set(want) == oracle.UNARY_TO_BOOL
+    for dt, code in ((torch.float32, F32), (torch.bfloat16, BF16), (torch.float16, oracle.F16)):
+        xs = oracle.to_storage(x, code)
+        for name, w in want.items():
+            w = getattr(t.to(dt), name)() if name != "logical_not" else t.to(dt).logical_not()
+            keep = ~np.isnan(x) if name == "signbit" else np.ones(8, bool)  # a NaN's sign is payload
+            np.testing.assert_array_equal(port.unary(name, xs, code)[keep], w.numpy().view(np.uint8)[keep],
+                                          err_msg=name)
+    xi = np.array([0, -1, 5, np.iinfo(np.int64).min], np.int64)
+    ti = torch.from_numpy(xi)
+    for name in ("isfinite", "isinf", "isnan", "signbit", "logical_not"):
+        np.testing.assert_array_equal(port.unary(name, xi, I64), getattr(ti, name)().numpy().view(np.uint8))
+    np.testing.assert_array_equal(port.unary("bitwise_not", xi, I64), (~ti).numpy())
+    x32 = xi[:3].astype(np.int32)
+    np.testing.assert_array_equal(port.unary("bitwise_not", x32, oracle.I32), ~x32)
+    xb = np.array([0, 1, 1, 0], np.uint8)
+    np.testing.assert_array_equal(port.unary("bitwise_not", xb, oracle.BOOL), 1 - xb)
+    np.testing.assert_array_equal(port.unary("logical_not", xb, oracle.BOOL), 1 - xb)
+
+
+def test_binary_tail_float_ops_vs_torch(port):
+    rng = np.random.default_rng(6)
+    a = (3 * rng.standard_normal(3000)).astype(np.float32)
+    b = (3 * rng.standard_normal(3000)).astype(np.float32)
+    a[:8] = [0.0, -0.0, 5.5, -5.5, 5.5, -5.5, np.inf, np.nan]
+    b[:8] = [1.0, 2.0, 2.0, 2.0, -2.0, -2.0, 3.0, 1.0]
+    ta, tb = torch.from_numpy(a), torch.from_numpy(b)
+    pa, pb = np.abs(a) + 0.1, np.abs(b) + 0.1
+    tpa, tpb = torch.from_numpy(pa), torch.from_numpy(pb)
+    u = (np.abs(np.tanh(b)) * 0.98 + 0.01).astype(np.float32)
+    tu = torch.from_numpy(u)
+    e = np.round(b).astype(np.float32)
+    cases = {
+        "pow": (pa, b, tpa.pow(tb)), "fmod": (a, b, ta.fmod(tb)), "remainder": (a, b, ta.remainder(tb)),
+        "atan2": (a, b, ta.atan2(tb)), "copysign": (a, b, ta.copysign(tb)), "hypot": (a, b, ta.hypot(tb)),
+        "xlogy": (a, pb, ta.xlogy(tpb)), "xlog1py": (a, pb, torch.special.xlog1py(ta, tpb)),
+        "logaddexp": (a, b, ta.logaddexp(tb)), "logaddexp2": (a, b, ta.logaddexp2(tb)),
+        "nextafter": (a, b, ta.nextafter(tb)), "heaviside": (a, b, ta.heaviside(tb)),
+        "rsub": (a, b, tb - ta), "tanh_backward": (a, u, ta * (1 - tu * tu)),
+        "sigmoid_backward": (a, u, ta * tu * (1 - tu)),
+        "silu_backward": (a, b, ta * (tb.sigmoid() * (1 + tb * (1 - tb.sigmoid())))),
+        "logit_backward": (a, u, ta / (tu * (1 - tu))), "mse_loss": (a, b, (ta - tb) ** 2),
+        "ldexp": (a, e, ta.ldexp(torch.from_numpy(e))),
+    }
+    exact = {"fmod", "remainder", "copysign", "nextafter", "heaviside", "rsub", "mse_loss", "ldexp"}
+    for name, (x, y, want) in cases.items():
+        got = port.binary(name, x, y, F32)
+        w = want.numpy()
+        if name == "heaviside":  # heaviside(NaN, y): the reference's functor falls through to y, torch gives 0
+            assert got[7] == y[7]
+            got, w = np.delete(got, 7), np.delete(w, 7)
+        np.testing.assert_array_equal(np.isnan(got), np.isnan(w), err_msg=name)
+        if name in exact:
+            np.testing.assert_array_equal(got[~np.isnan(w)], w[~np.isnan(w)], err_msg=name)
+        else:
+            fin = np.isfinite(w)
+            np.testing.assert_allclose(got[fin], w[fin], rtol=2e-5, atol=1e-6, err_msg=name)
+    tail = oracle.BINARY[oracle.BINARY.index("pow"):oracle.BINARY.index("bitwise_and")]
+    assert set(cases) == set(tail)
+
+
+def test_integer_and_logical_ops_vs_torch(port):
+    rng = np.random.default_rng(7)
+    a = rng.integers(-2 ** 40, 2 ** 40, 2000).astype(np.int64)
+    b = rng.integers(-50, 50, 2000).astype(np.int64)
+    a[:4] = [np.iinfo(np.int64).min, 0, -7, 7]
+    b[:4] = [-1, 0, 2, -2]
+    ta, tb = torch.from_numpy(a), torch.from_numpy(b)
+    sh = np.abs(b) % 70
+    tsh = torch.from_numpy(sh)
+    want = {"bitwise_and": ta & tb, "bitwise_or": ta | tb, "bitwise_xor": ta ^ tb,
+            "gcd": torch.gcd(ta, tb), "remainder": None, "fmod": None}
+    for name in ("bitwise_and", "bitwise_or", "bitwise_xor", "gcd"):
+        np.testing.assert_array_equal(port.binary(name, a, b, I64), want[name].numpy(), err_msg=name)
+    small = rng.integers(-1000, 1000, 2000).astype(np.int64)
+    np.testing.assert_array_equal(port.binary("lcm", small, b, I64),
+                                  torch.lcm(torch.from_numpy(small), tb).abs().numpy())
+    nz = b != 0
+    ok = nz & ~((a == np.iinfo(np.int64).min) & (b == -1))
+    np.testing.assert_array_equal(port.binary("remainder", a, b, I64)[ok], ta.remainder(torch.where(tb == 0, 1, tb)).numpy()[ok])
+    np.testing.assert_array_equal(port.binary("fmod", a, b, I64)[ok], ta.fmod(torch.where(tb == 0, 1, tb)).numpy()[ok])
+    assert (port.binary("remainder", a, b, I64)[~ok] == 0).all()  # b == 0 and INT64_MIN % -1 give 0
+    # shifts: counts in [0, 64) agree with torch; counts outside give 0 / the sign fill
+    inr = sh < 64
+    np.testing.assert_array_equal(port.binary("lshift", a, sh, I64)[inr], (ta << tsh).numpy()[inr])
+    np.testing.assert_array_equal(port.binary("rshift", a, sh, I64)[inr], (ta >> tsh).numpy()[inr])
+    assert (port.binary("lshift", a, sh, I64)[~inr] == 0).all()
+    np.testing.assert_array_equal(port.binary("rshift", a, sh, I64)[~inr], np.where(a[~inr] < 0, -1, 0))
+    assert (port.binary("rshift", a, -1 - sh, I64) == np.where(a < 0, -1, 0)).all()
+    a32, s32 = (a % 2 ** 31).astype(np.int32) * np.where(a < 0, -1, 1).astype(np.int32), (sh % 32).astype(np.int32)
+    t32, ts32 = torch.from_numpy(a32), torch.from_numpy(s32)
+    np.testing.assert_array_equal(port.binary("lshift", a32, s32, oracle.I32), (t32 << ts32).numpy())
+    np.testing.assert_array_equal(port.binary("rshift", a32, s32, oracle.I32), (t32 >> ts32).numpy())
+    np.testing.assert_array_equal(port.binary("bitwise_xor", a32, s32, oracle.I32), a32 ^ s32)
+    xb, yb = (a & 1).astype(np.uint8), (b & 1).astype(np.uint8)
+    for name, w in (("bitwise_and", xb & yb), ("bitwise_or", xb | yb), ("bitwise_xor", xb ^ yb),
+                    ("logical_and", xb & yb), ("logical_or", xb | yb), ("logical_xor", xb ^ yb)):
+        np.testing.assert_array_equal(port.binary(name, xb, yb, oracle.BOOL), w, err_msg=name)
+    fa = np.where(a % 3 == 0, 0.0, a).astype(np.float32)
+    fb = np.where(b % 2 == 0, 0.0, np.nan).astype(np.float32)
+    for name in ("logical_and", "logical_or", "logical_xor"):
+        w = getattr(torch, name)(torch.from_numpy(fa), torch.from_numpy(fb)).numpy().view(np.uint8)
+        np.testing.assert_array_equal(port.binary(name, fa, fb, F32), w, err_msg=name)
+        wi = getattr(torch, name)(ta, tb).numpy().view(np.uint8)
+        np.testing.assert_array_equal(port.binary(name, a, b, I64), wi, err_msg=name)
+
+
+def test_loss_ternaries_vs_torch(port):
+    rng = np.random.default_rng(8)
+    a = rng.standard_normal(500).astype(np.float32) * 2
+    b = rng.standard_normal(500).astype(np.float32) * 2
+    d = np.full(500, 1.25, np.float32)
+    F = torch.nn.functional
+    ta, tb = torch.from_numpy(a), torch.from_numpy(b)
+    np.testing.assert_allclose(port.ternary("huber_loss", a, b, d, F32),
+                               F.huber_loss(ta, tb, reduction="none", delta=1.25).numpy(), rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(port.ternary("smooth_l1_loss", a, b, d, F32),
+                               F.smooth_l1_loss(ta, tb, reduction="none", beta=1.25).numpy(), rtol=1e-6, atol=1e-7)

@@ -3,24 +3,29 @@
 #include "ew_kernels.cuh"
 
 namespace vb {
-static const char* const kBinaryNames[VBT_B200_B_COUNT] = {
+static const char* const kBinaryNames[kBinaryCore] = {
     "vt::add", "vt::sub", "vt::mul", "vt::div", "vt::maximum", "vt::minimum", "vt::fmax", "vt::fmin",
     "vt::eq", "vt::ne", "vt::lt", "vt::gt", "vt::le", "vt::ge"};
 
 static vbt_b200_status check_binary(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                                     int b_dtype, const char** name_out) {
-  VB_ARG(op >= 0 && op < VBT_B200_B_COUNT, "binary: unknown op code");
+  VB_ARG(op >= 0 && op < kBinaryCore, "binary: unknown op code");
   const char* name = kBinaryNames[op];
   *name_out = name;
   VB_ARG(out && a, std::string(name) + ": null tensor descriptor");
   VB_ARG(a->dtype == b_dtype, std::string(name) + ": dtype mismatch");
-  const bool cmp = op >= VBT_B200_B_EQ;
+  const bool cmp = binary_is_compare(op);
   VB_ARG(out->dtype == (cmp ? VBT_B200_BOOL : a->dtype), std::string(name) + ": output dtype mismatch");
   const int dt = a->dtype;
   VB_ARG(dt == VBT_B200_I64 || is_float_dtype(dt), std::string(name) + ": unsupported dtype");
   if (op == VBT_B200_B_DIV) VB_ARG(dt != VBT_B200_I64, std::string(name) + ": unsupported dtype");
   return VBT_B200_OK;
 }
+// ew_binary_ext.cu
+vbt_b200_status binary_ext(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                           const vbt_b200_tensor* b, void* stream);
+vbt_b200_status binary_scalar_ext(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                                  const void* scalar, int32_t scalar_on_left, void* stream);
 }  // namespace vb
 
 extern "C" vbt_b200_status vbt_b200_binary(int32_t op, const vbt_b200_tensor* out,
@@ -29,6 +34,7 @@ extern "C" vbt_b200_status vbt_b200_binary(int32_t op, const vbt_b200_tensor* ou
   using namespace vb;
   const char* name = "binary";
   VB_ARG(b != nullptr, "binary: null tensor descriptor");
+  if (op >= kBinaryCore && op < VBT_B200_B_COUNT) return binary_ext(op, out, a, b, stream);
   VB_TRY(check_binary(op, out, a, b->dtype, &name));
   const int dt = a->dtype;
   const vbt_b200_tensor* ops[3] = {out, a, b};
@@ -37,9 +43,9 @@ extern "C" vbt_b200_status vbt_b200_binary(int32_t op, const vbt_b200_tensor* ou
   DeviceScope scope(out->data);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   vbt_b200_status st = VBT_B200_OK;
-  dispatch_op<0, VBT_B200_B_COUNT>(op, [&](auto opc) {
+  dispatch_op<0, kBinaryCore>(op, [&](auto opc) {
     constexpr int OP = decltype(opc)::value;
-    if constexpr (OP >= VBT_B200_B_EQ) {
+    if constexpr (binary_is_compare(OP)) {
       if (dt == VBT_B200_I64)
         st = launch_ew<CompareF<OP, int64_t>, uint8_t, int64_t, int64_t, int64_t, 2>(plan, {}, s);
       else
@@ -62,6 +68,8 @@ extern "C" vbt_b200_status vbt_b200_binary_scalar(int32_t op, const vbt_b200_ten
   using namespace vb;
   const char* name = "binary";
   VB_ARG(a != nullptr && scalar != nullptr, "binary_scalar: null argument");
+  if (op >= kBinaryCore && op < VBT_B200_B_COUNT)
+    return binary_scalar_ext(op, out, a, scalar, scalar_on_left, stream);
   VB_TRY(check_binary(op, out, a, a->dtype, &name));
   const int dt = a->dtype;
   // the reference's scalar path takes Float32 / Int64 only (cuda_elementwise.cu:2953-2957)
@@ -74,9 +82,9 @@ extern "C" vbt_b200_status vbt_b200_binary_scalar(int32_t op, const vbt_b200_ten
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool left = scalar_on_left != 0;
   vbt_b200_status st = VBT_B200_OK;
-  dispatch_op<0, VBT_B200_B_COUNT>(op, [&](auto opc) {
+  dispatch_op<0, kBinaryCore>(op, [&](auto opc) {
     constexpr int OP = decltype(opc)::value;
-    constexpr bool CMP = OP >= VBT_B200_B_EQ;
+    constexpr bool CMP = binary_is_compare(OP);
     if (dt == VBT_B200_I64) {
       if constexpr (OP != VBT_B200_B_DIV) {
         int64_t v;

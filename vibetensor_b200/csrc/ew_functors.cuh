@@ -9,6 +9,15 @@
 
 namespace vb {
 
+// Op codes below these bounds are served by ew_unary.cu / ew_binary.cu / ew_ternary.cu with
+// every kernel variant; the codes above them by the *_ext translation units.
+constexpr int kUnaryCore = VBT_B200_U_HARDTANH + 1;
+constexpr int kBinaryCore = VBT_B200_B_GE + 1;
+constexpr bool binary_is_compare(int op) { return op >= VBT_B200_B_EQ && op <= VBT_B200_B_GE; }
+constexpr bool ternary_is_chain(int op) {
+  return op >= VBT_B200_T_ADDCMUL && op <= VBT_B200_T_WHERE_GT0_ADDCMUL;
+}
+
 template <int OP>
 __device__ __forceinline__ float unary_math(float a) {
   if constexpr (OP == VBT_B200_U_RELU) return a > 0.f ? a : 0.f;
@@ -176,6 +185,12 @@ struct TernaryF {
       return __fadd_rn(a, to_f(from_f<T>(__fmul_rn(b, c))));
     } else if constexpr (OP == VBT_B200_T_ADDCDIV) {
       return __fadd_rn(a, to_f(from_f<T>(__fdiv_rn(b, c))));
+    } else if constexpr (OP == VBT_B200_T_HUBER_LOSS) {
+      const float d = a - b, ad = fabsf(d);
+      return ad < c ? 0.5f * d * d : c * (ad - 0.5f * c);
+    } else if constexpr (OP == VBT_B200_T_SMOOTH_L1_LOSS) {
+      const float d = a - b, ad = fabsf(d);
+      return ad < c ? 0.5f * d * d / c : ad - 0.5f * c;
     } else {  // where(a > 0, a + b*c, 0): mul, add, gt, where of the reference, fused
       const float t2 = __fadd_rn(a, to_f(from_f<T>(__fmul_rn(b, c))));
       return a > 0.f ? t2 : 0.f;
@@ -186,7 +201,7 @@ struct TernaryF {
   }
   // Split form of the fused chains, fn(a, b, c) == fin(a, pre(b, c)): the kernel evaluates
   // pre once per thread when b and c do not change along the rows it walks.
-  static constexpr bool kSplit = OP >= VBT_B200_T_ADDCMUL;
+  static constexpr bool kSplit = ternary_is_chain(OP);
   __device__ __forceinline__ float pre(float b, float c) const {
     if constexpr (OP == VBT_B200_T_ADDCDIV) return to_f(from_f<T>(__fdiv_rn(b, c)));
     else return to_f(from_f<T>(__fmul_rn(b, c)));

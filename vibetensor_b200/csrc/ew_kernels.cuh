@@ -448,7 +448,10 @@ ew_transpose_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, c
 // Host: picks the kernel for the plan and launches it.  INV_SPECIAL >= 0 additionally
 // instantiates the tiled vector kernel for that compile-time invariance mask and uses it
 // when the plan's strides match it.
-template <class F, class TO, class T1, class T2, class T3, int NIN, int INV_SPECIAL = -1, int BC0_SPECIAL = 0>
+// LEAN leaves out the transposing kernels (used for the long tail of ops, to bound the size of
+// the library): such plans run on the tiled kernel, which takes any strides.
+template <class F, class TO, class T1, class T2, class T3, int NIN, int INV_SPECIAL = -1, int BC0_SPECIAL = 0,
+          bool LEAN = false>
 vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
   if (plan.numel == 0) return VBT_B200_OK;
   constexpr int kMaxEs = static_cast<int>(std::max({sizeof(TO), sizeof(T1), NIN >= 2 ? sizeof(T2) : size_t{1},
@@ -477,7 +480,7 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
     return VBT_B200_OK;
   }
 
-  {
+  if constexpr (!LEAN) {
     int dimj = -1;
     const int tmask = transpose_candidates(plan, &dimj);
     if (tmask != 0) {

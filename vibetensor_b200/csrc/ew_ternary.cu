@@ -4,7 +4,8 @@
 
 namespace vb {
 static const char* const kTernaryNames[VBT_B200_T_COUNT] = {
-    "vt::clamp", "vt::lerp", "vt::threshold", "vt::addcmul", "vt::addcdiv", "vt::where_gt0_addcmul"};
+    "vt::clamp", "vt::lerp", "vt::threshold", "vt::addcmul", "vt::addcdiv", "vt::where_gt0_addcmul",
+    "vt::huber_loss", "vt::smooth_l1_loss"};
 }
 
 extern "C" vbt_b200_status vbt_b200_ternary(int32_t op, const vbt_b200_tensor* out,
@@ -31,8 +32,8 @@ extern "C" vbt_b200_status vbt_b200_ternary(int32_t op, const vbt_b200_tensor* o
     // ... and where the first input is also a per-row scalar (broadcast along the output's
     // inner dim), which is the layout of a[n,1,h,1] + b[1,c,1,w] * c[n,c,1,w] written
     // channels-last: the per-element work shrinks to one add and one select.
-    constexpr int INV = OP >= VBT_B200_T_ADDCMUL ? 6 : -1;
-    constexpr int BC0 = OP >= VBT_B200_T_ADDCMUL ? 1 : 0;
+    constexpr int INV = ternary_is_chain(OP) ? 6 : -1;
+    constexpr int BC0 = ternary_is_chain(OP) ? 1 : 0;
     VB_DISPATCH_FLOAT(dt, T, (st = launch_ew<TernaryF<OP, T>, T, T, T, T, 3, INV, BC0>(plan, {}, s)));
   });
   return st;

@@ -3,17 +3,20 @@
 #include "ew_kernels.cuh"
 
 namespace vb {
-static const char* const kUnaryNames[VBT_B200_U_COUNT] = {
+static const char* const kUnaryNames[kUnaryCore] = {
     "vt::relu", "vt::neg", "vt::abs", "vt::square", "vt::exp", "vt::log", "vt::sqrt", "vt::rsqrt",
     "vt::sin", "vt::cos", "vt::tanh", "vt::sigmoid", "vt::silu", "vt::gelu", "vt::reciprocal",
     "vt::sign", "vt::floor", "vt::ceil", "vt::trunc", "vt::round", "vt::expm1", "vt::log1p",
     "vt::softplus", "vt::relu6", "vt::hardtanh"};
+vbt_b200_status unary_ext(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                          void* stream);  // ew_unary_ext.cu
 }  // namespace vb
 
 extern "C" vbt_b200_status vbt_b200_unary(int32_t op, const vbt_b200_tensor* out,
                                           const vbt_b200_tensor* a, void* stream) {
   using namespace vb;
   VB_ARG(op >= 0 && op < VBT_B200_U_COUNT, "unary: unknown op code");
+  if (op >= kUnaryCore) return unary_ext(op, out, a, stream);
   const char* name = kUnaryNames[op];
   VB_ARG(out && a, std::string(name) + ": null tensor descriptor");
   VB_ARG(out->dtype == a->dtype, std::string(name) + ": dtype mismatch");
@@ -27,7 +30,7 @@ extern "C" vbt_b200_status vbt_b200_unary(int32_t op, const vbt_b200_tensor* out
   DeviceScope scope(out->data);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   vbt_b200_status st = VBT_B200_OK;
-  const bool ok = dispatch_op<0, VBT_B200_U_COUNT>(op, [&](auto opc) {
+  const bool ok = dispatch_op<0, kUnaryCore>(op, [&](auto opc) {
     constexpr int OP = decltype(opc)::value;
     if (dt == VBT_B200_I64) {
       if constexpr (unary_int_ok(OP))

@@ -104,8 +104,10 @@ struct ArgR {
   static constexpr bool kIndexed = true;
   static constexpr I kNone = sizeof(I) == 4 ? static_cast<I>(INT_MAX) : static_cast<I>(LLONG_MAX);
   __device__ static acc_t init() { return acc_t{MAX ? lowest<A>() : highest<A>(), kNone}; }
+  // Every kernel feeds one accumulator indices in increasing order, so an equal value never
+  // displaces the one already held: the tie-break is only needed when partials meet (combine).
   __device__ static void accum(acc_t& a, A v, idx_t i) {
-    if ((MAX ? (v > a.v) : (v < a.v)) || (v == a.v && i < a.i)) { a.v = v; a.i = i; }
+    if (MAX ? (v > a.v) : (v < a.v)) { a.v = v; a.i = i; }
   }
   __device__ static acc_t combine(acc_t a, acc_t b) {
     return ((MAX ? (b.v > a.v) : (b.v < a.v)) || (b.v == a.v && b.i < a.i)) ? b : a;
@@ -180,6 +182,9 @@ template <class R, class A>
 __device__ __forceinline__ void finalize(const OutSpec& o, int64_t i, typename R::acc_t acc, A first) {
   if constexpr (R::kIndexed) {
     if (is_nan(first)) { acc.v = first; acc.i = 0; }
+    // nothing beat the identity: every element is the identity value (or NaN), the CPU scan
+    // keeps its first element
+    if (acc.i == R::kNone) acc.i = 0;
     if (o.out) store_value(o, i, acc.v);
     if (o.out_idx) o.out_idx[i] = static_cast<int64_t>(acc.i);
   } else {

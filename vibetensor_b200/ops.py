@@ -22,10 +22,21 @@ from ._lib import check, desc, i64_array, lib, stream_ptr
 
 UNARY = ["relu", "neg", "abs", "square", "exp", "log", "sqrt", "rsqrt", "sin", "cos", "tanh",
          "sigmoid", "silu", "gelu", "reciprocal", "sign", "floor", "ceil", "trunc", "round",
-         "expm1", "log1p", "softplus", "relu6", "hardtanh"]
+         "expm1", "log1p", "softplus", "relu6", "hardtanh",
+         "exp2", "log2", "log10", "sinh", "cosh", "asinh", "acosh", "atanh", "tan", "asin", "acos",
+         "atan", "erf", "erfc", "lgamma", "sinc", "frac", "deg2rad", "rad2deg", "mish", "selu", "elu",
+         "hardsigmoid", "hardshrink", "softshrink", "logit", "angle", "positive", "sgn", "nan_to_num",
+         "isfinite", "isinf", "isnan", "isneginf", "isposinf", "signbit", "logical_not", "bitwise_not"]
+UNARY_TO_BOOL = {"isfinite", "isinf", "isnan", "isneginf", "isposinf", "signbit", "logical_not"}
 BINARY = ["add", "sub", "mul", "div", "maximum", "minimum", "fmax", "fmin", "eq", "ne", "lt", "gt",
-          "le", "ge"]
-TERNARY = ["clamp", "lerp", "threshold", "addcmul", "addcdiv", "where_gt0_addcmul"]
+          "le", "ge",
+          "pow", "fmod", "remainder", "atan2", "copysign", "hypot", "xlogy", "xlog1py", "logaddexp",
+          "logaddexp2", "nextafter", "heaviside", "rsub", "tanh_backward", "sigmoid_backward",
+          "silu_backward", "logit_backward", "mse_loss", "ldexp", "bitwise_and", "bitwise_or",
+          "bitwise_xor", "lshift", "rshift", "gcd", "lcm", "logical_and", "logical_or", "logical_xor"]
+BINARY_TO_BOOL = {"eq", "ne", "lt", "gt", "le", "ge", "logical_and", "logical_or", "logical_xor"}
+TERNARY = ["clamp", "lerp", "threshold", "addcmul", "addcdiv", "where_gt0_addcmul", "huber_loss",
+           "smooth_l1_loss"]
 REDUCE = ["sum", "mean", "max", "min", "prod", "argmax", "argmin"]
 INDEX_WRAP, INDEX_STRICT, INDEX_CLAMP = 0, 1, 2
 
@@ -75,7 +86,7 @@ def _bshape(*ts):
 # --------------------------------------------------------------------------------------
 def unary(name: str, a: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _require_cuda(*([out] if out is not None else []), a)
-    o = _alloc_out(out, a.shape, a.dtype, a)
+    o = _alloc_out(out, a.shape, torch.bool if name in UNARY_TO_BOOL else a.dtype, a)
     do, da = desc(o), desc(a)
     check(lib().vbt_b200_unary(UNARY.index(name), do.ref, da.ref, stream_ptr(a)))
     return o
@@ -85,7 +96,7 @@ def binary(name: str, a, b, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """a, b: CUDA tensors of one dtype, or one of them a Python number (the reference's CPU
     0-d scalar operand, float32 / int64 tensors only)."""
     op = BINARY.index(name)
-    cmp_ = op >= BINARY.index("eq")
+    cmp_ = name in BINARY_TO_BOOL
     a_t, b_t = isinstance(a, torch.Tensor), isinstance(b, torch.Tensor)
     if a_t and b_t:
         _require_cuda(*([out] if out is not None else []), a, b)
@@ -176,6 +187,14 @@ for _n in TERNARY:
 clamp_min = globals()["maximum"]   # cuda_elementwise.cu:3912-3917
 clamp_max = globals()["minimum"]
 clip = globals()["clamp"]
+# names the reference registers on the same functors (cuda_elementwise.cu:3957-4276)
+true_divide = globals()["div"]
+celu = globals()["elu"]
+conj_physical = globals()["positive"]
+float_power = globals()["pow"]
+special_xlog1py = globals()["xlog1py"]
+bitwise_left_shift = globals()["lshift"]
+bitwise_right_shift = globals()["rshift"]
 
 
 def ti_plan(out: torch.Tensor, *inputs: torch.Tensor):
