@@ -358,7 +358,13 @@ def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4", "ew")
         ot = torch.empty_like(xt)
         ms = time_op(torch, lambda i: ops.copy_(ot, xt.t()), 10)
         add("contiguous() of a transposed view", "[16384,16384] fp32 transpose -> dense", 8 * nE, nE, ms)
-        del x, y, o, xb, yb, ob, cm, xt, ot
+        xbt = xb.view(1 << 14, 1 << 14)
+        obt = torch.empty_like(xbt)
+        ms = time_op(torch, lambda i: ops.copy_(obt, xbt.t()), 10)
+        add("contiguous() of a transposed view", "[16384,16384] bf16 transpose -> dense", 4 * nE, nE, ms)
+        ms = time_op(torch, lambda i: ops.add(xbt, xbt.t(), out=obt), 10)
+        add("add bf16, tensor + its transpose", "[16384,16384] bf16", 6 * nE, nE, ms)
+        del x, y, o, xb, yb, ob, cm, xt, ot, xbt, obt
     torch.cuda.empty_cache()
     return res
 

@@ -445,6 +445,114 @@ ew_transpose_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, c
   }
 }
 
+// Transposing variant for 16-bit outputs and staged inputs: a (64 x 64) tile, but every lane
+// moves FOUR elements (8 bytes) per access instead of two, so a warp instruction covers two
+// rows of 16 lanes.  Staged inputs are written to shared memory already transposed
+// (tile[j][i], 2-byte stores) with the 4-element groups of a row XOR-swizzled by the row's
+// group index: the 16 lanes of a half-warp then hit 16 different banks on the store, and the
+// 8-byte reads along i are conflict-free.  Needs sizes, strides and bases that keep groups of
+// four aligned; the host checks.
+template <class F, class TO, class T1, class T2, class T3, int NIN>
+__global__ void __launch_bounds__(kEwThreads)
+ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, const int tmask) {
+  constexpr int TILE = 64;
+  __shared__ __align__(16) uint16_t sm[kTrMaxStaged][TILE * TILE];
+  uint32_t b = blockIdx.x, t0, t1;
+  p.div_t0.divmod(b, b, t0);
+  p.div_t1.divmod(b, b, t1);
+  int64_t base[NIN + 1];
+#pragma unroll
+  for (int k = 0; k <= NIN; ++k) base[k] = 0;
+  for (int d = 0; d < p.n_outer; ++d) {
+    uint32_t c;
+    p.odiv[d].divmod(b, b, c);
+#pragma unroll
+    for (int k = 0; k <= NIN; ++k) base[k] += static_cast<int64_t>(c) * p.so[k][d];
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int h = lane >> 4, q = lane & 15;
+  const int64_t i0 = static_cast<int64_t>(t0) * TILE, j0 = static_cast<int64_t>(t1) * TILE;
+  const int64_t size0 = p.n0v;
+  const int slot2 = (tmask & 1) ? 1 : 0, slot3 = ((tmask & 1) ? 1 : 0) + ((tmask & 2) ? 1 : 0);
+  uint16_t* s1 = sm[0];
+  uint16_t* s2 = sm[slot2 < kTrMaxStaged ? slot2 : 0];
+  uint16_t* s3 = sm[slot3 < kTrMaxStaged ? slot3 : 0];
+  const T1* g1 = reinterpret_cast<const T1*>(p.ptr[1]) + base[1];
+  const T2* g2 = reinterpret_cast<const T2*>(p.ptr[NIN >= 2 ? 2 : 0]) + base[NIN >= 2 ? 2 : 0];
+  const T3* g3 = reinterpret_cast<const T3*>(p.ptr[NIN >= 3 ? 3 : 0]) + base[NIN >= 3 ? 3 : 0];
+  const int64_t a0 = p.s0[1], a1 = p.s1[1];
+  const int64_t b0 = p.s0[NIN >= 2 ? 2 : 0], b1 = p.s1[NIN >= 2 ? 2 : 0];
+  const int64_t c0 = p.s0[NIN >= 3 ? 3 : 0], c1 = p.s1[NIN >= 3 ? 3 : 0];
+  auto stage = [&](uint16_t* sdst, const void* gsrc, int64_t st0, int il, int64_t i, int64_t j) {
+    const uint2 v = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(gsrc) + i * st0 + j);
+    const int col = (((il >> 2) ^ q) << 2) + (il & 3);  // swizzled position of row-element il
+    uint16_t* d = sdst + (q * 4) * TILE + col;
+    d[0] = static_cast<uint16_t>(v.x & 0xffffu);
+    d[TILE] = static_cast<uint16_t>(v.x >> 16);
+    d[2 * TILE] = static_cast<uint16_t>(v.y & 0xffffu);
+    d[3 * TILE] = static_cast<uint16_t>(v.y >> 16);
+  };
+#pragma unroll
+  for (int r = 0; r < TILE / 16; ++r) {
+    const int il = w * 2 + h + 16 * r;
+    const int64_t i = i0 + il, j = j0 + q * 4;
+    if (i < size0 && j < p.size1) {
+      if constexpr (sizeof(T1) == 2) { if (tmask & 1) stage(s1, g1, a0, il, i, j); }
+      if constexpr (NIN >= 2 && sizeof(T2) == 2) { if (tmask & 2) stage(s2, g2, b0, il, i, j); }
+      if constexpr (NIN >= 3 && sizeof(T3) == 2) { if (tmask & 4) stage(s3, g3, c0, il, i, j); }
+    }
+  }
+  __syncthreads();
+  const bool k1 = !(tmask & 1) && a0 == 0 && a1 == 0;
+  const bool k2 = NIN >= 2 && !(tmask & 2) && b0 == 0 && b1 == 0;
+  const bool k3 = NIN >= 3 && !(tmask & 4) && c0 == 0 && c1 == 0;
+  T1 ka{};
+  T2 kb{};
+  T3 kc{};
+  if (k1) ka = g1[0];
+  if constexpr (NIN >= 2) { if (k2) kb = g2[0]; }
+  if constexpr (NIN >= 3) { if (k3) kc = g3[0]; }
+  TO* go = reinterpret_cast<TO*>(p.ptr[0]) + base[0];
+#pragma unroll
+  for (int r = 0; r < TILE / 16; ++r) {
+    const int jl = w * 2 + h + 16 * r;
+    const int64_t i = i0 + q * 4, j = j0 + jl;
+    if (i < size0 && j < p.size1) {
+      const int so = jl * TILE + ((q ^ ((jl >> 2) & 15)) << 2);
+      Vec<T1, 4> va;
+      Vec<T2, 4> vb{};
+      Vec<T3, 4> vc{};
+      if constexpr (sizeof(T1) == 2) {
+        if (tmask & 1) va = *reinterpret_cast<const Vec<T1, 4>*>(s1 + so);
+      }
+      if (!(tmask & 1) || sizeof(T1) != 2) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) va.v[e] = k1 ? ka : g1[(i + e) * a0 + j * a1];
+      }
+      if constexpr (NIN >= 2) {
+        if constexpr (sizeof(T2) == 2) {
+          if (tmask & 2) vb = *reinterpret_cast<const Vec<T2, 4>*>(s2 + so);
+        }
+        if (!(tmask & 2) || sizeof(T2) != 2) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) vb.v[e] = k2 ? kb : g2[(i + e) * b0 + j * b1];
+        }
+      }
+      if constexpr (NIN >= 3) {
+        if constexpr (sizeof(T3) == 2) {
+          if (tmask & 4) vc = *reinterpret_cast<const Vec<T3, 4>*>(s3 + so);
+        }
+        if (!(tmask & 4) || sizeof(T3) != 2) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) vc.v[e] = k3 ? kc : g3[(i + e) * c0 + j * c1];
+        }
+      }
+      const Vec<TO, 4> o = apply_vec<F, TO, T1, T2, T3, NIN, 4>(f, va, vb, vc);
+      *reinterpret_cast<Vec<TO, 4>*>(go + i + j * p.s1[0]) = o;
+    }
+  }
+}
+
 // Host: picks the kernel for the plan and launches it.  INV_SPECIAL >= 0 additionally
 // instantiates the tiled vector kernel for that compile-time invariance mask and uses it
 // when the plan's strides match it.
@@ -505,18 +613,20 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
         outer *= tpl.shape[d];
       }
       // element pairs: every staged input and the output must keep pairs aligned
-      auto pair_ok = [&](int k, bool along1) {
+      auto group_ok = [&](int k, bool along1, int g) {
         const int es = tpl.esize[k];
         if (es > 4) return false;
-        if (reinterpret_cast<uintptr_t>(tpl.ptr[k]) % (2 * es)) return false;
+        if (reinterpret_cast<uintptr_t>(tpl.ptr[k]) % (g * es)) return false;
         for (int d = 0; d < nd; ++d) {
           const bool unit = along1 ? d == 1 : d == 0;
-          if (unit ? tpl.stride[k][d] != 1 : (tpl.stride[k][d] % 2 != 0)) return false;
+          if (unit ? tpl.stride[k][d] != 1 : (tpl.stride[k][d] % g != 0)) return false;
         }
         return true;
       };
+      auto pair_ok = [&](int k, bool along1) { return group_ok(k, along1, 2); };
       bool pairs = sizeof(TO) <= 4 && sizeof(T1) <= 4 && (NIN < 2 || sizeof(T2) <= 4) && (NIN < 3 || sizeof(T3) <= 4) &&
                    tpl.shape[0] % 2 == 0 && tpl.shape[1] % 2 == 0 && pair_ok(0, false);
+      bool quads = sizeof(TO) == 2 && tpl.shape[0] % 4 == 0 && tpl.shape[1] % 4 == 0 && group_ok(0, false, 4);
       int staged = 0, use_mask = 0;
       for (int k = 1; k <= NIN; ++k)
         if ((tmask >> (k - 1)) & 1) {
@@ -524,7 +634,20 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
           ++staged;
           use_mask |= 1 << (k - 1);
           pairs = pairs && pair_ok(k, true);
+          quads = quads && tpl.esize[k] == 2 && group_ok(k, true, 4);
         }
+      if constexpr (sizeof(TO) == 2) {
+        const int64_t q0 = (tpl.shape[0] + 63) / 64, q1 = (tpl.shape[1] + 63) / 64;
+        if (quads && q0 * q1 * outer <= 0x7fffffff && tpl.shape[0] <= 0x7fffffff) {
+          tp.div_t0 = FastDiv(static_cast<uint32_t>(q0));
+          tp.div_t1 = FastDiv(static_cast<uint32_t>(q1));
+          tp.n0v = static_cast<uint32_t>(tpl.shape[0]);
+          tp.size1 = tpl.shape[1];
+          ew_transpose4_kernel<F, TO, T1, T2, T3, NIN><<<static_cast<unsigned>(q0 * q1 * outer), kEwThreads, 0, stream>>>(tp, f, use_mask);
+          VB_LAUNCH_CHECK();
+          return VBT_B200_OK;
+        }
+      }
       const int tile = pairs ? 64 : 32;
       const int64_t tiles0 = (tpl.shape[0] + tile - 1) / tile;
       const int64_t tiles1 = (tpl.shape[1] + tile - 1) / tile;

@@ -107,7 +107,10 @@ struct ArgR {
   // Every kernel feeds one accumulator indices in increasing order, so an equal value never
   // displaces the one already held: the tie-break is only needed when partials meet (combine).
   __device__ static void accum(acc_t& a, A v, idx_t i) {
-    if (MAX ? (v > a.v) : (v < a.v)) { a.v = v; a.i = i; }
+    // branch-free: one compare feeding two selects
+    const bool take = MAX ? (v > a.v) : (v < a.v);
+    a.v = take ? v : a.v;
+    a.i = take ? i : a.i;
   }
   __device__ static acc_t combine(acc_t a, acc_t b) {
     return ((MAX ? (b.v > a.v) : (b.v < a.v)) || (b.v == a.v && b.i < a.i)) ? b : a;
