@@ -262,7 +262,16 @@ def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4", "ew")
             add("softmax", f"C4 {list(shape)} {str(dt)[6:]}", 2 * n * es, n, ms)
             ms = time_op(torch, lambda i: kernels.rmsnorm(xs[i % nbuf], gamma, 1e-6), 20)
             add("rmsnorm", f"C4 {list(shape)} {str(dt)[6:]}", 2 * n * es + shape[1] * 4 + shape[0] * 4, n, ms)
-            del xs
+            # backward: the saved tensor rotates through the forward's buffers, dy has its own
+            inv = kernels.rmsnorm(xs[0], gamma, 1e-6)[1]
+            dyb = torch.randn(shape, device=dev, generator=g).to(dt)
+            ms = time_op(torch, lambda i: kernels.rmsnorm_backward(dyb, xs[i % nbuf], inv, gamma), 20)
+            add("rmsnorm_backward (dx, dgamma)", f"C4 {list(shape)} {str(dt)[6:]}",
+                3 * n * es + 2 * shape[1] * 4 + shape[0] * 4, n, ms, launches=2,
+                note="per-block dgamma partial rows + fixed-order fold, no atomics")
+            ms = time_op(torch, lambda i: kernels.softmax_backward(dyb, xs[i % nbuf]), 20)
+            add("softmax_backward", f"C4 {list(shape)} {str(dt)[6:]}", 3 * n * es, n, ms)
+            del xs, dyb
     if "c2" in which:
         # ---- C2: gather / scatter_add on a [1,048,576 x 256] table with 4,194,304 indices
         V, D, N = 1 << 20, 256, (1 << 19 if small else 1 << 22)

@@ -401,6 +401,31 @@ VBT_B200_API vbt_b200_status vbt_b200_rmsnorm(void* out, float* inv_rms, const v
                                  int32_t dtype, int64_t rows, int64_t cols, int64_t x_row_stride,
                                  float eps, void* stream);
 
+/* Backward of the row ops.  dy and y / x are [rows, cols] with column stride 1 and any row
+ * stride, dx is dense, all of one dtype (F32, BF16, F16); math in FP32.
+ *   softmax_backward      dx = y * (dy - sum(dy*y));  log_softmax: dx = dy - exp(y)*sum(dy)
+ *                         (SoftmaxBackward / LogSoftmaxBackward of
+ *                         vibe_kernels/softmax/impl/cutedsl_softmax/softmax.py:236-423, :640-828)
+ *   rmsnorm_backward      n = x*inv_rms; dx = inv_rms*(dy*gamma - n*mean(dy*gamma*n));
+ *                         dgamma[c] = sum over rows of dy*n  (F32 [cols], or NULL to skip)
+ *                         replaces Triton _rmsnorm_bwd_kernel + host wrapper
+ *                         (vibe_kernels/rmsnorm/vbt_native.py:110-176, :409-492), whose dgamma
+ *                         is a float atomic per element; here per-block partial rows in
+ *                         `workspace` (F32, 16-byte aligned; size from
+ *                         vbt_b200_rmsnorm_backward_workspace_bytes for the device the call
+ *                         runs on; only needed when dgamma != NULL) are folded in a fixed order
+ *                         by a second launch, so dgamma is reproducible run to run.          */
+VBT_B200_API vbt_b200_status vbt_b200_softmax_backward(void* dx, const void* dy, const void* y, int32_t dtype,
+                                          int64_t rows, int64_t cols, int64_t dy_row_stride,
+                                          int64_t y_row_stride, int32_t log_softmax, void* stream);
+VBT_B200_API vbt_b200_status vbt_b200_rmsnorm_backward_workspace_bytes(int64_t rows, int64_t cols, int32_t dtype,
+                                                          int32_t device, size_t* bytes);
+VBT_B200_API vbt_b200_status vbt_b200_rmsnorm_backward(void* dx, float* dgamma, const void* dy, const void* x,
+                                          const float* inv_rms, const float* gamma, int32_t dtype,
+                                          int64_t rows, int64_t cols, int64_t dy_row_stride,
+                                          int64_t x_row_stride, void* workspace, size_t workspace_bytes,
+                                          void* stream);
+
 /* =====================================================================================
  * 5. Fabric: sharded reductions and elementwise on a row-sharded tensor
  *    sits behind FabricTensor.sharded_1d_row (python/vibetensor/fabric.py:483-533) and

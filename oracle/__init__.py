@@ -127,6 +127,8 @@ class Port:
         L.vbo_index_put_lastdim.argtypes = [_int, _i64, _i64, _vp, _vp, _i64, _vp, _int, _int]
         L.vbo_softmax.argtypes = [_int, _i64, _i64, _vp, _i64, _vp, _int]
         L.vbo_rmsnorm.argtypes = [_int, _i64, _i64, _vp, _i64, _vp, ctypes.c_float, _vp, _vp]
+        L.vbo_softmax_backward.argtypes = [_int, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _int]
+        L.vbo_rmsnorm_backward.argtypes = [_int, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp]
         L.vbo_scale_cast.argtypes = [_int, _vp, _i64, ctypes.c_float, _vp]
         L.vbo_offset_elems.argtypes = [_i64, _int, _i64p, _i64p]
         L.vbo_offset_elems.restype = _i64
@@ -267,6 +269,26 @@ class Port:
         self.L.vbo_rmsnorm(dtype, x.shape[0], x.shape[1], _ptr(x), _estrides(x)[0],
                            _ptr(g) if g is not None else None, float(eps), _ptr(out), _ptr(inv))
         return out, inv
+
+    def softmax_backward(self, dy, y, dtype, log=False):
+        assert dy.shape == y.shape and y.ndim == 2
+        assert dy.strides[1] == dy.itemsize and y.strides[1] == y.itemsize
+        dx = np.zeros(y.shape, y.dtype)
+        self.L.vbo_softmax_backward(dtype, y.shape[0], y.shape[1], _ptr(dy), _estrides(dy)[0], _ptr(y),
+                                    _estrides(y)[0], _ptr(dx), int(log))
+        return dx
+
+    def rmsnorm_backward(self, dy, x, inv_rms, gamma, dtype):
+        assert dy.shape == x.shape and x.ndim == 2
+        assert dy.strides[1] == dy.itemsize and x.strides[1] == x.itemsize
+        dx = np.zeros(x.shape, x.dtype)
+        inv = np.ascontiguousarray(inv_rms, np.float32)
+        g = None if gamma is None else np.ascontiguousarray(gamma, np.float32)
+        dg = None if gamma is None else np.zeros(x.shape[1], np.float32)
+        self.L.vbo_rmsnorm_backward(dtype, x.shape[0], x.shape[1], _ptr(dy), _estrides(dy)[0], _ptr(x),
+                                    _estrides(x)[0], _ptr(inv), _ptr(g) if g is not None else None,
+                                    _ptr(dx), _ptr(dg) if dg is not None else None)
+        return dx, dg
 
     def scale_cast(self, partial, scale, out_dtype):
         partial = np.ascontiguousarray(partial, np.float32)

@@ -699,6 +699,71 @@ int vbo_rmsnorm(int dtype, int64_t rows, int64_t cols, const void* x, int64_t ro
   return 0;
 }
 
+/* Softmax / log_softmax backward (SoftmaxBackward / LogSoftmaxBackward,
+ * vibe_kernels/softmax/impl/cutedsl_softmax/softmax.py:405-423, :809-828):
+ *   softmax:     dx = y * (dy - sum(dy*y));   log_softmax: dx = dy - exp(log_y) * sum(dy).
+ * The row sum is a float reduction whose order is a schedule detail of the CuTe kernel; it is
+ * accumulated in double here and rounded once, so any float order agrees to a few ulp. */
+int vbo_softmax_backward(int dtype, int64_t rows, int64_t cols, const void* dy, int64_t dy_stride,
+                         const void* y, int64_t y_stride, void* dx, int log_softmax) {
+  const int es = itemsize(dtype);
+  for (int64_t r = 0; r < rows; ++r) {
+    const char* pd = (const char*)dy + r * dy_stride * es;
+    const char* py = (const char*)y + r * y_stride * es;
+    char* po = (char*)dx + r * cols * es;
+    double acc = 0.0;
+    for (int64_t j = 0; j < cols; ++j) {
+      const float a = load_f(pd + j * es, dtype), b = load_f(py + j * es, dtype);
+      acc += log_softmax ? (double)a : (double)a * (double)b;
+    }
+    const float s = (float)acc;
+    for (int64_t j = 0; j < cols; ++j) {
+      const float a = load_f(pd + j * es, dtype), b = load_f(py + j * es, dtype);
+      store_f(po + j * es, dtype, log_softmax ? a - expf(b) * s : b * (a - s));
+    }
+  }
+  return 0;
+}
+
+/* Triton _rmsnorm_bwd_kernel (vibe_kernels/rmsnorm/vbt_native.py:110-176): per row
+ *   normed = x*inv_rms; dot = sum(dy*gamma*normed) (block sums per chunk of BLOCK, added chunk
+ *   by chunk); dx = inv_rms*(dy*gamma - normed*dot/cols); grad_gamma[c] += dy*normed.
+ * grad_gamma is a float atomic per element there (order undefined): accumulated in double
+ * here and rounded once. */
+int vbo_rmsnorm_backward(int dtype, int64_t rows, int64_t cols, const void* dy, int64_t dy_stride,
+                         const void* x, int64_t x_stride, const float* inv_rms, const float* gamma,
+                         void* dx, float* dgamma) {
+  const int es = itemsize(dtype);
+  int64_t block = next_pow2(cols);
+  if (block > 256) block = 256;
+  float* pr = (float*)malloc(sizeof(float) * (size_t)(cols > 0 ? cols : 1));
+  float* tmp = (float*)malloc(sizeof(float) * (size_t)block);
+  double* gg = (double*)calloc((size_t)(cols > 0 ? cols : 1), sizeof(double));
+  for (int64_t r = 0; r < rows; ++r) {
+    const char* pd = (const char*)dy + r * dy_stride * es;
+    const char* px = (const char*)x + r * x_stride * es;
+    char* po = (char*)dx + r * cols * es;
+    const float inv = inv_rms[r];
+    for (int64_t j = 0; j < cols; ++j) {
+      const float a = load_f(pd + j * es, dtype), n = load_f(px + j * es, dtype) * inv;
+      gg[j] += (double)a * (double)n;
+      pr[j] = (gamma ? a * gamma[j] : a) * n;
+    }
+    const float dot_mean = block_tree_sum(pr, cols, block, tmp) / (float)cols;
+    for (int64_t j = 0; j < cols; ++j) {
+      const float a = load_f(pd + j * es, dtype), n = load_f(px + j * es, dtype) * inv;
+      const float ds = gamma ? a * gamma[j] : a;
+      store_f(po + j * es, dtype, inv * (ds - n * dot_mean));
+    }
+  }
+  if (dgamma)
+    for (int64_t j = 0; j < cols; ++j) dgamma[j] = (float)gg[j];
+  free(pr);
+  free(tmp);
+  free(gg);
+  return 0;
+}
+
 /* out[i] = cast(partial[i] * scale): finish of a sharded mean. */
 int vbo_scale_cast(int out_dtype, const float* partial, int64_t n, float scale, void* out) {
   for (int64_t i = 0; i < n; ++i)

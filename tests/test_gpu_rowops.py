@@ -123,3 +123,94 @@ def test_config4_full_size_properties(kernels, dtype, shape):
     rows = torch.arange(0, shape[0], max(1, shape[0] // 257), device="cuda")
     want = (x[rows].double().pow(2).mean(-1) + 1e-6).rsqrt()
     torch.testing.assert_close(inv[rows].double(), want, rtol=1e-5, atol=0)
+
+
+# ---- backward ------------------------------------------------------------------------------
+BWD_COLS = [8, 32, 64, 200, 256, 512, 1000, 1024, 2048, 4096, 8192, 16384, 20000, 33, 1]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cols", BWD_COLS)
+def test_softmax_backward(kernels, port, dtype, cols):
+    rng = np.random.default_rng(31)
+    rows = 70 if cols <= 4096 else 9
+    tol = TOL[dtype]
+    dy = _x(rng, rows, cols, dtype, 1.0)
+    for log in (False, True):
+        y = port.softmax(_x(rng, rows, cols, dtype), CODE[dtype], log=log)
+        fn = kernels.log_softmax_backward if log else kernels.softmax_backward
+        got = as_f32(to_np(fn(from_np(dy, dtype), from_np(y, dtype))), dtype)
+        want = as_f32(port.softmax_backward(dy, y, CODE[dtype], log=log), dtype)
+        # dx is a difference of O(|dy|) terms: absolute bound of a few float ulps of |dy| ~ 1
+        np.testing.assert_allclose(got, want, rtol=tol, atol=tol if dtype == torch.float32 else tol * 0.1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cols", BWD_COLS)
+def test_rmsnorm_backward(kernels, port, dtype, cols):
+    rng = np.random.default_rng(32)
+    rows = 700 if cols <= 256 else 70 if cols <= 4096 else 9
+    tol = TOL[dtype]
+    x = _x(rng, rows, cols, dtype)
+    dy = _x(rng, rows, cols, dtype, 1.0)
+    gamma = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    _, inv = port.rmsnorm(x, gamma, 1e-6, CODE[dtype])
+    tg = torch.from_numpy(gamma).cuda()
+    dx, dg = kernels.rmsnorm_backward(from_np(dy, dtype), from_np(x, dtype), torch.from_numpy(inv).cuda(), tg)
+    wdx, wdg = port.rmsnorm_backward(dy, x, inv, gamma, CODE[dtype])
+    np.testing.assert_allclose(as_f32(to_np(dx), dtype), as_f32(wdx, dtype), rtol=tol, atol=tol * 0.1)
+    # the reference's own test bound for fp32 RMSNorm (vibe_kernels/rmsnorm/tests/test_rmsnorm.py:19-46)
+    np.testing.assert_allclose(dg.cpu().numpy(), wdg, rtol=1e-4, atol=1e-4)
+    dx2, dg2 = kernels.rmsnorm_backward(from_np(dy, dtype), from_np(x, dtype), torch.from_numpy(inv).cuda())
+    assert dg2 is None
+    wdx2, _ = port.rmsnorm_backward(dy, x, inv, None, CODE[dtype])
+    np.testing.assert_allclose(as_f32(to_np(dx2), dtype), as_f32(wdx2, dtype), rtol=tol, atol=tol * 0.1)
+
+
+def test_backward_matches_torch_autograd_and_is_reproducible(kernels):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((513, 1536), device="cuda", generator=g, requires_grad=True)
+    dy = torch.randn((513, 1536), device="cuda", generator=g)
+    gamma = torch.rand((1536,), device="cuda", generator=g, requires_grad=True) + 0.5
+    gamma = gamma.detach().requires_grad_(True)
+    y, inv = kernels.rmsnorm(x.detach(), gamma.detach(), 1e-6)
+    dx, dg = kernels.rmsnorm_backward(dy, x.detach(), inv, gamma.detach())
+    wdx, wdg = torch.autograd.grad(torch.nn.functional.rms_norm(x, (1536,), gamma, 1e-6), (x, gamma), dy)
+    torch.testing.assert_close(dx, wdx, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(dg, wdg, rtol=1e-4, atol=1e-4)
+    for _ in range(3):  # fixed-order fold of the partial rows: bit-identical run to run
+        dx_b, dg_b = kernels.rmsnorm_backward(dy, x.detach(), inv, gamma.detach())
+        assert torch.equal(dg_b, dg) and torch.equal(dx_b, dx)
+    p = kernels.softmax(x.detach())
+    (w,) = torch.autograd.grad(torch.softmax(x, -1), x, dy)
+    torch.testing.assert_close(kernels.softmax_backward(dy, p), w, rtol=1e-4, atol=1e-6)
+    lp = kernels.log_softmax(x.detach())
+    (w,) = torch.autograd.grad(torch.log_softmax(x, -1), x, dy)
+    torch.testing.assert_close(kernels.log_softmax_backward(dy, lp), w, rtol=1e-4, atol=1e-5)
+
+
+def test_backward_row_strided_views_and_errors(kernels, port):
+    rng = np.random.default_rng(33)
+    base = oracle.to_storage(rng.standard_normal((40, 768), dtype=np.float32), oracle.F32)
+    dyb = oracle.to_storage(rng.standard_normal((40, 768), dtype=np.float32), oracle.F32)
+    x, dy = base[:, :512], dyb[:, 256:]                       # row stride 768, 512 columns
+    tx, tdy = torch.from_numpy(base).cuda()[:, :512], torch.from_numpy(dyb).cuda()[:, 256:]
+    gamma = np.ones(512, np.float32)
+    _, inv = port.rmsnorm(np.ascontiguousarray(x), gamma, 1e-6, oracle.F32)
+    dx, dg = kernels.rmsnorm_backward(tdy, tx, torch.from_numpy(inv).cuda(), torch.from_numpy(gamma).cuda())
+    wdx, wdg = port.rmsnorm_backward(dy, x, inv, gamma, oracle.F32)
+    np.testing.assert_allclose(dx.cpu().numpy(), wdx, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(dg.cpu().numpy(), wdg, rtol=1e-4, atol=1e-4)
+    y = port.softmax(np.ascontiguousarray(x), oracle.F32)
+    got = kernels.softmax_backward(tdy, torch.from_numpy(y).cuda())
+    np.testing.assert_allclose(got.cpu().numpy(), port.softmax_backward(np.ascontiguousarray(dy), y, oracle.F32),
+                               rtol=1e-5, atol=1e-7)
+    with pytest.raises(TypeError):
+        kernels.softmax_backward(tdy, tx.bfloat16())
+    with pytest.raises(ValueError):
+        kernels.softmax_backward(tdy[:, :100], tx)
+    with pytest.raises(RuntimeError):
+        kernels.rmsnorm_backward(tdy.cpu(), tx.cpu(), torch.from_numpy(inv))
+    e = torch.empty((0, 16), device="cuda")
+    dx, dg = kernels.rmsnorm_backward(e, e, torch.empty((0,), device="cuda"), torch.ones(16, device="cuda"))
+    assert dx.shape == (0, 16) and dg.tolist() == [0.0] * 16

@@ -436,3 +436,34 @@ def test_loss_ternaries_vs_torch(port):
                                F.huber_loss(ta, tb, reduction="none", delta=1.25).numpy(), rtol=1e-6, atol=1e-7)
     np.testing.assert_allclose(port.ternary("smooth_l1_loss", a, b, d, F32),
                                F.smooth_l1_loss(ta, tb, reduction="none", beta=1.25).numpy(), rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype,tol", [(F32, 2e-5), (BF16, 2e-2)])
+def test_row_op_backwards_vs_torch_autograd(port, dtype, tol):
+    """No CPU code for these in the reference: the restatement of its CuTe / Triton backward
+    kernels is pinned on torch autograd of the same forward, in float32 on the stored values."""
+    rng = np.random.default_rng(9)
+    rows, cols = 7, 300
+    x = rng.standard_normal((rows, cols)).astype(np.float32) * 2
+    dy = rng.standard_normal((rows, cols)).astype(np.float32)
+    gamma = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    xs, dys = oracle.to_storage(x, dtype), oracle.to_storage(dy, dtype)
+    tx = torch.from_numpy(oracle.to_f32(xs, dtype)).requires_grad_(True)
+    tdy = torch.from_numpy(oracle.to_f32(dys, dtype))
+    for log in (False, True):
+        ty = torch.log_softmax(tx, -1) if log else torch.softmax(tx, -1)
+        (want,) = torch.autograd.grad(ty, tx, tdy)
+        ys = oracle.to_storage(ty.detach().numpy(), dtype)
+        got = oracle.to_f32(port.softmax_backward(dys, ys, dtype, log=log), dtype)
+        np.testing.assert_allclose(got, want.numpy(), rtol=tol, atol=tol)
+    tg = torch.from_numpy(gamma).requires_grad_(True)
+    ty = torch.nn.functional.rms_norm(tx, (cols,), tg, 1e-6)
+    wdx, wdg = torch.autograd.grad(ty, (tx, tg), tdy)
+    _, inv = port.rmsnorm(xs, gamma, 1e-6, dtype)
+    dx, dg = port.rmsnorm_backward(dys, xs, inv, gamma, dtype)
+    np.testing.assert_allclose(oracle.to_f32(dx, dtype), wdx.numpy(), rtol=tol, atol=tol)
+    np.testing.assert_allclose(dg, wdg.numpy(), rtol=1e-4, atol=1e-4)
+    dx2, dg2 = port.rmsnorm_backward(dys, xs, inv, None, dtype)
+    assert dg2 is None
+    (wdx2,) = torch.autograd.grad(torch.nn.functional.rms_norm(tx, (cols,), None, 1e-6), tx, tdy)
+    np.testing.assert_allclose(oracle.to_f32(dx2, dtype), wdx2.numpy(), rtol=tol, atol=tol)

@@ -68,6 +68,10 @@ SIGNATURES = {
     "vbt_b200_index_status_check": (_i32, [_vp, ctypes.c_char_p, _i64, _vp]),
     "vbt_b200_softmax": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _i32, _vp]),
     "vbt_b200_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, ctypes.c_float, _vp]),
+    "vbt_b200_softmax_backward": (_i32, [_vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "vbt_b200_rmsnorm_backward_workspace_bytes": (_i32, [_i64, _i64, _i32, _i32, ctypes.POINTER(ctypes.c_size_t)]),
+    "vbt_b200_rmsnorm_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp,
+                                         ctypes.c_size_t, _vp]),
     "vbt_b200_enable_peer_access": (_i32, [_i32, _i32]),
     "vbt_b200_reduce_partial": (_i32, [_i32, _P, _P, _i64p, _i32, _i32, _vp, ctypes.c_size_t, _vp]),
     "vbt_b200_scale_cast": (_i32, [_vp, _i32, _vp, _i64, ctypes.c_float, _vp]),

@@ -4,6 +4,9 @@ Triton kernels compiled at run time:
 
 * ``softmax`` / ``log_softmax``  -- vibe_kernels/softmax/vbt_native.py:193-328
 * ``rmsnorm``                    -- vibe_kernels/rmsnorm/vbt_native.py:340-406
+* ``rmsnorm_backward``           -- vibe_kernels/rmsnorm/vbt_native.py:409-492
+* ``softmax_backward`` / ``log_softmax_backward``
+                                 -- vibe_kernels/softmax/impl/cutedsl_softmax/softmax.py:992-1017
 * ``gather`` / ``scatter_add``   -- vibe_kernels/indexing/vbt_native.py:197-280, :490-580
 
 Same argument meaning and the same exception classes for the same misuse (RuntimeError for a
@@ -93,6 +96,80 @@ def rmsnorm(x: torch.Tensor, gamma: Optional[torch.Tensor] = None, eps: float = 
                                  ctypes.c_void_p(gamma.data_ptr()) if gamma is not None else None,
                                  dtype_code(x.dtype), rows, cols, rs, float(eps), stream_ptr(x)))
     return out, inv
+
+
+def _softmax_backward(dy: torch.Tensor, y: torch.Tensor, log: bool) -> torch.Tensor:
+    what = "log_softmax_backward" if log else "softmax_backward"
+    if dy.shape != y.shape:
+        raise ValueError(f"{what}: dy and y must have the same shape")
+    if dy.dtype != y.dtype:
+        raise TypeError(f"{what}: dy and y must have the same dtype")
+    dyv, rows, cols, rs_dy = _rows_view(dy, what)
+    yv, _, _, rs_y = _rows_view(y, what)
+    dx = torch.empty(y.shape, dtype=y.dtype, device=y.device)
+    if rows == 0 or cols == 0:
+        return dx
+    check(lib().vbt_b200_softmax_backward(ctypes.c_void_p(dx.data_ptr()), ctypes.c_void_p(dyv.data_ptr()),
+                                          ctypes.c_void_p(yv.data_ptr()), dtype_code(y.dtype), rows, cols,
+                                          rs_dy, rs_y, int(log), stream_ptr(y)))
+    return dx
+
+
+def softmax_backward(dy: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """dx of y = softmax(x, -1): y * (dy - sum(dy * y))."""
+    return _softmax_backward(dy, y, False)
+
+
+def log_softmax_backward(dy: torch.Tensor, log_y: torch.Tensor) -> torch.Tensor:
+    """dx of log_y = log_softmax(x, -1): dy - exp(log_y) * sum(dy)."""
+    return _softmax_backward(dy, log_y, True)
+
+
+_bwd_ws: dict = {}  # (device index) -> float32 scratch for the dgamma partial rows
+
+
+def rmsnorm_backward(grad_output: torch.Tensor, x: torch.Tensor, inv_rms: torch.Tensor,
+                     gamma: Optional[torch.Tensor] = None):
+    """Returns (grad_input, grad_gamma); grad_gamma is None when gamma is None, float32
+    [hidden_size] otherwise.  inv_rms is the second result of ``rmsnorm``."""
+    what = "rmsnorm_backward"
+    if grad_output.shape != x.shape:
+        raise ValueError(f"{what}: grad_output and x must have the same shape")
+    if grad_output.dtype != x.dtype:
+        raise TypeError(f"{what}: grad_output and x must have the same dtype")
+    xv, rows, cols, rs_x = _rows_view(x, what)
+    gv, _, _, rs_g = _rows_view(grad_output, what)
+    if not inv_rms.is_cuda:
+        raise RuntimeError(f"{what} requires CUDA tensors")
+    if inv_rms.dtype != torch.float32 or inv_rms.numel() != rows:
+        raise TypeError("inv_rms must be float32 of shape [rows]")
+    inv_rms = inv_rms.contiguous()
+    if gamma is not None:
+        if not gamma.is_cuda:
+            raise RuntimeError(f"{what} requires CUDA tensors")
+        if gamma.dtype != torch.float32 or gamma.numel() != cols:
+            raise TypeError("gamma must be float32 of shape [hidden_size]")
+        gamma = gamma.contiguous()
+    dx = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    dgamma = torch.empty((cols,), dtype=torch.float32, device=x.device) if gamma is not None else None
+    ws, ws_bytes = None, 0
+    if dgamma is not None and cols:
+        need = ctypes.c_size_t()
+        check(lib().vbt_b200_rmsnorm_backward_workspace_bytes(rows, cols, dtype_code(x.dtype), x.device.index,
+                                                              ctypes.byref(need)))
+        ws = _bwd_ws.get(x.device.index)
+        if ws is None or ws.numel() * 4 < need.value:
+            ws = torch.empty((max(need.value // 4, 1),), dtype=torch.float32, device=x.device)
+            _bwd_ws[x.device.index] = ws
+        ws_bytes = ws.numel() * 4
+    if cols == 0:
+        return dx, dgamma
+    check(lib().vbt_b200_rmsnorm_backward(
+        ctypes.c_void_p(dx.data_ptr()), ctypes.c_void_p(dgamma.data_ptr()) if dgamma is not None else None,
+        ctypes.c_void_p(gv.data_ptr()), ctypes.c_void_p(xv.data_ptr()), ctypes.c_void_p(inv_rms.data_ptr()),
+        ctypes.c_void_p(gamma.data_ptr()) if gamma is not None else None, dtype_code(x.dtype), rows, cols,
+        rs_g, rs_x, ctypes.c_void_p(ws.data_ptr()) if ws is not None else None, ws_bytes, stream_ptr(x)))
+    return dx, dgamma
 
 
 def _check_gather_args(src, dim, index, what):
