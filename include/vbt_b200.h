@@ -378,6 +378,28 @@ VBT_B200_API vbt_b200_status vbt_b200_embedding_backward(const vbt_b200_tensor* 
                                             const vbt_b200_tensor* idx,
                                             const vbt_b200_tensor* grad_out, int64_t padding_idx,
                                             void* index_status, void* stream);
+/* The same with scale_grad_by_freq: every row's gradient is divided by the number of times the
+ * row occurs in idx (padding excluded) -- embedding_count_by_freq_i64_kernel +
+ * embedding_backward_accum_scaled_f32_kernel (embedding_cuda.cu:89-131).  `counts` is scratch,
+ * 4 bytes per weight row, cleared by the call. */
+VBT_B200_API vbt_b200_status vbt_b200_embedding_backward_by_freq(const vbt_b200_tensor* grad_weight,
+                                                    const vbt_b200_tensor* idx,
+                                                    const vbt_b200_tensor* grad_out, int64_t padding_idx,
+                                                    void* counts, size_t counts_bytes,
+                                                    void* index_status, void* stream);
+/* Boolean mask -> ascending INT64 indices of its true elements, on the stream, without a host
+ * pass over the mask.  Replaces the reference's bool-mask front end of advanced indexing
+ * (indexing_advanced_cuda.cu:2191-2429: CUB count + select, or D2H mask / host scan / H2D
+ * indices).  mask: BOOL, rank 1, any non-negative stride.  *count_out (device, 8 bytes)
+ * receives the number of true elements; positions are written to out_indices[0 .. min(count,
+ * capacity)).  Either call once with capacity = mask length, or call with capacity = 0, read
+ * the count, allocate, and call again.  workspace: 8-byte aligned, size from
+ * vbt_b200_mask_select_workspace_bytes(mask length).  The indices feed vbt_b200_index_lastdim /
+ * vbt_b200_index_rows like any other index tensor. */
+VBT_B200_API vbt_b200_status vbt_b200_mask_select_workspace_bytes(int64_t n, size_t* bytes);
+VBT_B200_API vbt_b200_status vbt_b200_mask_select(const vbt_b200_tensor* mask, int64_t* out_indices,
+                                     int64_t capacity, uint64_t* count_out, void* workspace,
+                                     size_t workspace_bytes, void* stream);
 /* Synchronises `stream`, reads the status block; OK if count == 0, else OUT_OF_RANGE with
  * message "<what>: index out of range ..." and clears the block. */
 VBT_B200_API vbt_b200_status vbt_b200_index_status_check(void* index_status, const char* what, int64_t dim_size,

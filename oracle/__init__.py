@@ -123,6 +123,7 @@ class Port:
         L.vbo_reduce.argtypes = [_int, _int, _int, _i64, _i64, _i64, _vp, _vp, _vp]
         L.vbo_gather_rows.argtypes = [_int, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _int, _vp]
         L.vbo_scatter_rows.argtypes = [_int, _i64, _i64, _vp, _vp, _i64, _vp, _int, _int, _int, _i64]
+        L.vbo_embedding_backward_by_freq.argtypes = [_i64, _i64, _vp, _vp, _i64, _vp, _int, _i64]
         L.vbo_index_lastdim.argtypes = [_int, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _int, _vp]
         L.vbo_index_put_lastdim.argtypes = [_int, _i64, _i64, _vp, _vp, _i64, _vp, _int, _int]
         L.vbo_softmax.argtypes = [_int, _i64, _i64, _vp, _i64, _vp, _int]
@@ -229,6 +230,16 @@ class Port:
         if rc:
             raise ValueError("oracle scatter rejected dtype")
         return table
+
+    def embedding_backward_by_freq(self, grad, idx, num_weights, padding_idx=None):
+        grad = np.ascontiguousarray(grad, np.float32)
+        idx = np.ascontiguousarray(idx, np.int64)
+        gw = np.zeros((num_weights, grad.shape[1]), np.float32)
+        rc = self.L.vbo_embedding_backward_by_freq(num_weights, grad.shape[1], _ptr(gw), _ptr(idx), idx.size,
+                                                   _ptr(grad), int(padding_idx is not None), int(padding_idx or 0))
+        if rc:
+            raise IndexError("index out of range")
+        return gw
 
     def index_lastdim(self, src, idx, policy=WRAP):
         B, K0 = src.shape

@@ -587,6 +587,28 @@ int vbo_scatter_rows(int dtype, int64_t V, int64_t D, void* table, const int64_t
   }
   return 0;
 }
+/* Embedding backward with scale_grad_by_freq (embedding_count_by_freq_i64_kernel and
+ * embedding_backward_accum_scaled_f32_kernel, src/vbt/ops/embedding_cuda.cu:89-131):
+ * counts[row] = occurrences of row outside padding; gw[row, :] += grad[i, :] * (1 / counts[row]),
+ * here in index order (the device order is undefined). */
+int vbo_embedding_backward_by_freq(int64_t V, int64_t D, float* gw, const int64_t* idx, int64_t N,
+                                   const float* grad, int use_padding, int64_t padding_idx) {
+  int64_t* counts = (int64_t*)calloc((size_t)(V > 0 ? V : 1), sizeof(int64_t));
+  for (int64_t i = 0; i < N; ++i) {
+    const int64_t v = idx[i];
+    if (use_padding && v == padding_idx) continue;
+    if (v < 0 || v >= V) { free(counts); return 3; }
+    counts[v]++;
+  }
+  for (int64_t i = 0; i < N; ++i) {
+    const int64_t v = idx[i];
+    if (use_padding && v == padding_idx) continue;
+    const float scale = 1.0f / (float)counts[v];
+    for (int64_t j = 0; j < D; ++j) gw[v * D + j] += grad[i * D + j] * scale;
+  }
+  free(counts);
+  return 0;
+}
 /* out[b, k] = src[b*sb + idx[k]*sk]: the reference's CUDA last-dim pattern
  * (advanced_index_gather_1d_kernel, indexing_advanced_cuda.cu:953-978). */
 int vbo_index_lastdim(int esize, int64_t B, int64_t K0, const void* src, int64_t sb, int64_t sk,

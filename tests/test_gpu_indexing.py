@@ -176,6 +176,24 @@ def test_embedding_backward_duplicates_and_padding(ops):
     np.testing.assert_allclose(gw, exp, rtol=1e-6, atol=1e-6)
 
 
+@pytest.mark.parametrize("D", [3, 64, 256, 1000])
+def test_embedding_backward_scale_grad_by_freq(ops, port, D):
+    rng = np.random.default_rng(36)
+    V, N = 300, 5000
+    ranks = np.minimum((rng.pareto(1.1, N) * 3).astype(np.int64), V - 1)     # heavy duplicates
+    idx = rng.permutation(V)[ranks].astype(np.int64)
+    g = rng.standard_normal((N, D)).astype(np.float32)
+    pad = int(idx[0])
+    got = ops.embedding_backward(torch.from_numpy(g).cuda(), torch.from_numpy(idx).cuda(), V, padding_idx=pad,
+                                 scale_grad_by_freq=True).cpu().numpy()
+    want = port.embedding_backward_by_freq(g, idx, V, padding_idx=pad)
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5)
+    assert not got[pad].any()
+    with pytest.raises(IndexError):
+        ops.embedding_backward(torch.from_numpy(g).cuda(), torch.from_numpy(idx + V).cuda(), V,
+                               scale_grad_by_freq=True)
+
+
 def test_lastdim_index_and_put(ops, port):
     rng = np.random.default_rng(35)
     src = rng.standard_normal((37, 50), dtype=np.float32)
@@ -288,3 +306,41 @@ def test_sorted_scatter_add_unique_rows_is_bit_exact_and_flags_bad_indices(ops, 
     keep[5] = False
     np.testing.assert_array_equal(
         acc3.cpu().numpy(), port.scatter_rows(np.zeros((V, D), np.float32), idx[keep], vf[keep], oracle.F32))
+
+
+@pytest.mark.parametrize("n", [1, 15, 16, 4095, 4096, 4097, 100003, 5_000_000])
+@pytest.mark.parametrize("density", [0.0, 0.01, 0.5, 1.0])
+def test_mask_to_indices(ops, n, density):
+    rng = np.random.default_rng(37)
+    m = rng.random(n) < density
+    got = ops.mask_to_indices(torch.from_numpy(m).cuda())
+    np.testing.assert_array_equal(got.cpu().numpy(), np.flatnonzero(m))
+
+
+def test_mask_strided_unaligned_and_truthy_bytes(ops):
+    rng = np.random.default_rng(38)
+    raw = rng.integers(0, 3, 30001).astype(np.uint8)          # bytes 0 / 1 / 2: any non-zero is true
+    t = torch.from_numpy(raw).cuda()
+    for view, ref in ((t[1:], raw[1:]), (t[::3], raw[::3]), (t[5::7], raw[5::7])):
+        got = ops.mask_to_indices(view.view(torch.bool))
+        np.testing.assert_array_equal(got.cpu().numpy(), np.flatnonzero(ref))
+    assert ops.mask_to_indices(torch.zeros((0,), dtype=torch.bool, device="cuda")).numel() == 0
+    with pytest.raises(ValueError, match="boolean mask"):
+        ops.mask_to_indices(torch.ones((2, 2), dtype=torch.bool, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.int64])
+def test_bool_mask_indexing(ops, port, dtype):
+    rng = np.random.default_rng(39)
+    src = rng.integers(-99, 100, (37, 501)).astype(np.float32 if dtype == torch.float32 else np.int64)
+    m = rng.random(501) < 0.3
+    ts = torch.from_numpy(src).cuda()
+    got = ops.index_mask_lastdim(ts, torch.from_numpy(m).cuda())
+    np.testing.assert_array_equal(got.cpu().numpy(), port.index_lastdim(src, np.flatnonzero(m)))
+    mr = rng.random(37) < 0.5
+    got = ops.index_mask_rows(ts, torch.from_numpy(mr).cuda())
+    np.testing.assert_array_equal(got.cpu().numpy(), port.gather_rows(src, np.flatnonzero(mr)))
+    with pytest.raises(ValueError, match="boolean mask"):
+        ops.index_mask_lastdim(ts.bfloat16() if dtype == torch.float32 else ts.int(), torch.from_numpy(m).cuda())
+    with pytest.raises(ValueError, match="boolean mask"):
+        ops.index_mask_lastdim(ts, torch.from_numpy(m[:100]).cuda())

@@ -467,3 +467,14 @@ def test_row_op_backwards_vs_torch_autograd(port, dtype, tol):
     assert dg2 is None
     (wdx2,) = torch.autograd.grad(torch.nn.functional.rms_norm(tx, (cols,), None, 1e-6), tx, tdy)
     np.testing.assert_allclose(oracle.to_f32(dx2, dtype), wdx2.numpy(), rtol=tol, atol=tol)
+
+
+def test_embedding_backward_scale_grad_by_freq_vs_torch(port):
+    rng = np.random.default_rng(10)
+    idx = rng.integers(0, 50, 400).astype(np.int64)
+    g = rng.standard_normal((400, 24)).astype(np.float32)
+    w = torch.zeros((50, 24), requires_grad=True)
+    out = torch.nn.functional.embedding(torch.from_numpy(idx), w, padding_idx=3, scale_grad_by_freq=True)
+    out.backward(torch.from_numpy(g))
+    np.testing.assert_allclose(port.embedding_backward_by_freq(g, idx, 50, padding_idx=3), w.grad.numpy(),
+                               rtol=1e-5, atol=1e-6)

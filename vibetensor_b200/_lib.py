@@ -65,6 +65,9 @@ SIGNATURES = {
     "vbt_b200_index_put_lastdim": (_i32, [_P, _P, _P, _i32, _i32, _vp, _vp]),
     "vbt_b200_embedding": (_i32, [_P, _P, _P, _vp, _vp]),
     "vbt_b200_embedding_backward": (_i32, [_P, _P, _P, _i64, _vp, _vp]),
+    "vbt_b200_mask_select_workspace_bytes": (_i32, [_i64, ctypes.POINTER(ctypes.c_size_t)]),
+    "vbt_b200_mask_select": (_i32, [_P, _vp, _i64, _vp, _vp, ctypes.c_size_t, _vp]),
+    "vbt_b200_embedding_backward_by_freq": (_i32, [_P, _P, _P, _i64, _vp, ctypes.c_size_t, _vp, _vp]),
     "vbt_b200_index_status_check": (_i32, [_vp, ctypes.c_char_p, _i64, _vp]),
     "vbt_b200_softmax": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _i32, _vp]),
     "vbt_b200_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, ctypes.c_float, _vp]),

@@ -152,6 +152,7 @@ struct ScatterParams {
   unsigned long long* status;
   int use_padding;
   int64_t padding_idx;
+  const unsigned* counts;  // float tables only: scale every row's sum by 1 / counts[row] (may be null)
 };
 
 template <class T> struct AddVec;
@@ -236,6 +237,13 @@ __global__ void __launch_bounds__(kThreads) scatter_add_rows_kernel(const __grid
     uint64_t cur = kSkipKey;  // current row (key >> 8), kSkipKey = none
     auto flush = [&](uint64_t row) {
       char* dst = p.table + static_cast<int64_t>(row) * row_bytes;
+      if constexpr (std::is_same_v<T, float>) {
+        if (p.counts != nullptr) {  // scale_grad_by_freq: this block's share of the row, over the row's count
+          const float sc = 1.0f / static_cast<float>(p.counts[row]);
+#pragma unroll
+          for (int k = 0; k < K; ++k) { acc[k].x *= sc; acc[k].y *= sc; acc[k].z *= sc; acc[k].w *= sc; }
+        }
+      }
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const uint32_t c = cb + k * 32 + lane;
@@ -285,6 +293,7 @@ struct ScatterElemParams {
   unsigned long long* status;
   int use_padding;
   int64_t padding_idx;
+  const unsigned* counts;  // as ScatterParams::counts
 };
 template <class T>
 __device__ __forceinline__ void atomic_add_elem(T* dst, T v);
@@ -302,7 +311,25 @@ __global__ void __launch_bounds__(kThreads) scatter_add_elem_kernel(const __grid
   int64_t v = p.idx.get(row);
   if (p.use_padding && v == p.padding_idx) return;
   if (!normalize(v, p.V, p.policy, p.status, j == 0)) return;
-  atomic_add_elem<T>(reinterpret_cast<T*>(p.table) + v * p.D + j, reinterpret_cast<const T*>(p.values)[e]);
+  T val = reinterpret_cast<const T*>(p.values)[e];
+  if constexpr (std::is_same_v<T, float>) {
+    if (p.counts != nullptr) val *= 1.0f / static_cast<float>(p.counts[v]);
+  }
+  atomic_add_elem<T>(reinterpret_cast<T*>(p.table) + v * p.D + j, val);
+}
+
+// occurrences of every in-range, non-padding row (embedding_count_by_freq_i64_kernel,
+// src/vbt/ops/embedding_cuda.cu:89-103); bad indices are reported by the accumulate pass
+__global__ void __launch_bounds__(kThreads) count_rows_kernel(IndexSrc idx, int64_t N, int64_t V, int policy,
+                                                              int use_padding, int64_t padding_idx,
+                                                              unsigned* counts) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < N;
+       i += static_cast<int64_t>(gridDim.x) * kThreads) {
+    int64_t v = idx.get(i);
+    if (use_padding && v == padding_idx) continue;
+    if (!normalize(v, V, policy, nullptr, false)) continue;
+    atomicAdd(&counts[v], 1u);
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -700,7 +727,7 @@ vbt_b200_status scatter_add_typed(const ScatterParams& p, const ScatterElemParam
 
 vbt_b200_status scatter_add_rows(const char* name, const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
                                  const vbt_b200_tensor* values, int policy, void* status, int use_padding,
-                                 int64_t padding_idx, cudaStream_t s) {
+                                 int64_t padding_idx, cudaStream_t s, unsigned* counts = nullptr) {
   VB_TRY(validate_tensor(table, name));
   VB_TRY(validate_tensor(values, name));
   VB_ARG(table->ndim == 2, std::string(name) + ": table must be rank 2");
@@ -731,9 +758,18 @@ vbt_b200_status scatter_add_rows(const char* name, const vbt_b200_tensor* table,
   p.status = static_cast<unsigned long long*>(status);
   p.use_padding = use_padding;
   p.padding_idx = padding_idx;
+  p.counts = counts;
   ScatterElemParams pe{};
   pe.table = p.table; pe.values = p.values; pe.idx = is; pe.N = N; pe.V = V; pe.D = D;
   pe.policy = policy; pe.status = p.status; pe.use_padding = use_padding; pe.padding_idx = padding_idx;
+  pe.counts = counts;
+  if (counts != nullptr) {
+    VB_ARG(dt == VBT_B200_F32, std::string(name) + ": scale_grad_by_freq needs a float32 table");
+    VB_CUDA(cudaMemsetAsync(counts, 0, static_cast<size_t>(V) * 4, s));
+    const unsigned g = static_cast<unsigned>(std::min<int64_t>((N + kThreads - 1) / kThreads, 148 * 8));
+    count_rows_kernel<<<g, kThreads, 0, s>>>(is, N, V, policy, use_padding, padding_idx, counts);
+    VB_LAUNCH_CHECK();
+  }
   switch (dt) {
     case VBT_B200_F32: return scatter_add_typed<float>(p, pe, chunked, s);
     case VBT_B200_I64: return scatter_add_typed<int64_t>(p, pe, chunked, s);
@@ -922,6 +958,18 @@ vbt_b200_status vbt_b200_embedding_backward(const vbt_b200_tensor* grad_weight, 
                                             void* index_status, void* stream) {
   return vb::scatter_add_rows("vt::embedding", grad_weight, idx, grad_out, VBT_B200_INDEX_STRICT,
                               index_status, 1, padding_idx, static_cast<cudaStream_t>(stream));
+}
+
+vbt_b200_status vbt_b200_embedding_backward_by_freq(const vbt_b200_tensor* grad_weight,
+                                                    const vbt_b200_tensor* idx, const vbt_b200_tensor* grad_out,
+                                                    int64_t padding_idx, void* counts, size_t counts_bytes,
+                                                    void* index_status, void* stream) {
+  using namespace vb;
+  VB_ARG(grad_weight != nullptr && grad_weight->ndim == 2, "vt::embedding: grad_weight must be rank 2");
+  VB_ARG(counts != nullptr && counts_bytes >= static_cast<size_t>(grad_weight->sizes[0]) * 4,
+         "vt::embedding: scale_grad_by_freq needs 4 bytes of count scratch per weight row");
+  return scatter_add_rows("vt::embedding", grad_weight, idx, grad_out, VBT_B200_INDEX_STRICT, index_status, 1,
+                          padding_idx, static_cast<cudaStream_t>(stream), static_cast<unsigned*>(counts));
 }
 
 vbt_b200_status vbt_b200_index_status_check(void* index_status, const char* what, int64_t dim_size,

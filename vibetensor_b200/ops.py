@@ -400,6 +400,44 @@ def index_lastdim(src: torch.Tensor, idx: torch.Tensor, status=None, eager_check
     return o
 
 
+def mask_to_indices(mask: torch.Tensor) -> torch.Tensor:
+    """Ascending int64 positions of the true elements of a 1-D bool mask, computed on the
+    device.  Reads the count back (one 8-byte D2H copy and a stream synchronise, as the
+    reference's bool-mask path does) to size the result."""
+    _require_cuda(mask)
+    if mask.dtype != torch.bool:
+        raise ValueError("index: mask must be a bool tensor")
+    if mask.dim() != 1:
+        raise ValueError("index: CUDA advanced indexing does not support boolean mask indices of rank other than 1")
+    n = mask.numel()
+    need = ctypes.c_size_t()
+    check(lib().vbt_b200_mask_select_workspace_bytes(n, ctypes.byref(need)))
+    ws = torch.empty((max(need.value // 8, 1),), dtype=torch.int64, device=mask.device)
+    idx = torch.empty((n,), dtype=torch.int64, device=mask.device)
+    count = torch.empty((1,), dtype=torch.int64, device=mask.device)
+    dm = desc(mask)
+    check(lib().vbt_b200_mask_select(dm.ref, ctypes.c_void_p(idx.data_ptr()), n, ctypes.c_void_p(count.data_ptr()),
+                                     ctypes.c_void_p(ws.data_ptr()), ws.numel() * 8, stream_ptr(mask)))
+    return idx[: int(count.item())]
+
+
+def index_mask_lastdim(src: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """``src[..., mask]`` for 2-D src and a 1-D bool mask over its last dim: the form the
+    reference's CUDA bool-mask indexing takes (float32 / int64 data only, as there)."""
+    if src.dtype not in (torch.float32, torch.int64):
+        raise ValueError("index: CUDA advanced indexing does not support boolean mask indices")
+    if mask.dim() != 1 or mask.numel() != src.shape[-1]:
+        raise ValueError("index: CUDA advanced indexing does not support boolean mask indices")
+    return index_lastdim(src, mask_to_indices(mask), eager_check=False)
+
+
+def index_mask_rows(src: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """``src[mask]`` for a 1-D bool mask over dim 0 (row compaction)."""
+    if mask.dim() != 1 or mask.numel() != src.shape[0]:
+        raise ValueError("index: mask length must equal the size of dim 0")
+    return index_rows(src, mask_to_indices(mask), eager_check=False)
+
+
 def index_put_lastdim_(self_: torch.Tensor, idx, values, accumulate=False, status=None,
                        eager_check=True):
     _require_cuda(self_, idx, values)
@@ -425,15 +463,23 @@ def embedding(weight: torch.Tensor, indices: torch.Tensor, status=None, eager_ch
 
 
 def embedding_backward(grad_out: torch.Tensor, indices: torch.Tensor, num_weights: int,
-                       padding_idx: int = -1, status=None, eager_check=True) -> torch.Tensor:
-    """Dense weight gradient: gw[idx[i], :] += grad_out[i, :], padding_idx rows skipped."""
+                       padding_idx: int = -1, status=None, eager_check=True,
+                       scale_grad_by_freq: bool = False) -> torch.Tensor:
+    """Dense weight gradient: gw[idx[i], :] += grad_out[i, :], padding_idx rows skipped; with
+    scale_grad_by_freq every row's gradient is divided by the row's number of occurrences."""
     _require_cuda(grad_out, indices)
     st, own = _status(status, eager_check, grad_out.device)
     D = grad_out.shape[-1]
     gw = torch.zeros((num_weights, D), dtype=grad_out.dtype, device=grad_out.device)
     dg, di, do = desc(gw), desc(indices), desc(grad_out.reshape(-1, D))
-    check(lib().vbt_b200_embedding_backward(dg.ref, di.ref, do.ref, int(padding_idx),
-                                            st.ptr if st else None, stream_ptr(gw)))
+    if scale_grad_by_freq:
+        counts = torch.empty((max(num_weights, 1),), dtype=torch.int32, device=grad_out.device)
+        check(lib().vbt_b200_embedding_backward_by_freq(dg.ref, di.ref, do.ref, int(padding_idx),
+                                                        ctypes.c_void_p(counts.data_ptr()), counts.numel() * 4,
+                                                        st.ptr if st else None, stream_ptr(gw)))
+    else:
+        check(lib().vbt_b200_embedding_backward(dg.ref, di.ref, do.ref, int(padding_idx),
+                                                st.ptr if st else None, stream_ptr(gw)))
     if own:
         st.check("vt::embedding", num_weights)
     return gw
