@@ -25,7 +25,8 @@ Headline line (one JSON object on stdout, printed by rank 0):
             (vbt_default_sum_impl compiled from its sources) on a bounded sample.
 
 --impl reference times the reference's CPU implementation of the headline workload on the
-host cores (bounded sample per step) and prints the same line with "impl": "reference".
+host cores -- one thread per slice, every thread running the reference's (single-threaded) sum,
+a bounded sample per step -- and prints the same line with "impl": "reference".
 """
 from __future__ import annotations
 
@@ -141,30 +142,44 @@ def run_reference(args):
     rank, _, world = env_ranks()
     if rank != 0:
         return
-    sample = 1 << 27  # 512 MiB of the 16 GiB tensor per step
+    # The reference's CPU sum is single-threaded code; the workload is a sharded sum, so the
+    # host's threads each take one slice (as the reference's Fabric takes one shard per device)
+    # and the per-slice partials are added on the host.
+    import concurrent.futures as cf
     import numpy as np
     import oracle
+    threads = max(1, min(os.cpu_count() or 1, 64))
+    per_thread = max(1 << 22, (1 << 29) // threads)  # about 2 GiB of the 16 GiB tensor per step in all
+    sample = threads * per_thread
     rng = np.random.default_rng(4)
-    x = rng.standard_normal(sample, dtype=np.float32)
+    xs = [rng.standard_normal(per_thread, dtype=np.float32) for _ in range(threads)]
     if oracle.have_ref():
-        fn, kind = (lambda: oracle.ref().sum(x, oracle.F32, [])), "reference"
+        ref = oracle.ref()
+        one, kind = (lambda x: float(ref.sum(x, oracle.F32, []))), "reference"
     else:
-        fn, kind = (lambda: oracle.port().reduce("sum", x, oracle.F32)), "port"
+        port = oracle.port()
+        one, kind = (lambda x: float(port.reduce("sum", x, oracle.F32))), "port"
+    pool = cf.ThreadPoolExecutor(max_workers=threads)
+
+    def fn():
+        return sum(pool.map(one, xs))
     for _ in range(max(1, min(args.warmup, 3))):
         fn()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         fn()
     dt = (time.perf_counter() - t0) / args.steps
+    pool.shutdown()
     value = sample / dt
-    sample_desc = f"{sample} of {TOTAL_ELEMS} fp32 elements per step (contiguous slice), 1 thread"
+    sample_desc = (f"{sample} of {TOTAL_ELEMS} fp32 elements per step ({threads} contiguous slices of "
+                   f"{per_thread}), {threads} threads")
     line = {
         "impl": "reference", "metric": "sharded fp32 sum throughput (elements/s; HBM GB/s in roofline)",
         "value": value, "unit": "elements/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": value, "unit": "elements/s", "cores": 1, "kind": kind, "sample": sample_desc},
+        "cpu_baseline": {"value": value, "unit": "elements/s", "cores": threads, "kind": kind, "sample": sample_desc},
         "e2e": {"value": value, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "host_cores": os.cpu_count(),
     }

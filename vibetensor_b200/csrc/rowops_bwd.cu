@@ -169,9 +169,10 @@ __global__ void __launch_bounds__(kBwdThreads) rowop_bwd_kernel(const __grid_con
           } else if constexpr (KIND == B_LOG_SOFTMAX) {
             s[i] += av;
           } else {
-            const float n = bv * inv[i];             // normalised input
-            ggk[e] = fmaf(av, n, ggk[e]);
-            s[i] = fmaf(av * gk[e], n, s[i]);
+            // dy * x once; 1/rms enters dgamma through the fma and the row sum after the loop
+            const float dyx = av * bv;
+            ggk[e] = fmaf(dyx, inv[i], ggk[e]);
+            s[i] = fmaf(dyx, gk[e], s[i]);
           }
         }
       if constexpr (KIND == B_RMSNORM) {
@@ -185,7 +186,8 @@ __global__ void __launch_bounds__(kBwdThreads) rowop_bwd_kernel(const __grid_con
       if (!live[i]) continue;
       const int64_t row = r0 + i * R + rl;
       T* orow = static_cast<T*>(p.dx) + row * p.cols;
-      const float dm = s[i] / static_cast<float>(p.cols);
+      // rmsnorm: s = sum(dy*gamma*x); dx = r*dy*gamma - x * r^3 * s / cols
+      const float c2 = inv[i] * inv[i] * (s[i] * inv[i] / static_cast<float>(p.cols));
 #pragma unroll
       for (int k = 0; k < VPL; ++k) {
         const int j = tl + k * TPR;
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(kBwdThreads) rowop_bwd_kernel(const __grid_con
           float r;
           if constexpr (KIND == B_SOFTMAX) r = bv * (av - s[i]);
           else if constexpr (KIND == B_LOG_SOFTMAX) r = av - expf(bv) * s[i];
-          else r = inv[i] * (av * gk[e] - bv * inv[i] * dm);
+          else r = fmaf(av * gk[e], inv[i], -(bv * c2));
           raw.v[e] = from_f<T>(r);
         }
         *reinterpret_cast<Vec<T, V>*>(orow + static_cast<int64_t>(j) * V) = raw;
