@@ -339,11 +339,11 @@ __global__ void __launch_bounds__(kThreads) count_rows_kernel(IndexSrc idx, int6
 // 64-bit integer rows (256 scalar atomics per 2 KiB row) the L2 atomic units, not HBM, set
 // the pace.  Sorting ALL updates by destination row first makes every row one contiguous
 // run: a warp walks 32 sorted entries, sums each run in update order in registers, and a
-// run that lies wholly inside the warp's slice is the ONLY writer of its row, so it is
-// finished with a plain read-add-write.  Only runs that cross a slice boundary (rows with
-// more updates than a slice holds) use atomics.  Results are exact for integers; for fp32
-// every row updated from a single slice is summed in update order -- bit-identical to a
-// sequential loop when the destination starts at zero -- and independent of scheduling.
+// run that lies wholly inside the warp's slice is the ONLY writer of its row, so it starts
+// from the row's old contents and ends with a plain store.  Only runs that cross a slice
+// boundary (rows with more updates than a slice holds) use atomics.  Results are exact for
+// integers; for fp32 every row updated from a single slice is old + u1 + u2 + ... in update
+// order -- bit-identical to a sequential loop -- and independent of scheduling.
 //
 // Sort: LSD radix, 8 bits per pass over just the bits the row range needs; per pass a
 // block histogram, one exclusive scan, and a stable scatter (ranks from __match_any_sync).
@@ -504,30 +504,25 @@ struct SortedScatterParams {
   uint32_t cpr;
 };
 
-template <class T> struct PlainAdd;
-template <> struct PlainAdd<float> {
-  __device__ static void rmw(char* dst, const float4& a) {
-    float4 t = *reinterpret_cast<const float4*>(dst);
-    t.x += a.x; t.y += a.y; t.z += a.z; t.w += a.w;
-    *reinterpret_cast<float4*>(dst) = t;
+template <class T> struct PlainStore;
+template <> struct PlainStore<float> {
+  __device__ static void st(char* dst, const float4& a) { *reinterpret_cast<float4*>(dst) = a; }
+};
+template <> struct PlainStore<int64_t> {
+  __device__ static void st(char* dst, const AddVec<int64_t>::acc_t& a) {
+    *reinterpret_cast<ulonglong2*>(dst) = make_ulonglong2(a.a, a.b);
   }
 };
-template <> struct PlainAdd<int64_t> {
-  __device__ static void rmw(char* dst, const AddVec<int64_t>::acc_t& a) {
-    ulonglong2 t = *reinterpret_cast<const ulonglong2*>(dst);
-    t.x += a.a; t.y += a.b;
-    *reinterpret_cast<ulonglong2*>(dst) = t;
-  }
-};
-template <> struct PlainAdd<int32_t> {
-  __device__ static void rmw(char* dst, const uint4& a) {
-    uint4 t = *reinterpret_cast<const uint4*>(dst);
-    t.x += a.x; t.y += a.y; t.z += a.z; t.w += a.w;
-    *reinterpret_cast<uint4*>(dst) = t;
-  }
+template <> struct PlainStore<int32_t> {
+  __device__ static void st(char* dst, const uint4& a) { *reinterpret_cast<uint4*>(dst) = a; }
 };
 
-// one warp per slice of 32 sorted entries
+// One warp per slice of 32 sorted entries.  A run (equal keys) that lies wholly inside the
+// slice has this warp as the only writer of its row: the row's old contents are fetched
+// TOGETHER with the run's first update (so the read of the destination is one more load in
+// flight, not a dependent round trip at the end of the run), the updates are added to them in
+// update order, and the sum is stored back.  Runs that continue from the previous slice or
+// into the next one are summed from zero and added with atomics.
 template <class T, int K>
 __global__ void __launch_bounds__(kThreads) scatter_add_sorted_kernel(const __grid_constant__ SortedScatterParams p) {
   using AV = AddVec<T>;
@@ -544,13 +539,13 @@ __global__ void __launch_bounds__(kThreads) scatter_add_sorted_kernel(const __gr
   const uint32_t prev_last = s0 > 0 ? p.keys[s0 - 1] : 0xffffffffu;
   const uint32_t next_first = s0 + 32 < p.N ? p.keys[s0 + 32] : 0xffffffffu;
   const int64_t row_bytes = static_cast<int64_t>(p.cpr) * 16;
-  constexpr int U = K >= 4 ? 2 : 4;
+  constexpr int U = 2;
   for (uint32_t cb = 0; cb < p.cpr; cb += 32 * K) {
     acc_t acc[K];
 #pragma unroll
     for (int k = 0; k < K; ++k) acc[k] = AV::zero();
     uint32_t cur = skip;      // row of the open run (skip = none)
-    bool cur_shared = false;  // the open run started in an earlier slice
+    bool cur_shared = false;  // the open run also has updates in a neighbouring slice
     auto flush = [&](uint32_t row, bool shared) {
       char* dst = p.table + static_cast<int64_t>(row) * row_bytes;
 #pragma unroll
@@ -558,41 +553,55 @@ __global__ void __launch_bounds__(kThreads) scatter_add_sorted_kernel(const __gr
         const uint32_t c = cb + k * 32 + lane;
         if (c < p.cpr) {
           if (shared) AV::flush(dst + static_cast<int64_t>(c) * 16, acc[k]);
-          else PlainAdd<T>::rmw(dst + static_cast<int64_t>(c) * 16, acc[k]);
+          else PlainStore<T>::st(dst + static_cast<int64_t>(c) * 16, acc[k]);
         }
         acc[k] = AV::zero();
       }
     };
+    uint32_t key_before = 0xffffffffu;  // key of the entry in front of the group (none before entry 0)
     for (int e0 = 0; e0 < 32; e0 += U) {
       uint32_t key[U];
-      int4 raw[U][K];
+      bool head[U], shared[U];
+      int4 raw[U][K], old[U][K];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         key[u] = __shfl_sync(0xffffffffu, my_key, e0 + u);
         const uint32_t pos = __shfl_sync(0xffffffffu, my_pos, e0 + u);
+        const uint32_t before = u == 0 ? key_before : key[u - 1];
+        head[u] = key[u] != skip && (e0 + u == 0 || key[u] != before);
+        shared[u] = (e0 + u == 0 && key[u] == prev_last) || key[u] == next_first;
         if (key[u] != skip) {
           const char* src = p.values + static_cast<int64_t>(pos) * row_bytes;
+          const char* dst = p.table + static_cast<int64_t>(key[u]) * row_bytes;
+          const bool fetch_old = head[u] && !shared[u];
 #pragma unroll
           for (int k = 0; k < K; ++k) {
             const uint32_t c = cb + k * 32 + lane;
             raw[u][k] = c < p.cpr ? *reinterpret_cast<const int4*>(src + static_cast<int64_t>(c) * 16)
                                   : make_int4(0, 0, 0, 0);
+            old[u][k] = (fetch_old && c < p.cpr) ? *reinterpret_cast<const int4*>(dst + static_cast<int64_t>(c) * 16)
+                                                 : make_int4(0, 0, 0, 0);
           }
         }
       }
+      key_before = key[U - 1];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         if (key[u] == skip) continue;  // skipped updates sort to the very end
-        if (key[u] != cur) {
+        if (head[u]) {
           if (cur != skip) flush(cur, cur_shared);
           cur = key[u];
-          cur_shared = (e0 + u == 0) && (cur == prev_last);
+          cur_shared = shared[u];
+          if (!cur_shared) {
+#pragma unroll
+            for (int k = 0; k < K; ++k) AV::add(acc[k], old[u][k]);  // start from the row's contents
+          }
         }
 #pragma unroll
         for (int k = 0; k < K; ++k) AV::add(acc[k], raw[u][k]);
       }
     }
-    if (cur != skip) flush(cur, cur_shared || cur == next_first);
+    if (cur != skip) flush(cur, cur_shared);
   }
 }
 

@@ -67,7 +67,7 @@ __device__ __forceinline__ void load_raw(const T* row, int first, int step, int 
 // registers in their storage type (16-bit rows cost half the registers of their float form,
 // which pays for the second row in flight) and are widened where they are used.
 template <class T, int KIND, int TPR, int VPL, int RIF>
-__global__ void __launch_bounds__(kBwdThreads) rowop_bwd_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads, VPL * (16 / sizeof(T)) <= 16 ? 2 : 1) rowop_bwd_kernel(const __grid_constant__ BwdParams p) {
   constexpr int V = 16 / sizeof(T);
   constexpr int R = kBwdThreads / TPR;           // row slots per block
   constexpr int kWarpsPerRow = TPR > 32 ? TPR / 32 : 1;
