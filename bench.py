@@ -326,6 +326,20 @@ def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4", "ew")
             N * D * 8 + N * 8 + 2 * U * D * 8, N * D, ms, note="block-local aggregation + 64-bit atomics")
         st.check("bench", V)
         del updi, acci
+        # ---- the reference's CUDA advanced-index form x[..., idx] and the bool-mask front end
+        Bn, K0 = (1024, 65536) if small else (4096, 65536)
+        src = torch.randn((Bn, K0), device=dev)
+        idxl = torch.from_numpy(rng.integers(0, K0, K0).astype(np.int64)).to(dev)
+        ms = time_op(torch, lambda i: ops.index_lastdim(src, idxl, status=st), 5)
+        add("index (x[..., idx])", f"[{Bn},{K0}] fp32, {K0} uniform int64 indices", 2 * Bn * K0 * 4 + K0 * 8, Bn * K0, ms)
+        del src
+        nm = 1 << (26 if small else 28)
+        mask = torch.from_numpy(rng.random(nm) < 0.5).to(dev)
+        cnt = int(mask.sum().item())
+        ms = time_op(torch, lambda i: ops.mask_to_indices(mask), 5, graph=False)
+        add("bool mask -> indices", f"[{nm}] bool, half true", 2 * nm + 8 * cnt, nm, ms, launches=3,
+            note="includes the 8-byte D2H read of the count and the stream synchronise; eager timing")
+        del mask
     if "c3" in which:
         # ---- C3: bf16 broadcast chain into a transposed output view
         g.manual_seed(1)
@@ -375,6 +389,11 @@ def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4", "ew")
         ob = torch.empty_like(xb)
         ms = time_op(torch, lambda i: ops.mul(xb.view(-1, 1 << 14), yb, out=ob.view(-1, 1 << 14)), 10)
         add("mul bf16, row-broadcast operand", f"[{nE >> 14},16384] * [16384]", 4 * nE, nE, ms)
+        ycol = yb[: nE >> 14].reshape(-1, 1)
+        ms = time_op(torch, lambda i: ops.mul(xb.view(-1, 1 << 14), ycol, out=ob.view(-1, 1 << 14)), 10)
+        add("mul bf16, column-broadcast operand", f"[{nE >> 14},16384] * [{nE >> 14},1]", 4 * nE, nE, ms)
+        ms = time_op(torch, lambda i: ops.add(x.view(-1, 1 << 14), y[: nE >> 14].reshape(-1, 1), out=o.view(-1, 1 << 14)), 10)
+        add("add fp32, column-broadcast operand", f"[{nE >> 14},16384] + [{nE >> 14},1]", 8 * nE, nE, ms)
         cm = x > 0
         ms = time_op(torch, lambda i: ops.where(cm, x, y, out=o), 10)
         add("where fp32 dense", f"[{nE}] contiguous, bool condition", 13 * nE, nE, ms)

@@ -157,8 +157,9 @@ __device__ __forceinline__ Vec<TO, V> apply_vec(const F& f, const Vec<T1, V>& a,
 template <class F, class TO, class T1, class T2, class T3, int NIN, int V, int INV, int BC0 = 0>
 __global__ void __launch_bounds__(kEwThreads, NIN >= 3 ? 1 : 4)
 ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
-  // rows in flight per thread: fewer for three-input ops and wide vectors (register budget)
-  constexpr int UNR = (NIN >= 3 && V >= 8 && INV < 0) ? 2 : kEwUnroll;
+  // rows in flight per thread: fewer when two or three inputs of eight 16-bit lanes each are
+  // widened to float (register budget)
+  constexpr int UNR = (V >= 8 && INV < 0 && (NIN >= 3 || (NIN == 2 && !has_packed2<F>::value))) ? 2 : kEwUnroll;
   uint32_t b = blockIdx.x, t0, t1;
   p.div_t0.divmod(b, b, t0);
   p.div_t1.divmod(b, b, t1);
@@ -233,8 +234,10 @@ ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
   }
   if constexpr (NIN <= 2 && INV < 0) {
     // exactly one input varies along the rows (a unary op, or a binary op whose other operand
-    // is constant along them): eight rows in flight per thread.  Two separate loops so that
-    // only one eight-deep buffer is live at a time.
+    // is constant along them): DEEP rows in flight per thread (eight; four when 16-bit
+    // values are widened to float lane by lane, which would not fit the register budget
+    // eight deep).  Two separate loops so that only one buffer is live at a time.
+    constexpr int DEEP = ((sizeof(T1) == 2 || sizeof(T2) == 2) && !has_packed2<F>::value) ? 4 : 8;
     auto emit = [&](const Vec<T1, V>& av, const Vec<T2, V>& bv, int l) {
       const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(f, av, bv, c0);
       if constexpr (V == 1) po[l * so_] = o.v[0];
@@ -243,12 +246,12 @@ ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
     if (!inv1 && (NIN == 1 || inv2) && (V == 1 || s01 == 0 || s01 == 1)) {
       const bool unit = s01 == 1;
       int l = 0;
-      for (; l + 8 <= n; l += 8) {
-        Vec<T1, V> av[8];
+      for (; l + DEEP <= n; l += DEEP) {
+        Vec<T1, V> av[DEEP];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) av[u] = load_vec01<T1, V>(p1 + (l + u) * st1, unit);
+        for (int u = 0; u < DEEP; ++u) av[u] = load_vec01<T1, V>(p1 + (l + u) * st1, unit);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) emit(av[u], b0, l + u);
+        for (int u = 0; u < DEEP; ++u) emit(av[u], b0, l + u);
       }
       for (; l < n; ++l) emit(load_vec01<T1, V>(p1 + l * st1, unit), b0, l);
       return;
@@ -257,37 +260,61 @@ ew_tiled_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f) {
       if (inv1 && !inv2 && (V == 1 || s02 == 0 || s02 == 1)) {
         const bool unit = s02 == 1;
         int l = 0;
-        for (; l + 8 <= n; l += 8) {
-          Vec<T2, V> bv[8];
+        for (; l + DEEP <= n; l += DEEP) {
+          Vec<T2, V> bv[DEEP];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) bv[u] = load_vec01<T2, V>(p2 + (l + u) * st2, unit);
+          for (int u = 0; u < DEEP; ++u) bv[u] = load_vec01<T2, V>(p2 + (l + u) * st2, unit);
 #pragma unroll
-          for (int u = 0; u < 8; ++u) emit(a0, bv[u], l + u);
+          for (int u = 0; u < DEEP; ++u) emit(a0, bv[u], l + u);
         }
         for (; l < n; ++l) emit(a0, load_vec01<T2, V>(p2 + l * st2, unit), l);
         return;
       }
     }
   }
+  // General case.  When no input needs a gather along dim 0 (every stride there is 0 or 1) the
+  // loads are the two-way load_vec01 and UNR rows are in flight; the gather form (V scalar loads
+  // per input) is kept out of that loop -- with it inside, the 16-bit kernels spill -- and
+  // runs one row at a time.
+  const bool u1 = s01 == 1, u2 = s02 == 1, u3 = s03 == 1;
+  const bool nogather = V == 1 || ((inv1 || s01 == 0 || u1) && (NIN < 2 || inv2 || s02 == 0 || u2) &&
+                                   (NIN < 3 || inv3 || s03 == 0 || u3));
   int l = 0;
-  for (; l + UNR <= n; l += UNR) {
+  if (nogather) {
+    // invariant inputs sit in every slot of the row buffers once, so that the loop body has no
+    // select between two vectors (which the compiler would do through local memory)
     Vec<T1, V> a[UNR];
     Vec<T2, V> bb[NIN >= 2 ? UNR : 1];
     Vec<T3, V> c[NIN >= 3 ? UNR : 1];
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
-      if (!inv1) a[u] = load_vec<T1, V, sp1>(p1 + (l + u) * st1, s01);
-      if constexpr (NIN >= 2) { if (!inv2) bb[u] = load_vec<T2, V, sp2>(p2 + (l + u) * st2, s02); }
-      if constexpr (NIN >= 3) { if (!inv3) c[u] = load_vec<T3, V, sp3>(p3 + (l + u) * st3, s03); }
+      a[u] = a0;
+      if constexpr (NIN >= 2) bb[u] = b0; else bb[0] = b0;
+      if constexpr (NIN >= 3) c[u] = c0; else c[0] = c0;
     }
+    for (; l + UNR <= n; l += UNR) {
 #pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(
-          f, inv1 ? a0 : a[u], (NIN >= 2 && !inv2) ? bb[NIN >= 2 ? u : 0] : b0,
-          (NIN >= 3 && !inv3) ? c[NIN >= 3 ? u : 0] : c0);
-      if constexpr (V == 1) po[(l + u) * so_] = o.v[0];
-      else *reinterpret_cast<Vec<TO, V>*>(po + (l + u) * so_) = o;
+      for (int u = 0; u < UNR; ++u) {
+        if (!inv1) a[u] = load_vec01<T1, V>(p1 + (l + u) * st1, u1);
+        if constexpr (NIN >= 2) { if (!inv2) bb[u] = load_vec01<T2, V>(p2 + (l + u) * st2, u2); }
+        if constexpr (NIN >= 3) { if (!inv3) c[u] = load_vec01<T3, V>(p3 + (l + u) * st3, u3); }
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(f, a[u], bb[NIN >= 2 ? u : 0], c[NIN >= 3 ? u : 0]);
+        if constexpr (V == 1) po[(l + u) * so_] = o.v[0];
+        else *reinterpret_cast<Vec<TO, V>*>(po + (l + u) * so_) = o;
+      }
     }
+    for (; l < n; ++l) {
+      if (!inv1) a[0] = load_vec01<T1, V>(p1 + l * st1, u1);
+      if constexpr (NIN >= 2) { if (!inv2) bb[0] = load_vec01<T2, V>(p2 + l * st2, u2); }
+      if constexpr (NIN >= 3) { if (!inv3) c[0] = load_vec01<T3, V>(p3 + l * st3, u3); }
+      const Vec<TO, V> o = apply_vec<F, TO, T1, T2, T3, NIN, V>(f, a[0], bb[0], c[0]);
+      if constexpr (V == 1) po[l * so_] = o.v[0];
+      else *reinterpret_cast<Vec<TO, V>*>(po + l * so_) = o;
+    }
+    return;
   }
   for (; l < n; ++l) {
     const Vec<T1, V> a = inv1 ? a0 : load_vec<T1, V, sp1>(p1 + l * st1, s01);
@@ -445,18 +472,18 @@ ew_transpose_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, c
   }
 }
 
-// Transposing variant for 16-bit outputs and staged inputs: a (64 x 64) tile, but every lane
-// moves FOUR elements (8 bytes) per access instead of two, so a warp instruction covers two
-// rows of 16 lanes.  Staged inputs are written to shared memory already transposed
-// (tile[j][i], 2-byte stores) with the 4-element groups of a row XOR-swizzled by the row's
-// group index: the 16 lanes of a half-warp then hit 16 different banks on the store, and the
-// 8-byte reads along i are conflict-free.  Needs sizes, strides and bases that keep groups of
-// four aligned; the host checks.
+// Transposing variant for 16-bit outputs and 8- or 16-bit staged inputs (a bool mask, a bf16
+// operand): a (64 x 64) tile, but every lane moves FOUR elements per access instead of two, so
+// a warp instruction covers two rows of 16 lanes.  Staged inputs are written to shared memory
+// already transposed (tile[j][i], one store per element) with the 4-element groups of a row
+// XOR-swizzled by the row's group index: the 16 lanes of a half-warp then hit 16 different banks
+// on the store, and the vector reads along i are conflict-free.  Needs sizes, strides and bases
+// that keep groups of four aligned; the host checks.
 template <class F, class TO, class T1, class T2, class T3, int NIN>
 __global__ void __launch_bounds__(kEwThreads)
 ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, const int tmask) {
   constexpr int TILE = 64;
-  __shared__ __align__(16) uint16_t sm[kTrMaxStaged][TILE * TILE];
+  __shared__ __align__(16) unsigned char sm[kTrMaxStaged][TILE * TILE * 2];
   uint32_t b = blockIdx.x, t0, t1;
   p.div_t0.divmod(b, b, t0);
   p.div_t1.divmod(b, b, t1);
@@ -474,32 +501,31 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
   const int64_t i0 = static_cast<int64_t>(t0) * TILE, j0 = static_cast<int64_t>(t1) * TILE;
   const int64_t size0 = p.n0v;
   const int slot2 = (tmask & 1) ? 1 : 0, slot3 = ((tmask & 1) ? 1 : 0) + ((tmask & 2) ? 1 : 0);
-  uint16_t* s1 = sm[0];
-  uint16_t* s2 = sm[slot2 < kTrMaxStaged ? slot2 : 0];
-  uint16_t* s3 = sm[slot3 < kTrMaxStaged ? slot3 : 0];
+  T1* s1 = reinterpret_cast<T1*>(sm[0]);
+  T2* s2 = reinterpret_cast<T2*>(sm[slot2 < kTrMaxStaged ? slot2 : 0]);
+  T3* s3 = reinterpret_cast<T3*>(sm[slot3 < kTrMaxStaged ? slot3 : 0]);
   const T1* g1 = reinterpret_cast<const T1*>(p.ptr[1]) + base[1];
   const T2* g2 = reinterpret_cast<const T2*>(p.ptr[NIN >= 2 ? 2 : 0]) + base[NIN >= 2 ? 2 : 0];
   const T3* g3 = reinterpret_cast<const T3*>(p.ptr[NIN >= 3 ? 3 : 0]) + base[NIN >= 3 ? 3 : 0];
   const int64_t a0 = p.s0[1], a1 = p.s1[1];
   const int64_t b0 = p.s0[NIN >= 2 ? 2 : 0], b1 = p.s1[NIN >= 2 ? 2 : 0];
   const int64_t c0 = p.s0[NIN >= 3 ? 3 : 0], c1 = p.s1[NIN >= 3 ? 3 : 0];
-  auto stage = [&](uint16_t* sdst, const void* gsrc, int64_t st0, int il, int64_t i, int64_t j) {
-    const uint2 v = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(gsrc) + i * st0 + j);
+  auto stage = [&](auto* sdst, const auto* gsrc, int64_t st0, int il, int64_t i, int64_t j) {
+    using E = std::remove_cv_t<std::remove_pointer_t<decltype(gsrc)>>;
+    const Vec<E, 4> v = *reinterpret_cast<const Vec<E, 4>*>(gsrc + i * st0 + j);
     const int col = (((il >> 2) ^ q) << 2) + (il & 3);  // swizzled position of row-element il
-    uint16_t* d = sdst + (q * 4) * TILE + col;
-    d[0] = static_cast<uint16_t>(v.x & 0xffffu);
-    d[TILE] = static_cast<uint16_t>(v.x >> 16);
-    d[2 * TILE] = static_cast<uint16_t>(v.y & 0xffffu);
-    d[3 * TILE] = static_cast<uint16_t>(v.y >> 16);
+    E* d = sdst + (q * 4) * TILE + col;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) d[e * TILE] = v.v[e];
   };
 #pragma unroll
   for (int r = 0; r < TILE / 16; ++r) {
     const int il = w * 2 + h + 16 * r;
     const int64_t i = i0 + il, j = j0 + q * 4;
     if (i < size0 && j < p.size1) {
-      if constexpr (sizeof(T1) == 2) { if (tmask & 1) stage(s1, g1, a0, il, i, j); }
-      if constexpr (NIN >= 2 && sizeof(T2) == 2) { if (tmask & 2) stage(s2, g2, b0, il, i, j); }
-      if constexpr (NIN >= 3 && sizeof(T3) == 2) { if (tmask & 4) stage(s3, g3, c0, il, i, j); }
+      if constexpr (sizeof(T1) <= 2) { if (tmask & 1) stage(s1, g1, a0, il, i, j); }
+      if constexpr (NIN >= 2 && sizeof(T2) <= 2) { if (tmask & 2) stage(s2, g2, b0, il, i, j); }
+      if constexpr (NIN >= 3 && sizeof(T3) <= 2) { if (tmask & 4) stage(s3, g3, c0, il, i, j); }
     }
   }
   __syncthreads();
@@ -522,27 +548,27 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
       Vec<T1, 4> va;
       Vec<T2, 4> vb{};
       Vec<T3, 4> vc{};
-      if constexpr (sizeof(T1) == 2) {
+      if constexpr (sizeof(T1) <= 2) {
         if (tmask & 1) va = *reinterpret_cast<const Vec<T1, 4>*>(s1 + so);
       }
-      if (!(tmask & 1) || sizeof(T1) != 2) {
+      if (!(tmask & 1) || sizeof(T1) > 2) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) va.v[e] = k1 ? ka : g1[(i + e) * a0 + j * a1];
       }
       if constexpr (NIN >= 2) {
-        if constexpr (sizeof(T2) == 2) {
+        if constexpr (sizeof(T2) <= 2) {
           if (tmask & 2) vb = *reinterpret_cast<const Vec<T2, 4>*>(s2 + so);
         }
-        if (!(tmask & 2) || sizeof(T2) != 2) {
+        if (!(tmask & 2) || sizeof(T2) > 2) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) vb.v[e] = k2 ? kb : g2[(i + e) * b0 + j * b1];
         }
       }
       if constexpr (NIN >= 3) {
-        if constexpr (sizeof(T3) == 2) {
+        if constexpr (sizeof(T3) <= 2) {
           if (tmask & 4) vc = *reinterpret_cast<const Vec<T3, 4>*>(s3 + so);
         }
-        if (!(tmask & 4) || sizeof(T3) != 2) {
+        if (!(tmask & 4) || sizeof(T3) > 2) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) vc.v[e] = k3 ? kc : g3[(i + e) * c0 + j * c1];
         }
@@ -634,7 +660,7 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
           ++staged;
           use_mask |= 1 << (k - 1);
           pairs = pairs && pair_ok(k, true);
-          quads = quads && tpl.esize[k] == 2 && group_ok(k, true, 4);
+          quads = quads && tpl.esize[k] <= 2 && group_ok(k, true, 4);
         }
       if constexpr (sizeof(TO) == 2) {
         const int64_t q0 = (tpl.shape[0] + 63) / 64, q1 = (tpl.shape[1] + 63) / 64;

@@ -619,26 +619,43 @@ struct LastDimParams {
   int mode;  // 0 gather, 1 put overwrite, 2 put accumulate
   int dtype;
 };
+// A thread owns one index position k and walks kLdRows rows: the index is read and normalised
+// once, writes (gather) / reads (put) of the dense operand are coalesced along k, and the
+// kLdRows strided accesses to `self` are independent loads in flight.  E is an unsigned integer
+// of the element size; accumulate uses the typed atomics.
+constexpr int kLdRows = 8;
+template <class E>
 __global__ void __launch_bounds__(kThreads) lastdim_kernel(const __grid_constant__ LastDimParams p) {
-  const int64_t e = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  if (e >= p.B * p.K) return;
-  const int64_t b = e / p.K, k = e - b * p.K;
+  const int64_t k = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (k >= p.K) return;
   int64_t v = p.idx.get(k);
-  const bool good = normalize(v, p.K0, p.policy, p.status, b == 0);
-  char* s = p.self + (b * p.sb + v * p.sk) * p.es;
-  char* o = p.other + e * p.es;
-  if (p.mode == 0) {
-    for (int i = 0; i < p.es; ++i) o[i] = good ? s[i] : 0;
-  } else if (good) {
-    if (p.mode == 1) {
-      for (int i = 0; i < p.es; ++i) s[i] = o[i];
-    } else {
-      switch (p.dtype) {
-        case VBT_B200_F32: atomicAdd(reinterpret_cast<float*>(s), *reinterpret_cast<const float*>(o)); break;
-        case VBT_B200_I64:
-          atomicAdd(reinterpret_cast<unsigned long long*>(s), *reinterpret_cast<const unsigned long long*>(o));
-          break;
-        case VBT_B200_I32: atomicAdd(reinterpret_cast<int*>(s), *reinterpret_cast<const int*>(o)); break;
+  const bool good = normalize(v, p.K0, p.policy, p.status, blockIdx.y == 0);
+  E* self = reinterpret_cast<E*>(p.self) + v * p.sk;
+  E* other = reinterpret_cast<E*>(p.other) + k;
+  for (int64_t b0 = static_cast<int64_t>(blockIdx.y) * kLdRows; b0 < p.B;
+       b0 += static_cast<int64_t>(gridDim.y) * kLdRows) {
+    E val[kLdRows];
+    if (p.mode == 0) {
+#pragma unroll
+      for (int r = 0; r < kLdRows; ++r) val[r] = (good && b0 + r < p.B) ? self[(b0 + r) * p.sb] : E(0);
+#pragma unroll
+      for (int r = 0; r < kLdRows; ++r)
+        if (b0 + r < p.B) other[(b0 + r) * p.K] = val[r];
+    } else if (good) {
+#pragma unroll
+      for (int r = 0; r < kLdRows; ++r) val[r] = b0 + r < p.B ? other[(b0 + r) * p.K] : E(0);
+#pragma unroll
+      for (int r = 0; r < kLdRows; ++r) {
+        if (b0 + r >= p.B) continue;
+        E* d = self + (b0 + r) * p.sb;
+        if (p.mode == 1) {
+          *d = val[r];
+        } else if constexpr (sizeof(E) == 4) {
+          if (p.dtype == VBT_B200_F32) atomicAdd(reinterpret_cast<float*>(d), __uint_as_float(val[r]));
+          else atomicAdd(reinterpret_cast<unsigned*>(d), static_cast<unsigned>(val[r]));
+        } else if constexpr (sizeof(E) == 8) {
+          atomicAdd(reinterpret_cast<unsigned long long*>(d), static_cast<unsigned long long>(val[r]));
+        }
       }
     }
   }
@@ -896,9 +913,14 @@ vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt
   p.status = static_cast<unsigned long long*>(status);
   p.mode = mode;
   p.dtype = self->dtype;
-  const int64_t blocks = (B * K + kThreads - 1) / kThreads;
-  VB_ARG(blocks <= 0x7fffffff, std::string(name) + ": too large for one call");
-  lastdim_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p);
+  const int64_t gx = (K + kThreads - 1) / kThreads, gy = (B + kLdRows - 1) / kLdRows;
+  const dim3 g(static_cast<unsigned>(gx), static_cast<unsigned>(std::min<int64_t>(gy, 65535)));
+  switch (p.es) {
+    case 1: lastdim_kernel<uint8_t><<<g, kThreads, 0, s>>>(p); break;
+    case 2: lastdim_kernel<uint16_t><<<g, kThreads, 0, s>>>(p); break;
+    case 4: lastdim_kernel<uint32_t><<<g, kThreads, 0, s>>>(p); break;
+    default: lastdim_kernel<uint64_t><<<g, kThreads, 0, s>>>(p); break;
+  }
   VB_LAUNCH_CHECK();
   return VBT_B200_OK;
 }
