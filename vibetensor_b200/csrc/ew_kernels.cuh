@@ -511,10 +511,12 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
   const int64_t b0 = p.s0[NIN >= 2 ? 2 : 0], b1 = p.s1[NIN >= 2 ? 2 : 0];
   const int64_t c0 = p.s0[NIN >= 3 ? 3 : 0], c1 = p.s1[NIN >= 3 ? 3 : 0];
   auto stage = [&](auto* sdst, const auto* gsrc, int64_t st0, int il, int64_t i, int64_t j) {
+    // moved as raw 8- / 16-bit words: one vector load, four plain stores
     using E = std::remove_cv_t<std::remove_pointer_t<decltype(gsrc)>>;
-    const Vec<E, 4> v = *reinterpret_cast<const Vec<E, 4>*>(gsrc + i * st0 + j);
+    using R = std::conditional_t<sizeof(E) == 1, uint8_t, uint16_t>;
+    const Vec<R, 4> v = *reinterpret_cast<const Vec<R, 4>*>(gsrc + i * st0 + j);
     const int col = (((il >> 2) ^ q) << 2) + (il & 3);  // swizzled position of row-element il
-    E* d = sdst + (q * 4) * TILE + col;
+    R* d = reinterpret_cast<R*>(sdst) + (q * 4) * TILE + col;
 #pragma unroll
     for (int e = 0; e < 4; ++e) d[e * TILE] = v.v[e];
   };
