@@ -73,20 +73,32 @@ __device__ __forceinline__ void row_math(float (&v)[VPL][16 / sizeof(T)], const 
                                          const float (&g)[VPL][16 / sizeof(T)], const RowParams& p,
                                          RMax reduce_max, RSum reduce_sum, float* inv_out) {
   constexpr int V = 16 / sizeof(T);
+  // Arithmetic on float pairs with the packed fp32 instructions of sm_100 (__fmul2_rn,
+  // __fadd2_rn, __ffma2_rn): one issue slot per two lanes; these kernels keep the issue slots
+  // about half busy, so instruction count matters next to bytes.
   if constexpr (KIND == K_RMSNORM) {
-    float ss = 0.f;
+    float2 ss2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int k = 0; k < VPL; ++k)
       if (valid[k])
 #pragma unroll
-        for (int j = 0; j < V; ++j) ss = fmaf(v[k][j], v[k][j], ss);
-    ss = reduce_sum(ss);
+        for (int j = 0; j < V; j += 2) {
+          const float2 x2 = make_float2(v[k][j], v[k][j + 1]);
+          ss2 = __ffma2_rn(x2, x2, ss2);
+        }
+    const float ss = reduce_sum(ss2.x + ss2.y);
     const float inv = rsqrtf(ss / static_cast<float>(p.cols) + p.eps);
     *inv_out = inv;
+    const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
     for (int k = 0; k < VPL; ++k)
 #pragma unroll
-      for (int j = 0; j < V; ++j) v[k][j] = v[k][j] * inv * g[k][j];
+      for (int j = 0; j < V; j += 2) {
+        const float2 r2 = __fmul2_rn(__fmul2_rn(make_float2(v[k][j], v[k][j + 1]), inv2),
+                                     make_float2(g[k][j], g[k][j + 1]));
+        v[k][j] = r2.x;
+        v[k][j + 1] = r2.y;
+      }
   } else {
     float m = -INFINITY;
 #pragma unroll
@@ -95,31 +107,43 @@ __device__ __forceinline__ void row_math(float (&v)[VPL][16 / sizeof(T)], const 
 #pragma unroll
         for (int j = 0; j < V; ++j) m = fmaxf(m, v[k][j]);
     m = reduce_max(m);
-    float s = 0.f;
+    float2 s2 = make_float2(0.f, 0.f);
+    const float2 nm2 = make_float2(-m, -m);
 #pragma unroll
     for (int k = 0; k < VPL; ++k)
       if (valid[k])
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const float d = v[k][j] - m;
-          const float e = fast_exp<T>(d);
-          s += e;
-          v[k][j] = KIND == K_SOFTMAX ? e : d;
+        for (int j = 0; j < V; j += 2) {
+          const float2 d2 = __fadd2_rn(make_float2(v[k][j], v[k][j + 1]), nm2);
+          const float2 e2 = make_float2(fast_exp<T>(d2.x), fast_exp<T>(d2.y));
+          s2 = __fadd2_rn(s2, e2);
+          v[k][j] = KIND == K_SOFTMAX ? e2.x : d2.x;
+          v[k][j + 1] = KIND == K_SOFTMAX ? e2.y : d2.y;
         }
-    s = reduce_sum(s);
+    float s = reduce_sum(s2.x + s2.y);
     s = fmaxf(s, 1e-20f);
     if constexpr (KIND == K_SOFTMAX) {
       const float r = 1.0f / s;
+      const float2 r2 = make_float2(r, r);
 #pragma unroll
       for (int k = 0; k < VPL; ++k)
 #pragma unroll
-        for (int j = 0; j < V; ++j) v[k][j] *= r;
+        for (int j = 0; j < V; j += 2) {
+          const float2 y2 = __fmul2_rn(make_float2(v[k][j], v[k][j + 1]), r2);
+          v[k][j] = y2.x;
+          v[k][j + 1] = y2.y;
+        }
     } else {
       const float ls = logf(s);
+      const float2 nls2 = make_float2(-ls, -ls);
 #pragma unroll
       for (int k = 0; k < VPL; ++k)
 #pragma unroll
-        for (int j = 0; j < V; ++j) v[k][j] -= ls;
+        for (int j = 0; j < V; j += 2) {
+          const float2 y2 = __fadd2_rn(make_float2(v[k][j], v[k][j + 1]), nls2);
+          v[k][j] = y2.x;
+          v[k][j + 1] = y2.y;
+        }
     }
   }
 }
@@ -256,8 +280,14 @@ __global__ void __launch_bounds__(THREADS) rowop_block_kernel(const __grid_const
 #pragma unroll
           for (int q = 0; q < V / 4; ++q) {
             const float4 gq = gp[q];
-            v[k][4 * q + 0] *= gq.x; v[k][4 * q + 1] *= gq.y;
-            v[k][4 * q + 2] *= gq.z; v[k][4 * q + 3] *= gq.w;
+            if constexpr (V == 4) {  // packed multiply; with eight lanes it costs registers, hence blocks per SM
+              const float2 lo = __fmul2_rn(make_float2(v[k][0], v[k][1]), make_float2(gq.x, gq.y));
+              const float2 hi = __fmul2_rn(make_float2(v[k][2], v[k][3]), make_float2(gq.z, gq.w));
+              v[k][0] = lo.x; v[k][1] = lo.y; v[k][2] = hi.x; v[k][3] = hi.y;
+            } else {
+              v[k][4 * q + 0] *= gq.x; v[k][4 * q + 1] *= gq.y;
+              v[k][4 * q + 2] *= gq.z; v[k][4 * q + 3] *= gq.w;
+            }
           }
         }
       }

@@ -47,6 +47,23 @@ __device__ __forceinline__ float lanes_sum(float v) {
   return v;
 }
 
+// two adjacent storage values <-> float2; the RMSNorm path does its arithmetic on float pairs with
+// the packed fp32 instructions of sm_100 (__fmul2_rn / __ffma2_rn: one issue slot per two lanes)
+__device__ __forceinline__ float2 pair_f(const float* p) { return make_float2(p[0], p[1]); }
+__device__ __forceinline__ float2 pair_f(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ float2 pair_f(const __half* p) {
+  return __half22float2(*reinterpret_cast<const __half2*>(p));
+}
+__device__ __forceinline__ void store_pair(float* p, float2 v) { p[0] = v.x; p[1] = v.y; }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float2 v) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __float22bfloat162_rn(v);
+}
+__device__ __forceinline__ void store_pair(__half* p, float2 v) {
+  *reinterpret_cast<__half2*>(p) = __float22half2_rn(v);
+}
+
 template <class T, int VPL>
 __device__ __forceinline__ void load_raw(const T* row, int first, int step, int nvec,
                                          Vec<T, 16 / sizeof(T)> (&v)[VPL]) {
@@ -153,32 +170,42 @@ __global__ void __launch_bounds__(kBwdThreads, VPL * (16 / sizeof(T)) <= 16 ? 2 
     float s[RIF];
 #pragma unroll
     for (int i = 0; i < RIF; ++i) s[i] = 0.f;
+    if constexpr (KIND == B_RMSNORM) {
+      float2 s2[RIF];
 #pragma unroll
-    for (int k = 0; k < VPL; ++k) {
-      float gk[V], ggk[V];
-      gamma_vec(k, gk);
+      for (int i = 0; i < RIF; ++i) s2[i] = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int e = 0; e < V; ++e) ggk[e] = 0.f;
+      for (int k = 0; k < VPL; ++k) {
+        float gk[V];
+        gamma_vec(k, gk);
 #pragma unroll
-      for (int i = 0; i < RIF; ++i)
+        for (int e = 0; e < V; e += 2) {
+          const float2 g2 = make_float2(gk[e], gk[e + 1]);
+          float2 gacc = make_float2(gg[k][e], gg[k][e + 1]);
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          const float av = to_f(a[i][k].v[e]), bv = to_f(b[i][k].v[e]);
-          if constexpr (KIND == B_SOFTMAX) {
-            s[i] = fmaf(av, bv, s[i]);
-          } else if constexpr (KIND == B_LOG_SOFTMAX) {
-            s[i] += av;
-          } else {
+          for (int i = 0; i < RIF; ++i) {
             // dy * x once; 1/rms enters dgamma through the fma and the row sum after the loop
-            const float dyx = av * bv;
-            ggk[e] = fmaf(dyx, inv[i], ggk[e]);
-            s[i] = fmaf(dyx, gk[e], s[i]);
+            const float2 dyx = __fmul2_rn(pair_f(&a[i][k].v[e]), pair_f(&b[i][k].v[e]));
+            gacc = __ffma2_rn(dyx, make_float2(inv[i], inv[i]), gacc);
+            s2[i] = __ffma2_rn(dyx, g2, s2[i]);
           }
+          gg[k][e] = gacc.x;
+          gg[k][e + 1] = gacc.y;
         }
-      if constexpr (KIND == B_RMSNORM) {
-#pragma unroll
-        for (int e = 0; e < V; ++e) gg[k][e] += ggk[e];
       }
+#pragma unroll
+      for (int i = 0; i < RIF; ++i) s[i] = s2[i].x + s2[i].y;
+    } else {
+#pragma unroll
+      for (int k = 0; k < VPL; ++k)
+#pragma unroll
+        for (int i = 0; i < RIF; ++i)
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            const float av = to_f(a[i][k].v[e]), bv = to_f(b[i][k].v[e]);
+            if constexpr (KIND == B_SOFTMAX) s[i] = fmaf(av, bv, s[i]);
+            else s[i] += av;
+          }
     }
     row_sums(s);
 #pragma unroll
@@ -193,16 +220,22 @@ __global__ void __launch_bounds__(kBwdThreads, VPL * (16 / sizeof(T)) <= 16 ? 2 
         const int j = tl + k * TPR;
         if (j >= nvec) continue;
         Vec<T, V> raw;
-        float gk[V];
-        gamma_vec(k, gk);
+        if constexpr (KIND == B_RMSNORM) {
+          float gk[V];
+          gamma_vec(k, gk);
+          const float2 inv2 = make_float2(inv[i], inv[i]), nc2 = make_float2(-c2, -c2);
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          const float av = to_f(a[i][k].v[e]), bv = to_f(b[i][k].v[e]);
-          float r;
-          if constexpr (KIND == B_SOFTMAX) r = bv * (av - s[i]);
-          else if constexpr (KIND == B_LOG_SOFTMAX) r = av - expf(bv) * s[i];
-          else r = fmaf(av * gk[e], inv[i], -(bv * c2));
-          raw.v[e] = from_f<T>(r);
+          for (int e = 0; e < V; e += 2) {
+            const float2 t2 = __fmul2_rn(pair_f(&a[i][k].v[e]), make_float2(gk[e], gk[e + 1]));
+            const float2 u2 = __fmul2_rn(pair_f(&b[i][k].v[e]), nc2);
+            store_pair(&raw.v[e], __ffma2_rn(t2, inv2, u2));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            const float av = to_f(a[i][k].v[e]), bv = to_f(b[i][k].v[e]);
+            raw.v[e] = from_f<T>(KIND == B_SOFTMAX ? bv * (av - s[i]) : av - expf(bv) * s[i]);
+          }
         }
         *reinterpret_cast<Vec<T, V>*>(orow + static_cast<int64_t>(j) * V) = raw;
       }
