@@ -347,6 +347,13 @@ def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4", "ew")
         ms = time_op(torch, lambda i: ops.index_lastdim(src, idxl, status=st), 5)
         add("index (x[..., idx])", f"[{Bn},{K0}] fp32, {K0} uniform int64 indices", 2 * Bn * K0 * 4 + K0 * 8, Bn * K0, ms)
         del src
+        Bn2, K02 = (4096, 16384) if small else (16384, 16384)
+        src = torch.randn((Bn2, K02), device=dev)
+        idx2 = torch.from_numpy(rng.integers(0, K02, K02).astype(np.int64)).to(dev)
+        ms = time_op(torch, lambda i: ops.index_lastdim(src, idx2, status=st), 5)
+        add("index (x[..., idx]), rows of 64 KiB", f"[{Bn2},{K02}] fp32, {K02} uniform int64 indices",
+            2 * Bn2 * K02 * 4 + K02 * 8, Bn2 * K02, ms, note="row staged in shared memory")
+        del src
         nm = 1 << (26 if small else 28)
         mask = torch.from_numpy(rng.random(nm) < 0.5).to(dev)
         cnt = int(mask.sum().item())

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import oracle
-from tests.util import from_np, to_np
+from tests.util import CODE, from_np, to_np
 
 pytestmark = pytest.mark.gpu
 GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_vectors.npz"))
@@ -344,3 +344,37 @@ def test_bool_mask_indexing(ops, port, dtype):
         ops.index_mask_lastdim(ts.bfloat16() if dtype == torch.float32 else ts.int(), torch.from_numpy(m).cuda())
     with pytest.raises(ValueError, match="boolean mask"):
         ops.index_mask_lastdim(ts, torch.from_numpy(m[:100]).cuda())
+
+
+@pytest.mark.parametrize("dtype,shape,K", [(torch.float32, (5, 70001), 10000), (torch.int64, (3, 30000), 9000),
+                                           (torch.bfloat16, (4, 50001), 20000), (torch.float32, (2, 8192), 8192),
+                                           (torch.float32, (7, 25001), 9001), (torch.int64, (3, 12800), 8200)])
+def test_index_lastdim_long_rows_shared_memory_path(ops, port, dtype, shape, K):
+    """Rows of 32 to 100 KiB with 8192+ indices are gathered through shared memory (longer rows
+    take the plain kernel): rows whose base is not 16-byte aligned, negative (wrapped) indices,
+    a strided source view."""
+    rng = np.random.default_rng(40)
+    if dtype == torch.int64:
+        src = rng.integers(-10 ** 12, 10 ** 12, shape).astype(np.int64)
+    else:
+        src = oracle.to_storage(rng.standard_normal(shape, dtype=np.float32), CODE[dtype])
+    idx = rng.integers(-shape[1], shape[1], K).astype(np.int64)
+    ts, ti = from_np(src, dtype), torch.from_numpy(idx).cuda()
+    got = to_np(ops.index_lastdim(ts, ti))
+    np.testing.assert_array_equal(got, port.index_lastdim(src, idx))
+    # the same through a view with a column stride of 2
+    wide = np.zeros((shape[0], 2 * shape[1]), src.dtype)
+    wide[:, ::2] = src
+    tv = from_np(wide, dtype)[:, ::2]
+    np.testing.assert_array_equal(to_np(ops.index_lastdim(tv, ti)), got)
+    # out-of-range positions come back as zeros and are counted once each
+    bad = idx.copy()
+    bad[::1000] = shape[1] + 5
+    st = ops.IndexStatus(ts.device)
+    got_bad = to_np(ops.index_lastdim(ts, torch.from_numpy(bad).cuda(), status=st, eager_check=False))
+    assert not got_bad[:, ::1000].any()
+    keep = np.ones(K, bool)
+    keep[::1000] = False
+    np.testing.assert_array_equal(got_bad[:, keep], got[:, keep])
+    with pytest.raises(IndexError, match=f"{len(bad[::1000])} bad indices"):
+        st.check("index", shape[1])

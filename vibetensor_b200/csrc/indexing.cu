@@ -661,6 +661,66 @@ __global__ void __launch_bounds__(kThreads) lastdim_kernel(const __grid_constant
   }
 }
 
+// Gather form for long rows: the kernel above sends one 32-byte sector request through L1 per
+// element (random positions), which saturates the L1/TEX pipe at about a third of HBM speed.
+// Here a block stages a contiguous piece of one source row in shared memory (coalesced 16-byte
+// loads), then every thread walks the index list and serves the positions that fall inside the
+// piece from shared memory, where 32 random 4-byte reads cost a few cycles.  A row takes
+// ceil(K0 / piece) passes and the index list is re-read per pass (coalesced, L2-resident); the
+// host only picks this kernel for rows of one piece, where it runs at about twice the speed of
+// the kernel above.
+constexpr int kLdsThreads = 512;
+template <class E>
+__global__ void __launch_bounds__(kLdsThreads, 2) lastdim_gather_smem_kernel(const __grid_constant__ LastDimParams p,
+                                                                             const int piece) {
+  extern __shared__ __align__(16) unsigned char lds_raw[];
+  E* tile = reinterpret_cast<E*>(lds_raw);
+  const int t = threadIdx.x;
+  constexpr int VE = 16 / sizeof(E);
+  bool first = blockIdx.x == 0;  // bad indices are counted once: block 0, its first row, first pass
+  for (int64_t b = blockIdx.x; b < p.B; b += gridDim.x) {
+    const E* src = reinterpret_cast<const E*>(p.self) + b * p.sb;
+    E* out = reinterpret_cast<E*>(p.other) + b * p.K;
+    for (int64_t c0 = 0; c0 < p.K0; c0 += piece) {
+      const int n = static_cast<int>(p.K0 - c0 < piece ? p.K0 - c0 : piece);
+      __syncthreads();  // readers of the previous piece are done
+      if (p.sk == 1 && (reinterpret_cast<uintptr_t>(src + c0) % 16) == 0) {
+        const int nv = n / VE;
+        const int4* s4 = reinterpret_cast<const int4*>(src + c0);
+        int4* d4 = reinterpret_cast<int4*>(tile);
+#pragma unroll 4
+        for (int i = t; i < nv; i += kLdsThreads) d4[i] = s4[i];
+        for (int i = nv * VE + t; i < n; i += kLdsThreads) tile[i] = src[c0 + i];
+      } else {
+        for (int i = t; i < n; i += kLdsThreads) tile[i] = src[(c0 + i) * p.sk];
+      }
+      __syncthreads();
+      // eight index loads in flight per thread: the walk is otherwise one L2 round trip per index
+      constexpr int U = 8;
+      for (int64_t k0 = t; k0 < p.K; k0 += U * kLdsThreads) {
+        int64_t v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t k = k0 + u * kLdsThreads;
+          v[u] = k < p.K ? p.idx.get(k) : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t k = k0 + u * kLdsThreads;
+          if (k >= p.K) continue;
+          const bool good = normalize(v[u], p.K0, p.policy, p.status, first && c0 == 0);
+          if (good) {
+            if (v[u] >= c0 && v[u] < c0 + n) out[k] = tile[v[u] - c0];
+          } else if (c0 == 0) {
+            out[k] = E(0);
+          }
+        }
+      }
+    }
+    first = false;
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // host
 // ------------------------------------------------------------------------------------
@@ -913,6 +973,33 @@ vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt
   p.status = static_cast<unsigned long long*>(status);
   p.mode = mode;
   p.dtype = self->dtype;
+  // long rows, many indices: serve the gather from shared memory
+  // (rows that fit one piece only: with several pieces per row the index list is re-read per
+  // piece and that traffic costs what the sector requests cost)
+  constexpr int kPieceBytes = 100 * 1024;
+  if (mode == 0 && K >= 8192 && p.K0 * p.es >= 32 * 1024 && p.K0 * p.es <= kPieceBytes && p.es >= 2) {
+    const int piece = static_cast<int>(std::min<int64_t>(p.K0, kPieceBytes / p.es / 4 * 4));
+    const size_t smem = static_cast<size_t>(piece) * p.es;
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(B, int64_t{sm_count(scope.device())} * 2));
+    cudaError_t e = cudaSuccess;
+    switch (p.es) {
+      case 2:
+        e = cudaFuncSetAttribute(lastdim_gather_smem_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPieceBytes);
+        if (e == cudaSuccess) lastdim_gather_smem_kernel<uint16_t><<<grid, kLdsThreads, smem, s>>>(p, piece);
+        break;
+      case 4:
+        e = cudaFuncSetAttribute(lastdim_gather_smem_kernel<uint32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPieceBytes);
+        if (e == cudaSuccess) lastdim_gather_smem_kernel<uint32_t><<<grid, kLdsThreads, smem, s>>>(p, piece);
+        break;
+      default:
+        e = cudaFuncSetAttribute(lastdim_gather_smem_kernel<uint64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPieceBytes);
+        if (e == cudaSuccess) lastdim_gather_smem_kernel<uint64_t><<<grid, kLdsThreads, smem, s>>>(p, piece);
+        break;
+    }
+    VB_CUDA(e);
+    VB_LAUNCH_CHECK();
+    return VBT_B200_OK;
+  }
   const int64_t gx = (K + kThreads - 1) / kThreads, gy = (B + kLdRows - 1) / kLdRows;
   const dim3 g(static_cast<unsigned>(gx), static_cast<unsigned>(std::min<int64_t>(gy, 65535)));
   switch (p.es) {
