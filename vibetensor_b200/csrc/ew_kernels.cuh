@@ -472,9 +472,9 @@ ew_transpose_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, c
   }
 }
 
-// Transposing variant for 16-bit outputs and 8- or 16-bit staged inputs (a bool mask, a bf16
-// operand): a (64 x 64) tile, but every lane moves FOUR elements per access instead of two, so
-// a warp instruction covers two rows of 16 lanes.  Staged inputs are written to shared memory
+// Transposing variant for 16- and 32-bit outputs and staged inputs of up to 32 bits (a bool mask,
+// a bf16 or fp32 operand): a (64 x 64) tile, but every lane moves FOUR elements per access
+// instead of two (8 or 16 bytes), so a warp instruction covers two rows of 16 lanes.  Staged inputs are written to shared memory
 // already transposed (tile[j][i], one store per element) with the 4-element groups of a row
 // XOR-swizzled by the row's group index: the 16 lanes of a half-warp then hit 16 different banks
 // on the store, and the vector reads along i are conflict-free.  Needs sizes, strides and bases
@@ -483,7 +483,8 @@ template <class F, class TO, class T1, class T2, class T3, int NIN>
 __global__ void __launch_bounds__(kEwThreads)
 ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, const int tmask) {
   constexpr int TILE = 64;
-  __shared__ __align__(16) unsigned char sm[kTrMaxStaged][TILE * TILE * 2];
+  constexpr int kStageEs = (sizeof(T1) == 4 || (NIN >= 2 && sizeof(T2) == 4) || (NIN >= 3 && sizeof(T3) == 4)) ? 4 : 2;
+  __shared__ __align__(16) unsigned char sm[kTrMaxStaged][TILE * TILE * kStageEs];
   uint32_t b = blockIdx.x, t0, t1;
   p.div_t0.divmod(b, b, t0);
   p.div_t1.divmod(b, b, t1);
@@ -511,9 +512,9 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
   const int64_t b0 = p.s0[NIN >= 2 ? 2 : 0], b1 = p.s1[NIN >= 2 ? 2 : 0];
   const int64_t c0 = p.s0[NIN >= 3 ? 3 : 0], c1 = p.s1[NIN >= 3 ? 3 : 0];
   auto stage = [&](auto* sdst, const auto* gsrc, int64_t st0, int il, int64_t i, int64_t j) {
-    // moved as raw 8- / 16-bit words: one vector load, four plain stores
+    // moved as raw 8- / 16- / 32-bit words: one vector load, four plain stores
     using E = std::remove_cv_t<std::remove_pointer_t<decltype(gsrc)>>;
-    using R = std::conditional_t<sizeof(E) == 1, uint8_t, uint16_t>;
+    using R = std::conditional_t<sizeof(E) == 1, uint8_t, std::conditional_t<sizeof(E) == 2, uint16_t, uint32_t>>;
     const Vec<R, 4> v = *reinterpret_cast<const Vec<R, 4>*>(gsrc + i * st0 + j);
     const int col = (((il >> 2) ^ q) << 2) + (il & 3);  // swizzled position of row-element il
     R* d = reinterpret_cast<R*>(sdst) + (q * 4) * TILE + col;
@@ -525,9 +526,9 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
     const int il = w * 2 + h + 16 * r;
     const int64_t i = i0 + il, j = j0 + q * 4;
     if (i < size0 && j < p.size1) {
-      if constexpr (sizeof(T1) <= 2) { if (tmask & 1) stage(s1, g1, a0, il, i, j); }
-      if constexpr (NIN >= 2 && sizeof(T2) <= 2) { if (tmask & 2) stage(s2, g2, b0, il, i, j); }
-      if constexpr (NIN >= 3 && sizeof(T3) <= 2) { if (tmask & 4) stage(s3, g3, c0, il, i, j); }
+      if constexpr (sizeof(T1) <= 4) { if (tmask & 1) stage(s1, g1, a0, il, i, j); }
+      if constexpr (NIN >= 2 && sizeof(T2) <= 4) { if (tmask & 2) stage(s2, g2, b0, il, i, j); }
+      if constexpr (NIN >= 3 && sizeof(T3) <= 4) { if (tmask & 4) stage(s3, g3, c0, il, i, j); }
     }
   }
   __syncthreads();
@@ -550,27 +551,27 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
       Vec<T1, 4> va;
       Vec<T2, 4> vb{};
       Vec<T3, 4> vc{};
-      if constexpr (sizeof(T1) <= 2) {
+      if constexpr (sizeof(T1) <= 4) {
         if (tmask & 1) va = *reinterpret_cast<const Vec<T1, 4>*>(s1 + so);
       }
-      if (!(tmask & 1) || sizeof(T1) > 2) {
+      if (!(tmask & 1) || sizeof(T1) > 4) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) va.v[e] = k1 ? ka : g1[(i + e) * a0 + j * a1];
       }
       if constexpr (NIN >= 2) {
-        if constexpr (sizeof(T2) <= 2) {
+        if constexpr (sizeof(T2) <= 4) {
           if (tmask & 2) vb = *reinterpret_cast<const Vec<T2, 4>*>(s2 + so);
         }
-        if (!(tmask & 2) || sizeof(T2) > 2) {
+        if (!(tmask & 2) || sizeof(T2) > 4) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) vb.v[e] = k2 ? kb : g2[(i + e) * b0 + j * b1];
         }
       }
       if constexpr (NIN >= 3) {
-        if constexpr (sizeof(T3) <= 2) {
+        if constexpr (sizeof(T3) <= 4) {
           if (tmask & 4) vc = *reinterpret_cast<const Vec<T3, 4>*>(s3 + so);
         }
-        if (!(tmask & 4) || sizeof(T3) > 2) {
+        if (!(tmask & 4) || sizeof(T3) > 4) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) vc.v[e] = k3 ? kc : g3[(i + e) * c0 + j * c1];
         }
@@ -654,7 +655,7 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
       auto pair_ok = [&](int k, bool along1) { return group_ok(k, along1, 2); };
       bool pairs = sizeof(TO) <= 4 && sizeof(T1) <= 4 && (NIN < 2 || sizeof(T2) <= 4) && (NIN < 3 || sizeof(T3) <= 4) &&
                    tpl.shape[0] % 2 == 0 && tpl.shape[1] % 2 == 0 && pair_ok(0, false);
-      bool quads = sizeof(TO) == 2 && tpl.shape[0] % 4 == 0 && tpl.shape[1] % 4 == 0 && group_ok(0, false, 4);
+      bool quads = (sizeof(TO) == 2 || sizeof(TO) == 4) && tpl.shape[0] % 4 == 0 && tpl.shape[1] % 4 == 0 && group_ok(0, false, 4);
       int staged = 0, use_mask = 0;
       for (int k = 1; k <= NIN; ++k)
         if ((tmask >> (k - 1)) & 1) {
@@ -662,9 +663,9 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
           ++staged;
           use_mask |= 1 << (k - 1);
           pairs = pairs && pair_ok(k, true);
-          quads = quads && tpl.esize[k] <= 2 && group_ok(k, true, 4);
+          quads = quads && tpl.esize[k] <= 4 && group_ok(k, true, 4);
         }
-      if constexpr (sizeof(TO) == 2) {
+      if constexpr (sizeof(TO) == 2 || sizeof(TO) == 4) {
         const int64_t q0 = (tpl.shape[0] + 63) / 64, q1 = (tpl.shape[1] + 63) / 64;
         if (quads && q0 * q1 * outer <= 0x7fffffff && tpl.shape[0] <= 0x7fffffff) {
           tp.div_t0 = FastDiv(static_cast<uint32_t>(q0));
