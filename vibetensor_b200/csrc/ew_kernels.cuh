@@ -511,26 +511,47 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
   const int64_t a0 = p.s0[1], a1 = p.s1[1];
   const int64_t b0 = p.s0[NIN >= 2 ? 2 : 0], b1 = p.s1[NIN >= 2 ? 2 : 0];
   const int64_t c0 = p.s0[NIN >= 3 ? 3 : 0], c1 = p.s1[NIN >= 3 ? 3 : 0];
-  auto stage = [&](auto* sdst, const auto* gsrc, int64_t st0, int il, int64_t i, int64_t j) {
-    // moved as raw 8- / 16- / 32-bit words: one vector load, four plain stores
+  // 8- and 32-bit inputs: a lane takes four elements of ONE row and stores them one by one.
+  // 16-bit inputs: a lane takes four elements of TWO adjacent rows and stores, per column, the
+  // (even row, odd row) pair as one 32-bit word -- half the shared-memory stores per element.
+  // Both produce the same layout: tile[j][i] with the groups of four along i XOR-swizzled by j / 4.
+  auto stage = [&](auto* sdst, const auto* gsrc, int64_t st0) {
     using E = std::remove_cv_t<std::remove_pointer_t<decltype(gsrc)>>;
-    using R = std::conditional_t<sizeof(E) == 1, uint8_t, std::conditional_t<sizeof(E) == 2, uint16_t, uint32_t>>;
-    const Vec<R, 4> v = *reinterpret_cast<const Vec<R, 4>*>(gsrc + i * st0 + j);
-    const int col = (((il >> 2) ^ q) << 2) + (il & 3);  // swizzled position of row-element il
-    R* d = reinterpret_cast<R*>(sdst) + (q * 4) * TILE + col;
+    const int64_t j = j0 + q * 4;
+    if (j >= p.size1) return;
+    if constexpr (sizeof(E) == 2) {
+      uint32_t* d = reinterpret_cast<uint32_t*>(sdst) + (q * 4) * (TILE / 2);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) d[e * TILE] = v.v[e];
-  };
+      for (int r = 0; r < TILE / 32; ++r) {
+        const int pi = w * 2 + h + 16 * r;  // row pair within the tile
+        const int64_t i = i0 + 2 * pi;
+        if (i >= size0) continue;           // size0 is a multiple of four: the odd row exists too
+        const uint2 ve = *reinterpret_cast<const uint2*>(gsrc + i * st0 + j);
+        const uint2 vo = *reinterpret_cast<const uint2*>(gsrc + (i + 1) * st0 + j);
+        const int wi = pi ^ (2 * q);
+        d[0 * (TILE / 2) + wi] = __byte_perm(ve.x, vo.x, 0x5410);
+        d[1 * (TILE / 2) + wi] = __byte_perm(ve.x, vo.x, 0x7632);
+        d[2 * (TILE / 2) + wi] = __byte_perm(ve.y, vo.y, 0x5410);
+        d[3 * (TILE / 2) + wi] = __byte_perm(ve.y, vo.y, 0x7632);
+      }
+    } else {
+      using R = std::conditional_t<sizeof(E) == 1, uint8_t, uint32_t>;
 #pragma unroll
-  for (int r = 0; r < TILE / 16; ++r) {
-    const int il = w * 2 + h + 16 * r;
-    const int64_t i = i0 + il, j = j0 + q * 4;
-    if (i < size0 && j < p.size1) {
-      if constexpr (sizeof(T1) <= 4) { if (tmask & 1) stage(s1, g1, a0, il, i, j); }
-      if constexpr (NIN >= 2 && sizeof(T2) <= 4) { if (tmask & 2) stage(s2, g2, b0, il, i, j); }
-      if constexpr (NIN >= 3 && sizeof(T3) <= 4) { if (tmask & 4) stage(s3, g3, c0, il, i, j); }
+      for (int r = 0; r < TILE / 16; ++r) {
+        const int il = w * 2 + h + 16 * r;
+        const int64_t i = i0 + il;
+        if (i >= size0) continue;
+        const Vec<R, 4> v = *reinterpret_cast<const Vec<R, 4>*>(gsrc + i * st0 + j);
+        const int col = (((il >> 2) ^ q) << 2) + (il & 3);  // swizzled position of row-element il
+        R* d = reinterpret_cast<R*>(sdst) + (q * 4) * TILE + col;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) d[e * TILE] = v.v[e];
+      }
     }
-  }
+  };
+  if constexpr (sizeof(T1) <= 4) { if (tmask & 1) stage(s1, g1, a0); }
+  if constexpr (NIN >= 2 && sizeof(T2) <= 4) { if (tmask & 2) stage(s2, g2, b0); }
+  if constexpr (NIN >= 3 && sizeof(T3) <= 4) { if (tmask & 4) stage(s3, g3, c0); }
   __syncthreads();
   const bool k1 = !(tmask & 1) && a0 == 0 && a1 == 0;
   const bool k2 = NIN >= 2 && !(tmask & 2) && b0 == 0 && b1 == 0;
