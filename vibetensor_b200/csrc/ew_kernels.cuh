@@ -499,7 +499,7 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
   }
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int h = lane >> 4, q = lane & 15;
-  const int64_t i0 = static_cast<int64_t>(t0) * TILE, j0 = static_cast<int64_t>(t1) * TILE;
+  const int64_t i0 = static_cast<int64_t>(t0) * TILE;
   const int64_t size0 = p.n0v;
   const int slot2 = (tmask & 1) ? 1 : 0, slot3 = ((tmask & 1) ? 1 : 0) + ((tmask & 2) ? 1 : 0);
   T1* s1 = reinterpret_cast<T1*>(sm[0]);
@@ -511,6 +511,11 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
   const int64_t a0 = p.s0[1], a1 = p.s1[1];
   const int64_t b0 = p.s0[NIN >= 2 ? 2 : 0], b1 = p.s1[NIN >= 2 ? 2 : 0];
   const int64_t c0 = p.s0[NIN >= 3 ? 3 : 0], c1 = p.s1[NIN >= 3 ? 3 : 0];
+  // a block walks p.L consecutive tiles along dim 1: the offset decoding above is paid once
+  for (int tt = 0; tt < p.L; ++tt) {
+  const int64_t j0 = (static_cast<int64_t>(t1) * p.L + tt) * TILE;
+  if (j0 >= p.size1) break;
+  if (tt > 0) __syncthreads();  // readers of the previous tile are done
   // 8- and 32-bit inputs: a lane takes four elements of ONE row and stores them one by one.
   // 16-bit inputs: a lane takes four elements of TWO adjacent rows and stores, per column, the
   // (even row, odd row) pair as one 32-bit word -- half the shared-memory stores per element.
@@ -601,6 +606,7 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
       *reinterpret_cast<Vec<TO, 4>*>(go + i + j * p.s1[0]) = o;
     }
   }
+  }
 }
 
 // Host: picks the kernel for the plan and launches it.  INV_SPECIAL >= 0 additionally
@@ -687,7 +693,11 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
           quads = quads && tpl.esize[k] <= 4 && group_ok(k, true, 4);
         }
       if constexpr (sizeof(TO) == 2 || sizeof(TO) == 4) {
-        const int64_t q0 = (tpl.shape[0] + 63) / 64, q1 = (tpl.shape[1] + 63) / 64;
+        // one-input ops (copies, unary ops on a transposed view) walk four tiles per block; with
+        // more operands in play that order measured slower than one tile per block
+        constexpr int kTilesPerBlock = NIN == 1 ? 4 : 1;
+        const int64_t q0 = (tpl.shape[0] + 63) / 64, q1 = ((tpl.shape[1] + 63) / 64 + kTilesPerBlock - 1) / kTilesPerBlock;
+        tp.L = kTilesPerBlock;
         if (quads && q0 * q1 * outer <= 0x7fffffff && tpl.shape[0] <= 0x7fffffff) {
           tp.div_t0 = FastDiv(static_cast<uint32_t>(q0));
           tp.div_t1 = FastDiv(static_cast<uint32_t>(q1));
