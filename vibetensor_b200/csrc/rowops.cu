@@ -14,7 +14,7 @@
 //                  (online max/sum, then write); the second pass is served by L2.
 //
 // Math is FP32 whatever the storage type.
-//   softmax:  m = max x;  e = exp(x - m);  s = max(sum e, 1e-20);  y = e / s
+//   softmax:  m = max x;  e = exp(x - m) = 2^((x - m) * log2 e);  s = max(sum e, 1e-20);  y = e / s
 //             (the reference evaluates exp(x - (log s + m)), the same value; log_softmax is
 //              x - m - log s)
 //   rmsnorm:  r = rsqrt(sum x^2 / n + eps);  y = x * r * gamma
@@ -39,11 +39,13 @@ struct RowParams {
   int gamma_smem;  // block kernel: gamma staged in dynamic shared memory (cols floats)
 };
 
-template <class T> __device__ __forceinline__ float fast_exp(float x) {
-  // 16-bit outputs keep 8-11 mantissa bits: the 2-ulp ex2.approx path is far inside their
-  // rounding; FP32 uses the accurate expf.
-  if constexpr (sizeof(T) == 2) return __expf(x);
-  else return expf(x);
+// 2^x on the special-function unit.  exp(d) is taken as 2^(d * log2 e), the form Triton's tl.exp
+// lowers to in the reference's softmax kernel (2 ulp, far inside every tolerance of this path);
+// the multiply is done on float pairs by the caller.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 template <int G>
@@ -115,7 +117,8 @@ __device__ __forceinline__ void row_math(float (&v)[VPL][16 / sizeof(T)], const 
 #pragma unroll
         for (int j = 0; j < V; j += 2) {
           const float2 d2 = __fadd2_rn(make_float2(v[k][j], v[k][j + 1]), nm2);
-          const float2 e2 = make_float2(fast_exp<T>(d2.x), fast_exp<T>(d2.y));
+          const float2 t2 = __fmul2_rn(d2, make_float2(1.4426950408889634f, 1.4426950408889634f));
+          const float2 e2 = make_float2(ex2_approx(t2.x), ex2_approx(t2.y));
           s2 = __fadd2_rn(s2, e2);
           v[k][j] = KIND == K_SOFTMAX ? e2.x : d2.x;
           v[k][j + 1] = KIND == K_SOFTMAX ? e2.y : d2.y;
