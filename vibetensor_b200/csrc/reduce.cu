@@ -461,17 +461,25 @@ __global__ void __launch_bounds__(kThreads) col_cluster_kernel(const __grid_cons
 #pragma unroll
   for (int j = 0; j < V; ++j) acc[j] = R::init();
   if (active) {
-    constexpr int U = 8;
     int64_t r = r0 + w;
-    for (; r + (U - 1) * kWarps < r1; r += U * kWarps) {
-      A v[U][V];
+    // UU rows in flight per thread, while that many are left
+    auto batches = [&](auto uu) {
+      constexpr int UU = decltype(uu)::value;
+      for (; r + (UU - 1) * kWarps < r1; r += UU * kWarps) {
+        A v[UU][V];
 #pragma unroll
-      for (int u = 0; u < U; ++u) load_widen<T, V>(x + (r + u * kWarps) * p.S, v[u]);
+        for (int u = 0; u < UU; ++u) load_widen<T, V>(x + (r + u * kWarps) * p.S, v[u]);
 #pragma unroll
-      for (int u = 0; u < U; ++u)
+        for (int u = 0; u < UU; ++u)
 #pragma unroll
-        for (int j = 0; j < V; ++j) R::accum(acc[j], v[u][j], static_cast<typename R::idx_t>(r + u * kWarps));
-    }
+          for (int j = 0; j < V; ++j) R::accum(acc[j], v[u][j], static_cast<typename R::idx_t>(r + u * kWarps));
+      }
+    };
+    // (value, index) reducers: written sixteen deep, the compiler keeps about eight loads in
+    // flight under the compare-select chains; written eight deep, about four
+    if constexpr (R::kIndexed) batches(std::integral_constant<int, 16>{});
+    batches(std::integral_constant<int, 8>{});
+    batches(std::integral_constant<int, 2>{});
     for (; r < r1; r += kWarps) {
       A v[V];
       load_widen<T, V>(x + r * p.S, v);
