@@ -479,6 +479,10 @@ ew_transpose_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, c
 // XOR-swizzled by the row's group index: the 16 lanes of a half-warp then hit 16 different banks
 // on the store, and the vector reads along i are conflict-free.  Needs sizes, strides and bases
 // that keep groups of four aligned; the host checks.
+// one-input ops (copies, unary ops on a transposed view) walk four tiles per block; with more
+// operands in play that order measured slower than one tile per block
+template <int NIN> constexpr int kTr4TilesPerBlock = NIN == 1 ? 4 : 1;
+
 template <class F, class TO, class T1, class T2, class T3, int NIN>
 __global__ void __launch_bounds__(kEwThreads)
 ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, const int tmask) {
@@ -511,9 +515,11 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
   const int64_t a0 = p.s0[1], a1 = p.s1[1];
   const int64_t b0 = p.s0[NIN >= 2 ? 2 : 0], b1 = p.s1[NIN >= 2 ? 2 : 0];
   const int64_t c0 = p.s0[NIN >= 3 ? 3 : 0], c1 = p.s1[NIN >= 3 ? 3 : 0];
-  // a block walks p.L consecutive tiles along dim 1: the offset decoding above is paid once
-  for (int tt = 0; tt < p.L; ++tt) {
-  const int64_t j0 = (static_cast<int64_t>(t1) * p.L + tt) * TILE;
+  // a block walks kTiles consecutive tiles along dim 1: the offset decoding above is paid once
+  constexpr int kTiles = kTr4TilesPerBlock<NIN>;
+#pragma unroll 1
+  for (int tt = 0; tt < kTiles; ++tt) {
+  const int64_t j0 = (static_cast<int64_t>(t1) * kTiles + tt) * TILE;
   if (j0 >= p.size1) break;
   if (tt > 0) __syncthreads();  // readers of the previous tile are done
   // 8- and 32-bit inputs: a lane takes four elements of ONE row and stores them one by one.
@@ -693,11 +699,8 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
           quads = quads && tpl.esize[k] <= 4 && group_ok(k, true, 4);
         }
       if constexpr (sizeof(TO) == 2 || sizeof(TO) == 4) {
-        // one-input ops (copies, unary ops on a transposed view) walk four tiles per block; with
-        // more operands in play that order measured slower than one tile per block
-        constexpr int kTilesPerBlock = NIN == 1 ? 4 : 1;
+        constexpr int kTilesPerBlock = kTr4TilesPerBlock<NIN>;
         const int64_t q0 = (tpl.shape[0] + 63) / 64, q1 = ((tpl.shape[1] + 63) / 64 + kTilesPerBlock - 1) / kTilesPerBlock;
-        tp.L = kTilesPerBlock;
         if (quads && q0 * q1 * outer <= 0x7fffffff && tpl.shape[0] <= 0x7fffffff) {
           tp.div_t0 = FastDiv(static_cast<uint32_t>(q0));
           tp.div_t1 = FastDiv(static_cast<uint32_t>(q1));
