@@ -270,15 +270,29 @@ enum vbt_b200_reduce_op {
   VBT_B200_R_COUNT
 };
 
-/* Bytes of scratch the call below needs for these arguments (0 for most shapes; the
- * split reductions keep per-block partials and a ticket counter there).  A binding takes
- * it from the caching allocator; contents need no initialisation. */
+/* Bytes of scratch the call below needs for these arguments on the device that owns self
+ * (0 for most shapes; the split reductions keep a VBT_B200_REDUCE_TICKET_BYTES area of ticket
+ * counters at the start of it and per-block partials behind).  A binding takes it from the
+ * caching allocator; for vbt_b200_reduce the contents need no initialisation. */
+#define VBT_B200_REDUCE_TICKET_BYTES 4096
 VBT_B200_API size_t vbt_b200_reduce_workspace_bytes(int32_t op, const vbt_b200_tensor* self,
                                        const int64_t* dims, int32_t ndims);
 VBT_B200_API vbt_b200_status vbt_b200_reduce(int32_t op, const vbt_b200_tensor* out,
                                 const vbt_b200_tensor* out_index, const vbt_b200_tensor* self,
                                 const int64_t* dims, int32_t ndims, int32_t keepdim,
                                 void* workspace, size_t workspace_bytes, void* stream);
+/* The same call for a binding that KEEPS its workspace (one per stream, say): the first
+ * VBT_B200_REDUCE_TICKET_BYTES of the workspace must be zero before the first call -- zero the
+ * buffer once when it is created -- and every call leaves them zero again (the block that
+ * draws the last ticket resets the counter), so the per-call clearing of the ticket counters
+ * that vbt_b200_reduce enqueues in front of its kernel is not needed.  The rest of the
+ * workspace needs no initialisation.  Results are bit-identical to vbt_b200_reduce.  Calls
+ * that share a workspace must not overlap on the GPU. */
+VBT_B200_API vbt_b200_status vbt_b200_reduce_zeroed_ws(int32_t op, const vbt_b200_tensor* out,
+                                          const vbt_b200_tensor* out_index,
+                                          const vbt_b200_tensor* self, const int64_t* dims,
+                                          int32_t ndims, int32_t keepdim, void* workspace,
+                                          size_t workspace_bytes, void* stream);
 /* The same reduction for callers that cannot supply scratch memory (no counterpart in the
  * reference, whose kernels take their temporaries from its caching allocator).  Meant for
  * hosts that cannot allocate at call time -- a plugin whose host API only creates "dense
@@ -467,15 +481,88 @@ VBT_B200_API vbt_b200_status vbt_b200_rmsnorm_backward(void* dx, float* dgamma, 
  * first. */
 VBT_B200_API vbt_b200_status vbt_b200_enable_peer_access(int32_t compute_device, int32_t peer_device);
 /* partial (F32/I64, dense, reduced shape) = local SUM/MAX/MIN of the shard; BF16/F16
- * shards accumulate and emit FP32.  Same workspace contract as vbt_b200_reduce. */
+ * shards accumulate and emit FP32.  Workspace as for vbt_b200_reduce.  flags:
+ *   VBT_B200_PARTIAL_WS_ZEROED  the vbt_b200_reduce_zeroed_ws contract holds for `workspace`
+ *   VBT_B200_PARTIAL_NOT_FIRST  the shard does not hold the first element of the global
+ *                               tensor: MAX / MIN then skip the "a NaN at position 0 wins" rule,
+ *                               which belongs to the global position 0 only */
+#define VBT_B200_PARTIAL_WS_ZEROED 1
+#define VBT_B200_PARTIAL_NOT_FIRST 2
 VBT_B200_API vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_tensor* partial,
                                         const vbt_b200_tensor* shard, const int64_t* dims,
                                         int32_t ndims, int32_t keepdim, void* workspace,
-                                        size_t workspace_bytes, void* stream);
+                                        size_t workspace_bytes, int32_t flags, void* stream);
 /* out[i] = cast(partial[i] * scale): the "divide by the global N and cast" step of a
  * sharded mean.  partial F32 [n]; out F32/BF16/F16 [n]. */
 VBT_B200_API vbt_b200_status vbt_b200_scale_cast(void* out, int32_t out_dtype, const float* partial, int64_t n,
                                     float scale, void* stream);
+
+/* =====================================================================================
+ * 6. Observability
+ *    stands in for the reference's test hooks and counters: TensorIterStats
+ *    (cuda_ti_kernel_launches, num_32bit_splits; include/vbt/core/tensor_iterator/core.h:559-600)
+ *    and CudaReductionLastStats (selected kernel, grid, block, slice length, workspace bytes;
+ *    include/vbt/cuda/reduction_env.h:97-138).  Host-side bookkeeping only: nothing here
+ *    touches the device.
+ * ===================================================================================== */
+#define VBT_B200_FAMILY_NONE 0
+#define VBT_B200_FAMILY_ELEMENTWISE 1
+#define VBT_B200_FAMILY_REDUCE 2
+#define VBT_B200_FAMILY_INDEX 3
+#define VBT_B200_FAMILY_ROWOP 4
+#define VBT_B200_FAMILY_FABRIC 5
+#define VBT_B200_FAMILY_COUNT 6
+/* `kernel` values.  ELEMENTWISE: the codes of vbt_b200_ti_plan (0 flat, 1 tiled vector,
+ * 2 tiled scalar, 3 transposing).  REDUCE: */
+#define VBT_B200_RK_ROW_WARP 1     /* one warp per output                                   */
+#define VBT_B200_RK_ROW_BLOCK 2    /* `splits` blocks per output, ticket fold                */
+#define VBT_B200_RK_COL 3          /* column tiles, `splits` blocks along the reduced dim   */
+#define VBT_B200_RK_COL_CLUSTER 4  /* the same folded inside a thread-block cluster         */
+#define VBT_B200_RK_GENERIC 5
+#define VBT_B200_RK_FILL 6         /* empty reduction domain: constant fill                 */
+/* INDEX: */
+#define VBT_B200_IK_ROWS_COPY 1
+#define VBT_B200_IK_ROWS_COPY_ELEM 2
+#define VBT_B200_IK_SCATTER_ADD 3
+#define VBT_B200_IK_SCATTER_ADD_ELEM 4
+#define VBT_B200_IK_SCATTER_ADD_SORTED 5
+#define VBT_B200_IK_LASTDIM 6
+#define VBT_B200_IK_LASTDIM_STAGED 7  /* rows staged in shared memory by bulk copies, index
+                                         list in registers; `splits` = pieces per row       */
+#define VBT_B200_IK_MASK_SELECT 8
+/* ROWOP: */
+#define VBT_B200_WK_GROUP 1
+#define VBT_B200_WK_BLOCK 2
+#define VBT_B200_WK_STREAM 3
+#define VBT_B200_WK_BACKWARD 4
+#define VBT_B200_WK_SCALE_CAST 5
+/* FABRIC: */
+#define VBT_B200_FK_PEER_LOAD 1      /* the elementwise kernel reads the peer operand over NVLink */
+#define VBT_B200_FK_COPY_FALLBACK 2  /* peer operand copied to local scratch first           */
+#define VBT_B200_FK_LOCAL 3          /* both operands on the compute device                  */
+
+typedef struct vbt_b200_launch_info {
+  int32_t family;           /* VBT_B200_FAMILY_*; NONE when the call launched nothing         */
+  int32_t kernel;           /* per-family code above (the call's main kernel)                 */
+  uint32_t grid[3];
+  uint32_t block[3];
+  int32_t vec;              /* elements per vector access                                     */
+  int32_t splits;           /* reductions: blocks that share one output                       */
+  int32_t cluster;          /* thread-block cluster size, 0 = none                            */
+  int32_t launches;         /* stream operations the call enqueued (kernels + memsets/copies) */
+  int64_t out_numel;
+  int64_t slice_len;        /* reductions: reduced extent; indexing: indices                  */
+  uint64_t workspace_bytes; /* scratch bytes the launch used                                  */
+  void* stream;
+} vbt_b200_launch_info;
+
+/* What the last successful launching call on the CALLING THREAD enqueued. */
+VBT_B200_API vbt_b200_status vbt_b200_last_launch_info(vbt_b200_launch_info* out);
+VBT_B200_API void vbt_b200_reset_last_launch_info(void);
+/* Process-wide launch counts per family (counts[f], f < VBT_B200_FAMILY_COUNT) since load or
+ * the last reset. */
+VBT_B200_API vbt_b200_status vbt_b200_launch_counts(uint64_t* counts, int32_t n);
+VBT_B200_API void vbt_b200_reset_launch_counts(void);
 
 #ifdef __cplusplus
 } /* extern "C" */

@@ -40,3 +40,17 @@ def ref():
     if not oracle.have_ref():
         pytest.skip("oracle/_ref not built (no reference checkout on this machine)")
     return oracle.ref()
+
+
+def pytest_terminal_summary(terminalreporter):
+    """Worst observed error of every tolerance check that recorded one (error / scale, bound)."""
+    try:
+        from tests.util import WORST
+    except Exception:  # pragma: no cover
+        return
+    if not WORST:
+        return
+    terminalreporter.write_line("worst observed error / scale per tolerance check (bound):")
+    for label in sorted(WORST):
+        err, bound = WORST[label]
+        terminalreporter.write_line(f"  {label}: {err:.3e} ({bound:.0e})")

@@ -27,15 +27,25 @@ class CpuStandIn:
         return {"add": torch.add, "mul": torch.mul}[name](a, b)
 
     @staticmethod
-    def reduce(name, x, dims, keepdim=False, partial=False):
+    def reduce(name, x, dims, keepdim=False, partial=False, first_shard=True):
         dims = list(dims) if dims else list(range(x.dim()))
         acc = x.float() if (partial and x.dtype in (torch.bfloat16, torch.float16)) else x
         if name == "sum":
             return acc.sum(dim=dims, keepdim=keepdim)
         if name == "mean":
             return acc.mean(dim=dims, keepdim=keepdim)
+        # the library's scan: NaN never wins a comparison; a NaN at position 0 of the reduced
+        # slice wins outright -- unless the shard is not the first one (first_shard=False)
+        ident = float("-inf") if name == "max" else float("inf")
         f = torch.amax if name == "max" else torch.amin
-        return f(acc, dim=dims, keepdim=keepdim)
+        if not acc.dtype.is_floating_point:
+            return f(acc, dim=dims, keepdim=keepdim)
+        out = f(torch.nan_to_num(acc, nan=ident, posinf=float("inf"), neginf=float("-inf")), dim=dims, keepdim=keepdim)
+        if first_shard:
+            first = acc[tuple(slice(0, 1) if d in dims else slice(None) for d in range(acc.dim()))]
+            first = first if keepdim else first.reshape(out.shape)
+            out = torch.where(torch.isnan(first), first, out)
+        return out
 
     @staticmethod
     def scale_cast(partial, scale, out_dtype):
@@ -122,6 +132,38 @@ def case_reductions(rank, world):
     np.testing.assert_allclose(mb.float().numpy(), want.numpy(), rtol=1e-2, atol=1e-2)
 
 
+def case_nan_rule_across_shards(rank, world):
+    """max / min: a NaN wins only at GLOBAL position 0.  A NaN in the first row of a later shard
+    is ignored, exactly as on one GPU; a NaN in the very first row decides the result on every
+    rank; and an empty leading shard hands the rule to the next rank."""
+    from vibetensor_b200 import fabric
+    mesh = fabric.FabricMesh.from_world()
+    ops = CpuStandIn
+    x, rows, offs = _global(world, (4,), seed=6)
+    x[offs[1], 2] = np.nan          # first row of shard 1, column 2: must be ignored
+    x[0, 1] = np.nan                # global row 0, column 1: wins
+    ft = fabric.FabricTensor.sharded_1d_row(mesh, torch.from_numpy(x[offs[rank]:offs[rank + 1]].copy()))
+    got = fabric.amax(ft, dim=0, local_ops=ops).numpy()
+    want = np.nanmax(x, axis=0)
+    want[1] = np.nan
+    np.testing.assert_array_equal(got, want)
+    got = fabric.amin(ft, dim=0, local_ops=ops).numpy()
+    want = np.nanmin(x, axis=0)
+    want[1] = np.nan
+    np.testing.assert_array_equal(got, want)
+    # full reduce: global element 0 is not NaN here, so the NaNs elsewhere are ignored
+    assert fabric.amax(ft, local_ops=ops).item() == np.nanmax(x)
+    # rank 0 empty: rank 1 owns global row 0
+    y = x[offs[1]:]
+    lo = 0 if rank == 0 else offs[rank] - offs[1]
+    hi = 0 if rank == 0 else offs[rank + 1] - offs[1]
+    fy = fabric.FabricTensor.sharded_1d_row(mesh, torch.from_numpy(y[lo:hi].copy()))
+    got = fabric.amax(fy, dim=0, local_ops=ops).numpy()
+    want = np.nanmax(y, axis=0)
+    want[2] = np.nan                # y[0, 2] is the NaN planted above: now at global position 0
+    np.testing.assert_array_equal(got, want)
+
+
 def case_empty_shard_and_errors(rank, world):
     from vibetensor_b200 import fabric
     mesh = fabric.FabricMesh.from_world()
@@ -182,6 +224,11 @@ def case_rank_failure_between_steps(rank, world):
 @pytest.mark.parametrize("world", [2, 3])
 def test_sharded_reductions_and_elementwise(world):
     _run("case_reductions", world)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_nan_wins_only_at_global_position_zero(world):
+    _run("case_nan_rule_across_shards", world)
 
 
 def test_empty_shard_and_error_paths():

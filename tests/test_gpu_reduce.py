@@ -1,9 +1,10 @@
 """CUDA dim reductions vs the CPU oracle through the C ABI.
 
 Bit-exact: int64 everything, amax / amin / argmax / argmin (values and indices).
-fp32 sum / mean / prod: |delta| <= 1e-5 * scale, scale = sum |x| over the slice (the size of
-the terms being added; the reference's own left-to-right fp32 sum differs from the fp64
-truth by the same order).  bf16 / f16: 1e-2."""
+fp32 sum / mean: |delta| <= 1e-5 * scale against the fp64 truth, scale = max(|truth|,
+sigma * sqrt(N)) of the reduced slice (sigma * sqrt(N) computed as sqrt(sum x^2)); the oracle's
+own left-to-right fp32 sum is held to the same bound, and the worst observed error of each is
+reported on failure.  bf16 / f16: 1e-2 on the same scale."""
 import os
 
 import numpy as np
@@ -11,7 +12,7 @@ import pytest
 import torch
 
 import oracle
-from tests.util import CODE, as_f32, from_np, rand_storage, to_np
+from tests.util import CODE, as_f32, from_np, note_worst, rand_storage, to_np
 
 pytestmark = pytest.mark.gpu
 GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_vectors.npz"))
@@ -42,16 +43,17 @@ def _check(ops, port, name, x_np, dtype, dim, view=None, keepdim=False):
         np.testing.assert_allclose(as_f32(g, dtype), as_f32(want, dtype), rtol=1e-4 if tol < 1e-3 else 3e-2)
         return
     ax = None if dim is None else dim
-    scale = np.abs(xf).sum(axis=ax, keepdims=keepdim)
     truth = xf.sum(axis=ax, keepdims=keepdim)
+    scale = np.maximum(np.abs(truth), np.sqrt((xf * xf).sum(axis=ax, keepdims=keepdim)))
     if name == "mean":
         n = xf.size if dim is None else xf.shape[dim]
         scale, truth = scale / n, truth / n
     err = np.abs(as_f32(g, dtype).astype(np.float64) - truth)
     ref_err = np.abs(as_f32(want, dtype).astype(np.float64) - truth)
-    assert (err <= tol * scale + 1e-30).all(), (name, err.max(), (tol * scale).min())
-    # and never worse than a storage ulp beyond the reference's own drift
-    assert err.max() <= max(ref_err.max(), 0) + tol * scale.max()
+    worst, ref_worst = float((err / (scale + 1e-300)).max()), float((ref_err / (scale + 1e-300)).max())
+    note_worst(f"reduce {name} {str(dtype)[6:]}", worst, tol)
+    assert (err <= tol * scale + 1e-30).all(), \
+        f"{name}: worst error {worst:.3e} of scale (oracle's own: {ref_worst:.3e}), bound {tol:.0e}"
 
 
 SHAPES = [((64, 96), -1), ((64, 96), 0), ((4096, 17), 0), ((17, 4096), -1), ((3, 5000), 1),
@@ -211,7 +213,8 @@ def test_large_sum_properties(ops):
     x = torch.randn(n, device="cuda")
     s = ops.sum(x).item()
     truth = x.double().sum().item()
-    scale = x.abs().double().sum().item()
+    scale = max(abs(truth), float(x.double().pow(2).sum().sqrt().item()))
+    note_worst("reduce sum float32 [2^28]", abs(s - truth) / scale, 1e-5)
     assert abs(s - truth) <= 1e-5 * scale
     s2 = ops.sum(ops.mul(x, 2.0)).item()
     assert s2 == 2.0 * s  # scaling by 2 is exact, so the fixed-order sum doubles exactly

@@ -53,3 +53,11 @@ def strided_like(t_np: np.ndarray, dtype, strides_elems, storage_elems, offset=0
     base_t = from_np(base_np, dtype, device)
     view_t = torch.as_strided(base_t, t_np.shape, strides_elems, offset)
     return view_t, view_np
+
+
+WORST: dict = {}  # label -> (largest error / scale seen in this run, bound); printed at the end of the run
+
+
+def note_worst(label: str, err_over_scale: float, bound: float) -> None:
+    prev = WORST.get(label, (0.0, bound))[0]
+    WORST[label] = (max(prev, float(err_over_scale)), bound)

@@ -22,6 +22,14 @@ _TORCH_TO_CODE = {
 MAX_NDIM = 25
 
 
+class LaunchInfo(ctypes.Structure):
+    """vbt_b200_launch_info: what the last launching call on this thread enqueued."""
+    _fields_ = [("family", ctypes.c_int32), ("kernel", ctypes.c_int32), ("grid", ctypes.c_uint32 * 3),
+                ("block", ctypes.c_uint32 * 3), ("vec", ctypes.c_int32), ("splits", ctypes.c_int32),
+                ("cluster", ctypes.c_int32), ("launches", ctypes.c_int32), ("out_numel", ctypes.c_int64),
+                ("slice_len", ctypes.c_int64), ("workspace_bytes", ctypes.c_uint64), ("stream", ctypes.c_void_p)]
+
+
 class VbtTensor(ctypes.Structure):
     _fields_ = [("data", ctypes.c_void_p), ("dtype", ctypes.c_int32), ("ndim", ctypes.c_int32),
                 ("sizes", ctypes.POINTER(ctypes.c_int64)), ("strides", ctypes.POINTER(ctypes.c_int64))]
@@ -55,6 +63,7 @@ SIGNATURES = {
     "vbt_b200_ti_plan": (_i32, [ctypes.POINTER(_P), _i32, _i64p, _i64p, _i32p, _i32p, _i32p]),
     "vbt_b200_reduce_workspace_bytes": (ctypes.c_size_t, [_i32, _P, _i64p, _i32]),
     "vbt_b200_reduce": (_i32, [_i32, _P, _P, _P, _i64p, _i32, _i32, _vp, ctypes.c_size_t, _vp]),
+    "vbt_b200_reduce_zeroed_ws": (_i32, [_i32, _P, _P, _P, _i64p, _i32, _i32, _vp, ctypes.c_size_t, _vp]),
     "vbt_b200_reduce_noalloc": (_i32, [_i32, _P, _P, _P, _i64p, _i32, _i32, _vp]),
     "vbt_b200_reduce_shape": (_i32, [_P, _i64p, _i32, _i32, _i64p, _i32p]),
     "vbt_b200_index_rows": (_i32, [_P, _P, _P, _i32, _vp, _vp]),
@@ -76,8 +85,12 @@ SIGNATURES = {
     "vbt_b200_rmsnorm_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp,
                                          ctypes.c_size_t, _vp]),
     "vbt_b200_enable_peer_access": (_i32, [_i32, _i32]),
-    "vbt_b200_reduce_partial": (_i32, [_i32, _P, _P, _i64p, _i32, _i32, _vp, ctypes.c_size_t, _vp]),
+    "vbt_b200_reduce_partial": (_i32, [_i32, _P, _P, _i64p, _i32, _i32, _vp, ctypes.c_size_t, _i32, _vp]),
     "vbt_b200_scale_cast": (_i32, [_vp, _i32, _vp, _i64, ctypes.c_float, _vp]),
+    "vbt_b200_last_launch_info": (_i32, [ctypes.POINTER(LaunchInfo)]),
+    "vbt_b200_reset_last_launch_info": (None, []),
+    "vbt_b200_launch_counts": (_i32, [ctypes.POINTER(ctypes.c_uint64), _i32]),
+    "vbt_b200_reset_launch_counts": (None, []),
 }
 
 _EXC = {1: ValueError, 2: RuntimeError, 3: IndexError, 4: RuntimeError}
@@ -142,6 +155,22 @@ def stream_ptr(t: torch.Tensor | None = None) -> ctypes.c_void_p:
     """Current torch stream of the tensor's device as a cudaStream_t."""
     dev = t.device if t is not None else None
     return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+FAMILIES = ("none", "elementwise", "reduce", "index", "rowop", "fabric")
+
+
+def last_launch_info() -> LaunchInfo:
+    info = LaunchInfo()
+    check(lib().vbt_b200_last_launch_info(ctypes.byref(info)))
+    return info
+
+
+def launch_counts() -> dict:
+    """Process-wide launch counts per kernel family since load (or the last reset)."""
+    arr = (ctypes.c_uint64 * len(FAMILIES))()
+    check(lib().vbt_b200_launch_counts(arr, len(FAMILIES)))
+    return {name: int(arr[i]) for i, name in enumerate(FAMILIES)}
 
 
 def i64_array(vals):

@@ -68,6 +68,26 @@ class DeviceScope {
 };
 
 int sm_count(int device);
+// SM count of the device that is current on the calling thread (launchers run under a DeviceScope).
+inline int current_sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return 148;
+  }
+  return sm_count(dev);
+}
+// Device that owns `ptr`, or the current device for a pointer CUDA does not know.
+inline int device_of(const void* ptr) {
+  cudaPointerAttributes attr{};
+  if (ptr && cudaPointerGetAttributes(&attr, ptr) == cudaSuccess &&
+      (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged))
+    return attr.device;
+  cudaGetLastError();
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev;
+}
 
 inline int itemsize(int dtype) {
   switch (dtype) {
@@ -98,6 +118,34 @@ inline bool is_dense_row_major(const vbt_b200_tensor& t) {
   return true;
 }
 vbt_b200_status validate_tensor(const vbt_b200_tensor* t, const char* what);
+// validate_tensor plus: a tensor with elements must have a data pointer (a kernel given a null
+// base would fault on the device).
+vbt_b200_status validate_data(const vbt_b200_tensor* t, const char* what);
+
+// ---------------------------------------------------------------------------------------
+// observability: what the last call on this thread launched, and process-wide launch counts
+// (the counterpart of the reference's TensorIterStats / CudaReductionLastStats test hooks)
+// ---------------------------------------------------------------------------------------
+vbt_b200_launch_info& launch_info_ref();
+void count_launches(int family, int n);
+inline void note_launch(int family, int kernel, dim3 grid, dim3 block, int vec, int splits, int cluster,
+                        int launches, int64_t out_numel, int64_t slice_len, size_t workspace_bytes,
+                        const void* stream) {
+  vbt_b200_launch_info& li = launch_info_ref();
+  li.family = family;
+  li.kernel = kernel;
+  li.grid[0] = grid.x; li.grid[1] = grid.y; li.grid[2] = grid.z;
+  li.block[0] = block.x; li.block[1] = block.y; li.block[2] = block.z;
+  li.vec = vec;
+  li.splits = splits;
+  li.cluster = cluster;
+  li.launches = launches;
+  li.out_numel = out_numel;
+  li.slice_len = slice_len;
+  li.workspace_bytes = workspace_bytes;
+  li.stream = const_cast<void*>(stream);
+  count_launches(family, launches);
+}
 
 // ---------------------------------------------------------------------------------------
 // 32-bit division by an invariant (n < 2^31): q = (umulhi(n, m) + n) >> s
@@ -124,6 +172,32 @@ struct FastDiv {
     r = n - q * d;
   }
 };
+
+// ---------------------------------------------------------------------------------------
+// linear index over a list of dims (last dim fastest) -> element offset; used for the kept /
+// reduced dims of a reduction and for the leading dims of an indexed tensor
+// ---------------------------------------------------------------------------------------
+struct DimList {
+  int n;
+  FastDiv div[VBT_B200_MAX_NDIM];
+  int64_t stride[VBT_B200_MAX_NDIM];
+  __device__ __forceinline__ int64_t offset(uint32_t lin) const {
+    int64_t off = 0;
+    for (int d = n - 1; d >= 0; --d) {
+      uint32_t c;
+      div[d].divmod(lin, lin, c);
+      off += static_cast<int64_t>(c) * stride[d];
+    }
+    return off;
+  }
+};
+inline void fill_dimlist(DimList& dl, const int64_t* sizes, const int64_t* strides, int n) {
+  dl.n = n;
+  for (int i = 0; i < n; ++i) {
+    dl.div[i] = FastDiv(static_cast<uint32_t>(sizes[i]));
+    dl.stride[i] = strides[i];
+  }
+}
 
 // ---------------------------------------------------------------------------------------
 // device-side element helpers

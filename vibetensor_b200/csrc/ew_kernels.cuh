@@ -624,6 +624,9 @@ template <class F, class TO, class T1, class T2, class T3, int NIN, int INV_SPEC
           bool LEAN = false>
 vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
   if (plan.numel == 0) return VBT_B200_OK;
+  auto note = [&](int kind, unsigned grid, int vec) {
+    note_launch(VBT_B200_FAMILY_ELEMENTWISE, kind, dim3(grid), dim3(kEwThreads), vec, 1, 0, 1, plan.numel, 0, 0, stream);
+  };
   constexpr int kMaxEs = static_cast<int>(std::max({sizeof(TO), sizeof(T1), NIN >= 2 ? sizeof(T2) : size_t{1},
                                                     NIN >= 3 ? sizeof(T3) : size_t{1}}));
   constexpr int V = 16 / kMaxEs > 8 ? 8 : 16 / kMaxEs;  // 1-byte types: 8 lanes keep the register count sane
@@ -641,10 +644,12 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
       const int64_t blocks = std::max<int64_t>(1, (nvec + kEwThreads * kEwUnroll - 1) / (kEwThreads * kEwUnroll));
       VB_ARG(blocks <= 0x7fffffff, "elementwise: tensor too large for one launch");
       ew_flat_kernel<F, TO, T1, T2, T3, NIN, V><<<static_cast<unsigned>(blocks), kEwThreads, 0, stream>>>(fp, f);
+      note(0, static_cast<unsigned>(blocks), V);
     } else {
       const int64_t blocks = (plan.numel + kEwThreads * kEwUnroll - 1) / (kEwThreads * kEwUnroll);
       VB_ARG(blocks <= 0x7fffffff, "elementwise: tensor too large for one launch");
       ew_flat_kernel<F, TO, T1, T2, T3, NIN, 1><<<static_cast<unsigned>(blocks), kEwThreads, 0, stream>>>(fp, f);
+      note(0, static_cast<unsigned>(blocks), 1);
     }
     VB_LAUNCH_CHECK();
     return VBT_B200_OK;
@@ -708,6 +713,7 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
           tp.size1 = tpl.shape[1];
           ew_transpose4_kernel<F, TO, T1, T2, T3, NIN><<<static_cast<unsigned>(q0 * q1 * outer), kEwThreads, 0, stream>>>(tp, f, use_mask);
           VB_LAUNCH_CHECK();
+          note(3, static_cast<unsigned>(q0 * q1 * outer), 4);
           return VBT_B200_OK;
         }
       }
@@ -725,6 +731,7 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
           tp.size1 = tpl.shape[1];
           ew_transpose_kernel<F, TO, T1, T2, T3, NIN, 2><<<static_cast<unsigned>(blocks), kEwThreads, 0, stream>>>(tp, f, use_mask);
           VB_LAUNCH_CHECK();
+          note(3, static_cast<unsigned>(blocks), 2);
           return VBT_B200_OK;
         }
         tp.div_t0 = FastDiv(static_cast<uint32_t>(tiles0));
@@ -733,6 +740,7 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
         tp.size1 = tpl.shape[1];
         ew_transpose_kernel<F, TO, T1, T2, T3, NIN, 1><<<static_cast<unsigned>(blocks), kEwThreads, 0, stream>>>(tp, f, use_mask);
         VB_LAUNCH_CHECK();
+        note(3, static_cast<unsigned>(blocks), 1);
         return VBT_B200_OK;
       }
     }
@@ -766,20 +774,10 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
   // rows per block: long enough to amortise the per-block offset decode and to reuse
   // hoisted operands, short enough to leave >= ~16 blocks per SM when the tensor allows
   // rows per thread.  Long walks (32) pay when an operand that has to be GATHERED along dim 0
-  // is constant along dim 1: it is fetched once and reused for every row.  Otherwise one
-  // unrolled batch per thread is best: blocks retire quickly and the next ones start with
-  // all their loads in flight, as in the flat kernel.
-  bool reuse_gather = false;
-  for (int k = 1; k <= NIN; ++k)
-    reuse_gather = reuse_gather || (tp.s1[k] == 0 && tp.s0[k] != 0 && tp.s0[k] != 1);
-  int want_rows = 32;
-  (void)reuse_gather;
-  if (const char* e = std::getenv("VBT_B200_EW_ROWS_PER_THREAD")) {  // tuning knob, like the reference's VBT_* flags
-    const int v = std::atoi(e);
-    if (v >= 1 && v <= 1024) want_rows = v;
-  }
+  // is constant along dim 1: it is fetched once and reused for every row.
+  const int want_rows = 32;
   int L = static_cast<int>(std::min<int64_t>(want_rows, (size1 + R - 1) / R));
-  const int sms = 148;
+  const int sms = current_sm_count();
   while (L > 4 && tiles0 * ((size1 + int64_t{R} * L - 1) / (int64_t{R} * L)) * outer < int64_t{sms} * 16) L /= 2;
   L = std::max(L, 1);
   const int64_t tiles1 = (size1 + int64_t{R} * L - 1) / (int64_t{R} * L);
@@ -793,6 +791,7 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
   tp.log2_w0 = log2_w0;
   tp.L = L;
   const unsigned g = static_cast<unsigned>(blocks);
+  note(vec ? 1 : 2, g, v);
   if (vec) {
     if constexpr (INV_SPECIAL >= 0) {
       int mask = 0;

@@ -16,6 +16,10 @@
 //                 Zipf-distributed rows this removes most same-address atomic traffic.
 //
 // Bad indices never fault: they are skipped and counted in the caller's status block.
+#include <climits>
+#include <mutex>
+
+#include "bulk_copy.cuh"
 #include "common.cuh"
 
 namespace vb {
@@ -606,13 +610,14 @@ __global__ void __launch_bounds__(kThreads) scatter_add_sorted_kernel(const __gr
 }
 
 // ------------------------------------------------------------------------------------
-// last-dim index / index_put: out[b, k] = src[b, idx[k]]
+// last-dim index / index_put: out[r, k] = src[r, idx[k]], r running over the leading dims
 // ------------------------------------------------------------------------------------
 struct LastDimParams {
-  char* self;       // [B, K0] strides (sb, sk) elements
+  char* self;       // [leading dims..., K0]: row r starts rows.offset(r) elements in, column stride sk
   char* other;      // dense [B, K]
   IndexSrc idx;
-  int64_t B, K0, K, sb, sk;
+  int64_t B, K0, K, sk;
+  DimList rows;     // the leading dims of self (any strides), collapsed where they merge
   int es;
   int policy;
   unsigned long long* status;
@@ -635,9 +640,12 @@ __global__ void __launch_bounds__(kThreads) lastdim_kernel(const __grid_constant
   for (int64_t b0 = static_cast<int64_t>(blockIdx.y) * kLdRows; b0 < p.B;
        b0 += static_cast<int64_t>(gridDim.y) * kLdRows) {
     E val[kLdRows];
+    int64_t off[kLdRows];
+#pragma unroll
+    for (int r = 0; r < kLdRows; ++r) off[r] = b0 + r < p.B ? p.rows.offset(static_cast<uint32_t>(b0 + r)) : 0;
     if (p.mode == 0) {
 #pragma unroll
-      for (int r = 0; r < kLdRows; ++r) val[r] = (good && b0 + r < p.B) ? self[(b0 + r) * p.sb] : E(0);
+      for (int r = 0; r < kLdRows; ++r) val[r] = (good && b0 + r < p.B) ? self[off[r]] : E(0);
 #pragma unroll
       for (int r = 0; r < kLdRows; ++r)
         if (b0 + r < p.B) other[(b0 + r) * p.K] = val[r];
@@ -647,7 +655,7 @@ __global__ void __launch_bounds__(kThreads) lastdim_kernel(const __grid_constant
 #pragma unroll
       for (int r = 0; r < kLdRows; ++r) {
         if (b0 + r >= p.B) continue;
-        E* d = self + (b0 + r) * p.sb;
+        E* d = self + off[r];
         if (p.mode == 1) {
           *d = val[r];
         } else if constexpr (sizeof(E) == 4) {
@@ -661,63 +669,100 @@ __global__ void __launch_bounds__(kThreads) lastdim_kernel(const __grid_constant
   }
 }
 
-// Gather form for long rows: the kernel above sends one 32-byte sector request through L1 per
-// element (random positions), which saturates the L1/TEX pipe at about a third of HBM speed.
-// Here a block stages a contiguous piece of one source row in shared memory (coalesced 16-byte
-// loads), then every thread walks the index list and serves the positions that fall inside the
-// piece from shared memory, where 32 random 4-byte reads cost a few cycles.  A row takes
-// ceil(K0 / piece) passes and the index list is re-read per pass (coalesced, L2-resident); the
-// host only picks this kernel for rows of one piece, where it runs at about twice the speed of
-// the kernel above.
-constexpr int kLdsThreads = 512;
-template <class E>
-__global__ void __launch_bounds__(kLdsThreads, 2) lastdim_gather_smem_kernel(const __grid_constant__ LastDimParams p,
-                                                                             const int piece) {
-  extern __shared__ __align__(16) unsigned char lds_raw[];
-  E* tile = reinterpret_cast<E*>(lds_raw);
+// Gather form for long rows.  The kernel above sends one 32-byte sector request through L1 per
+// element (random positions): eight times the useful bytes on the L2 -> SM path, which
+// saturates at about a third of HBM speed.  Here the index list -- the same for every row --
+// is read ONCE per block and kept in registers (EPT entries per thread, position
+// k = chunk start + j * blockDim + t), and the block then walks its rows: each row is brought
+// into shared memory piece by piece with bulk asynchronous copies (two stages, so the next
+// piece loads while the current one is served), and every thread serves those of its entries
+// that fall inside the piece from shared memory, where a random 4-byte read costs a few
+// cycles.  Per output element the row is read once (coalesced, at DRAM speed) and the
+// output written once; a warp's stores cover 32 consecutive positions with about 1 / pieces
+// of the lanes active.  Index lists longer than one block's registers hold are split over
+// blockIdx.y (each such block stages the rows again; they come from L2).
+constexpr int kStThreads = 1024;
+static __device__ unsigned vb_index_fault;  // a bounded wait on a staged copy gave up
+
+template <class E, int EPT>
+__global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __grid_constant__ LastDimParams p,
+                                                                       const int piece, const int npieces,
+                                                                       const int use_bulk) {
+  extern __shared__ __align__(128) unsigned char st_raw[];
+  __shared__ __align__(8) uint64_t bars[2];
   const int t = threadIdx.x;
-  constexpr int VE = 16 / sizeof(E);
-  bool first = blockIdx.x == 0;  // bad indices are counted once: block 0, its first row, first pass
-  for (int64_t b = blockIdx.x; b < p.B; b += gridDim.x) {
-    const E* src = reinterpret_cast<const E*>(p.self) + b * p.sb;
-    E* out = reinterpret_cast<E*>(p.other) + b * p.K;
-    for (int64_t c0 = 0; c0 < p.K0; c0 += piece) {
-      const int n = static_cast<int>(p.K0 - c0 < piece ? p.K0 - c0 : piece);
-      __syncthreads();  // readers of the previous piece are done
-      if (p.sk == 1 && (reinterpret_cast<uintptr_t>(src + c0) % 16) == 0) {
-        const int nv = n / VE;
-        const int4* s4 = reinterpret_cast<const int4*>(src + c0);
-        int4* d4 = reinterpret_cast<int4*>(tile);
-#pragma unroll 4
-        for (int i = t; i < nv; i += kLdsThreads) d4[i] = s4[i];
-        for (int i = nv * VE + t; i < n; i += kLdsThreads) tile[i] = src[c0 + i];
-      } else {
-        for (int i = t; i < n; i += kLdsThreads) tile[i] = src[(c0 + i) * p.sk];
-      }
-      __syncthreads();
-      // eight index loads in flight per thread: the walk is otherwise one L2 round trip per index
-      constexpr int U = 8;
-      for (int64_t k0 = t; k0 < p.K; k0 += U * kLdsThreads) {
-        int64_t v[U];
+  const size_t stage_bytes = (static_cast<size_t>(piece) * sizeof(E) + 127) / 128 * 128;
+  E* const tile0 = reinterpret_cast<E*>(st_raw);
+  E* const tile1 = reinterpret_cast<E*>(st_raw + stage_bytes);
+  // this block's index entries; an entry that must be skipped holds 0xffffffff, which lies in no piece
+  const int64_t kc0 = static_cast<int64_t>(blockIdx.y) * (kStThreads * EPT);
+  uint32_t v[EPT];
+  uint32_t bad = 0;
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int64_t k = k0 + u * kLdsThreads;
-          v[u] = k < p.K ? p.idx.get(k) : 0;
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int64_t k = k0 + u * kLdsThreads;
-          if (k >= p.K) continue;
-          const bool good = normalize(v[u], p.K0, p.policy, p.status, first && c0 == 0);
-          if (good) {
-            if (v[u] >= c0 && v[u] < c0 + n) out[k] = tile[v[u] - c0];
-          } else if (c0 == 0) {
-            out[k] = E(0);
-          }
-        }
-      }
+  for (int j = 0; j < EPT; ++j) {
+    const int64_t k = kc0 + static_cast<int64_t>(j) * kStThreads + t;
+    v[j] = 0xffffffffu;
+    if (k < p.K) {
+      int64_t x = p.idx.get(k);
+      if (normalize(x, p.K0, p.policy, p.status, blockIdx.x == 0)) v[j] = static_cast<uint32_t>(x);
+      else bad |= 1u << j;
     }
-    first = false;
+  }
+  if (use_bulk && t == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  const int64_t nrows = (p.B - blockIdx.x + gridDim.x - 1) / gridDim.x;
+  const int64_t iters = nrows * npieces;
+  auto where = [&](int64_t it, int64_t& b, int& q, uint32_t& c0, uint32_t& n) {
+    const int64_t ri = it / npieces;
+    q = static_cast<int>(it - ri * npieces);
+    b = blockIdx.x + ri * gridDim.x;
+    c0 = static_cast<uint32_t>(q) * static_cast<uint32_t>(piece);
+    const int64_t left = p.K0 - static_cast<int64_t>(c0);
+    n = static_cast<uint32_t>(left < piece ? left : piece);
+  };
+  auto issue = [&](int64_t it) {  // thread 0 only; the stage's previous readers are past a barrier
+    int64_t b; int q; uint32_t c0, n;
+    where(it, b, q, c0, n);
+    const E* src = reinterpret_cast<const E*>(p.self) + p.rows.offset(static_cast<uint32_t>(b)) + c0;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    const uint32_t bytes = n * static_cast<uint32_t>(sizeof(E));
+    mbar_arrive_expect_tx(&bars[it & 1], bytes);
+    bulk_copy_g2s((it & 1) ? tile1 : tile0, src, bytes, &bars[it & 1]);
+  };
+  if (use_bulk && t == 0 && iters > 0) issue(0);
+  for (int64_t it = 0; it < iters; ++it) {
+    int64_t b; int q; uint32_t c0, n;
+    where(it, b, q, c0, n);
+    E* const tl = (it & 1) ? tile1 : tile0;
+    if (use_bulk) {
+      const bool ok = mbar_wait_bounded(&bars[it & 1], static_cast<uint32_t>(it >> 1) & 1u);
+      if (__syncthreads_or(!ok)) {
+        // give up: note the fault, let a copy that may still be in flight land, and leave
+        if (t == 0) {
+          atomicExch(&vb_index_fault, 1u);
+          mbar_wait_bounded(&bars[it & 1], static_cast<uint32_t>(it >> 1) & 1u);
+        }
+        __syncthreads();
+        return;
+      }
+      if (t == 0 && it + 1 < iters) issue(it + 1);
+    } else {
+      __syncthreads();  // readers of the previous piece are done
+      const E* src = reinterpret_cast<const E*>(p.self) + p.rows.offset(static_cast<uint32_t>(b)) + c0;
+      for (uint32_t i = t; i < n; i += kStThreads) tl[i] = src[i];
+      __syncthreads();
+    }
+    E* out = reinterpret_cast<E*>(p.other) + b * p.K + kc0 + t;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+      const uint32_t d = v[j] - c0;
+      if (d < n) out[static_cast<int64_t>(j) * kStThreads] = tl[d];
+      else if (q == 0 && ((bad >> j) & 1u)) out[static_cast<int64_t>(j) * kStThreads] = E(0);
+    }
   }
 }
 
@@ -725,7 +770,7 @@ __global__ void __launch_bounds__(kLdsThreads, 2) lastdim_gather_smem_kernel(con
 // host
 // ------------------------------------------------------------------------------------
 vbt_b200_status check_idx(const vbt_b200_tensor* idx, const char* name, IndexSrc* src, int64_t* n) {
-  VB_TRY(validate_tensor(idx, name));
+  VB_TRY(validate_data(idx, name));
   VB_ARG(idx->dtype == VBT_B200_I64 || idx->dtype == VBT_B200_I32,
          std::string(name) + ": only Int32 and Int64 index tensors are supported");
   VB_ARG(is_dense_row_major(*idx), std::string(name) + ": index tensor must be contiguous");
@@ -739,8 +784,8 @@ vbt_b200_status check_idx(const vbt_b200_tensor* idx, const char* name, IndexSrc
 vbt_b200_status rows_copy(const char* name, const vbt_b200_tensor* dense, const vbt_b200_tensor* table,
                           const vbt_b200_tensor* idx, int policy, void* status, cudaStream_t s,
                           int scatter) {
-  VB_TRY(validate_tensor(dense, name));
-  VB_TRY(validate_tensor(table, name));
+  VB_TRY(validate_data(dense, name));
+  VB_TRY(validate_data(table, name));
   VB_ARG(table->ndim == 2, std::string(name) + ": table must be rank 2");
   VB_ARG(dense->dtype == table->dtype, std::string(name) + ": dtype mismatch");
   VB_ARG(policy >= 0 && policy <= 2, std::string(name) + ": unknown index policy");
@@ -777,6 +822,8 @@ vbt_b200_status rows_copy(const char* name, const vbt_b200_tensor* dense, const 
     const int64_t blocks = (p.total + kThreads * 4 - 1) / (kThreads * 4);
     VB_ARG(blocks <= 0x7fffffff, std::string(name) + ": too large for one call");
     rows_copy_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p);
+    note_launch(VBT_B200_FAMILY_INDEX, VBT_B200_IK_ROWS_COPY, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 16 / es,
+                1, 0, 1, N * D, N, 0, s);
   } else {
     ElemParams p{};
     p.table = static_cast<const char*>(table->data);
@@ -789,6 +836,8 @@ vbt_b200_status rows_copy(const char* name, const vbt_b200_tensor* dense, const 
     const int64_t blocks = (N * D + kThreads - 1) / kThreads;
     VB_ARG(blocks <= 0x7fffffff, std::string(name) + ": too large for one call");
     rows_copy_elem_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p);
+    note_launch(VBT_B200_FAMILY_INDEX, VBT_B200_IK_ROWS_COPY_ELEM, dim3(static_cast<unsigned>(blocks)), dim3(kThreads), 1,
+                1, 0, 1, N * D, N, 0, s);
   }
   VB_LAUNCH_CHECK();
   return VBT_B200_OK;
@@ -802,10 +851,14 @@ vbt_b200_status scatter_add_typed(const ScatterParams& p, const ScatterElemParam
     if (p.cpr <= 32) scatter_add_rows_kernel<T, 1><<<g, kThreads, 0, s>>>(p);
     else if (p.cpr <= 64) scatter_add_rows_kernel<T, 2><<<g, kThreads, 0, s>>>(p);
     else scatter_add_rows_kernel<T, 4><<<g, kThreads, 0, s>>>(p);
+    note_launch(VBT_B200_FAMILY_INDEX, VBT_B200_IK_SCATTER_ADD, dim3(g), dim3(kThreads), 16 / static_cast<int>(sizeof(T)),
+                1, 0, 1 + (p.counts ? 2 : 0), p.N * p.cpr * (16 / static_cast<int64_t>(sizeof(T))), p.N, 0, s);
   } else {
     const int64_t blocks = (pe.N * pe.D + kThreads - 1) / kThreads;
     VB_ARG(blocks <= 0x7fffffff, "index_put_: too large for one call");
     scatter_add_elem_kernel<T><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(pe);
+    note_launch(VBT_B200_FAMILY_INDEX, VBT_B200_IK_SCATTER_ADD_ELEM, dim3(static_cast<unsigned>(blocks)), dim3(kThreads),
+                1, 1, 0, 1 + (pe.counts ? 2 : 0), pe.N * pe.D, pe.N, 0, s);
   }
   VB_LAUNCH_CHECK();
   return VBT_B200_OK;
@@ -814,8 +867,8 @@ vbt_b200_status scatter_add_typed(const ScatterParams& p, const ScatterElemParam
 vbt_b200_status scatter_add_rows(const char* name, const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
                                  const vbt_b200_tensor* values, int policy, void* status, int use_padding,
                                  int64_t padding_idx, cudaStream_t s, unsigned* counts = nullptr) {
-  VB_TRY(validate_tensor(table, name));
-  VB_TRY(validate_tensor(values, name));
+  VB_TRY(validate_data(table, name));
+  VB_TRY(validate_data(values, name));
   VB_ARG(table->ndim == 2, std::string(name) + ": table must be rank 2");
   VB_ARG(values->dtype == table->dtype, std::string(name) + ": dtype mismatch");
   VB_ARG(policy >= 0 && policy <= 2, std::string(name) + ": unknown index policy");
@@ -852,7 +905,8 @@ vbt_b200_status scatter_add_rows(const char* name, const vbt_b200_tensor* table,
   if (counts != nullptr) {
     VB_ARG(dt == VBT_B200_F32, std::string(name) + ": scale_grad_by_freq needs a float32 table");
     VB_CUDA(cudaMemsetAsync(counts, 0, static_cast<size_t>(V) * 4, s));
-    const unsigned g = static_cast<unsigned>(std::min<int64_t>((N + kThreads - 1) / kThreads, 148 * 8));
+    const unsigned g = static_cast<unsigned>(
+        std::min<int64_t>((N + kThreads - 1) / kThreads, int64_t{sm_count(scope.device())} * 8));
     count_rows_kernel<<<g, kThreads, 0, s>>>(is, N, V, policy, use_padding, padding_idx, counts);
     VB_LAUNCH_CHECK();
   }
@@ -882,8 +936,8 @@ vbt_b200_status scatter_add_rows_sorted(const char* name, const vbt_b200_tensor*
                                         const vbt_b200_tensor* idx, const vbt_b200_tensor* values, int policy,
                                         void* status, int use_padding, int64_t padding_idx, void* ws,
                                         size_t ws_bytes, cudaStream_t s) {
-  VB_TRY(validate_tensor(table, name));
-  VB_TRY(validate_tensor(values, name));
+  VB_TRY(validate_data(table, name));
+  VB_TRY(validate_data(values, name));
   VB_ARG(table->ndim == 2, std::string(name) + ": table must be rank 2");
   const int dt = table->dtype;
   const int64_t V = table->sizes[0], D = table->sizes[1];
@@ -943,61 +997,120 @@ vbt_b200_status scatter_add_rows_sorted(const char* name, const vbt_b200_tensor*
     default: launch_sorted<int32_t>(sp, s); break;
   }
   VB_LAUNCH_CHECK();
+  note_launch(VBT_B200_FAMILY_INDEX, VBT_B200_IK_SCATTER_ADD_SORTED, dim3(static_cast<unsigned>((N + 255) / 256)),
+              dim3(kThreads), 16 / es, 1, 0, 3 + 3 * ((bits + 7) / 8), N * D, N, need, s);
   return VBT_B200_OK;
 }
 
+template <class E, int EPT>
+vbt_b200_status launch_staged_ept(const LastDimParams& p, int piece, int npieces, int use_bulk, dim3 grid,
+                                  size_t smem, cudaStream_t s) {
+  // the opt-in to more than 48 KiB of dynamic shared memory is per function and per device
+  static std::mutex mu;
+  static bool done[64] = {};
+  int dev = 0;
+  VB_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+      VB_CUDA(cudaFuncSetAttribute(lastdim_staged_kernel<E, EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   220 * 1024));
+      if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+  }
+  lastdim_staged_kernel<E, EPT><<<grid, kStThreads, smem, s>>>(p, piece, npieces, use_bulk);
+  return VBT_B200_OK;
+}
+template <class E>
+vbt_b200_status launch_staged(const LastDimParams& p, int ept, int piece, int npieces, int use_bulk, dim3 grid,
+                              size_t smem, cudaStream_t s) {
+  switch (ept) {
+    case 8: return launch_staged_ept<E, 8>(p, piece, npieces, use_bulk, grid, smem, s);
+    case 16: return launch_staged_ept<E, 16>(p, piece, npieces, use_bulk, grid, smem, s);
+    default: return launch_staged_ept<E, 32>(p, piece, npieces, use_bulk, grid, smem, s);
+  }
+}
+
+// self: rank >= 1, any strides; the index applies to its LAST dim.  other: dense
+// [leading dims of self..., index shape...] (only its element count and density are checked).
 vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt_b200_tensor* idx,
                         const vbt_b200_tensor* other, int mode, int policy, void* status, cudaStream_t s) {
-  VB_TRY(validate_tensor(self, name));
-  VB_TRY(validate_tensor(other, name));
-  VB_ARG(self->ndim == 2, std::string(name) + ": tensor must be rank 2");
+  VB_TRY(validate_data(self, name));
+  VB_TRY(validate_data(other, name));
+  VB_ARG(self->ndim >= 1,
+         std::string(name) + ": advanced indexing is not supported for 0-d tensors on CUDA");
+  VB_ARG(self->ndim <= VBT_B200_MAX_NDIM, std::string(name) + ": rank too large");
   VB_ARG(other->dtype == self->dtype, std::string(name) + ": dtype mismatch");
+  VB_ARG(policy >= 0 && policy <= 2, std::string(name) + ": unknown index policy");
   IndexSrc is{};
   int64_t K = 0;
   VB_TRY(check_idx(idx, name, &is, &K));
-  const int64_t B = self->sizes[0];
+  const int nd = self->ndim;
+  int64_t B = 1;
+  for (int d = 0; d + 1 < nd; ++d) B *= self->sizes[d];
   VB_ARG(is_dense_row_major(*other) && numel(*other) == B * K,
-         std::string(name) + ": dense operand must be contiguous [B, K]");
+         std::string(name) + ": dense operand must be contiguous [leading dims..., index shape...]");
   if (mode == 2)
     VB_ARG(self->dtype == VBT_B200_F32 || self->dtype == VBT_B200_I64 || self->dtype == VBT_B200_I32,
            std::string(name) + ": accumulate supports float32, int32 and int64");
   if (B * K == 0) return VBT_B200_OK;
+  VB_ARG(B <= 0x7fffffff, std::string(name) + ": too many rows for one call");
   DeviceScope scope(other->data);
   LastDimParams p{};
   p.self = static_cast<char*>(self->data);
   p.other = static_cast<char*>(other->data);
   p.idx = is;
-  p.B = B; p.K0 = self->sizes[1]; p.K = K; p.sb = self->strides[0]; p.sk = self->strides[1];
+  p.B = B; p.K0 = self->sizes[nd - 1]; p.K = K; p.sk = self->strides[nd - 1];
+  // leading dims: drop size 1, merge neighbours that one stride walks
+  int64_t lsz[VBT_B200_MAX_NDIM], lst[VBT_B200_MAX_NDIM];
+  int nl = 0;
+  for (int d = 0; d + 1 < nd; ++d) {
+    const int64_t size = self->sizes[d], stride = self->strides[d];
+    if (size == 1) continue;
+    if (nl > 0 && lst[nl - 1] == stride * size) {
+      lsz[nl - 1] *= size;
+      lst[nl - 1] = stride;
+    } else {
+      lsz[nl] = size;
+      lst[nl] = stride;
+      ++nl;
+    }
+  }
+  fill_dimlist(p.rows, lsz, lst, nl);
   p.es = itemsize(self->dtype);
   p.policy = policy;
   p.status = static_cast<unsigned long long*>(status);
   p.mode = mode;
   p.dtype = self->dtype;
-  // long rows, many indices: serve the gather from shared memory
-  // (rows that fit one piece only: with several pieces per row the index list is re-read per
-  // piece and that traffic costs what the sector requests cost)
-  constexpr int kPieceBytes = 100 * 1024;
-  if (mode == 0 && K >= 8192 && p.K0 * p.es >= 32 * 1024 && p.K0 * p.es <= kPieceBytes && p.es >= 2) {
-    const int piece = static_cast<int>(std::min<int64_t>(p.K0, kPieceBytes / p.es / 4 * 4));
-    const size_t smem = static_cast<size_t>(piece) * p.es;
-    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(B, int64_t{sm_count(scope.device())} * 2));
-    cudaError_t e = cudaSuccess;
+  // Long rows and many indices: serve the gather from shared memory.  Staging reads the whole
+  // row once per K-chunk; the direct kernel pays a 32-byte sector per element.
+  const int64_t row_bytes = p.K0 * p.es;
+  const int ept = K <= 8 * kStThreads ? 8 : (K <= 16 * kStThreads ? 16 : 32);
+  const int64_t nchunks = (K + int64_t{kStThreads} * ept - 1) / (int64_t{kStThreads} * ept);
+  if (mode == 0 && p.sk == 1 && K >= 4096 && B >= 32 && row_bytes >= 32 * 1024 && p.K0 <= 0x7fffffff &&
+      nchunks * row_bytes * 2 <= K * 32 && nchunks <= 65535) {
+    constexpr int64_t kStageMax = 100 * 1024;
+    const int npieces = static_cast<int>((row_bytes + kStageMax - 1) / kStageMax);
+    const int64_t per = (p.K0 + npieces - 1) / npieces;
+    const int piece = static_cast<int>((per + 15) / 16 * 16);  // whole 16-byte units for every element size
+    const size_t stage = (static_cast<size_t>(piece) * p.es + 127) / 128 * 128;
+    // bulk copies need 16-byte aligned sources and sizes: every row start and every piece boundary
+    bool bulk = reinterpret_cast<uintptr_t>(self->data) % 16 == 0 && row_bytes % 16 == 0;
+    for (int i = 0; i < nl; ++i) bulk = bulk && (lst[i] * p.es) % 16 == 0;
+    const int sms = sm_count(scope.device());
+    const unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(B, sms / nchunks)));
+    const dim3 grid(gx, static_cast<unsigned>(nchunks));
+    vbt_b200_status st;
     switch (p.es) {
-      case 2:
-        e = cudaFuncSetAttribute(lastdim_gather_smem_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPieceBytes);
-        if (e == cudaSuccess) lastdim_gather_smem_kernel<uint16_t><<<grid, kLdsThreads, smem, s>>>(p, piece);
-        break;
-      case 4:
-        e = cudaFuncSetAttribute(lastdim_gather_smem_kernel<uint32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPieceBytes);
-        if (e == cudaSuccess) lastdim_gather_smem_kernel<uint32_t><<<grid, kLdsThreads, smem, s>>>(p, piece);
-        break;
-      default:
-        e = cudaFuncSetAttribute(lastdim_gather_smem_kernel<uint64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPieceBytes);
-        if (e == cudaSuccess) lastdim_gather_smem_kernel<uint64_t><<<grid, kLdsThreads, smem, s>>>(p, piece);
-        break;
+      case 1: st = launch_staged<uint8_t>(p, ept, piece, npieces, bulk, grid, 2 * stage, s); break;
+      case 2: st = launch_staged<uint16_t>(p, ept, piece, npieces, bulk, grid, 2 * stage, s); break;
+      case 4: st = launch_staged<uint32_t>(p, ept, piece, npieces, bulk, grid, 2 * stage, s); break;
+      default: st = launch_staged<uint64_t>(p, ept, piece, npieces, bulk, grid, 2 * stage, s); break;
     }
-    VB_CUDA(e);
+    VB_TRY(st);
     VB_LAUNCH_CHECK();
+    note_launch(VBT_B200_FAMILY_INDEX, VBT_B200_IK_LASTDIM_STAGED, grid, dim3(kStThreads), ept, npieces, 0, 1, B * K,
+                K, 0, s);
     return VBT_B200_OK;
   }
   const int64_t gx = (K + kThreads - 1) / kThreads, gy = (B + kLdRows - 1) / kLdRows;
@@ -1009,6 +1122,7 @@ vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt
     default: lastdim_kernel<uint64_t><<<g, kThreads, 0, s>>>(p); break;
   }
   VB_LAUNCH_CHECK();
+  note_launch(VBT_B200_FAMILY_INDEX, VBT_B200_IK_LASTDIM, g, dim3(kThreads), 1, 1, 0, 1, B * K, K, 0, s);
   return VBT_B200_OK;
 }
 
@@ -1097,8 +1211,18 @@ vbt_b200_status vbt_b200_index_status_check(void* index_status, const char* what
   DeviceScope scope(index_status);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   unsigned long long h[2] = {0, 0};
+  unsigned fault = 0;
   VB_CUDA(cudaMemcpyAsync(h, index_status, sizeof(h), cudaMemcpyDeviceToHost, s));
+  VB_CUDA(cudaMemcpyFromSymbolAsync(&fault, vb_index_fault, sizeof(fault), 0, cudaMemcpyDeviceToHost, s));
   VB_CUDA(cudaStreamSynchronize(s));
+  if (fault != 0) {
+    const unsigned zero = 0;
+    VB_CUDA(cudaMemcpyToSymbolAsync(vb_index_fault, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, s));
+    VB_CUDA(cudaStreamSynchronize(s));
+    return fail(VBT_B200_CUDA_ERROR, std::string(what ? what : "index") +
+                                         ": a staged row copy did not complete in time; the output of an "
+                                         "earlier last-dim index call on this device is incomplete");
+  }
   if (h[0] == 0) return VBT_B200_OK;
   VB_CUDA(cudaMemsetAsync(index_status, 0, sizeof(h), s));
   return fail(VBT_B200_OUT_OF_RANGE,

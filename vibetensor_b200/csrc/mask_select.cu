@@ -150,6 +150,7 @@ vbt_b200_status vbt_b200_mask_select(const vbt_b200_tensor* mask, int64_t* out_i
                                      void* stream) {
   using namespace vb;
   VB_ARG(mask != nullptr && count_out != nullptr, "index: null argument");
+  VB_TRY(validate_tensor(mask, "index"));
   VB_ARG(mask->dtype == VBT_B200_BOOL, "index: mask must be a bool tensor");
   VB_ARG(mask->ndim == 1, std::string("index: ") + "CUDA advanced indexing does not support boolean mask indices"
                               " of rank other than 1");

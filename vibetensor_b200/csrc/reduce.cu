@@ -5,9 +5,11 @@
 // reduction is brought to one of three shapes on the host:
 //
 //   ROW      the reduced dims are one run with stride 1: each output owns a contiguous
-//            slice.  Short slices: one warp per output.  Long slices: one block per
-//            (output, chunk); chunk partials go to the workspace and the block that
-//            arrives last folds them in chunk order.
+//            slice.  Short slices: one warp per output.  Long slices: `splits` blocks per
+//            output sweep the slice together, block b taking the 16 KiB pieces b, b + splits,
+//            b + 2*splits, ... so that at any moment the resident blocks read one compact
+//            window of memory; block partials go to the workspace and the block that
+//            arrives last folds them in block order.
 //   COL      memory is [A, R, B] with B contiguous and R reduced: a warp reads whole
 //            16-byte-per-lane rows (coalesced), the 8 warps of a block split R, blocks
 //            split R further through the same workspace + last-arriver fold.
@@ -16,12 +18,18 @@
 //
 // No floating-point atomics anywhere: for a given shape the order of additions is fixed,
 // so results repeat bit for bit from run to run.  There are no spin waits either -- the
-// cross-block fold is done by whichever block draws the last ticket.
+// cross-block fold is done by whichever block draws the last ticket, and that block puts the
+// ticket counter back to zero, so a workspace whose ticket area was zero before a call is zero
+// again after it.
+//
+// Workspace layout: [kTicketBytes of uint32 ticket counters][partials, 16-byte aligned].
 #include <cooperative_groups.h>
 
 #include <cfloat>
 #include <climits>
+#include <map>
 #include <mutex>
+#include <tuple>
 
 #include "common.cuh"
 
@@ -31,6 +39,16 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxDims = VBT_B200_MAX_NDIM;
+constexpr size_t kTicketBytes = 4096;  // fixed ticket area at the start of every workspace
+// 16-byte loads a thread of the long-slice ROW kernel keeps in flight
+#ifndef VB_ROW_U
+#define VB_ROW_U 4
+#endif
+constexpr int kRowU = VB_ROW_U;
+// blocks per SM the long-slice ROW kernel is split into when few outputs share the GPU
+#ifndef VB_ROW_BLOCKS_PER_SM
+#define VB_ROW_BLOCKS_PER_SM 4
+#endif
 
 // ------------------------------------------------------------------------------------
 // reducers
@@ -165,6 +183,8 @@ struct OutSpec {
   int out_dtype;
   int op;
   float inv_count_n;  // reduce count as float, for MEAN
+  int nan_first;      // MAX / MIN: a NaN at position 0 of the slice wins (off for the shards of a
+                      // sharded reduction that do not hold the global position 0)
 };
 
 __device__ __forceinline__ void store_value(const OutSpec& o, int64_t i, float v) {
@@ -191,7 +211,7 @@ __device__ __forceinline__ void finalize(const OutSpec& o, int64_t i, typename R
     if (o.out) store_value(o, i, acc.v);
     if (o.out_idx) o.out_idx[i] = static_cast<int64_t>(acc.i);
   } else {
-    if (o.op == OP_MAX || o.op == OP_MIN) {
+    if ((o.op == OP_MAX || o.op == OP_MIN) && o.nan_first) {
       if (is_nan(first)) acc = first;
     }
     if constexpr (sizeof(A) == 4) {
@@ -200,25 +220,6 @@ __device__ __forceinline__ void finalize(const OutSpec& o, int64_t i, typename R
     store_value(o, i, acc);
   }
 }
-
-// ------------------------------------------------------------------------------------
-// offset decoding for the kept / reduced dims
-// ------------------------------------------------------------------------------------
-struct DimList {
-  int n;
-  FastDiv div[kMaxDims];
-  int64_t stride[kMaxDims];
-  // linear index (last dim fastest) -> element offset
-  __device__ __forceinline__ int64_t offset(uint32_t lin) const {
-    int64_t off = 0;
-    for (int d = n - 1; d >= 0; --d) {
-      uint32_t c;
-      div[d].divmod(lin, lin, c);
-      off += static_cast<int64_t>(c) * stride[d];
-    }
-    return off;
-  }
-};
 
 // ------------------------------------------------------------------------------------
 // ROW kernels
@@ -238,10 +239,8 @@ struct RowParams {
   const void* x;
   int64_t n;          // slice length
   int64_t rows;
-  int64_t row_stride; // used when kept.n == 0 is false? (see kept)
   DimList kept;       // row index -> slice base offset
-  int splits;
-  int64_t chunk;      // elements per split (multiple of the vector width)
+  int splits;         // blocks that share one slice
   void* ws_partials;
   unsigned* ws_counters;
   OutSpec o;
@@ -273,8 +272,11 @@ __global__ void __launch_bounds__(kThreads) row_warp_kernel(const __grid_constan
   if (lane == 0) finalize<R, A>(p.o, row, acc, widen(x[0]));
 }
 
-// one block per (slice, chunk)
-template <class T, class R, int V>
+// `splits` blocks per slice (grid = rows x splits).  One sweep of a slice's blocks covers
+// splits * U * kThreads consecutive vectors: block b reads the b-th run of U * kThreads
+// vectors of every sweep.  All blocks of the grid therefore work inside one window of
+// splits * 16 KiB that slides over the slice, instead of `splits` far-apart streams.
+template <class T, class R, int V, int U>
 __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_constant__ RowParams p) {
   using A = typename Widen<T>::type;
   using acc_t = typename R::acc_t;
@@ -284,15 +286,13 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
   const int64_t row = blockIdx.x;
   const int split = blockIdx.y;
   const T* x = static_cast<const T*>(p.x) + p.kept.offset(static_cast<uint32_t>(row));
-  const int64_t c0 = static_cast<int64_t>(split) * p.chunk;
-  const int64_t c1 = min(p.n, c0 + p.chunk);
-  constexpr int U = 4;
   acc_t acc[U];
 #pragma unroll
   for (int u = 0; u < U; ++u) acc[u] = R::init();
-  const int64_t v0 = c0 / V, v1 = c1 / V;  // whole vectors in [c0, c1); c0 is a multiple of V
-  int64_t i = v0 + threadIdx.x;
-  for (; i + (U - 1) * kThreads < v1; i += U * kThreads) {
+  const int64_t nvec = p.n / V;
+  const int64_t sweep = static_cast<int64_t>(p.splits) * (U * kThreads);
+  int64_t i = static_cast<int64_t>(split) * (U * kThreads) + threadIdx.x;
+  for (; i + (U - 1) * kThreads < nvec; i += sweep) {
     A w[U][V];
 #pragma unroll
     for (int u = 0; u < U; ++u) load_widen<T, V>(x + (i + u * kThreads) * V, w[u]);
@@ -303,19 +303,27 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
       for (int j = 0; j < V; ++j) R::accum(acc[u], w[u][j], base + j);
     }
   }
-  for (; i < v1; i += kThreads) {
-    A w[V];
-    load_widen<T, V>(x + i * V, w);
-    const idx_t base = static_cast<idx_t>(i) * V;
+  // the sweep that runs off the end of the slice
 #pragma unroll
-    for (int j = 0; j < V; ++j) R::accum(acc[0], w[j], base + j);
+  for (int u = 0; u < U; ++u) {
+    const int64_t iv = i + u * kThreads;
+    if (iv < nvec) {
+      A w[V];
+      load_widen<T, V>(x + iv * V, w);
+      const idx_t base = static_cast<idx_t>(iv) * V;
+#pragma unroll
+      for (int j = 0; j < V; ++j) R::accum(acc[u], w[j], base + j);
+    }
   }
   if constexpr (V > 1) {
-    const int64_t t = v1 * V + threadIdx.x;  // ragged tail, only in the last chunk
-    if (t < c1) R::accum(acc[0], widen(x[t]), static_cast<idx_t>(t));
+    const int64_t t = nvec * V + threadIdx.x;  // elements after the last whole vector
+    if (split == 0 && t < p.n) R::accum(acc[U - 1], widen(x[t]), static_cast<idx_t>(t));
   }
-  acc_t a = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
-  a = block_reduce<R>(a, smem);
+#pragma unroll
+  for (int d = 1; d < U; d <<= 1)
+#pragma unroll
+    for (int u = 0; u + d < U; u += 2 * d) acc[u] = R::combine(acc[u], acc[u + d]);
+  acc_t a = block_reduce<R>(acc[0], smem);
   if (p.splits == 1) {
     if (threadIdx.x == 0) finalize<R, A>(p.o, row, a, widen(x[0]));
     return;
@@ -330,13 +338,16 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // fold the chunk partials in chunk order: thread t takes chunks t, t+256, ... in order,
+  // fold the block partials in block order: thread t takes blocks t, t+256, ... in order,
   // then the fixed shuffle tree -- the same order on every run
   acc_t f = R::init();
   for (int s = threadIdx.x; s < p.splits; s += kThreads) f = R::combine(f, ld_cg(part + s));
   __syncthreads();
   f = block_reduce<R>(f, smem);
-  if (threadIdx.x == 0) finalize<R, A>(p.o, row, f, widen(x[0]));
+  if (threadIdx.x == 0) {
+    p.ws_counters[row] = 0u;  // every block of this slice has drawn its ticket: leave the counter as found
+    finalize<R, A>(p.o, row, f, widen(x[0]));
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -422,6 +433,7 @@ __global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ C
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  if (threadIdx.x == 0) p.ws_counters[a * p.ctiles + ct] = 0u;  // all tickets drawn: leave the counter as found
   if (owner) {
     // chunk order, eight independent loads in flight at a time (a loop of load-then-combine
     // would pay one L2 round trip per chunk)
@@ -591,8 +603,9 @@ size_t acc_bytes(int op, int dtype) {
   return (op == OP_ARGMAX || op == OP_ARGMIN) ? 16 : a;
 }
 
+// sms: SM count of the device the call runs on (grid sizing only; any value gives a correct plan)
 vbt_b200_status make_plan(int op, const vbt_b200_tensor& self, const int64_t* dims, int ndims,
-                          bool keepdim, Plan* pl) {
+                          bool keepdim, int sms, Plan* pl) {
   const char* name = op_name(op);
   VB_ARG(self.ndim <= kMaxDims, std::string(name) + ": rank too large");
   bool reduced[kMaxDims + 1];
@@ -638,7 +651,6 @@ vbt_b200_status make_plan(int op, const vbt_b200_tensor& self, const int64_t* di
       if (st[i] % v) return false;
     return true;
   };
-  const int sms = 148;
   const size_t ab = acc_bytes(op, self.dtype);
   if (pl->nr == 1 && pl->rstride[0] == 1) {
     // ROW
@@ -649,20 +661,18 @@ vbt_b200_status make_plan(int op, const vbt_b200_tensor& self, const int64_t* di
       return VBT_B200_OK;
     }
     pl->shape = kRowBlock;
-    const int64_t per_block_min = int64_t{kThreads} * vmax * 4;  // one unrolled pass
+    const int64_t per_block_min = int64_t{kThreads} * vmax * kRowU;  // one unrolled pass
     int64_t splits = 1;
     if (pl->nout < 2 * sms) {
       splits = std::min<int64_t>((n + per_block_min - 1) / per_block_min,
-                                 (int64_t{sms} * 4 + pl->nout - 1) / pl->nout);
+                                 (int64_t{sms} * VB_ROW_BLOCKS_PER_SM + pl->nout - 1) / pl->nout);
       splits = std::max<int64_t>(splits, 1);
     }
-    int64_t chunk = (n + splits - 1) / splits;
-    chunk = (chunk + vmax - 1) / vmax * vmax;
-    splits = (n + chunk - 1) / chunk;
-    pl->splits = static_cast<int>(splits);
-    pl->chunk = chunk;
-    if (splits > 1) {
-      pl->ws_partial_bytes = static_cast<size_t>(pl->nout) * splits * ab;
+    pl->splits = static_cast<int>(std::min<int64_t>(splits, 65535));
+    pl->chunk = 0;
+    if (static_cast<size_t>(pl->nout) * 4 > kTicketBytes) pl->splits = 1;  // more slices than tickets
+    if (pl->splits > 1) {
+      pl->ws_partial_bytes = static_cast<size_t>(pl->nout) * pl->splits * ab;
       pl->ws_counter_bytes = static_cast<size_t>(pl->nout) * 4;
     }
     return VBT_B200_OK;
@@ -684,6 +694,7 @@ vbt_b200_status make_plan(int op, const vbt_b200_tensor& self, const int64_t* di
       pl->ctiles = static_cast<int>((B + ncols - 1) / ncols);
       // about one resident wave of blocks (4 per SM): a second, partial wave only adds a tail
       int64_t want = (int64_t{sms} * 4) / (pl->ctiles * A);
+      if (static_cast<size_t>(A) * pl->ctiles * 4 > kTicketBytes) want = 1;  // more tiles than tickets
       int64_t splits = std::max<int64_t>(1, std::min<int64_t>(want, (Rn + 31) / 32));
       splits = std::min<int64_t>(splits, 65535);
       int64_t chunk = (Rn + splits - 1) / splits;
@@ -710,18 +721,37 @@ vbt_b200_status make_plan(int op, const vbt_b200_tensor& self, const int64_t* di
   return VBT_B200_OK;
 }
 
-void fill_dimlist(DimList& dl, const int64_t* sizes, const int64_t* strides, int n) {
-  dl.n = n;
-  for (int i = 0; i < n; ++i) {
-    dl.div[i] = FastDiv(static_cast<uint32_t>(sizes[i]));
-    dl.stride[i] = strides[i];
-  }
+// Whether this device can co-schedule clusters of `cluster` blocks of `kern`; asked once per
+// (kernel, cluster size, device) -- the query and the attribute call cost several microseconds
+// of host time, which matters on the small problems the cluster path exists for.
+bool cluster_launch_ok(const void* kern, int cluster, const cudaLaunchConfig_t& cfg) {
+  static std::mutex mu;
+  static std::map<std::tuple<const void*, int, int>, bool> known;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const auto key = std::make_tuple(kern, cluster, dev);
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = known.find(key);
+  if (it != known.end()) return it->second;
+  bool ok = true;
+  if (cluster > 8)
+    ok = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+  int max_clusters = 0;
+  ok = ok && cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) == cudaSuccess && max_clusters > 0;
+  if (!ok) cudaGetLastError();
+  known[key] = ok;
+  return ok;
 }
 
+// ws: [kTicketBytes tickets][partials].  tickets_zeroed: the caller guarantees the ticket area
+// is zero (it was zeroed once and only this library has written to it since).
 template <class T, class R>
 vbt_b200_status launch(const Plan& pl, const vbt_b200_tensor& self, const OutSpec& o, void* ws,
-                       cudaStream_t s) {
+                       bool tickets_zeroed, cudaStream_t s) {
   constexpr int VMAX = 16 / sizeof(T);
+  unsigned* tickets = static_cast<unsigned*>(ws);
+  void* partials = ws ? static_cast<char*>(ws) + kTicketBytes : nullptr;
+  const size_t ws_used = pl.ws_partial_bytes ? kTicketBytes + pl.ws_partial_bytes : 0;
   if (pl.shape == kRowWarp || pl.shape == kRowBlock) {
     RowParams p{};
     p.x = self.data;
@@ -729,24 +759,31 @@ vbt_b200_status launch(const Plan& pl, const vbt_b200_tensor& self, const OutSpe
     p.rows = pl.nout;
     fill_dimlist(p.kept, pl.ksize, pl.kstride, pl.nk);
     p.splits = pl.splits;
-    p.chunk = pl.chunk;
     p.o = o;
     if (pl.shape == kRowWarp) {
       const unsigned g = static_cast<unsigned>((pl.nout + kWarps - 1) / kWarps);
       if (pl.V > 1) row_warp_kernel<T, R, VMAX><<<g, kThreads, 0, s>>>(p);
       else row_warp_kernel<T, R, 1><<<g, kThreads, 0, s>>>(p);
+      VB_LAUNCH_CHECK();
+      note_launch(VBT_B200_FAMILY_REDUCE, VBT_B200_RK_ROW_WARP, dim3(g), dim3(kThreads), pl.V, 1, 0, 1, pl.nout,
+                  pl.nred, 0, s);
     } else {
+      int launches = 1;
       if (pl.splits > 1) {
-        p.ws_partials = ws;
-        p.ws_counters = reinterpret_cast<unsigned*>(static_cast<char*>(ws) + pl.ws_partial_bytes);
-        VB_CUDA(cudaMemsetAsync(p.ws_counters, 0, pl.ws_counter_bytes, s));
+        p.ws_partials = partials;
+        p.ws_counters = tickets;
+        if (!tickets_zeroed) {
+          VB_CUDA(cudaMemsetAsync(tickets, 0, pl.ws_counter_bytes, s));
+          ++launches;
+        }
       }
-      VB_ARG(pl.splits <= 65535, "reduce: too many chunks");
       dim3 g(static_cast<unsigned>(pl.nout), static_cast<unsigned>(pl.splits));
-      if (pl.V > 1) row_block_kernel<T, R, VMAX><<<g, kThreads, 0, s>>>(p);
-      else row_block_kernel<T, R, 1><<<g, kThreads, 0, s>>>(p);
+      if (pl.V > 1) row_block_kernel<T, R, VMAX, kRowU><<<g, kThreads, 0, s>>>(p);
+      else row_block_kernel<T, R, 1, kRowU><<<g, kThreads, 0, s>>>(p);
+      VB_LAUNCH_CHECK();
+      note_launch(VBT_B200_FAMILY_REDUCE, VBT_B200_RK_ROW_BLOCK, g, dim3(kThreads), pl.V, pl.splits, 0, launches,
+                  pl.nout, pl.nred, ws_used, s);
     }
-    VB_LAUNCH_CHECK();
     return VBT_B200_OK;
   }
   if (pl.shape == kCol) {
@@ -777,28 +814,31 @@ vbt_b200_status launch(const Plan& pl, const vbt_b200_tensor& self, const OutSpe
       attr[0].val.clusterDim.z = 1;
       cfg.attrs = attr;
       cfg.numAttrs = 1;
-      bool ok = true;
-      if (pl.cluster > 8)
-        ok = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
-      int max_clusters = 0;
-      ok = ok && cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) == cudaSuccess && max_clusters > 0;
-      if (ok) {
+      if (cluster_launch_ok(reinterpret_cast<const void*>(kern), pl.cluster, cfg)) {
         VB_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+        note_launch(VBT_B200_FAMILY_REDUCE, VBT_B200_RK_COL_CLUSTER, cfg.gridDim, cfg.blockDim, pl.V, pl.cluster,
+                    pl.cluster, 1, pl.nout, pl.nred, 0, s);
         return VBT_B200_OK;
       }
-      cudaGetLastError();  // this device cannot co-schedule such a cluster: use the workspace path
+      // this device cannot co-schedule such a cluster: use the workspace path
       p.splits = pl.splits;
       p.chunk = pl.chunk;
     }
+    int launches = 1;
     if (pl.splits > 1) {
-      p.ws_partials = ws;
-      p.ws_counters = reinterpret_cast<unsigned*>(static_cast<char*>(ws) + pl.ws_partial_bytes);
-      VB_CUDA(cudaMemsetAsync(p.ws_counters, 0, pl.ws_counter_bytes, s));
+      p.ws_partials = partials;
+      p.ws_counters = tickets;
+      if (!tickets_zeroed) {
+        VB_CUDA(cudaMemsetAsync(tickets, 0, pl.ws_counter_bytes, s));
+        ++launches;
+      }
     }
     dim3 g(static_cast<unsigned>(pl.ctiles), static_cast<unsigned>(pl.splits), static_cast<unsigned>(p.A));
     if (pl.V > 1) col_kernel<T, R, VMAX><<<g, kThreads, 0, s>>>(p);
     else col_kernel<T, R, 1><<<g, kThreads, 0, s>>>(p);
     VB_LAUNCH_CHECK();
+    note_launch(VBT_B200_FAMILY_REDUCE, VBT_B200_RK_COL, g, dim3(kThreads), pl.V, pl.splits, 0, launches, pl.nout,
+                pl.nred, ws_used, s);
     return VBT_B200_OK;
   }
   GenParams p{};
@@ -811,25 +851,26 @@ vbt_b200_status launch(const Plan& pl, const vbt_b200_tensor& self, const OutSpe
   const unsigned g = static_cast<unsigned>((pl.nout + kWarps - 1) / kWarps);
   generic_kernel<T, R><<<g, kThreads, 0, s>>>(p);
   VB_LAUNCH_CHECK();
+  note_launch(VBT_B200_FAMILY_REDUCE, VBT_B200_RK_GENERIC, dim3(g), dim3(kThreads), 1, 1, 0, 1, pl.nout, pl.nred, 0, s);
   return VBT_B200_OK;
 }
 
 template <class T>
 vbt_b200_status launch_op(int op, const Plan& pl, const vbt_b200_tensor& self, const OutSpec& o,
-                          void* ws, cudaStream_t s) {
+                          void* ws, bool tz, cudaStream_t s) {
   using A = typename Widen<T>::type;
   switch (op) {
     case OP_SUM:
-    case OP_MEAN: return launch<T, SumR<A>>(pl, self, o, ws, s);
-    case OP_PROD: return launch<T, ProdR<A>>(pl, self, o, ws, s);
-    case OP_MAX: return launch<T, ExtR<A, true>>(pl, self, o, ws, s);
-    case OP_MIN: return launch<T, ExtR<A, false>>(pl, self, o, ws, s);
+    case OP_MEAN: return launch<T, SumR<A>>(pl, self, o, ws, tz, s);
+    case OP_PROD: return launch<T, ProdR<A>>(pl, self, o, ws, tz, s);
+    case OP_MAX: return launch<T, ExtR<A, true>>(pl, self, o, ws, tz, s);
+    case OP_MIN: return launch<T, ExtR<A, false>>(pl, self, o, ws, tz, s);
     case OP_ARGMAX:
-      return pl.nred < 0x7fffffff ? launch<T, ArgR<A, true, int32_t>>(pl, self, o, ws, s)
-                                  : launch<T, ArgR<A, true, int64_t>>(pl, self, o, ws, s);
+      return pl.nred < 0x7fffffff ? launch<T, ArgR<A, true, int32_t>>(pl, self, o, ws, tz, s)
+                                  : launch<T, ArgR<A, true, int64_t>>(pl, self, o, ws, tz, s);
     case OP_ARGMIN:
-      return pl.nred < 0x7fffffff ? launch<T, ArgR<A, false, int32_t>>(pl, self, o, ws, s)
-                                  : launch<T, ArgR<A, false, int64_t>>(pl, self, o, ws, s);
+      return pl.nred < 0x7fffffff ? launch<T, ArgR<A, false, int32_t>>(pl, self, o, ws, tz, s)
+                                  : launch<T, ArgR<A, false, int64_t>>(pl, self, o, ws, tz, s);
   }
   return fail(VBT_B200_INVALID_ARGUMENT, "reduce: unknown op code");
 }
@@ -863,6 +904,73 @@ vbt_b200_status check_out_shape(const Plan& pl, const vbt_b200_tensor* t, const 
 }  // namespace
 }  // namespace vb
 
+namespace vb {
+namespace {
+
+size_t plan_workspace_bytes(const Plan& pl) {
+  if (pl.ws_partial_bytes == 0) return 0;
+  return kTicketBytes + (pl.ws_partial_bytes + 15) / 16 * 16;
+}
+
+vbt_b200_status reduce_impl(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* out_index,
+                            const vbt_b200_tensor* self, const int64_t* dims, int32_t ndims, int32_t keepdim,
+                            void* workspace, size_t workspace_bytes, bool tickets_zeroed, bool nan_first,
+                            void* stream) {
+  VB_ARG(op >= 0 && op < VBT_B200_R_COUNT, "reduce: unknown op code");
+  const char* name = op_name(op);
+  VB_TRY(validate_data(self, name));
+  if (out) VB_TRY(validate_data(out, name));
+  if (out_index) VB_TRY(validate_data(out_index, name));
+  VB_TRY(check_dtypes(op, *self, out, out_index));
+  const void* anchor = out ? out->data : out_index->data;
+  DeviceScope scope(anchor);
+  Plan pl;
+  VB_TRY(make_plan(op, *self, dims, ndims, keepdim != 0, sm_count(scope.device()), &pl));
+  VB_TRY(check_out_shape(pl, out, name));
+  VB_TRY(check_out_shape(pl, out_index, name));
+  if (pl.shape == kNoOutput) return VBT_B200_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pl.shape == kEmptyDomain) {
+    // cuda_reduction.cu:1176-1216
+    if (op == OP_MAX || op == OP_ARGMAX) return fail(VBT_B200_RUNTIME_ERROR, "amax: empty");
+    if (op == OP_MIN || op == OP_ARGMIN) return fail(VBT_B200_RUNTIME_ERROR, "amin: empty");
+    const double v = op == OP_SUM ? 0.0 : (op == OP_PROD ? 1.0 : NAN);
+    const unsigned g = static_cast<unsigned>((pl.nout + 255) / 256);
+    switch (out->dtype) {
+      case VBT_B200_F32: fill_kernel<float><<<g, 256, 0, s>>>(static_cast<float*>(out->data), pl.nout, static_cast<float>(v)); break;
+      case VBT_B200_F16: fill_kernel<__half><<<g, 256, 0, s>>>(static_cast<__half*>(out->data), pl.nout, __float2half_rn(static_cast<float>(v))); break;
+      case VBT_B200_BF16: fill_kernel<__nv_bfloat16><<<g, 256, 0, s>>>(static_cast<__nv_bfloat16*>(out->data), pl.nout, __float2bfloat16_rn(static_cast<float>(v))); break;
+      case VBT_B200_I64: fill_kernel<int64_t><<<g, 256, 0, s>>>(static_cast<int64_t*>(out->data), pl.nout, static_cast<int64_t>(op == OP_PROD ? 1 : 0)); break;
+    }
+    VB_LAUNCH_CHECK();
+    note_launch(VBT_B200_FAMILY_REDUCE, VBT_B200_RK_FILL, dim3(g), dim3(256), 1, 1, 0, 1, pl.nout, 0, 0, s);
+    return VBT_B200_OK;
+  }
+  const size_t need = plan_workspace_bytes(pl);
+  if (need > 0) {
+    VB_ARG(workspace != nullptr && workspace_bytes >= need,
+           std::string(name) + ": workspace too small (see vbt_b200_reduce_workspace_bytes)");
+    VB_ARG(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, std::string(name) + ": workspace must be 16-byte aligned");
+  }
+  OutSpec o{};
+  o.out = out ? out->data : nullptr;
+  o.out_idx = out_index ? static_cast<int64_t*>(out_index->data) : nullptr;
+  o.out_dtype = out ? out->dtype : self->dtype;
+  o.op = op;
+  o.inv_count_n = static_cast<float>(pl.nred);
+  o.nan_first = nan_first ? 1 : 0;
+  switch (self->dtype) {
+    case VBT_B200_F32: return launch_op<float>(op, pl, *self, o, workspace, tickets_zeroed, s);
+    case VBT_B200_F16: return launch_op<__half>(op, pl, *self, o, workspace, tickets_zeroed, s);
+    case VBT_B200_BF16: return launch_op<__nv_bfloat16>(op, pl, *self, o, workspace, tickets_zeroed, s);
+    case VBT_B200_I64: return launch_op<int64_t>(op, pl, *self, o, workspace, tickets_zeroed, s);
+  }
+  return fail(VBT_B200_INVALID_ARGUMENT, std::string(name) + ": unsupported dtype");
+}
+
+}  // namespace
+}  // namespace vb
+
 extern "C" {
 
 size_t vbt_b200_reduce_workspace_bytes(int32_t op, const vbt_b200_tensor* self, const int64_t* dims,
@@ -870,9 +978,8 @@ size_t vbt_b200_reduce_workspace_bytes(int32_t op, const vbt_b200_tensor* self, 
   using namespace vb;
   if (!self || validate_tensor(self, "reduce") != VBT_B200_OK) return 0;
   Plan pl;
-  if (make_plan(op, *self, dims, ndims, false, &pl) != VBT_B200_OK) return 0;
-  const size_t partial = (pl.ws_partial_bytes + 15) / 16 * 16;
-  return partial + pl.ws_counter_bytes;
+  if (make_plan(op, *self, dims, ndims, false, sm_count(device_of(self->data)), &pl) != VBT_B200_OK) return 0;
+  return plan_workspace_bytes(pl);
 }
 
 vbt_b200_status vbt_b200_reduce_shape(const vbt_b200_tensor* self, const int64_t* dims, int32_t ndims,
@@ -894,70 +1001,30 @@ vbt_b200_status vbt_b200_reduce_shape(const vbt_b200_tensor* self, const int64_t
 vbt_b200_status vbt_b200_reduce(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* out_index,
                                 const vbt_b200_tensor* self, const int64_t* dims, int32_t ndims,
                                 int32_t keepdim, void* workspace, size_t workspace_bytes, void* stream) {
-  using namespace vb;
-  VB_ARG(op >= 0 && op < VBT_B200_R_COUNT, "reduce: unknown op code");
-  const char* name = op_name(op);
-  VB_TRY(validate_tensor(self, name));
-  if (out) VB_TRY(validate_tensor(out, name));
-  if (out_index) VB_TRY(validate_tensor(out_index, name));
-  VB_TRY(check_dtypes(op, *self, out, out_index));
-  Plan pl;
-  VB_TRY(make_plan(op, *self, dims, ndims, keepdim != 0, &pl));
-  VB_TRY(check_out_shape(pl, out, name));
-  VB_TRY(check_out_shape(pl, out_index, name));
-  if (pl.shape == kNoOutput) return VBT_B200_OK;
-  DeviceScope scope(out ? out->data : out_index->data);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (pl.shape == kEmptyDomain) {
-    // cuda_reduction.cu:1176-1216
-    if (op == OP_MAX || op == OP_ARGMAX) return fail(VBT_B200_RUNTIME_ERROR, "amax: empty");
-    if (op == OP_MIN || op == OP_ARGMIN) return fail(VBT_B200_RUNTIME_ERROR, "amin: empty");
-    const double v = op == OP_SUM ? 0.0 : (op == OP_PROD ? 1.0 : NAN);
-    const unsigned g = static_cast<unsigned>((pl.nout + 255) / 256);
-    switch (out->dtype) {
-      case VBT_B200_F32: fill_kernel<float><<<g, 256, 0, s>>>(static_cast<float*>(out->data), pl.nout, static_cast<float>(v)); break;
-      case VBT_B200_F16: fill_kernel<__half><<<g, 256, 0, s>>>(static_cast<__half*>(out->data), pl.nout, __float2half_rn(static_cast<float>(v))); break;
-      case VBT_B200_BF16: fill_kernel<__nv_bfloat16><<<g, 256, 0, s>>>(static_cast<__nv_bfloat16*>(out->data), pl.nout, __float2bfloat16_rn(static_cast<float>(v))); break;
-      case VBT_B200_I64: fill_kernel<int64_t><<<g, 256, 0, s>>>(static_cast<int64_t*>(out->data), pl.nout, static_cast<int64_t>(op == OP_PROD ? 1 : 0)); break;
-    }
-    VB_LAUNCH_CHECK();
-    return VBT_B200_OK;
-  }
-  const size_t partial = (pl.ws_partial_bytes + 15) / 16 * 16;
-  Plan run = pl;
-  run.ws_partial_bytes = partial;
-  if (partial + pl.ws_counter_bytes > 0) {
-    VB_ARG(workspace != nullptr && workspace_bytes >= partial + pl.ws_counter_bytes,
-           std::string(name) + ": workspace too small (see vbt_b200_reduce_workspace_bytes)");
-    VB_ARG(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, std::string(name) + ": workspace must be 16-byte aligned");
-  }
-  OutSpec o{};
-  o.out = out ? out->data : nullptr;
-  o.out_idx = out_index ? static_cast<int64_t*>(out_index->data) : nullptr;
-  o.out_dtype = out ? out->dtype : self->dtype;
-  o.op = op;
-  o.inv_count_n = static_cast<float>(pl.nred);
-  switch (self->dtype) {
-    case VBT_B200_F32: return launch_op<float>(op, run, *self, o, workspace, s);
-    case VBT_B200_F16: return launch_op<__half>(op, run, *self, o, workspace, s);
-    case VBT_B200_BF16: return launch_op<__nv_bfloat16>(op, run, *self, o, workspace, s);
-    case VBT_B200_I64: return launch_op<int64_t>(op, run, *self, o, workspace, s);
-  }
-  return fail(VBT_B200_INVALID_ARGUMENT, std::string(name) + ": unsupported dtype");
+  return vb::reduce_impl(op, out, out_index, self, dims, ndims, keepdim, workspace, workspace_bytes, false, true,
+                         stream);
+}
+
+vbt_b200_status vbt_b200_reduce_zeroed_ws(int32_t op, const vbt_b200_tensor* out,
+                                          const vbt_b200_tensor* out_index, const vbt_b200_tensor* self,
+                                          const int64_t* dims, int32_t ndims, int32_t keepdim, void* workspace,
+                                          size_t workspace_bytes, void* stream) {
+  return vb::reduce_impl(op, out, out_index, self, dims, ndims, keepdim, workspace, workspace_bytes, true, true,
+                         stream);
 }
 
 vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_tensor* partial,
                                         const vbt_b200_tensor* shard, const int64_t* dims, int32_t ndims,
                                         int32_t keepdim, void* workspace, size_t workspace_bytes,
-                                        void* stream) {
+                                        int32_t flags, void* stream) {
   using namespace vb;
   VB_ARG(op == VBT_B200_R_SUM || op == VBT_B200_R_MAX || op == VBT_B200_R_MIN,
          "reduce_partial: only sum / max / min combine across shards");
   VB_ARG(partial && shard, "reduce_partial: null tensor descriptor");
   VB_ARG(partial->dtype == VBT_B200_F32 || partial->dtype == VBT_B200_I64,
          "reduce_partial: partials are float32 or int64");
-  return vbt_b200_reduce(op, partial, nullptr, shard, dims, ndims, keepdim, workspace, workspace_bytes,
-                         stream);
+  return reduce_impl(op, partial, nullptr, shard, dims, ndims, keepdim, workspace, workspace_bytes,
+                     (flags & VBT_B200_PARTIAL_WS_ZEROED) != 0, (flags & VBT_B200_PARTIAL_NOT_FIRST) == 0, stream);
 }
 
 }  // extern "C"

@@ -2,6 +2,7 @@
 #include "ti_plan.h"
 
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 
 namespace vb {
@@ -33,6 +34,25 @@ vbt_b200_status validate_tensor(const vbt_b200_tensor* t, const char* what) {
   for (int i = 0; i < t->ndim; ++i)
     VB_ARG(t->sizes[i] >= 0, std::string(what) + ": negative size");
   return VBT_B200_OK;
+}
+
+vbt_b200_status validate_data(const vbt_b200_tensor* t, const char* what) {
+  VB_TRY(validate_tensor(t, what));
+  VB_ARG(t->data != nullptr || numel(*t) == 0, std::string(what) + ": null data pointer");
+  return VBT_B200_OK;
+}
+
+vbt_b200_launch_info& launch_info_ref() {
+  thread_local vbt_b200_launch_info li{};
+  return li;
+}
+
+namespace {
+std::atomic<uint64_t> g_launches[VBT_B200_FAMILY_COUNT];
+}
+void count_launches(int family, int n) {
+  if (family >= 0 && family < VBT_B200_FAMILY_COUNT && n > 0)
+    g_launches[family].fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed);
 }
 
 vbt_b200_status broadcast_shape(const vbt_b200_tensor* const* ops, int n, const char* opname,
@@ -248,6 +268,25 @@ extern "C" {
 const char* vbt_b200_last_error(void) { return vb::last_error_ref().c_str(); }
 int32_t vbt_b200_version(void) { return 1000; }
 int32_t vbt_b200_compiled_arch(void) { return 100; }
+
+vbt_b200_status vbt_b200_last_launch_info(vbt_b200_launch_info* out) {
+  VB_ARG(out != nullptr, "last_launch_info: null argument");
+  *out = vb::launch_info_ref();
+  return VBT_B200_OK;
+}
+
+void vbt_b200_reset_last_launch_info(void) { vb::launch_info_ref() = vbt_b200_launch_info{}; }
+
+vbt_b200_status vbt_b200_launch_counts(uint64_t* counts, int32_t n) {
+  VB_ARG(counts != nullptr && n >= 0, "launch_counts: bad argument");
+  for (int i = 0; i < n; ++i)
+    counts[i] = i < VBT_B200_FAMILY_COUNT ? vb::g_launches[i].load(std::memory_order_relaxed) : 0;
+  return VBT_B200_OK;
+}
+
+void vbt_b200_reset_launch_counts(void) {
+  for (auto& c : vb::g_launches) c.store(0, std::memory_order_relaxed);
+}
 
 vbt_b200_status vbt_b200_enable_peer_access(int32_t compute_device, int32_t peer_device) {
   using namespace vb;

@@ -211,24 +211,56 @@ def _all_reduce(t: torch.Tensor, name: str, mesh: FabricMesh):
     return t
 
 
-def reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False, local_ops=None):
-    """sum / mean / max / min of a FabricTensor.
+def _first_owner(placement: FabricPlacement) -> int:
+    """The rank whose shard holds global row 0 (the first rank with any rows)."""
+    for r in range(placement.mesh.world_size):
+        if placement.rows_of(r) > 0:
+            return r
+    return 0
 
-    * the reduced dims include dim 0 of a sharded_1d_row tensor: local partial, all-reduce,
-      (mean: scale by 1 / global count, cast to the input dtype) -> a plain tensor, identical
-      on every rank;
-    * otherwise: local reduction -> FabricTensor sharded the same way.
-    """
+
+def _plan(name: str, ft: "FabricTensor", dim, keepdim: bool):
     if name not in _REDUCE_OP:
         raise FabricError(f"fabric.reduce: unsupported reduction {name!r}")
-    x = ft.shard
-    be = _backend(local_ops, x)
-    nd = x.dim()
+    nd = ft.shard.dim()
     dims = list(range(nd)) if dim is None else ([dim] if isinstance(dim, int) else list(dim))
     dims = sorted({d + nd if d < 0 else d for d in dims})
     if any(d < 0 or d >= nd for d in dims):
         raise ValueError(f"{name}: dim out of range")
     crosses = ft.placement.kind == "sharded_1d_row" and 0 in dims
+    return dims, crosses
+
+
+def _combine_extremum(name, partial, ft, be):
+    """max / min of floating partials across ranks.  The single-GPU rule is "a NaN wins only at
+    position 0 of the reduced slice"; across shards that position belongs to the first rank
+    that has rows.  The other ranks computed their partial without the rule (so it cannot be a
+    NaN that came from their own first row), and the partials are folded here in rank order
+    from the owner on by the SAME reduction kernel -- the owner's partial sits at position 0
+    of that fold -- instead of by the collective library's max, whose treatment of NaN is not
+    part of its contract."""
+    mesh = ft.placement.mesh
+    ws = mesh.world_size
+    if ws == 1:
+        return partial
+    flat = partial.contiguous().reshape(-1)
+    gathered = torch.empty(ws * flat.numel(), dtype=partial.dtype, device=partial.device)
+    dist.all_gather_into_tensor(gathered, flat, group=mesh.group)
+    stacked = gathered.view((ws,) + tuple(partial.shape))
+    return be.reduce(name, stacked[_first_owner(ft.placement):], [0], False)
+
+
+def reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False, local_ops=None):
+    """sum / mean / max / min of a FabricTensor.
+
+    * the reduced dims include dim 0 of a sharded_1d_row tensor: local partial, one exchange
+      (all-reduce; all-gather + ordered fold for floating max / min), then for mean the scale by
+      1 / global count and the cast to the input dtype -> a plain tensor, identical on every rank;
+    * otherwise: local reduction -> FabricTensor sharded the same way.
+    """
+    dims, crosses = _plan(name, ft, dim, keepdim)
+    x = ft.shard
+    be = _backend(local_ops, x)
     if not crosses:
         out = be.reduce(name, x, dims, keepdim)
         if ft.placement.kind == "replicated":
@@ -238,6 +270,7 @@ def reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False, local_o
                              ft.placement.shard_offsets)
         return FabricTensor(pl, out)
     local = "sum" if name == "mean" else name
+    floating_ext = local in ("max", "min") and x.dtype.is_floating_point
     if x.shape[0] == 0:
         # an empty shard contributes the identity
         oshape = [1 if i in dims else s for i, s in enumerate(x.shape) if keepdim or i not in dims]
@@ -246,8 +279,12 @@ def reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False, local_o
                  "min": float("inf") if pdt.is_floating_point else torch.iinfo(pdt).max}[local]
         partial = torch.full(oshape, ident, dtype=pdt, device=x.device)
     else:
-        partial = be.reduce(local, x, dims, keepdim, partial=True)
-    _all_reduce(partial, name, ft.placement.mesh)
+        first = ft.placement.mesh.rank == _first_owner(ft.placement)
+        partial = be.reduce(local, x, dims, keepdim, partial=True, first_shard=first)
+    if floating_ext:
+        partial = _combine_extremum(local, partial, ft, be)
+    else:
+        _all_reduce(partial, name, ft.placement.mesh)
     if name == "mean":
         count = 1
         for d in dims:
@@ -256,6 +293,67 @@ def reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False, local_o
     if partial.dtype != x.dtype:
         return be.scale_cast(partial, 1.0, x.dtype)
     return partial
+
+
+class PreparedReduce:
+    """A sharded reduction set up once and run many times: the reduction plan, tensor
+    descriptors, partial / result buffers and workspace are built here, so a ``run()`` is the
+    local kernel launch, the exchange, and (mean, 16-bit inputs) one scale-and-cast launch --
+    no shape queries or allocations in between.  ``run()`` returns the same result tensor every
+    time (it is overwritten by the next run).  The shard's storage must stay where it is; its
+    contents may change between runs.  CUDA tensors only."""
+
+    def __init__(self, name: str, ft: FabricTensor, dim=None, keepdim: bool = False):
+        from . import ops
+        self.name = name
+        self.ft = ft
+        self.mesh = ft.placement.mesh
+        dims, crosses = _plan(name, ft, dim, keepdim)
+        if not crosses:
+            raise FabricError("PreparedReduce is for reductions over the sharded dim")
+        x = ft.shard
+        _backend(None, x)
+        if x.shape[0] == 0:
+            raise FabricError("PreparedReduce needs a non-empty local shard")
+        self._ops = ops
+        local = "sum" if name == "mean" else name
+        self._floating_ext = local in ("max", "min") and x.dtype.is_floating_point
+        first = self.mesh.rank == _first_owner(ft.placement)
+        self._local = ops.PreparedReduce(local, x, dims, keepdim, partial=True, first_shard=first)
+        partial = self._local.out
+        self._gathered = None
+        self._fold = None
+        if self._floating_ext and self.mesh.world_size > 1:
+            ws = self.mesh.world_size
+            self._gathered = torch.empty(ws * partial.numel(), dtype=partial.dtype, device=x.device)
+            stacked = self._gathered.view((ws,) + tuple(partial.shape))
+            self._fold = ops.PreparedReduce(local, stacked[_first_owner(ft.placement):], [0], False)
+        src = self._fold.out if self._fold is not None else partial
+        self._scale = None
+        if name == "mean" or src.dtype != x.dtype:
+            count = 1
+            if name == "mean":
+                for d in dims:
+                    count *= ft.placement.global_shape[d]
+            scale = (1.0 / count if count else float("nan")) if name == "mean" else 1.0
+            self._scale = ops.PreparedScaleCast(src, scale, x.dtype)
+        self.out = self._scale.out if self._scale is not None else src
+
+    def run(self) -> torch.Tensor:
+        partial = self._local.run()
+        if self.mesh.world_size > 1:
+            if self._gathered is not None:
+                dist.all_gather_into_tensor(self._gathered, partial.view(-1), group=self.mesh.group)
+                self._fold.run()
+            else:
+                dist.all_reduce(partial, op=_REDUCE_OP[self.name], group=self.mesh.group)
+        if self._scale is not None:
+            self._scale.run()
+        return self.out
+
+
+def prepare_reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False) -> PreparedReduce:
+    return PreparedReduce(name, ft, dim, keepdim)
 
 
 def sum(ft, dim=None, keepdim=False, local_ops=None):  # noqa: A001

@@ -67,6 +67,8 @@ def _require_cuda(*ts: torch.Tensor) -> None:
 
 
 def _alloc_out(out, shape, dtype, like):
+    """The library computes on the device that owns the output, and the launch goes to that
+    device's current stream (every caller below passes stream_ptr(output))."""
     if out is None:
         return torch.empty(tuple(shape), dtype=dtype, device=like.device)
     if tuple(out.shape) != tuple(shape):
@@ -88,7 +90,7 @@ def unary(name: str, a: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
     _require_cuda(*([out] if out is not None else []), a)
     o = _alloc_out(out, a.shape, torch.bool if name in UNARY_TO_BOOL else a.dtype, a)
     do, da = desc(o), desc(a)
-    check(lib().vbt_b200_unary(UNARY.index(name), do.ref, da.ref, stream_ptr(a)))
+    check(lib().vbt_b200_unary(UNARY.index(name), do.ref, da.ref, stream_ptr(o)))
     return o
 
 
@@ -102,7 +104,7 @@ def binary(name: str, a, b, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         _require_cuda(*([out] if out is not None else []), a, b)
         o = _alloc_out(out, _bshape(a, b), torch.bool if cmp_ else a.dtype, a)
         do, da, db = desc(o), desc(a), desc(b)
-        check(lib().vbt_b200_binary(op, do.ref, da.ref, db.ref, stream_ptr(a)))
+        check(lib().vbt_b200_binary(op, do.ref, da.ref, db.ref, stream_ptr(o)))
         return o
     t, s, left = (a, b, False) if a_t else (b, a, True)
     _require_cuda(t)
@@ -116,7 +118,7 @@ def binary(name: str, a, b, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     else:
         raise ValueError(f"vt::{name}: unsupported dtype for scalar op")
     do, dt_ = desc(o), desc(t)
-    check(lib().vbt_b200_binary_scalar(op, do.ref, dt_.ref, ctypes.byref(sv), int(left), stream_ptr(t)))
+    check(lib().vbt_b200_binary_scalar(op, do.ref, dt_.ref, ctypes.byref(sv), int(left), stream_ptr(o)))
     return o
 
 
@@ -124,7 +126,7 @@ def ternary(name: str, a, b, c, out=None) -> torch.Tensor:
     _require_cuda(*([out] if out is not None else []), a, b, c)
     o = _alloc_out(out, _bshape(a, b, c), a.dtype, a)
     do, da, db, dc = desc(o), desc(a), desc(b), desc(c)
-    check(lib().vbt_b200_ternary(TERNARY.index(name), do.ref, da.ref, db.ref, dc.ref, stream_ptr(a)))
+    check(lib().vbt_b200_ternary(TERNARY.index(name), do.ref, da.ref, db.ref, dc.ref, stream_ptr(o)))
     return o
 
 
@@ -132,7 +134,7 @@ def where(cond, x, y, out=None) -> torch.Tensor:
     _require_cuda(*([out] if out is not None else []), x, cond, y)
     o = _alloc_out(out, _bshape(cond, x, y), x.dtype, x)
     do, dc, dx, dy = desc(o), desc(cond), desc(x), desc(y)
-    check(lib().vbt_b200_where(do.ref, dc.ref, dx.ref, dy.ref, stream_ptr(x)))
+    check(lib().vbt_b200_where(do.ref, dc.ref, dx.ref, dy.ref, stream_ptr(o)))
     return o
 
 
@@ -234,11 +236,12 @@ def reduce_shape(x: torch.Tensor, dims: Sequence[int], keepdim: bool):
 
 
 _ws_cache: dict = {}
+_reduce_ws_cache: dict = {}
 
 
 def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
-    """Scratch for split reductions.  One buffer per (device, stream), grown on demand and
-    reused: work on one stream is ordered, so successive calls cannot overlap."""
+    """General scratch (contents undefined).  One buffer per (device, stream), grown on demand
+    and reused: work on one stream is ordered, so successive calls cannot overlap."""
     if nbytes == 0:
         return None
     key = (device, torch.cuda.current_stream(device).cuda_stream)
@@ -249,33 +252,106 @@ def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
     return ws
 
 
+def _reduce_workspace(nbytes: int, device) -> Optional[torch.Tensor]:
+    """Scratch of the split reductions, one per (device, stream) like the buffer above but used
+    by reductions only and ZEROED when it is created: the kernels return its ticket counters to
+    zero, so no call has to clear them (vbt_b200_reduce_zeroed_ws)."""
+    if nbytes == 0:
+        return None
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _reduce_ws_cache.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 4 << 20), dtype=torch.uint8, device=device)
+        _reduce_ws_cache[key] = ws
+    return ws
+
+
 def reduce(name: str, x: torch.Tensor, dim=None, keepdim: bool = False,
-           out_dtype: Optional[torch.dtype] = None, partial: bool = False):
+           out_dtype: Optional[torch.dtype] = None, partial: bool = False,
+           out: Optional[torch.Tensor] = None, first_shard: bool = True):
     """sum / mean / max / min / prod -> values; argmax / argmin -> (values, int64 indices).
-    partial=True is the per-shard step of a sharded reduction (FP32 / INT64 partials)."""
+    partial=True is the per-shard step of a sharded reduction (FP32 / INT64 partials).
+    out= reuses a result buffer of the reduced shape (values only).  first_shard=False (partial
+    only): the shard does not start at the global position 0, so max / min ignore a NaN at its
+    own position 0."""
     _require_cuda(x)
     op = REDUCE.index(name)
     dims = _norm_dims(dim)
-    oshape = reduce_shape(x, dims, keepdim)
-    if out_dtype is None:
-        out_dtype = x.dtype
-        if partial and x.dtype in (torch.float16, torch.bfloat16):
-            out_dtype = torch.float32
-    o = torch.empty(oshape, dtype=out_dtype, device=x.device)
-    oi = torch.empty(oshape, dtype=torch.int64, device=x.device) if op >= 5 else None
+    if out is None:
+        oshape = reduce_shape(x, dims, keepdim)
+        if out_dtype is None:
+            out_dtype = x.dtype
+            if partial and x.dtype in (torch.float16, torch.bfloat16):
+                out_dtype = torch.float32
+        o = torch.empty(oshape, dtype=out_dtype, device=x.device)
+    else:
+        o = out
+    oi = torch.empty(o.shape, dtype=torch.int64, device=x.device) if op >= 5 else None
     dx, do = desc(x), desc(o)
     di = desc(oi) if oi is not None else None
     da = i64_array(dims)
     nbytes = lib().vbt_b200_reduce_workspace_bytes(op, dx.ref, da, len(dims))
-    ws = _workspace(nbytes, x.device)
+    ws = _reduce_workspace(nbytes, x.device)
     wp = ctypes.c_void_p(ws.data_ptr()) if ws is not None else None
     if partial:
         check(lib().vbt_b200_reduce_partial(op, do.ref, dx.ref, da, len(dims), int(keepdim), wp,
-                                            nbytes, stream_ptr(x)))
+                                            nbytes, 1 | (0 if first_shard else 2), stream_ptr(o)))
     else:
-        check(lib().vbt_b200_reduce(op, do.ref, di.ref if di else None, dx.ref, da, len(dims),
-                                    int(keepdim), wp, nbytes, stream_ptr(x)))
+        check(lib().vbt_b200_reduce_zeroed_ws(op, do.ref, di.ref if di else None, dx.ref, da, len(dims),
+                                              int(keepdim), wp, nbytes, stream_ptr(o)))
     return (o, oi) if oi is not None else o
+
+
+class PreparedReduce:
+    """reduce() with everything but the launch done ahead: output, workspace and the ctypes
+    argument list are built once, run() is a single C-ABI call on the current stream of the
+    output's device.  The input's storage must stay where it is; the result tensor (``out``)
+    is overwritten by every run.  Values only (no argmax / argmin)."""
+
+    def __init__(self, name: str, x: torch.Tensor, dim=None, keepdim: bool = False, partial: bool = False,
+                 first_shard: bool = True):
+        _require_cuda(x)
+        op = REDUCE.index(name)
+        if op >= 5:
+            raise ValueError("PreparedReduce: argmax / argmin are not supported")
+        dims = _norm_dims(dim)
+        out_dtype = x.dtype
+        if partial and x.dtype in (torch.float16, torch.bfloat16):
+            out_dtype = torch.float32
+        self.x = x
+        self.out = torch.empty(reduce_shape(x, dims, keepdim), dtype=out_dtype, device=x.device)
+        self._dx, self._do, self._da = desc(x), desc(self.out), i64_array(dims)
+        nbytes = lib().vbt_b200_reduce_workspace_bytes(op, self._dx.ref, self._da, len(dims))
+        self._ws = _reduce_workspace(nbytes, x.device)
+        wp = ctypes.c_void_p(self._ws.data_ptr()) if self._ws is not None else None
+        if partial:
+            self._fn = lib().vbt_b200_reduce_partial
+            self._args = (op, self._do.ref, self._dx.ref, self._da, len(dims), int(keepdim), wp, nbytes,
+                          1 | (0 if first_shard else 2))
+        else:
+            self._fn = lib().vbt_b200_reduce_zeroed_ws
+            self._args = (op, self._do.ref, None, self._dx.ref, self._da, len(dims), int(keepdim), wp, nbytes)
+
+    def run(self) -> torch.Tensor:
+        check(self._fn(*self._args, stream_ptr(self.out)))
+        return self.out
+
+
+class PreparedScaleCast:
+    """scale_cast() with its output and argument list built once."""
+
+    def __init__(self, partial: torch.Tensor, scale: float, out_dtype: torch.dtype):
+        _require_cuda(partial)
+        if partial.dtype != torch.float32 or not partial.is_contiguous():
+            raise ValueError("scale_cast: partial must be contiguous float32")
+        self.src = partial
+        self.out = torch.empty(partial.shape, dtype=out_dtype, device=partial.device)
+        self._args = (ctypes.c_void_p(self.out.data_ptr()), _lib.dtype_code(out_dtype),
+                      ctypes.c_void_p(partial.data_ptr()), partial.numel(), float(scale))
+
+    def run(self) -> torch.Tensor:
+        check(lib().vbt_b200_scale_cast(*self._args, stream_ptr(self.out)))
+        return self.out
 
 
 def sum(x, dim=None, keepdim=False):  # noqa: A001 - mirrors Tensor.sum
@@ -388,15 +464,21 @@ def index_put_rows_(table: torch.Tensor, idx: torch.Tensor, values: torch.Tensor
 
 
 def index_lastdim(src: torch.Tensor, idx: torch.Tensor, status=None, eager_check=True):
-    """The reference's CUDA advanced-index form ``src[..., idx]`` for 2-D src."""
+    """The reference's CUDA advanced-index form ``src[..., idx]``: src of any rank >= 1 and
+    any strides, one index tensor (any shape) applied to the last dim; the result is dense
+    ``src.shape[:-1] + idx.shape`` (src/vbt/core/indexing_advanced_cuda.cu:2156-2177)."""
     _require_cuda(src, idx)
+    if src.dim() < 1:
+        raise ValueError("index: advanced indexing is not supported for 0-d tensors on CUDA")
+    if idx.dim() < 1:
+        raise ValueError("index: advanced tensor indices must have dim() > 0")
     st, own = _status(status, eager_check, src.device)
-    o = torch.empty((src.shape[0], idx.numel()), dtype=src.dtype, device=src.device)
+    o = torch.empty(tuple(src.shape[:-1]) + tuple(idx.shape), dtype=src.dtype, device=src.device)
     do, ds, di = desc(o), desc(src), desc(idx.contiguous())
     check(lib().vbt_b200_index_lastdim(do.ref, ds.ref, di.ref, INDEX_WRAP, st.ptr if st else None,
-                                       stream_ptr(src)))
+                                       stream_ptr(o)))
     if own:
-        st.check("index", src.shape[1])
+        st.check("index", src.shape[-1])
     return o
 
 
@@ -446,7 +528,7 @@ def index_put_lastdim_(self_: torch.Tensor, idx, values, accumulate=False, statu
     check(lib().vbt_b200_index_put_lastdim(ds.ref, di.ref, dv.ref, int(accumulate), INDEX_WRAP,
                                            st.ptr if st else None, stream_ptr(self_)))
     if own:
-        st.check("index_put_", self_.shape[1])
+        st.check("index_put_", self_.shape[-1])
     return self_
 
 
