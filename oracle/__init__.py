@@ -55,11 +55,13 @@ _i64p = ctypes.POINTER(ctypes.c_int64)
 _int = ctypes.c_int
 
 
-def build(ref: bool = True) -> None:
-    """Compile the restatement (always) and, when a reference checkout is mounted, _ref."""
+def build(ref_dir=None) -> None:
+    """Compile the restatement (always) and, given a reference checkout (ref_dir, or
+    VBT_REFERENCE_DIR in the environment), the reference's own CPU sources into _ref."""
     subprocess.run(["make", "-s", "-C", HERE, "_build/libvbt_oracle.so"], check=True)
-    if ref and os.path.isdir("/root/reference/src/vbt"):
-        subprocess.run(["bash", os.path.join(HERE, "build_ref.sh")], check=True,
+    ref_dir = ref_dir or os.environ.get("VBT_REFERENCE_DIR")
+    if ref_dir and os.path.isdir(os.path.join(ref_dir, "src", "vbt")):
+        subprocess.run(["bash", os.path.join(HERE, "build_ref.sh"), ref_dir], check=True,
                        stdout=subprocess.DEVNULL)
 
 

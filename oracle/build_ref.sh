@@ -1,20 +1,20 @@
 #!/usr/bin/env bash
 # TEST INFRASTRUCTURE ONLY.  Compiles VibeTensor's own CPU implementation of the
-# vt:: op path from the sources where they lie (argument 1, default the mounted
+# vt:: op path from the sources where they lie (argument 1, or VBT_REFERENCE_DIR: the
 # reference checkout) plus oracle/ref_shim.cpp into oracle/_ref/libvbt_ref_cpu.so.
 # Reference sources are never copied into this repository; only the built .so
 # (git-ignored) lands in oracle/_ref/.  The reference's own CMake build is not
 # used: its third-party submodules are empty, so only the CPU files that compile
 # on their own are listed here.
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${VBT_REFERENCE_DIR:-}}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
 OBJ="$OUT/obj"
 mkdir -p "$OBJ/shim/absl/log" "$OBJ/shim/dlpack"
 
-if [ ! -d "$REF/src/vbt" ]; then
-  echo "build_ref: no reference checkout at $REF" >&2
+if [ -z "$REF" ] || [ ! -d "$REF/src/vbt" ]; then
+  echo "build_ref: no reference checkout (argument 1 or VBT_REFERENCE_DIR)" >&2
   exit 3
 fi
 

@@ -18,7 +18,7 @@ import oracle  # noqa: E402
 
 
 def main():
-    oracle.build()
+    oracle.build(ref_dir=sys.argv[1] if len(sys.argv) > 1 else None)  # argument 1 or VBT_REFERENCE_DIR: the reference checkout
     R = oracle.ref()
     F32, I64 = oracle.F32, oracle.I64
     rng = np.random.default_rng(20240)
