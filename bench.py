@@ -47,8 +47,8 @@ TOTAL_ELEMS = 1 << 32
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per element moved by one launch of the local reduce kernel, from the ncu capture
-# of a 2 GiB shard summarised in profiles/ncu_row_block_kernel_sum_f32_2GiB_shard.md
-# (dram__bytes_read.sum + dram__bytes_write.sum; traffic grows in proportion to the shard).
+# of a 2 GiB shard (dram__bytes_read.sum + dram__bytes_write.sum; traffic grows in proportion
+# to the shard).
 REDUCE_TRAFFIC_BYTES_PER_ELEM = 2151534080 / (1 << 29)  # 2 147 509 504 B read + 4 024 576 B written for 2^29 elements
 
 
@@ -130,13 +130,13 @@ def cpu_reference_sum(sample_elems: int, reps: int):
         fn, kind = (lambda: oracle.ref().sum(x, oracle.F32, [])), "reference"
     else:
         fn, kind = (lambda: oracle.port().reduce("sum", x, oracle.F32)), "port"
-    fn()
+    result = float(fn())
     best = []
     for _ in range(reps):
         t0 = time.perf_counter()
         fn()
         best.append(time.perf_counter() - t0)
-    return sample_elems / (sum(best) / len(best)), kind, sum(best)
+    return sample_elems / (sum(best) / len(best)), kind, sum(best), x, result
 
 
 def run_reference(args):
@@ -200,11 +200,18 @@ def run_reference(args):
     emit(line)
 
 
-def workload_config(n):
+def workload_config(n, fused=False):
+    if n == 1:
+        coll = "none"
+    elif fused:
+        coll = ("inside the reduce kernel: 4-byte partials written to every rank's exchange buffer with peer "
+                "stores over NVLink, per-rank flags, fold in rank order (no collective library call)")
+    else:
+        coll = "ncclAllReduce(sum, 4 bytes) after the local kernel"
     return {"workload": "c5_sharded_sum_f32_2p32" if TOTAL_ELEMS == 1 << 32 else "c5_sharded_sum_f32_reduced",
             "tensor": f"[{TOTAL_ELEMS}] fp32 N(0,1), seed 4",
             "sharding": f"sharded_1d_row over {n} rank(s), {TOTAL_ELEMS // n} elements per rank",
-            "collective": "none" if n == 1 else "ncclAllReduce(sum, 4 bytes) after the local kernel",
+            "collective": coll,
             "l2_policy": "inputs larger than L2 (>= 2 GiB per rank); no flush needed"}
 
 
@@ -291,16 +298,17 @@ def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4", "ew")
             add("softmax", f"C4 {list(shape)} {str(dt)[6:]}", 2 * n * es, n, ms)
             ms = time_op(torch, lambda i: kernels.rmsnorm(xs[i % nbuf], gamma, 1e-6), 20)
             add("rmsnorm", f"C4 {list(shape)} {str(dt)[6:]}", 2 * n * es + shape[1] * 4 + shape[0] * 4, n, ms)
-            # backward: the saved tensor rotates through the forward's buffers, dy has its own
+            # backward: the saved tensor rotates through the forward's buffers and dy through as
+            # many buffers of its own, so that neither stream is served from L2
             inv = kernels.rmsnorm(xs[0], gamma, 1e-6)[1]
-            dyb = torch.randn(shape, device=dev, generator=g).to(dt)
-            ms = time_op(torch, lambda i: kernels.rmsnorm_backward(dyb, xs[i % nbuf], inv, gamma), 20)
+            dys = [torch.randn(shape, device=dev, generator=g).to(dt) for _ in range(nbuf)]
+            ms = time_op(torch, lambda i: kernels.rmsnorm_backward(dys[i % nbuf], xs[i % nbuf], inv, gamma), 20)
             add("rmsnorm_backward (dx, dgamma)", f"C4 {list(shape)} {str(dt)[6:]}",
                 3 * n * es + 2 * shape[1] * 4 + shape[0] * 4, n, ms, launches=2,
                 note="per-block dgamma partial rows + fixed-order fold, no atomics")
-            ms = time_op(torch, lambda i: kernels.softmax_backward(dyb, xs[i % nbuf]), 20)
+            ms = time_op(torch, lambda i: kernels.softmax_backward(dys[i % nbuf], xs[i % nbuf]), 20)
             add("softmax_backward", f"C4 {list(shape)} {str(dt)[6:]}", 3 * n * es, n, ms)
-            del xs, dyb
+            del xs, dys
     if "c2" in which:
         # ---- C2: gather / scatter_add on a [1,048,576 x 256] table with 4,194,304 indices
         V, D, N = 1 << 20, 256, (1 << 19 if small else 1 << 22)
@@ -357,9 +365,12 @@ def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4", "ew")
         nm = 1 << (26 if small else 28)
         mask = torch.from_numpy(rng.random(nm) < 0.5).to(dev)
         cnt = int(mask.sum().item())
+        ms = time_op(torch, lambda i: ops.mask_select(mask), 5)
+        add("bool mask -> indices (device part)", f"[{nm}] bool, half true", nm + 8 * cnt, nm, ms, launches=3,
+            note="count + scan + ranked writes on the stream; bytes = the mask once + 8 per true element")
         ms = time_op(torch, lambda i: ops.mask_to_indices(mask), 5, graph=False)
-        add("bool mask -> indices", f"[{nm}] bool, half true", 2 * nm + 8 * cnt, nm, ms, launches=3,
-            note="includes the 8-byte D2H read of the count and the stream synchronise; eager timing")
+        add("bool mask -> indices, with the count read back", f"[{nm}] bool, half true", nm + 8 * cnt, nm, ms,
+            launches=3, note="adds the 8-byte D2H read of the count and the stream synchronise; eager timing")
         del mask
     if "c3" in which:
         # ---- C3: bf16 broadcast chain into a transposed output view
@@ -476,9 +487,13 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the step, set up once: plan, descriptors, partial buffer and workspace are built here, so a
+    # step is the local kernel launch plus (N > 1) the 4-byte all-reduce on the same stream
+    prep = fabric.prepare_reduce("sum", ft, fused=False if args.no_fused else None)
+    fused = prep.fused is not None
     result = None
     for _ in range(max(args.warmup, 3)):
-        result = fabric.sum(ft)
+        result = prep.run()
     barrier()
 
     sampler = ClockSampler(local_rank)
@@ -490,15 +505,9 @@ def run_ours(args):
     t_end = torch.cuda.Event(enable_timing=True)
     t_start.record()
     for _ in range(args.steps):
-        k0 = torch.cuda.Event(enable_timing=True)
-        k1 = torch.cuda.Event(enable_timing=True)
-        k0.record()
-        partial = ops.reduce("sum", shard, None, False, partial=True)   # the local kernel
-        k1.record()
-        kern_events.append((k0, k1))
-        if n > 1:
-            dist.all_reduce(partial)                                     # 4-byte combine
-        result = partial
+        ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        result = prep.run(kernel_events=ev)   # local kernel (timed by ev) + 4-byte combine
+        kern_events.append(ev)
     t_end.record()
     barrier()
     ms_total = t_start.elapsed_time(t_end)
@@ -506,17 +515,28 @@ def run_ours(args):
     if n > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = t.item() / args.steps
-    kern_ms = sum(a.elapsed_time(b) for a, b in kern_events) / len(kern_events)
+    kern_all = sorted(a.elapsed_time(b) for a, b in kern_events)
+    kern_ms = sum(kern_all) / len(kern_all)
+    kern_stats = {"mean": kern_ms, "median": kern_all[len(kern_all) // 2], "min": kern_all[0], "max": kern_all[-1]}
     clocks = sampler.stop() if rank == 0 else None
 
-    # correctness of what was timed: against an fp64 fold of the same shards
-    truth = shard.double().sum()
-    scale = shard.abs().double().sum()
+    # correctness of what was timed: against an fp64 fold of the same shards, on the scale
+    # max(|truth|, sigma * sqrt(N)) (sigma * sqrt(N) as sqrt(sum x^2))
+    truth = torch.zeros((), device=dev, dtype=torch.float64)
+    sq = torch.zeros((), device=dev, dtype=torch.float64)
+    for o in range(0, shard_elems, step_fill):
+        d = shard[o:o + step_fill].double()
+        truth += d.sum()
+        sq += d.pow(2).sum()
+        del d
     if n > 1:
         dist.all_reduce(truth)
-        dist.all_reduce(scale)
-    rel = abs(result.double().item() - truth.item()) / scale.item()
-    assert rel <= 1e-5, f"sharded sum off by {rel:.3e} of sum|x|"
+        dist.all_reduce(sq)
+    scale = max(abs(truth.item()), sq.item() ** 0.5)
+    rel = abs(result.double().item() - truth.item()) / scale
+    assert rel <= 1e-5, f"sharded sum off by {rel:.3e} of max(|truth|, sigma*sqrt(N))"
+    if fused:
+        prep.comm.check()  # no exchange on this rank gave up waiting for a peer
 
     # ---- the other sharded reductions of the configuration: amax over the same tensor and
     # mean(dim=0) over a [1,048,576 x 4096] bf16 tensor split by rows (fp32 column partials,
@@ -538,14 +558,18 @@ def run_ours(args):
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         return tt.item()
 
+    prep_amax = None
     if not args.no_sharded_extras:
         k = max(1, min(args.steps, 10))
-        ms = timed(lambda: fabric.amax(ft), k)
+        prep_amax = fabric.prepare_reduce("max", ft, fused=False if args.no_fused else None)
+        ms = timed(prep_amax.run, k)
         gmax = shard.max()
         if n > 1:
             dist.all_reduce(gmax, op=dist.ReduceOp.MAX)
         assert fabric.amax(ft).item() == gmax.item(), "sharded amax mismatch"
+        assert prep_amax.run().item() == gmax.item(), "prepared sharded amax mismatch"
         sharded.append({"op": "amax", "tensor": f"[{TOTAL_ELEMS}] fp32", "ms_per_step": ms,
+                        "fused_exchange": prep_amax.fused is not None,
                         "elements_per_s": TOTAL_ELEMS / (ms * 1e-3), "gb_per_s_whole_job": TOTAL_ELEMS * 4 / (ms * 1e-3) / 1e9})
         rows_total, cols = (1 << 20) * TOTAL_ELEMS // (1 << 32), 4096
         rows = rows_total // n
@@ -553,8 +577,10 @@ def run_ours(args):
         for o in range(0, rows, 1 << 14):
             xb[o:o + (1 << 14)].normal_(generator=g)
         fb = fabric.FabricTensor.sharded_1d_row(mesh, xb)
-        ms = timed(lambda: fabric.mean(fb, dim=0), k)
+        prep_mean = fabric.prepare_reduce("mean", fb, dim=0, fused=False if args.no_fused else None)
+        ms = timed(prep_mean.run, k)
         mcol = fabric.mean(fb, dim=0)
+        assert torch.equal(prep_mean.run(), mcol), "prepared and one-off sharded mean differ"
         ref_col = xb.float().sum(0)
         if n > 1:
             dist.all_reduce(ref_col)
@@ -562,8 +588,9 @@ def run_ours(args):
         assert torch.allclose(mcol.float(), ref_col, rtol=1e-2, atol=1e-2), "sharded bf16 mean(dim=0) off"
         ne = rows * n * cols
         sharded.append({"op": "mean(dim=0)", "tensor": f"[{rows * n},{cols}] bf16", "ms_per_step": ms,
+                        "fused_exchange": prep_mean.fused is not None,
                         "elements_per_s": ne / (ms * 1e-3), "gb_per_s_whole_job": ne * 2 / (ms * 1e-3) / 1e9})
-        del xb, fb
+        del xb, fb, prep_mean
 
     # ---- e2e: the shard starts in pinned host memory every step
     e2e = None
@@ -575,16 +602,29 @@ def run_ours(args):
 
     suite = None
     cpu = None
+    prep = prep_amax = None
     if n == 1 and rank == 0:
         del shard, ft
         torch.cuda.empty_cache()
         if not args.no_suite:
             suite = op_suite(torch, peak_gbs, args.suite_scale, tuple(args.suite_ops.split(',')))
+    ref_parity = None
     if n == 1 and rank == 0 and not args.no_cpu:
-        v, kind, secs = cpu_reference_sum(1 << 28, 8)
+        v, kind, secs, sample, ref_sum = cpu_reference_sum(1 << 28, 8)
         cpu = {"value": v, "unit": "elements/s", "cores": 1, "kind": kind,
                "sample": f"8 passes over {1 << 28} of {TOTAL_ELEMS} fp32 elements ({secs:.1f} s), single thread "
                          f"(the reference CPU path is single-threaded); host has {os.cpu_count()} cores"}
+        # the same sample through the GPU path: the kernel's and the reference loop's distance
+        # from the fp64 truth, both on the scale max(|truth|, sigma * sqrt(N))
+        ts = torch.from_numpy(sample).to(dev)
+        ours = ops.sum(ts).item()
+        t64 = ts.double().sum().item()
+        sc = max(abs(t64), float(ts.double().pow(2).sum().sqrt().item()))
+        ref_parity = {"sample_elements": int(sample.size), "kernel_vs_fp64": abs(ours - t64) / sc,
+                      "reference_cpu_sum_vs_fp64": abs(ref_sum - t64) / sc,
+                      "kernel_vs_reference_cpu_sum": abs(ours - ref_sum) / sc,
+                      "note": "the reference adds left to right in fp32; its drift from the truth is its own"}
+        del ts
 
     if rank == 0:
         shard_bytes = shard_elems * 4
@@ -593,17 +633,19 @@ def run_ours(args):
             "metric": "sharded fp32 sum throughput (elements/s; HBM GB/s in roofline)",
             "value": TOTAL_ELEMS / (ms_step * 1e-3), "unit": "elements/s", "n_gpus": n, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(n),
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(n, fused),
             "gb_per_s_whole_job": TOTAL_ELEMS * 4 / (ms_step * 1e-3) / 1e9,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak_gbs, "unit": "GB/s",
                          "frac": round(achieved / peak_gbs, 4), "peak_source": peak_kind,
                          "frac_of_nominal_8tbs": round(achieved / NOMINAL_HBM_GBS, 4),
                          "kernel": "row_block_kernel<float, SumR<float>, 4>",
                          "bytes_per_launch": shard_bytes, "ms_per_launch": kern_ms,
+                         "ms_per_launch_stats": kern_stats,
                          "traffic": (REDUCE_TRAFFIC_BYTES_PER_ELEM * shard_elems
                                      if REDUCE_TRAFFIC_BYTES_PER_ELEM is not None else None)},
             "e2e": e2e, "gpu_launches": args.steps * n, "clocks": clocks,
-            "parity": {"rel_err_vs_fp64_over_sum_abs": rel},
+            "parity": {"err_vs_fp64_over_max_abs_truth_sigma_sqrt_n": rel, "bound": 1e-5,
+                       "reference_sum_on_sample": ref_parity},
             "sharded_ops": sharded,
         }
         if cpu is not None:
@@ -615,61 +657,111 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def bind_to_gpu_numa_node(gpu_index: int):
+    """Host-side only: run this process (and so first-touch its pinned buffer) on the CPUs of
+    the NUMA node the GPU's PCIe slot hangs off.  Returns the node number, or None when the
+    topology cannot be read (then nothing is changed)."""
+    try:
+        bdf = subprocess.run(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=20).stdout.strip().lower()
+        if bdf.count(":") == 2 and len(bdf.split(":")[0]) == 8:
+            bdf = bdf[4:]  # nvidia-smi prints an 8-digit PCI domain, sysfs a 4-digit one
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 def run_e2e(torch, dist, ops, shard, n, args):
-    """Host-resident input: per step, H2D of the whole shard from pinned memory in 256 MiB
-    chunks on a copy stream, per-chunk partial sums on the compute stream behind events,
-    one combine, all-reduce, and a D2H read of the 4-byte result."""
+    """Host-resident input: per step, H2D of the whole shard from pinned memory in 64 MiB
+    chunks alternating over two copy streams, per-chunk partial sums on the compute stream
+    behind events, one combine, all-reduce, and a D2H read of the 4-byte result.  Also
+    measures the same copies with no kernel behind them: the ceiling this leg can reach."""
     dev = shard.device
     steps = max(1, min(args.steps, 3))
-    chunk = 1 << 26  # elements (256 MiB)
+    chunk = 1 << 24  # elements (64 MiB)
+    nstage = 4
     nchunks = (shard.numel() + chunk - 1) // chunk
+    node = bind_to_gpu_numa_node(dev.index or 0)
     host = torch.empty(shard.numel(), dtype=torch.float32, pin_memory=True)
-    host.copy_(shard)  # the synthetic shard, now host-resident
+    host.copy_(shard)  # the synthetic shard, now host-resident (first touched on the bound node)
     torch.cuda.synchronize()
-    stage = [torch.empty(chunk, device=dev, dtype=torch.float32) for _ in range(2)]
-    free_ev = [torch.cuda.Event() for _ in range(2)]
-    copy_stream = torch.cuda.Stream(device=dev)
+    stage = [torch.empty(chunk, device=dev, dtype=torch.float32) for _ in range(nstage)]
+    free_ev = [torch.cuda.Event() for _ in range(nstage)]
+    copy_streams = [torch.cuda.Stream(device=dev) for _ in range(2)]
     partials = torch.empty(nchunks, device=dev, dtype=torch.float32)
     out_host = torch.empty(1, dtype=torch.float32, pin_memory=True)
     compute = torch.cuda.current_stream(dev)
+    chunk_sum = [ops.PreparedReduce("sum", stage[i], None, False, partial=True) for i in range(nstage)]
+    final_sum = ops.PreparedReduce("sum", partials, None, False, partial=True)
+    tail = shard.numel() - (nchunks - 1) * chunk  # elements of the last chunk
 
-    def one_step():
+    def one_step(with_kernels=True):
         for c in range(nchunks):
             lo, hi = c * chunk, min((c + 1) * chunk, shard.numel())
-            buf = stage[c % 2][: hi - lo]
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(free_ev[c % 2])
-                buf.copy_(host[lo:hi], non_blocking=True)
+            k = c % nstage
+            cs = copy_streams[c % 2]
+            with torch.cuda.stream(cs):
+                cs.wait_event(free_ev[k])
+                stage[k][: hi - lo].copy_(host[lo:hi], non_blocking=True)
                 ready = torch.cuda.Event()
-                ready.record(copy_stream)
+                ready.record(cs)
             compute.wait_event(ready)
-            p = ops.reduce("sum", buf, None, False, partial=True)
-            partials[c:c + 1].copy_(p.reshape(1))
-            free_ev[c % 2].record(compute)
-        total = ops.reduce("sum", partials, None, False, partial=True)
+            if with_kernels:
+                if hi - lo == chunk:
+                    p = chunk_sum[k].run()
+                else:
+                    p = ops.reduce("sum", stage[k][:tail], None, False, partial=True)
+                partials[c:c + 1].copy_(p.reshape(1))
+            free_ev[k].record(compute)
+        if not with_kernels:
+            compute.synchronize()
+            return 0.0
+        total = final_sum.run()
         if n > 1:
             dist.all_reduce(total)
         out_host.copy_(total.reshape(1), non_blocking=True)
-        torch.cuda.current_stream(dev).synchronize()
+        compute.synchronize()
         return float(out_host[0])
 
-    for ev in free_ev:
-        ev.record(compute)
-    one_step()
-    if n > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        val = one_step()
-    torch.cuda.synchronize()
-    dt = torch.tensor([(time.perf_counter() - t0) / steps], device=dev, dtype=torch.float64)
-    if n > 1:
-        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    def timed(with_kernels):
+        for ev in free_ev:
+            ev.record(compute)
+        one_step(with_kernels)
+        if n > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            val = one_step(with_kernels)
+        torch.cuda.synchronize()
+        dt = torch.tensor([(time.perf_counter() - t0) / steps], device=dev, dtype=torch.float64)
+        if n > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        return dt.item(), val
+
+    dt, val = timed(True)
+    dt_copy, _ = timed(False)
     del host
-    return {"value": TOTAL_ELEMS / dt.item(), "unit": "elements/s", "ms_per_step": dt.item() * 1e3,
+    return {"value": TOTAL_ELEMS / dt, "unit": "elements/s", "ms_per_step": dt * 1e3,
             "h2d_bytes_per_step": shard.numel() * 4 * n, "d2h_bytes_per_step": 4 * n, "steps": steps,
-            "launches_per_step": (nchunks + 1) * n, "result": val}
+            "launches_per_step": (nchunks + 1) * n, "result": val,
+            "h2d_ceiling": {"value": TOTAL_ELEMS / dt_copy, "unit": "elements/s", "ms_per_step": dt_copy * 1e3,
+                            "gb_per_s_all_ranks": shard.numel() * 4 * n / dt_copy / 1e9,
+                            "note": "the same pinned-memory copies with no kernel behind them"},
+            "frac_of_h2d_ceiling": dt_copy / dt, "numa_node": node, "chunk_bytes": chunk * 4, "copy_streams": 2}
 
 
 _JSON_OUT = sys.stdout
@@ -696,6 +788,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-resident end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sharded-extras", action="store_true", help="skip the sharded amax / bf16 mean(dim=0) legs")
+    ap.add_argument("--no-fused", action="store_true",
+                    help="N > 1: combine with an NCCL all-reduce after the kernel instead of inside it")
     ap.add_argument("--suite-only", action="store_true", help="run only the per-op table")
     ap.add_argument("--suite-scale", default="full", choices=["full", "small"],
                     help="small: reduced C2/C3/C4 shapes (a few GB on the device) for profiler captures")

@@ -480,6 +480,24 @@ VBT_B200_API vbt_b200_status vbt_b200_rmsnorm_backward(void* dx, float* dgamma, 
  * (or the host framework's equivalent) is an invalid-address fault, so bindings must call it
  * first. */
 VBT_B200_API vbt_b200_status vbt_b200_enable_peer_access(int32_t compute_device, int32_t peer_device);
+/* vt::fabric_add / vt::fabric_mul (any binary op code is accepted): a and b have equal shapes
+ * and dtypes and may live on two GPUs of this process
+ * (vbt_cuda_fabric_{add,mul}_impl(a, b, compute_device, require_fabric, use_copy_fallback),
+ * src/vbt/cuda/fabric_elementwise.cu:820-1042, :1052-1115).
+ *   same device            the ordinary op there                          *mode = FK_LOCAL
+ *   two devices, P2P       compute_device (one of the two; owns `out`) reads the remote operand
+ *                          in place with loads over NVLink                *mode = FK_PEER_LOAD
+ *   two devices, no P2P    use_copy_fallback != 0 and require_fabric == 0: the remote operand
+ *                          (contiguous) is copied into `scratch` (numel * itemsize bytes on
+ *                          compute_device) and the op runs locally       *mode = FK_COPY_FALLBACK
+ *                          otherwise RUNTIME_ERROR "[Fabric] ...: peer access not available ..."
+ * use_copy_fallback == 2 takes the copy path even when P2P exists (the reference's dry-run
+ * mode), for comparing the two.  Errors carry the reference's "[Fabric] " prefix. */
+VBT_B200_API vbt_b200_status vbt_b200_fabric_binary(int32_t op, const vbt_b200_tensor* out,
+                                       const vbt_b200_tensor* a, const vbt_b200_tensor* b,
+                                       int32_t compute_device, int32_t require_fabric,
+                                       int32_t use_copy_fallback, void* scratch, size_t scratch_bytes,
+                                       int32_t* mode_out, void* stream);
 /* partial (F32/I64, dense, reduced shape) = local SUM/MAX/MIN of the shard; BF16/F16
  * shards accumulate and emit FP32.  Workspace as for vbt_b200_reduce.  flags:
  *   VBT_B200_PARTIAL_WS_ZEROED  the vbt_b200_reduce_zeroed_ws contract holds for `workspace`
@@ -492,6 +510,45 @@ VBT_B200_API vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_
                                         const vbt_b200_tensor* shard, const int64_t* dims,
                                         int32_t ndims, int32_t keepdim, void* workspace,
                                         size_t workspace_bytes, int32_t flags, void* stream);
+/* ---- the fused form: local reduction + cross-GPU combine + scale + cast in ONE launch ----
+ * Each rank owns an exchange buffer; ranks swap a handle to it once and map each other's
+ * buffer (IPC between processes, plain peer access between GPUs of one process).  After that
+ * vbt_b200_reduce_exchange is the whole sharded reduction: the block that finishes a tile of
+ * the local result writes it into every rank's buffer with peer stores over NVLink, raises a
+ * per-tile flag there, waits -- at most a few seconds, then it records an error instead -- for
+ * all ranks' flags, folds the `world` values in rank order (so every rank ends with the same
+ * bits), scales, casts and stores.  No collective library call and no kernel behind it.
+ * All ranks must make the same sequence of calls on a comm (as with any collective).
+ *
+ * vbt_b200_fabric_comm_create is the one place in this library that allocates device memory
+ * (cudaMalloc of 2*world*(slot_floats + 1024)*4 bytes, at set-up; freed by _destroy).
+ * slot_floats bounds the number of output elements of a fused call. */
+#define VBT_B200_FABRIC_MAX_RANKS 8
+#define VBT_B200_FABRIC_HANDLE_BYTES 128
+typedef struct vbt_b200_fabric_comm vbt_b200_fabric_comm;
+VBT_B200_API vbt_b200_status vbt_b200_fabric_comm_create(int32_t device, int32_t rank, int32_t world,
+                                            size_t slot_floats, vbt_b200_fabric_comm** out);
+/* handle_out: VBT_B200_FABRIC_HANDLE_BYTES bytes to hand to every other rank. */
+VBT_B200_API vbt_b200_status vbt_b200_fabric_comm_handle(const vbt_b200_fabric_comm* comm, void* handle_out);
+/* handles: world * VBT_B200_FABRIC_HANDLE_BYTES bytes, rank r's handle at offset r * BYTES.
+ * RUNTIME_ERROR when a peer's buffer cannot be mapped (no P2P path, IPC refused). */
+VBT_B200_API vbt_b200_status vbt_b200_fabric_comm_connect(vbt_b200_fabric_comm* comm, const void* handles);
+/* Synchronises `stream` and reports (RUNTIME_ERROR) if an exchange on this rank gave up waiting. */
+VBT_B200_API vbt_b200_status vbt_b200_fabric_comm_status(vbt_b200_fabric_comm* comm, void* stream);
+VBT_B200_API vbt_b200_status vbt_b200_fabric_comm_destroy(vbt_b200_fabric_comm* comm);
+/* out (F32/BF16/F16, dense, reduced shape) = cast(scale * combine over ranks of the local
+ * SUM/MAX/MIN of `shard`).  Supported layouts: everything reduced to one value, and reductions
+ * over the leading dim(s) of a tensor whose last kept dim is contiguous (mean(dim=0) of a
+ * row-sharded matrix); others return INVALID_ARGUMENT and the caller uses
+ * vbt_b200_reduce_partial + an all-reduce.  flags: VBT_B200_PARTIAL_WS_ZEROED.
+ * first_owner_rank: the rank whose shard holds global row 0 (its NaN-at-position-0 rule is the
+ * one that counts for MAX / MIN). */
+VBT_B200_API vbt_b200_status vbt_b200_reduce_exchange(int32_t op, const vbt_b200_tensor* out,
+                                         const vbt_b200_tensor* shard, const int64_t* dims,
+                                         int32_t ndims, int32_t keepdim, void* workspace,
+                                         size_t workspace_bytes, int32_t flags,
+                                         vbt_b200_fabric_comm* comm, int32_t first_owner_rank,
+                                         float scale, void* stream);
 /* out[i] = cast(partial[i] * scale): the "divide by the global N and cast" step of a
  * sharded mean.  partial F32 [n]; out F32/BF16/F16 [n]. */
 VBT_B200_API vbt_b200_status vbt_b200_scale_cast(void* out, int32_t out_dtype, const float* partial, int64_t n,

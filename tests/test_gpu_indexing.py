@@ -349,10 +349,9 @@ def test_bool_mask_indexing(ops, port, dtype):
 @pytest.mark.parametrize("dtype,shape,K", [(torch.float32, (5, 70001), 10000), (torch.int64, (3, 30000), 9000),
                                            (torch.bfloat16, (4, 50001), 20000), (torch.float32, (2, 8192), 8192),
                                            (torch.float32, (7, 25001), 9001), (torch.int64, (3, 12800), 8200)])
-def test_index_lastdim_long_rows_shared_memory_path(ops, port, dtype, shape, K):
-    """Rows of 32 to 100 KiB with 8192+ indices are gathered through shared memory (longer rows
-    take the plain kernel): rows whose base is not 16-byte aligned, negative (wrapped) indices,
-    a strided source view."""
+def test_index_lastdim_long_rows_few_of_them(ops, port, dtype, shape, K):
+    """Long rows, many indices, only a handful of rows (the direct kernel): rows whose base is not
+    16-byte aligned, negative (wrapped) indices, a strided source view."""
     rng = np.random.default_rng(40)
     if dtype == torch.int64:
         src = rng.integers(-10 ** 12, 10 ** 12, shape).astype(np.int64)
@@ -378,3 +377,93 @@ def test_index_lastdim_long_rows_shared_memory_path(ops, port, dtype, shape, K):
     np.testing.assert_array_equal(got_bad[:, keep], got[:, keep])
     with pytest.raises(IndexError, match=f"{len(bad[::1000])} bad indices"):
         st.check("index", shape[1])
+
+
+def _lastdim_oracle(port, src_view_np, idx):
+    """x[..., idx] for an N-d view through the 2-D oracle entry (rows = the flattened leading dims)."""
+    k0 = src_view_np.shape[-1]
+    flat = np.ascontiguousarray(src_view_np).reshape(-1, k0)
+    return port.index_lastdim(flat, idx.reshape(-1)).reshape(src_view_np.shape[:-1] + idx.shape)
+
+
+STAGED = [(torch.float32, (40, 70001), 30000),    # 3 pieces, rows not 16-byte aligned: plain staging loads
+          (torch.float32, (33, 65536), 65536),    # 3 pieces, bulk copies, index list over two blocks
+          (torch.bfloat16, (64, 50000), 40000),   # one piece, two index chunks
+          (torch.int64, (32, 12800), 9000),       # one piece of exactly 100 KiB
+          (torch.float32, (35, 16384), 16384),
+          (torch.bool, (32, 40000), 8192)]
+
+
+@pytest.mark.parametrize("dtype,shape,K", STAGED)
+def test_index_lastdim_staged_rows(ops, port, dtype, shape, K):
+    """Shapes that take the staged kernel (rows brought into shared memory by bulk copies, the
+    index list held in registers): every element size, one and several pieces per row, one and
+    several index chunks, aligned and unaligned rows, wrapped negative indices, bad indices."""
+    from vibetensor_b200 import _lib
+    rng = np.random.default_rng(44)
+    if dtype == torch.int64:
+        src = rng.integers(-10 ** 12, 10 ** 12, shape).astype(np.int64)
+    elif dtype == torch.bool:
+        src = (rng.random(shape) < 0.5).astype(np.uint8)
+    else:
+        src = oracle.to_storage(rng.standard_normal(shape, dtype=np.float32), CODE[dtype])
+    idx = rng.integers(-shape[1], shape[1], K).astype(np.int64)
+    ts, ti = from_np(src, dtype), torch.from_numpy(idx).cuda()
+    got = to_np(ops.index_lastdim(ts, ti))
+    info = _lib.last_launch_info()
+    assert (info.family, info.kernel) == (3, 7), "expected the staged last-dim kernel"
+    np.testing.assert_array_equal(got, port.index_lastdim(src, idx))
+    bad = idx.copy()
+    bad[::997] = shape[1] + 3
+    st = ops.IndexStatus(ts.device)
+    got_bad = to_np(ops.index_lastdim(ts, torch.from_numpy(bad).cuda(), status=st, eager_check=False))
+    assert not got_bad[:, ::997].any()
+    keep = np.ones(K, bool)
+    keep[::997] = False
+    np.testing.assert_array_equal(got_bad[:, keep], got[:, keep])
+    with pytest.raises(IndexError, match=f"{len(bad[::997])} bad indices"):
+        st.check("index", shape[1])
+    st.check("index", shape[1])  # the block is clear again and no staged copy timed out
+
+
+def test_index_lastdim_nd_strided_self(ops, port):
+    """The index applies to the last dim of an N-d strided base
+    (src/vbt/core/indexing_advanced_cuda.cu:2156-2177): leading dims that do not collapse onto
+    one stride, a multi-dim index tensor, both kernels, and index_put_ on the same views."""
+    from vibetensor_b200 import _lib
+    rng = np.random.default_rng(45)
+    base = rng.standard_normal((8, 10, 40000), dtype=np.float32)
+    tb = torch.from_numpy(base).cuda()
+    idx = rng.integers(-32768, 32768, (4, 5000)).astype(np.int64)
+    ti = torch.from_numpy(idx).cuda()
+    for sl in ((slice(None), slice(None, None, 2), slice(0, 32768)),      # aligned rows: bulk copies
+               (slice(None), slice(None, None, 2), slice(1, 32769))):     # rows start 4 bytes off
+        got = ops.index_lastdim(tb[sl], ti)
+        assert (_lib.last_launch_info().family, _lib.last_launch_info().kernel) == (3, 7)
+        assert got.shape == (8, 5, 4, 5000)
+        np.testing.assert_array_equal(got.cpu().numpy(), _lastdim_oracle(port, base[sl], idx))
+    # small N-d shapes on the direct kernel: permuted leading dims, rank 1, rank 4
+    small = rng.standard_normal((3, 4, 5, 50), dtype=np.float32)
+    tsm = torch.from_numpy(small).cuda()
+    i2 = rng.integers(-50, 50, (7, 3)).astype(np.int64)
+    ti2 = torch.from_numpy(i2).cuda()
+    for view_np, view_t in ((small, tsm), (small.transpose(1, 0, 2, 3), tsm.permute(1, 0, 2, 3)),
+                            (small[:, ::2, 1:4], tsm[:, ::2, 1:4]), (small[0, 0, 0], tsm[0, 0, 0]),
+                            (small.transpose(0, 1, 3, 2)[..., :4], tsm.permute(0, 1, 3, 2)[..., :4])):
+        k0 = view_np.shape[-1]
+        ii = np.mod(i2, k0) - (k0 if k0 > 4 else 0) * (i2 < 0)
+        got = ops.index_lastdim(view_t, torch.from_numpy(ii).cuda())
+        assert _lib.last_launch_info().kernel == 6
+        np.testing.assert_array_equal(got.cpu().numpy(), _lastdim_oracle(port, view_np, ii))
+    # index_put_ through a permuted 3-D view, accumulate with duplicates (int64: exact)
+    self_np = rng.integers(-5, 5, (4, 6, 30)).astype(np.int64)
+    t = torch.from_numpy(self_np.copy()).cuda()
+    view_t, view_np = t.permute(1, 0, 2), self_np.transpose(1, 0, 2)
+    ip = rng.integers(-30, 30, 77).astype(np.int64)
+    vals = rng.integers(-9, 10, (6, 4, 77)).astype(np.int64)
+    ops.index_put_lastdim_(view_t, torch.from_numpy(ip).cuda(), torch.from_numpy(vals).cuda(), accumulate=True)
+    want = np.ascontiguousarray(view_np).reshape(24, 30)
+    port.index_put_lastdim(want, ip, vals.reshape(24, 77), oracle.I64, True)
+    np.testing.assert_array_equal(view_t.cpu().numpy(), want.reshape(6, 4, 30))
+    with pytest.raises(ValueError, match="0-d"):
+        ops.index_lastdim(torch.zeros((), device="cuda"), ti2)

@@ -20,6 +20,7 @@ _TORCH_TO_CODE = {
     torch.float16: F16, torch.bfloat16: BF16, torch.uint8: BOOL,
 }
 MAX_NDIM = 25
+FABRIC_HANDLE_BYTES = 128
 
 
 class LaunchInfo(ctypes.Structure):
@@ -87,6 +88,14 @@ SIGNATURES = {
     "vbt_b200_enable_peer_access": (_i32, [_i32, _i32]),
     "vbt_b200_reduce_partial": (_i32, [_i32, _P, _P, _i64p, _i32, _i32, _vp, ctypes.c_size_t, _i32, _vp]),
     "vbt_b200_scale_cast": (_i32, [_vp, _i32, _vp, _i64, ctypes.c_float, _vp]),
+    "vbt_b200_fabric_binary": (_i32, [_i32, _P, _P, _P, _i32, _i32, _i32, _vp, ctypes.c_size_t, _i32p, _vp]),
+    "vbt_b200_fabric_comm_create": (_i32, [_i32, _i32, _i32, ctypes.c_size_t, ctypes.POINTER(_vp)]),
+    "vbt_b200_fabric_comm_handle": (_i32, [_vp, _vp]),
+    "vbt_b200_fabric_comm_connect": (_i32, [_vp, _vp]),
+    "vbt_b200_fabric_comm_status": (_i32, [_vp, _vp]),
+    "vbt_b200_fabric_comm_destroy": (_i32, [_vp]),
+    "vbt_b200_reduce_exchange": (_i32, [_i32, _P, _P, _i64p, _i32, _i32, _vp, ctypes.c_size_t, _i32, _vp, _i32,
+                                        ctypes.c_float, _vp]),
     "vbt_b200_last_launch_info": (_i32, [ctypes.POINTER(LaunchInfo)]),
     "vbt_b200_reset_last_launch_info": (None, []),
     "vbt_b200_launch_counts": (_i32, [ctypes.POINTER(ctypes.c_uint64), _i32]),

@@ -684,28 +684,43 @@ __global__ void __launch_bounds__(kThreads) lastdim_kernel(const __grid_constant
 constexpr int kStThreads = 1024;
 static __device__ unsigned vb_index_fault;  // a bounded wait on a staged copy gave up
 
-template <class E, int EPT>
+// PACK: the row has at most 65536 elements, so two index values share one register and a thread
+// holds EPT = 64 entries in 32 registers (entries to skip are marked in a 64-bit mask instead of
+// by a sentinel value, since every 16-bit value is a valid position then).
+template <class E, int EPT, bool PACK>
 __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __grid_constant__ LastDimParams p,
                                                                        const int piece, const int npieces,
                                                                        const int use_bulk) {
+  static_assert(!PACK || EPT == 64, "packed entries: 64 per thread");
   extern __shared__ __align__(128) unsigned char st_raw[];
   __shared__ __align__(8) uint64_t bars[2];
   const int t = threadIdx.x;
   const size_t stage_bytes = (static_cast<size_t>(piece) * sizeof(E) + 127) / 128 * 128;
   E* const tile0 = reinterpret_cast<E*>(st_raw);
   E* const tile1 = reinterpret_cast<E*>(st_raw + stage_bytes);
-  // this block's index entries; an entry that must be skipped holds 0xffffffff, which lies in no piece
+  // this block's index entries; unpacked form: an entry to skip holds 0xffffffff, which lies in no piece
   const int64_t kc0 = static_cast<int64_t>(blockIdx.y) * (kStThreads * EPT);
-  uint32_t v[EPT];
-  uint32_t bad = 0;
+  constexpr int NV = PACK ? EPT / 2 : EPT;
+  uint32_t v[NV];
+  // PACK: entries that take no part (index out of range, or position past the end of the list);
+  // unpacked: only the out-of-range ones (the sentinel covers the rest)
+  uint64_t dead = 0;
 #pragma unroll
   for (int j = 0; j < EPT; ++j) {
     const int64_t k = kc0 + static_cast<int64_t>(j) * kStThreads + t;
-    v[j] = 0xffffffffu;
+    uint32_t val = 0xffffffffu;
     if (k < p.K) {
       int64_t x = p.idx.get(k);
-      if (normalize(x, p.K0, p.policy, p.status, blockIdx.x == 0)) v[j] = static_cast<uint32_t>(x);
-      else bad |= 1u << j;
+      if (normalize(x, p.K0, p.policy, p.status, blockIdx.x == 0)) val = static_cast<uint32_t>(x);
+      else dead |= 1ull << j;
+    } else if (PACK) {
+      dead |= 1ull << j;
+    }
+    if constexpr (PACK) {
+      if (j & 1) v[j >> 1] |= (val & 0xffffu) << 16;
+      else v[j >> 1] = val & 0xffffu;
+    } else {
+      v[j] = val;
     }
   }
   if (use_bulk && t == 0) {
@@ -714,55 +729,74 @@ __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __g
     mbar_init_fence();
   }
   __syncthreads();
-  const int64_t nrows = (p.B - blockIdx.x + gridDim.x - 1) / gridDim.x;
-  const int64_t iters = nrows * npieces;
-  auto where = [&](int64_t it, int64_t& b, int& q, uint32_t& c0, uint32_t& n) {
-    const int64_t ri = it / npieces;
-    q = static_cast<int>(it - ri * npieces);
-    b = blockIdx.x + ri * gridDim.x;
-    c0 = static_cast<uint32_t>(q) * static_cast<uint32_t>(piece);
-    const int64_t left = p.K0 - static_cast<int64_t>(c0);
-    n = static_cast<uint32_t>(left < piece ? left : piece);
+  const uint32_t upiece = static_cast<uint32_t>(piece);
+  const uint32_t k0 = static_cast<uint32_t>(p.K0);
+  // (row, piece) pairs in the order this block visits them; `nb, nq` run one pair ahead
+  auto advance = [&](uint32_t& bb, int& qq) {
+    if (++qq == npieces) {
+      qq = 0;
+      bb += gridDim.x;
+    }
   };
-  auto issue = [&](int64_t it) {  // thread 0 only; the stage's previous readers are past a barrier
-    int64_t b; int q; uint32_t c0, n;
-    where(it, b, q, c0, n);
-    const E* src = reinterpret_cast<const E*>(p.self) + p.rows.offset(static_cast<uint32_t>(b)) + c0;
+  auto issue = [&](uint32_t bb, int qq, int stage) {  // thread 0 only; the stage's previous readers are past a barrier
+    const uint32_t c0 = static_cast<uint32_t>(qq) * upiece;
+    const uint32_t n = min(upiece, k0 - c0);
+    const E* src = reinterpret_cast<const E*>(p.self) + p.rows.offset(bb) + c0;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     const uint32_t bytes = n * static_cast<uint32_t>(sizeof(E));
-    mbar_arrive_expect_tx(&bars[it & 1], bytes);
-    bulk_copy_g2s((it & 1) ? tile1 : tile0, src, bytes, &bars[it & 1]);
+    mbar_arrive_expect_tx(&bars[stage], bytes);
+    bulk_copy_g2s(stage ? tile1 : tile0, src, bytes, &bars[stage]);
   };
-  if (use_bulk && t == 0 && iters > 0) issue(0);
-  for (int64_t it = 0; it < iters; ++it) {
-    int64_t b; int q; uint32_t c0, n;
-    where(it, b, q, c0, n);
-    E* const tl = (it & 1) ? tile1 : tile0;
+  uint32_t b = blockIdx.x, nb = blockIdx.x;  // B < 2^31 (checked by the host)
+  int q = 0, nq = 0;
+  if (use_bulk && t == 0 && nb < p.B) issue(nb, nq, 0);
+  advance(nb, nq);
+  for (uint32_t it = 0; b < p.B; ++it) {
+    const int stage = static_cast<int>(it & 1u);
+    const uint32_t c0 = static_cast<uint32_t>(q) * upiece;
+    const uint32_t n = min(upiece, k0 - c0);
+    E* const tl = stage ? tile1 : tile0;
     if (use_bulk) {
-      const bool ok = mbar_wait_bounded(&bars[it & 1], static_cast<uint32_t>(it >> 1) & 1u);
+      const bool ok = mbar_wait_bounded(&bars[stage], (it >> 1) & 1u);
       if (__syncthreads_or(!ok)) {
         // give up: note the fault, let a copy that may still be in flight land, and leave
         if (t == 0) {
           atomicExch(&vb_index_fault, 1u);
-          mbar_wait_bounded(&bars[it & 1], static_cast<uint32_t>(it >> 1) & 1u);
+          mbar_wait_bounded(&bars[stage], (it >> 1) & 1u);
         }
         __syncthreads();
         return;
       }
-      if (t == 0 && it + 1 < iters) issue(it + 1);
+      if (t == 0 && nb < p.B) issue(nb, nq, stage ^ 1);
     } else {
       __syncthreads();  // readers of the previous piece are done
-      const E* src = reinterpret_cast<const E*>(p.self) + p.rows.offset(static_cast<uint32_t>(b)) + c0;
+      const E* src = reinterpret_cast<const E*>(p.self) + p.rows.offset(b) + c0;
       for (uint32_t i = t; i < n; i += kStThreads) tl[i] = src[i];
       __syncthreads();
     }
-    E* out = reinterpret_cast<E*>(p.other) + b * p.K + kc0 + t;
+    advance(nb, nq);
+    E* out = reinterpret_cast<E*>(p.other) + static_cast<int64_t>(b) * p.K + kc0 + t;
+    if (dead == 0) {
 #pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-      const uint32_t d = v[j] - c0;
-      if (d < n) out[static_cast<int64_t>(j) * kStThreads] = tl[d];
-      else if (q == 0 && ((bad >> j) & 1u)) out[static_cast<int64_t>(j) * kStThreads] = E(0);
+      for (int j = 0; j < EPT; ++j) {
+        uint32_t d;
+        if constexpr (PACK) d = ((j & 1) ? (v[j >> 1] >> 16) : (v[j >> 1] & 0xffffu)) - c0;
+        else d = v[j] - c0;
+        if (d < n) out[static_cast<int64_t>(j) * kStThreads] = tl[d];
+      }
+    } else {  // rare: this thread holds an entry that is out of range (or, packed, past the end)
+#pragma unroll
+      for (int j = 0; j < EPT; ++j) {
+        uint32_t d;
+        if constexpr (PACK) d = ((j & 1) ? (v[j >> 1] >> 16) : (v[j >> 1] & 0xffffu)) - c0;
+        else d = v[j] - c0;
+        const bool is_dead = (dead >> j) & 1ull;
+        if (!is_dead && d < n) out[static_cast<int64_t>(j) * kStThreads] = tl[d];
+        else if (is_dead && q == 0 && kc0 + static_cast<int64_t>(j) * kStThreads + t < p.K)
+          out[static_cast<int64_t>(j) * kStThreads] = E(0);  // a bad index: the gathered value is zero
+      }
     }
+    advance(b, q);
   }
 }
 
@@ -1002,7 +1036,7 @@ vbt_b200_status scatter_add_rows_sorted(const char* name, const vbt_b200_tensor*
   return VBT_B200_OK;
 }
 
-template <class E, int EPT>
+template <class E, int EPT, bool PACK>
 vbt_b200_status launch_staged_ept(const LastDimParams& p, int piece, int npieces, int use_bulk, dim3 grid,
                                   size_t smem, cudaStream_t s) {
   // the opt-in to more than 48 KiB of dynamic shared memory is per function and per device
@@ -1013,21 +1047,22 @@ vbt_b200_status launch_staged_ept(const LastDimParams& p, int piece, int npieces
   {
     std::lock_guard<std::mutex> lk(mu);
     if (dev < 0 || dev >= 64 || !done[dev]) {
-      VB_CUDA(cudaFuncSetAttribute(lastdim_staged_kernel<E, EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      VB_CUDA(cudaFuncSetAttribute(lastdim_staged_kernel<E, EPT, PACK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    220 * 1024));
       if (dev >= 0 && dev < 64) done[dev] = true;
     }
   }
-  lastdim_staged_kernel<E, EPT><<<grid, kStThreads, smem, s>>>(p, piece, npieces, use_bulk);
+  lastdim_staged_kernel<E, EPT, PACK><<<grid, kStThreads, smem, s>>>(p, piece, npieces, use_bulk);
   return VBT_B200_OK;
 }
 template <class E>
 vbt_b200_status launch_staged(const LastDimParams& p, int ept, int piece, int npieces, int use_bulk, dim3 grid,
                               size_t smem, cudaStream_t s) {
   switch (ept) {
-    case 8: return launch_staged_ept<E, 8>(p, piece, npieces, use_bulk, grid, smem, s);
-    case 16: return launch_staged_ept<E, 16>(p, piece, npieces, use_bulk, grid, smem, s);
-    default: return launch_staged_ept<E, 32>(p, piece, npieces, use_bulk, grid, smem, s);
+    case 8: return launch_staged_ept<E, 8, false>(p, piece, npieces, use_bulk, grid, smem, s);
+    case 16: return launch_staged_ept<E, 16, false>(p, piece, npieces, use_bulk, grid, smem, s);
+    case 64: return launch_staged_ept<E, 64, true>(p, piece, npieces, use_bulk, grid, smem, s);
+    default: return launch_staged_ept<E, 32, false>(p, piece, npieces, use_bulk, grid, smem, s);
   }
 }
 
@@ -1085,7 +1120,9 @@ vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt
   // Long rows and many indices: serve the gather from shared memory.  Staging reads the whole
   // row once per K-chunk; the direct kernel pays a 32-byte sector per element.
   const int64_t row_bytes = p.K0 * p.es;
-  const int ept = K <= 8 * kStThreads ? 8 : (K <= 16 * kStThreads ? 16 : 32);
+  // 64 packed 16-bit entries per thread when the row is short enough for them and the index
+  // list would not fit one block's registers otherwise
+  const int ept = K <= 8 * kStThreads ? 8 : (K <= 16 * kStThreads ? 16 : (K <= 32 * kStThreads || p.K0 > 65536 ? 32 : 64));
   const int64_t nchunks = (K + int64_t{kStThreads} * ept - 1) / (int64_t{kStThreads} * ept);
   if (mode == 0 && p.sk == 1 && K >= 4096 && B >= 32 && row_bytes >= 32 * 1024 && p.K0 <= 0x7fffffff &&
       nchunks * row_bytes * 2 <= K * 32 && nchunks <= 65535) {

@@ -5,18 +5,23 @@
 // select_indices_from_u8_flags_i64) or, by default, a D2H copy of the whole mask, a host scan
 // and an H2D copy of the indices (src/vbt/core/indexing_advanced_cuda.cu:2191-2429).  Here:
 // three small launches on the caller's stream and no host pass over the mask --
-//   1. per-tile true counts (a tile = 4096 mask bytes),
+//   1. per-tile true counts (a tile = 16384 mask bytes, four 16-byte loads per thread); every
+//      thread also leaves each load's 16 flags as a 16-bit word in the workspace,
 //   2. one block turns the counts into exclusive offsets and writes the total,
-//   3. every tile writes the positions of its true bytes at offset + rank, in mask order.
-// The mask is read twice (2 bytes per element) and 8 bytes are written per true element.
+//   3. every tile reads its flag words back and writes the positions of the set bits at
+//      offset + rank, in mask order.
+// The mask itself is read once; the flag words add 1/8 byte per element written and read back,
+// and 8 bytes are written per true element.  No block waits on another.
 #include "common.cuh"
 
 namespace vb {
 namespace {
 
 constexpr int kMsThreads = 256;
-constexpr int kMsItems = 16;                       // mask bytes per thread
-constexpr int kMsTile = kMsThreads * kMsItems;     // 4096
+constexpr int kMsItems = 16;                       // mask bytes per thread and sub-tile (one 16-byte load)
+constexpr int kMsSub = 4;                          // sub-tiles a block walks
+constexpr int kMsSubTile = kMsThreads * kMsItems;  // 4096 mask bytes
+constexpr int kMsTile = kMsSubTile * kMsSub;       // 16384 mask bytes per block
 
 struct MaskParams {
   const uint8_t* mask;
@@ -47,11 +52,20 @@ __device__ __forceinline__ uint32_t load_flags(const MaskParams& p, int64_t firs
 }
 
 __global__ void __launch_bounds__(kMsThreads) mask_count_kernel(const __grid_constant__ MaskParams p,
-                                                                unsigned* tile_counts) {
+                                                                unsigned* tile_counts, uint16_t* flag_words) {
   __shared__ unsigned red[kMsThreads / 32];
   const int t = threadIdx.x;
-  const int64_t first = static_cast<int64_t>(blockIdx.x) * kMsTile + static_cast<int64_t>(t) * kMsItems;
-  unsigned c = __popc(load_flags(p, first));
+  const int64_t tile_first = static_cast<int64_t>(blockIdx.x) * kMsTile;
+  uint32_t bits[kMsSub];
+#pragma unroll
+  for (int q = 0; q < kMsSub; ++q)  // the loads of all sub-tiles are in flight together
+    bits[q] = load_flags(p, tile_first + q * kMsSubTile + static_cast<int64_t>(t) * kMsItems);
+  unsigned c = 0;
+#pragma unroll
+  for (int q = 0; q < kMsSub; ++q) {
+    flag_words[(static_cast<int64_t>(blockIdx.x) * kMsSub + q) * kMsThreads + t] = static_cast<uint16_t>(bits[q]);
+    c += __popc(bits[q]);
+  }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
   if ((t & 31) == 0) red[t >> 5] = c;
@@ -104,31 +118,53 @@ __global__ void __launch_bounds__(1024) mask_scan_kernel(const unsigned* tile_co
   if (t == 0) *count_out = carry_s;
 }
 
-__global__ void __launch_bounds__(kMsThreads) mask_select_kernel(const __grid_constant__ MaskParams p,
+__global__ void __launch_bounds__(kMsThreads) mask_select_kernel(const uint16_t* flag_words,
                                                                  const unsigned long long* tile_offsets,
                                                                  int64_t* out, int64_t capacity) {
-  __shared__ unsigned warp_tot[kMsThreads / 32];
+  __shared__ unsigned warp_tot[kMsSub][kMsThreads / 32];
+  __shared__ uint16_t pos[kMsTile];  // tile-relative positions of the set bits, in mask order
   const int t = threadIdx.x, lane = t & 31, w = t >> 5;
-  const int64_t first = static_cast<int64_t>(blockIdx.x) * kMsTile + static_cast<int64_t>(t) * kMsItems;
-  uint32_t bits = load_flags(p, first);
-  const unsigned c = __popc(bits);
-  unsigned x = c;
+  uint32_t bits[kMsSub];
+  unsigned c[kMsSub], x[kMsSub];
 #pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const unsigned y = __shfl_up_sync(0xffffffffu, x, d);
-    if (lane >= d) x += y;
+  for (int q = 0; q < kMsSub; ++q)
+    bits[q] = flag_words[(static_cast<int64_t>(blockIdx.x) * kMsSub + q) * kMsThreads + t];
+#pragma unroll
+  for (int q = 0; q < kMsSub; ++q) {
+    c[q] = __popc(bits[q]);
+    x[q] = c[q];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const unsigned y = __shfl_up_sync(0xffffffffu, x[q], d);
+      if (lane >= d) x[q] += y;
+    }
+    if (lane == 31) warp_tot[q][w] = x[q];
   }
-  if (lane == 31) warp_tot[w] = x;
   __syncthreads();
-  unsigned before = x - c;
-  for (int ww = 0; ww < w; ++ww) before += warp_tot[ww];
-  int64_t o = static_cast<int64_t>(tile_offsets[blockIdx.x]) + before;
-  while (bits) {
-    const int k = __ffs(bits) - 1;
-    bits &= bits - 1;
-    if (o < capacity) out[o] = first + k;
-    ++o;
+  // rank of this thread's first set bit: earlier sub-tiles, earlier warps of the sub-tile, earlier lanes
+  unsigned total = 0;
+#pragma unroll
+  for (int q = 0; q < kMsSub; ++q) {
+    unsigned before = total + x[q] - c[q];
+#pragma unroll
+    for (int ww = 0; ww < kMsThreads / 32; ++ww) {
+      if (ww < w) before += warp_tot[q][ww];
+      total += warp_tot[q][ww];
+    }
+    unsigned o = before;
+    uint32_t bq = bits[q];
+    while (bq) {
+      const int k = __ffs(bq) - 1;
+      bq &= bq - 1;
+      pos[o++] = static_cast<uint16_t>(q * kMsSubTile + t * kMsItems + k);
+    }
   }
+  __syncthreads();
+  // coalesced 8-byte stores: consecutive threads write consecutive output slots
+  const int64_t tile_first = static_cast<int64_t>(blockIdx.x) * kMsTile;
+  const int64_t base = static_cast<int64_t>(tile_offsets[blockIdx.x]);
+  for (unsigned i = t; i < total; i += kMsThreads)
+    if (base + i < capacity) out[base + i] = tile_first + pos[i];
 }
 
 }  // namespace
@@ -140,8 +176,8 @@ vbt_b200_status vbt_b200_mask_select_workspace_bytes(int64_t n, size_t* bytes) {
   using namespace vb;
   VB_ARG(bytes != nullptr && n >= 0, "mask_select: bad argument");
   const int64_t ntiles = (n + kMsTile - 1) / kMsTile;
-  // counts (u32, padded to 8 bytes) then offsets (u64)
-  *bytes = static_cast<size_t>((ntiles * 4 + 7) / 8 * 8 + ntiles * 8);
+  // counts (u32, padded to 8 bytes), offsets (u64), flag words (u16 per 16 mask bytes)
+  *bytes = static_cast<size_t>((ntiles * 4 + 7) / 8 * 8 + ntiles * 8 + ntiles * kMsSub * kMsThreads * 2);
   return VBT_B200_OK;
 }
 
@@ -175,17 +211,20 @@ vbt_b200_status vbt_b200_mask_select(const vbt_b200_tensor* mask, int64_t* out_i
   unsigned* counts = static_cast<unsigned*>(workspace);
   unsigned long long* offsets =
       reinterpret_cast<unsigned long long*>(static_cast<char*>(workspace) + (ntiles * 4 + 7) / 8 * 8);
+  uint16_t* flag_words = reinterpret_cast<uint16_t*>(reinterpret_cast<char*>(offsets) + ntiles * 8);
   MaskParams p{};
   p.mask = base; p.n = n; p.stride = stride;
   p.vec = (stride == 1 && reinterpret_cast<uintptr_t>(base) % 16 == 0) ? 1 : 0;
-  mask_count_kernel<<<static_cast<unsigned>(ntiles), kMsThreads, 0, s>>>(p, counts);
+  mask_count_kernel<<<static_cast<unsigned>(ntiles), kMsThreads, 0, s>>>(p, counts, flag_words);
   VB_LAUNCH_CHECK();
   mask_scan_kernel<<<1, 1024, 0, s>>>(counts, offsets, ntiles, reinterpret_cast<unsigned long long*>(count_out));
   VB_LAUNCH_CHECK();
   if (capacity > 0) {
-    mask_select_kernel<<<static_cast<unsigned>(ntiles), kMsThreads, 0, s>>>(p, offsets, out_indices, capacity);
+    mask_select_kernel<<<static_cast<unsigned>(ntiles), kMsThreads, 0, s>>>(flag_words, offsets, out_indices, capacity);
     VB_LAUNCH_CHECK();
   }
+  note_launch(VBT_B200_FAMILY_INDEX, VBT_B200_IK_MASK_SELECT, dim3(static_cast<unsigned>(ntiles)), dim3(kMsThreads), 16,
+              1, 0, capacity > 0 ? 3 : 2, n, n, need, s);
   return VBT_B200_OK;
 }
 

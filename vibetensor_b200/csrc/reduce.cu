@@ -49,6 +49,11 @@ constexpr int kRowU = VB_ROW_U;
 #ifndef VB_ROW_BLOCKS_PER_SM
 #define VB_ROW_BLOCKS_PER_SM 4
 #endif
+// 1 = the blocks of a slice each read one contiguous run instead of sweeping it together
+// (kept for A/B measurements of the two assignments; the library is built with 0)
+#ifndef VB_ROW_CONTIGUOUS
+#define VB_ROW_CONTIGUOUS 0
+#endif
 
 // ------------------------------------------------------------------------------------
 // reducers
@@ -177,6 +182,29 @@ __device__ __forceinline__ typename R::acc_t block_reduce(typename R::acc_t a, t
 // ------------------------------------------------------------------------------------
 enum { OP_SUM = 0, OP_MEAN, OP_MAX, OP_MIN, OP_PROD, OP_ARGMAX, OP_ARGMIN };
 
+// Cross-GPU combine of the local results (sharded reductions, one process per GPU).  The block
+// that holds a tile's final local values writes them into slot [rank] of EVERY rank's exchange
+// buffer with plain peer stores over NVLink, publishes a per-tile flag holding the call's epoch
+// on every rank, waits (bounded) until all ranks' flags for the tile show that epoch in its
+// own buffer, and folds the `world` values in rank order -- the same order on every rank, so
+// all ranks end with bit-identical results -- before scaling, casting and storing.  Buffers
+// alternate between two halves by the epoch's parity, so a rank that is already one call ahead
+// never overwrites values a slower rank is still reading.  world == 0: no exchange.
+constexpr int kXchgMaxRanks = VBT_B200_FABRIC_MAX_RANKS;
+constexpr int kXchgTiles = 1024;                             // flags per rank and half
+constexpr unsigned long long kXchgTimeoutNs = 5000000000ull;  // a peer that never arrives: give up after 5 s
+struct Xchg {
+  int world;
+  int rank;
+  int owner;        // rank whose shard holds global position 0 (the NaN rule of max / min)
+  unsigned epoch;
+  int slot_floats;  // floats per rank in a slot area
+  float scale;      // applied to the folded value (1 / global count for a mean)
+  float* slots[kXchgMaxRanks];     // rank r's slot area of this call's half: [world][slot_floats]
+  unsigned* flags[kXchgMaxRanks];  // rank r's flag area of this call's half: [world][kXchgTiles]
+  unsigned* status;                // this rank's error word
+};
+
 struct OutSpec {
   void* out;        // values (may be null for arg ops)
   int64_t* out_idx; // indices (arg ops)
@@ -185,6 +213,7 @@ struct OutSpec {
   float inv_count_n;  // reduce count as float, for MEAN
   int nan_first;      // MAX / MIN: a NaN at position 0 of the slice wins (off for the shards of a
                       // sharded reduction that do not hold the global position 0)
+  Xchg x;
 };
 
 __device__ __forceinline__ void store_value(const OutSpec& o, int64_t i, float v) {
@@ -220,6 +249,67 @@ __device__ __forceinline__ void finalize(const OutSpec& o, int64_t i, typename R
     store_value(o, i, acc);
   }
 }
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Every thread of the block that holds the final LOCAL values of `tile` calls this; `has` marks
+// the threads that own one (value v, slot e of the tile's vals_per_tile, output element out_i).
+// first: the thread's slice element 0 (for the owner rank's NaN rule).
+template <class R>
+__device__ void exchange_finalize(const OutSpec& o, int tile, int vals_per_tile, int e, bool has, float v,
+                                  int64_t out_i, float first) {
+  __shared__ int all_arrived;
+  const Xchg& x = o.x;
+  const int slot = tile * vals_per_tile + e;
+  if (has) {
+    if ((o.op == OP_MAX || o.op == OP_MIN) && o.nan_first && first != first) v = first;
+    for (int r = 0; r < x.world; ++r) x.slots[r][x.rank * x.slot_floats + slot] = v;
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < x.world; ++r) st_release_sys(x.flags[r] + x.rank * kXchgTiles + tile, x.epoch);
+    bool ok = true;
+    const unsigned long long t0 = global_timer_ns();
+    for (int r = 0; r < x.world && ok; ++r) {
+      const unsigned* f = x.flags[x.rank] + r * kXchgTiles + tile;
+      while (ld_acquire_sys(f) != x.epoch) {
+        if (global_timer_ns() - t0 > kXchgTimeoutNs) {
+          ok = false;
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+    if (!ok) atomicExch(x.status, 1u);  // the host reads this word; the output stays unwritten
+    all_arrived = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!all_arrived || !has) return;
+  const float* mine = x.slots[x.rank];
+  float acc = R::init();
+  for (int r = 0; r < x.world; ++r) acc = R::combine(acc, __ldcg(mine + r * x.slot_floats + slot));
+  if (o.op == OP_MAX || o.op == OP_MIN) {
+    const float fo = __ldcg(mine + x.owner * x.slot_floats + slot);
+    if (fo != fo) acc = fo;  // only the owner of global position 0 can have published a NaN
+  }
+  store_value(o, out_i, acc * x.scale);
+}
+
+template <class R>
+constexpr bool kCanExchange = !R::kIndexed && std::is_same_v<typename R::acc_t, float>;
 
 // ------------------------------------------------------------------------------------
 // ROW kernels
@@ -290,9 +380,18 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
 #pragma unroll
   for (int u = 0; u < U; ++u) acc[u] = R::init();
   const int64_t nvec = p.n / V;
+#if VB_ROW_CONTIGUOUS
+  // measurement build only: each block reads one contiguous run of the slice
+  const int64_t per = ((nvec + p.splits - 1) / p.splits + U * kThreads - 1) / (U * kThreads) * (U * kThreads);
+  const int64_t end = min(nvec, (static_cast<int64_t>(split) + 1) * per);
+  const int64_t sweep = U * kThreads;
+  int64_t i = static_cast<int64_t>(split) * per + threadIdx.x;
+#else
+  const int64_t end = nvec;
   const int64_t sweep = static_cast<int64_t>(p.splits) * (U * kThreads);
   int64_t i = static_cast<int64_t>(split) * (U * kThreads) + threadIdx.x;
-  for (; i + (U - 1) * kThreads < nvec; i += sweep) {
+#endif
+  for (; i + (U - 1) * kThreads < end; i += sweep) {
     A w[U][V];
 #pragma unroll
     for (int u = 0; u < U; ++u) load_widen<T, V>(x + (i + u * kThreads) * V, w[u]);
@@ -307,7 +406,7 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     const int64_t iv = i + u * kThreads;
-    if (iv < nvec) {
+    if (iv < end) {
       A w[V];
       load_widen<T, V>(x + iv * V, w);
       const idx_t base = static_cast<idx_t>(iv) * V;
@@ -325,6 +424,12 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
     for (int u = 0; u + d < U; u += 2 * d) acc[u] = R::combine(acc[u], acc[u + d]);
   acc_t a = block_reduce<R>(acc[0], smem);
   if (p.splits == 1) {
+    if constexpr (kCanExchange<R>) {
+      if (p.o.x.world > 0) {
+        exchange_finalize<R>(p.o, static_cast<int>(row), 1, 0, threadIdx.x == 0, a, row, widen(x[0]));
+        return;
+      }
+    }
     if (threadIdx.x == 0) finalize<R, A>(p.o, row, a, widen(x[0]));
     return;
   }
@@ -344,10 +449,14 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
   for (int s = threadIdx.x; s < p.splits; s += kThreads) f = R::combine(f, ld_cg(part + s));
   __syncthreads();
   f = block_reduce<R>(f, smem);
-  if (threadIdx.x == 0) {
-    p.ws_counters[row] = 0u;  // every block of this slice has drawn its ticket: leave the counter as found
-    finalize<R, A>(p.o, row, f, widen(x[0]));
+  if (threadIdx.x == 0) p.ws_counters[row] = 0u;  // every block of this slice has drawn its ticket: leave the counter as found
+  if constexpr (kCanExchange<R>) {
+    if (p.o.x.world > 0) {
+      exchange_finalize<R>(p.o, static_cast<int>(row), 1, 0, threadIdx.x == 0, f, row, widen(x[0]));
+      return;
+    }
   }
+  if (threadIdx.x == 0) finalize<R, A>(p.o, row, f, widen(x[0]));
 }
 
 // ------------------------------------------------------------------------------------
@@ -418,6 +527,13 @@ __global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ C
   const int64_t out_i = a * p.B + gcol;
   const T* first_p = static_cast<const T*>(p.x) + p.outer.offset(static_cast<uint32_t>(a)) + gcol;
   if (p.splits == 1) {
+    if constexpr (kCanExchange<R>) {
+      if (p.o.x.world > 0) {
+        exchange_finalize<R>(p.o, static_cast<int>(a * p.ctiles + ct), ncols, c, owner, colacc, out_i,
+                             owner ? widen(*first_p) : 0.f);
+        return;
+      }
+    }
     if (owner) finalize<R, A>(p.o, out_i, colacc, widen(*first_p));
     return;
   }
@@ -434,10 +550,10 @@ __global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ C
   if (!is_last) return;
   __threadfence();
   if (threadIdx.x == 0) p.ws_counters[a * p.ctiles + ct] = 0u;  // all tickets drawn: leave the counter as found
+  acc_t f = R::init();
   if (owner) {
     // chunk order, eight independent loads in flight at a time (a loop of load-then-combine
     // would pay one L2 round trip per chunk)
-    acc_t f = R::init();
     for (int s0 = 0; s0 < p.splits; s0 += 8) {
       acc_t t[8];
 #pragma unroll
@@ -446,8 +562,15 @@ __global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ C
 #pragma unroll
       for (int u = 0; u < 8; ++u) f = R::combine(f, t[u]);
     }
-    finalize<R, A>(p.o, out_i, f, widen(*first_p));
   }
+  if constexpr (kCanExchange<R>) {
+    if (p.o.x.world > 0) {
+      exchange_finalize<R>(p.o, static_cast<int>(a * p.ctiles + ct), ncols, c, owner, f, out_i,
+                           owner ? widen(*first_p) : 0.f);
+      return;
+    }
+  }
+  if (owner) finalize<R, A>(p.o, out_i, f, widen(*first_p));
 }
 
 // COL through a thread-block cluster: the blocks that split R for one column tile form a
@@ -915,7 +1038,7 @@ size_t plan_workspace_bytes(const Plan& pl) {
 vbt_b200_status reduce_impl(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* out_index,
                             const vbt_b200_tensor* self, const int64_t* dims, int32_t ndims, int32_t keepdim,
                             void* workspace, size_t workspace_bytes, bool tickets_zeroed, bool nan_first,
-                            void* stream) {
+                            void* stream, const Xchg* xchg = nullptr) {
   VB_ARG(op >= 0 && op < VBT_B200_R_COUNT, "reduce: unknown op code");
   const char* name = op_name(op);
   VB_TRY(validate_data(self, name));
@@ -926,6 +1049,19 @@ vbt_b200_status reduce_impl(int32_t op, const vbt_b200_tensor* out, const vbt_b2
   DeviceScope scope(anchor);
   Plan pl;
   VB_TRY(make_plan(op, *self, dims, ndims, keepdim != 0, sm_count(scope.device()), &pl));
+  if (xchg != nullptr) {
+    // the exchange lives in the ticket kernels' epilogue: no cluster fold, and only the layouts
+    // whose final values sit in one block per tile
+    pl.cluster = 0;
+    const bool row_ok = pl.shape == kRowBlock && pl.nout == 1;
+    const bool col_ok = pl.shape == kCol;
+    VB_ARG(row_ok || col_ok, std::string(name) + ": this layout has no fused exchange (use the partial + all-reduce path)");
+    if (col_ok) {
+      const int64_t tiles = (pl.nout / pl.ksize[pl.nk - 1]) * pl.ctiles;
+      VB_ARG(tiles <= kXchgTiles && tiles * 32 * pl.V <= xchg->slot_floats,
+             std::string(name) + ": too many outputs for the exchange buffer");
+    }
+  }
   VB_TRY(check_out_shape(pl, out, name));
   VB_TRY(check_out_shape(pl, out_index, name));
   if (pl.shape == kNoOutput) return VBT_B200_OK;
@@ -959,6 +1095,7 @@ vbt_b200_status reduce_impl(int32_t op, const vbt_b200_tensor* out, const vbt_b2
   o.op = op;
   o.inv_count_n = static_cast<float>(pl.nred);
   o.nan_first = nan_first ? 1 : 0;
+  if (xchg != nullptr) o.x = *xchg;
   switch (self->dtype) {
     case VBT_B200_F32: return launch_op<float>(op, pl, *self, o, workspace, tickets_zeroed, s);
     case VBT_B200_F16: return launch_op<__half>(op, pl, *self, o, workspace, tickets_zeroed, s);
@@ -1025,6 +1162,213 @@ vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_tensor* parti
          "reduce_partial: partials are float32 or int64");
   return reduce_impl(op, partial, nullptr, shard, dims, ndims, keepdim, workspace, workspace_bytes,
                      (flags & VBT_B200_PARTIAL_WS_ZEROED) != 0, (flags & VBT_B200_PARTIAL_NOT_FIRST) == 0, stream);
+}
+
+}  // extern "C"
+
+// =====================================================================================
+// Fabric exchange: the buffers behind the fused sharded reductions (one process per GPU, or
+// several GPUs in one process), and vbt_b200_reduce_exchange.
+//
+// Every rank owns one device buffer: two halves (call parity) of [world][slot_floats] floats,
+// two halves of [world][kXchgTiles] flags, and an error word.  Ranks exchange a handle to it
+// (an IPC memory handle plus, for ranks of the same process, the raw pointer) and map each
+// other's buffer; after that a sharded reduction is ONE kernel launch per rank -- no
+// collective library call, no scale-and-cast launch behind it.
+// =====================================================================================
+#include <unistd.h>
+
+struct vbt_b200_fabric_comm {
+  int device{0}, rank{0}, world{0};
+  size_t slot_floats{0};
+  char* local{nullptr};                          // this rank's buffer (cudaMalloc)
+  char* base[VBT_B200_FABRIC_MAX_RANKS]{};       // every rank's buffer as seen from this device
+  bool opened[VBT_B200_FABRIC_MAX_RANKS]{};      // mapped through cudaIpcOpenMemHandle
+  bool connected{false};
+  unsigned epoch{0};
+};
+
+namespace vb {
+namespace {
+struct CommHandle {  // what ranks exchange; VBT_B200_FABRIC_HANDLE_BYTES covers it
+  cudaIpcMemHandle_t ipc;
+  int64_t pid;
+  uint64_t ptr;
+  int32_t device;
+  int32_t world;
+  uint64_t slot_floats;
+};
+static_assert(sizeof(CommHandle) <= VBT_B200_FABRIC_HANDLE_BYTES, "handle size");
+
+size_t comm_slot_bytes(const vbt_b200_fabric_comm& c) { return static_cast<size_t>(c.world) * c.slot_floats * 4; }
+size_t comm_flag_bytes(const vbt_b200_fabric_comm& c) { return static_cast<size_t>(c.world) * kXchgTiles * 4; }
+size_t comm_total_bytes(const vbt_b200_fabric_comm& c) { return 2 * comm_slot_bytes(c) + 2 * comm_flag_bytes(c) + 256; }
+}  // namespace
+}  // namespace vb
+
+extern "C" {
+
+vbt_b200_status vbt_b200_fabric_comm_create(int32_t device, int32_t rank, int32_t world, size_t slot_floats,
+                                            vbt_b200_fabric_comm** out) {
+  using namespace vb;
+  VB_ARG(out != nullptr, "fabric_comm_create: null argument");
+  VB_ARG(world >= 1 && world <= VBT_B200_FABRIC_MAX_RANKS, "[Fabric] comm: world size must be 1..8");
+  VB_ARG(rank >= 0 && rank < world, "[Fabric] comm: rank out of range");
+  VB_ARG(slot_floats >= 1 && slot_floats <= (size_t{1} << 24), "[Fabric] comm: slot size out of range");
+  int prev = 0;
+  VB_CUDA(cudaGetDevice(&prev));
+  VB_CUDA(cudaSetDevice(device));
+  auto* c = new vbt_b200_fabric_comm();
+  c->device = device; c->rank = rank; c->world = world; c->slot_floats = slot_floats;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, comm_total_bytes(*c));
+  if (e == cudaSuccess) e = cudaMemset(p, 0, comm_total_bytes(*c));
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaSetDevice(prev);
+  if (e != cudaSuccess) {
+    if (p) cudaFree(p);
+    delete c;
+    return fail(VBT_B200_CUDA_ERROR, std::string("[Fabric] comm: allocating the exchange buffer: ") + cudaGetErrorString(e));
+  }
+  c->local = static_cast<char*>(p);
+  c->base[rank] = c->local;
+  *out = c;
+  return VBT_B200_OK;
+}
+
+vbt_b200_status vbt_b200_fabric_comm_handle(const vbt_b200_fabric_comm* c, void* handle_out) {
+  using namespace vb;
+  VB_ARG(c != nullptr && handle_out != nullptr, "fabric_comm_handle: null argument");
+  CommHandle h{};
+  int prev = 0;
+  VB_CUDA(cudaGetDevice(&prev));
+  VB_CUDA(cudaSetDevice(c->device));
+  const cudaError_t e = cudaIpcGetMemHandle(&h.ipc, c->local);
+  cudaSetDevice(prev);
+  if (e != cudaSuccess) cudaGetLastError();  // same-process peers need only the pointer below
+  h.pid = static_cast<int64_t>(getpid());
+  h.ptr = reinterpret_cast<uint64_t>(c->local);
+  h.device = c->device;
+  h.world = c->world;
+  h.slot_floats = c->slot_floats;
+  std::memset(handle_out, 0, VBT_B200_FABRIC_HANDLE_BYTES);
+  std::memcpy(handle_out, &h, sizeof(h));
+  return VBT_B200_OK;
+}
+
+vbt_b200_status vbt_b200_fabric_comm_connect(vbt_b200_fabric_comm* c, const void* handles) {
+  using namespace vb;
+  VB_ARG(c != nullptr && handles != nullptr, "fabric_comm_connect: null argument");
+  VB_ARG(!c->connected, "[Fabric] comm: already connected");
+  int prev = 0;
+  VB_CUDA(cudaGetDevice(&prev));
+  VB_CUDA(cudaSetDevice(c->device));
+  vbt_b200_status st = VBT_B200_OK;
+  for (int r = 0; r < c->world && st == VBT_B200_OK; ++r) {
+    if (r == c->rank) continue;
+    CommHandle h{};
+    std::memcpy(&h, static_cast<const char*>(handles) + static_cast<size_t>(r) * VBT_B200_FABRIC_HANDLE_BYTES, sizeof(h));
+    if (h.world != c->world || h.slot_floats != c->slot_floats) {
+      st = fail(VBT_B200_INVALID_ARGUMENT, "[Fabric] comm: ranks disagree on world size or slot size");
+      break;
+    }
+    if (h.pid == static_cast<int64_t>(getpid())) {
+      // another GPU of this process: plain peer access to its buffer
+      int can = 0;
+      cudaError_t e = cudaDeviceCanAccessPeer(&can, c->device, h.device);
+      if (e == cudaSuccess && can) {
+        e = cudaDeviceEnablePeerAccess(h.device, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); e = cudaSuccess; }
+      }
+      if (e != cudaSuccess || !can) {
+        cudaGetLastError();
+        st = fail(VBT_B200_RUNTIME_ERROR, "[Fabric] comm: device " + std::to_string(c->device) +
+                                              " cannot access device " + std::to_string(h.device) + " memory (no P2P path)");
+        break;
+      }
+      c->base[r] = reinterpret_cast<char*>(h.ptr);
+    } else {
+      void* p = nullptr;
+      const cudaError_t e = cudaIpcOpenMemHandle(&p, h.ipc, cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        st = fail(VBT_B200_RUNTIME_ERROR, std::string("[Fabric] comm: mapping rank ") + std::to_string(r) +
+                                              "'s exchange buffer: " + cudaGetErrorString(e));
+        break;
+      }
+      c->base[r] = static_cast<char*>(p);
+      c->opened[r] = true;
+    }
+  }
+  cudaSetDevice(prev);
+  if (st == VBT_B200_OK) c->connected = true;
+  return st;
+}
+
+vbt_b200_status vbt_b200_fabric_comm_status(vbt_b200_fabric_comm* c, void* stream) {
+  using namespace vb;
+  VB_ARG(c != nullptr, "fabric_comm_status: null argument");
+  int prev = 0;
+  VB_CUDA(cudaGetDevice(&prev));
+  VB_CUDA(cudaSetDevice(c->device));
+  unsigned word = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* status = c->local + 2 * comm_slot_bytes(*c) + 2 * comm_flag_bytes(*c);
+  cudaError_t e = cudaMemcpyAsync(&word, status, 4, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess && word != 0) e = cudaMemsetAsync(status, 0, 4, s);
+  cudaSetDevice(prev);
+  VB_CUDA(e);
+  VB_REQUIRE(word == 0, VBT_B200_RUNTIME_ERROR,
+             "[Fabric] exchange: a rank did not arrive within the time limit; the results of that call are missing");
+  return VBT_B200_OK;
+}
+
+vbt_b200_status vbt_b200_fabric_comm_destroy(vbt_b200_fabric_comm* c) {
+  if (c == nullptr) return VBT_B200_OK;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(c->device);
+  for (int r = 0; r < c->world; ++r)
+    if (c->opened[r]) cudaIpcCloseMemHandle(c->base[r]);
+  if (c->local) cudaFree(c->local);
+  cudaSetDevice(prev);
+  cudaGetLastError();
+  delete c;
+  return VBT_B200_OK;
+}
+
+vbt_b200_status vbt_b200_reduce_exchange(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* shard,
+                                         const int64_t* dims, int32_t ndims, int32_t keepdim, void* workspace,
+                                         size_t workspace_bytes, int32_t flags, vbt_b200_fabric_comm* comm,
+                                         int32_t first_owner_rank, float scale, void* stream) {
+  using namespace vb;
+  VB_ARG(op == VBT_B200_R_SUM || op == VBT_B200_R_MAX || op == VBT_B200_R_MIN,
+         "reduce_exchange: only sum / max / min combine across shards");
+  VB_ARG(out && shard && comm, "reduce_exchange: null argument");
+  VB_ARG(comm->connected || comm->world == 1, "[Fabric] comm: not connected");
+  VB_ARG(is_float_dtype(shard->dtype) && is_float_dtype(out->dtype),
+         "reduce_exchange: floating shards and outputs only");
+  VB_ARG(first_owner_rank >= 0 && first_owner_rank < comm->world, "reduce_exchange: owner rank out of range");
+  VB_ARG(device_of(out->data) == comm->device, "[Fabric] comm: the output lives on another device than the exchange buffer");
+  Xchg x{};
+  x.world = comm->world;
+  x.rank = comm->rank;
+  x.owner = first_owner_rank;
+  x.epoch = comm->epoch + 1;
+  x.slot_floats = static_cast<int>(comm->slot_floats);
+  x.scale = scale;
+  const size_t half = x.epoch & 1u;
+  for (int r = 0; r < comm->world; ++r) {
+    x.slots[r] = reinterpret_cast<float*>(comm->base[r] + half * comm_slot_bytes(*comm));
+    x.flags[r] = reinterpret_cast<unsigned*>(comm->base[r] + 2 * comm_slot_bytes(*comm) + half * comm_flag_bytes(*comm));
+  }
+  x.status = reinterpret_cast<unsigned*>(comm->local + 2 * comm_slot_bytes(*comm) + 2 * comm_flag_bytes(*comm));
+  const vbt_b200_status st =
+      reduce_impl(op, out, nullptr, shard, dims, ndims, keepdim, workspace, workspace_bytes,
+                  (flags & VBT_B200_PARTIAL_WS_ZEROED) != 0, comm->rank == first_owner_rank, stream, &x);
+  if (st == VBT_B200_OK) comm->epoch = x.epoch;  // the epoch only advances with a launch: ranks stay in step
+  return st;
 }
 
 }  // extern "C"

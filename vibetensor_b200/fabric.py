@@ -295,6 +295,66 @@ def reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False, local_o
     return partial
 
 
+class FabricComm:
+    """Exchange buffers of the fused sharded reductions (``vbt_b200_reduce_exchange``): every
+    rank allocates one small device buffer, the ranks swap handles to them with one
+    ``all_gather_object`` and map each other's buffer.  Built collectively, once per mesh."""
+
+    _by_mesh: dict = {}
+
+    def __init__(self, mesh: FabricMesh, device: torch.device, slot_floats: int = 1 << 16):
+        import ctypes
+        from . import _lib
+        self._lib, self._ct = _lib, ctypes
+        self.mesh, self.device = mesh, device
+        L = _lib.lib()
+        self.ptr = ctypes.c_void_p()
+        ok, err = True, ""
+        try:
+            _lib.check(L.vbt_b200_fabric_comm_create(device.index, mesh.rank, mesh.world_size, slot_floats,
+                                                     ctypes.byref(self.ptr)))
+            mine = ctypes.create_string_buffer(_lib.FABRIC_HANDLE_BYTES)
+            _lib.check(L.vbt_b200_fabric_comm_handle(self.ptr, mine))
+            payload = mine.raw
+        except Exception as ex:  # every rank still has to take part in the exchange below
+            ok, err, payload = False, str(ex), b""
+        gathered = [None] * mesh.world_size
+        dist.all_gather_object(gathered, (ok, payload), group=mesh.group)
+        if ok and all(g[0] for g in gathered):
+            try:
+                _lib.check(L.vbt_b200_fabric_comm_connect(self.ptr, b"".join(g[1] for g in gathered)))
+            except Exception as ex:
+                ok, err = False, str(ex)
+        else:
+            ok = False
+        flags = [None] * mesh.world_size
+        dist.all_gather_object(flags, ok, group=mesh.group)
+        self.ok = all(flags)
+        self.error = err
+        if not self.ok:
+            self.close()
+
+    @classmethod
+    def get(cls, mesh: FabricMesh, device: torch.device) -> Optional["FabricComm"]:
+        """The mesh's comm (created on first use; every rank must call this together), or None
+        when some rank could not map its peers -- then the all-reduce path is used."""
+        key = (mesh.devices, id(mesh.group), device.index)
+        if key not in cls._by_mesh:
+            comm = cls(mesh, device)
+            cls._by_mesh[key] = comm if comm.ok else None
+        return cls._by_mesh[key]
+
+    def check(self) -> None:
+        """Synchronises the current stream; raises if an exchange on this rank timed out."""
+        self._lib.check(self._lib.lib().vbt_b200_fabric_comm_status(self.ptr, self._lib.stream_ptr(
+            torch.empty(0, device=self.device))))
+
+    def close(self) -> None:
+        if self.ptr:
+            self._lib.lib().vbt_b200_fabric_comm_destroy(self.ptr)
+            self.ptr = self._ct.c_void_p()
+
+
 class PreparedReduce:
     """A sharded reduction set up once and run many times: the reduction plan, tensor
     descriptors, partial / result buffers and workspace are built here, so a ``run()`` is the
@@ -303,7 +363,10 @@ class PreparedReduce:
     time (it is overwritten by the next run).  The shard's storage must stay where it is; its
     contents may change between runs.  CUDA tensors only."""
 
-    def __init__(self, name: str, ft: FabricTensor, dim=None, keepdim: bool = False):
+    def __init__(self, name: str, ft: FabricTensor, dim=None, keepdim: bool = False, fused: Optional[bool] = None):
+        """fused=None: one launch that reduces, exchanges over NVLink peer memory, scales and casts
+        (vbt_b200_reduce_exchange) whenever every rank supports it for this layout, else the
+        partial + all-reduce (+ scale-and-cast) form; False forces the latter."""
         from . import ops
         self.name = name
         self.ft = ft
@@ -338,9 +401,72 @@ class PreparedReduce:
             scale = (1.0 / count if count else float("nan")) if name == "mean" else 1.0
             self._scale = ops.PreparedScaleCast(src, scale, x.dtype)
         self.out = self._scale.out if self._scale is not None else src
+        self.fused = None
+        if fused is not False and self.mesh.world_size > 1 and x.dtype.is_floating_point:
+            self._try_fused(local, x, dims, keepdim, first)
 
-    def run(self) -> torch.Tensor:
+    def _try_fused(self, local, x, dims, keepdim, first):
+        """Sets self.fused to a bound launch when ALL ranks can take the fused path."""
+        import ctypes
+        from . import _lib, ops
+        comm = FabricComm.get(self.mesh, x.device)
+        ok = comm is not None
+        launch = None
+        if ok:
+            try:
+                out = torch.empty(self.out.shape, dtype=x.dtype, device=x.device)
+                dx, do, da = _lib.desc(x), _lib.desc(out), _lib.i64_array(dims)
+                op = ops.REDUCE.index(local)
+                nbytes = _lib.lib().vbt_b200_reduce_workspace_bytes(op, dx.ref, da, len(dims))
+                ws = ops._reduce_workspace(nbytes, x.device)
+                wp = ctypes.c_void_p(ws.data_ptr()) if ws is not None else None
+                scale = 1.0
+                if self.name == "mean":
+                    count = 1
+                    for d in dims:
+                        count *= self.ft.placement.global_shape[d]
+                    scale = 1.0 / count if count else float("nan")
+                args = (op, do.ref, dx.ref, da, len(dims), int(keepdim), wp, nbytes, 1, comm.ptr,
+                        _first_owner(self.ft.placement), scale)
+                fn = _lib.lib().vbt_b200_reduce_exchange
+
+                def launch():
+                    _lib.check(fn(*args, _lib.stream_ptr(out)))
+                    return out
+                launch.keep = (dx, do, da, ws, out)
+                launch()                      # a first call validates the layout (and runs the exchange once)
+                torch.cuda.current_stream(x.device).synchronize()
+                comm.check()
+            except Exception:
+                ok = False
+        agreed = [None] * self.mesh.world_size
+        dist.all_gather_object(agreed, ok, group=self.mesh.group)
+        if all(agreed):
+            self.fused = launch
+            self.out = launch.keep[4]
+            self.comm = comm
+        elif any(agreed):
+            # some ranks ran the trial exchange and some did not: their call counts differ now, so
+            # this mesh stays on the all-reduce path from here on
+            for key, val in list(FabricComm._by_mesh.items()):
+                if val is comm:
+                    FabricComm._by_mesh[key] = None
+
+    def run(self, kernel_events=None) -> torch.Tensor:
+        """kernel_events: an optional (start, end) pair of CUDA events recorded around the local
+        reduction launch alone (for callers that time the kernel apart from the exchange)."""
+        if self.fused is not None:
+            if kernel_events is not None:
+                kernel_events[0].record()
+            out = self.fused()
+            if kernel_events is not None:
+                kernel_events[1].record()
+            return out
+        if kernel_events is not None:
+            kernel_events[0].record()
         partial = self._local.run()
+        if kernel_events is not None:
+            kernel_events[1].record()
         if self.mesh.world_size > 1:
             if self._gathered is not None:
                 dist.all_gather_into_tensor(self._gathered, partial.view(-1), group=self.mesh.group)
@@ -352,8 +478,9 @@ class PreparedReduce:
         return self.out
 
 
-def prepare_reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False) -> PreparedReduce:
-    return PreparedReduce(name, ft, dim, keepdim)
+def prepare_reduce(name: str, ft: FabricTensor, dim=None, keepdim: bool = False,
+                   fused: Optional[bool] = None) -> PreparedReduce:
+    return PreparedReduce(name, ft, dim, keepdim, fused)
 
 
 def sum(ft, dim=None, keepdim=False, local_ops=None):  # noqa: A001

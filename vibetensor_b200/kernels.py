@@ -125,9 +125,6 @@ def log_softmax_backward(dy: torch.Tensor, log_y: torch.Tensor) -> torch.Tensor:
     return _softmax_backward(dy, log_y, True)
 
 
-_bwd_ws: dict = {}  # (device index) -> float32 scratch for the dgamma partial rows
-
-
 def rmsnorm_backward(grad_output: torch.Tensor, x: torch.Tensor, inv_rms: torch.Tensor,
                      gamma: Optional[torch.Tensor] = None):
     """Returns (grad_input, grad_gamma); grad_gamma is None when gamma is None, float32
@@ -157,11 +154,9 @@ def rmsnorm_backward(grad_output: torch.Tensor, x: torch.Tensor, inv_rms: torch.
         need = ctypes.c_size_t()
         check(lib().vbt_b200_rmsnorm_backward_workspace_bytes(rows, cols, dtype_code(x.dtype), x.device.index,
                                                               ctypes.byref(need)))
-        ws = _bwd_ws.get(x.device.index)
-        if ws is None or ws.numel() * 4 < need.value:
-            ws = torch.empty((max(need.value // 4, 1),), dtype=torch.float32, device=x.device)
-            _bwd_ws[x.device.index] = ws
-        ws_bytes = ws.numel() * 4
+        # the dgamma partial rows live in the general scratch buffer of this (device, stream)
+        ws = _ops._workspace(max(need.value, 16), x.device)
+        ws_bytes = ws.numel()
     if cols == 0:
         return dx, dgamma
     check(lib().vbt_b200_rmsnorm_backward(

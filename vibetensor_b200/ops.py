@@ -482,10 +482,10 @@ def index_lastdim(src: torch.Tensor, idx: torch.Tensor, status=None, eager_check
     return o
 
 
-def mask_to_indices(mask: torch.Tensor) -> torch.Tensor:
-    """Ascending int64 positions of the true elements of a 1-D bool mask, computed on the
-    device.  Reads the count back (one 8-byte D2H copy and a stream synchronise, as the
-    reference's bool-mask path does) to size the result."""
+def mask_select(mask: torch.Tensor):
+    """Device part of bool-mask indexing, no host round trip: returns (indices, count) where
+    ``indices`` is an int64 buffer as long as the mask whose first ``count`` entries are the
+    ascending positions of the true elements and ``count`` is a 1-element int64 device tensor."""
     _require_cuda(mask)
     if mask.dtype != torch.bool:
         raise ValueError("index: mask must be a bool tensor")
@@ -494,12 +494,20 @@ def mask_to_indices(mask: torch.Tensor) -> torch.Tensor:
     n = mask.numel()
     need = ctypes.c_size_t()
     check(lib().vbt_b200_mask_select_workspace_bytes(n, ctypes.byref(need)))
-    ws = torch.empty((max(need.value // 8, 1),), dtype=torch.int64, device=mask.device)
+    ws = _workspace(max(need.value, 8), mask.device)
     idx = torch.empty((n,), dtype=torch.int64, device=mask.device)
     count = torch.empty((1,), dtype=torch.int64, device=mask.device)
     dm = desc(mask)
     check(lib().vbt_b200_mask_select(dm.ref, ctypes.c_void_p(idx.data_ptr()), n, ctypes.c_void_p(count.data_ptr()),
-                                     ctypes.c_void_p(ws.data_ptr()), ws.numel() * 8, stream_ptr(mask)))
+                                     ctypes.c_void_p(ws.data_ptr()), ws.numel(), stream_ptr(idx)))
+    return idx, count
+
+
+def mask_to_indices(mask: torch.Tensor) -> torch.Tensor:
+    """Ascending int64 positions of the true elements of a 1-D bool mask, computed on the
+    device.  Reads the count back (one 8-byte D2H copy and a stream synchronise, as the
+    reference's bool-mask path does) to size the result."""
+    idx, count = mask_select(mask)
     return idx[: int(count.item())]
 
 
@@ -565,6 +573,39 @@ def embedding_backward(grad_out: torch.Tensor, indices: torch.Tensor, num_weight
     if own:
         st.check("vt::embedding", num_weights)
     return gw
+
+
+FABRIC_MODES = {1: "peer_load", 2: "copy_fallback", 3: "local"}
+
+
+def fabric_binary(name: str, a: torch.Tensor, b: torch.Tensor, compute_device: Optional[int] = None,
+                  require_fabric: bool = False, use_copy_fallback=True, out: Optional[torch.Tensor] = None):
+    """vt::fabric_add / vt::fabric_mul (src/vbt/cuda/fabric_elementwise.cu:820-1042): a and b
+    of equal shape and dtype on one or two GPUs of this process; the result lives on
+    ``compute_device`` (default: a's device).  Returns (out, mode) with mode one of
+    "local", "peer_load" (the remote operand is read in place over NVLink) or "copy_fallback"
+    (it is copied to the compute device first).  ``use_copy_fallback="always"`` takes the copy
+    path even when peer access exists."""
+    for t in (a, b):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise RuntimeError(f"[Fabric] vt::fabric_{name}: expects CUDA tensors")
+    dev = a.device.index if compute_device is None else int(compute_device)
+    if out is None:
+        out = torch.empty(a.shape, dtype=a.dtype, device=torch.device("cuda", dev))
+    policy = 2 if use_copy_fallback == "always" else int(bool(use_copy_fallback))
+    scratch = None
+    if a.device != b.device and policy:
+        scratch = torch.empty(max(a.numel() * a.element_size(), 16), dtype=torch.uint8, device=out.device)
+    mode = ctypes.c_int32()
+    do, da, db = desc(out), desc(a), desc(b)
+    with torch.cuda.device(out.device):
+        check(lib().vbt_b200_fabric_binary(BINARY.index(name), do.ref, da.ref, db.ref, dev, int(require_fabric), policy,
+                                           ctypes.c_void_p(scratch.data_ptr()) if scratch is not None else None,
+                                           scratch.numel() if scratch is not None else 0, ctypes.byref(mode),
+                                           stream_ptr(out)))
+    if mode.value == 1 and a.device != b.device:
+        _peer_enabled.add((dev, (b if a.device.index == dev else a).device.index))
+    return out, FABRIC_MODES.get(mode.value, "none")
 
 
 def scale_cast(partial: torch.Tensor, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
