@@ -1,7 +1,9 @@
 #!/usr/bin/env bash
-# Puts an UNMODIFIED copy of the reference's Python kernel package (vibe_kernels: the Triton
-# softmax / RMSNorm / gather / scatter_add kernels this repository's CUDA kernels replace) under
-# baseline/_ref/, which is git-ignored and travels to the GPU machine with the working tree.
+# Puts an UNMODIFIED copy of the parts of the reference's Python kernel package that this
+# repository's CUDA kernels replace (vibe_kernels: its package file, common/, and the Triton
+# softmax / RMSNorm / gather / scatter_add sub-packages -- the other kernel families are not on
+# this path and are left out) under baseline/_ref/, which is git-ignored and travels to the GPU
+# machine with the working tree on single-GPU runs.
 # It is used for two things only: generating golden vectors from the reference's own kernels
 # (tests/golden/make_golden_gpu.py) and timing them beside ours (bench.py's per-op table).
 # The package is pure Python; its compiled companion (vibetensor._C) cannot be built here and
@@ -16,6 +18,10 @@ if [ -z "$REF" ] || [ ! -d "$REF/vibe_kernels" ]; then
 fi
 rm -rf "$HERE/_ref/vibe_kernels"
 mkdir -p "$HERE/_ref"
-cp -r "$REF/vibe_kernels" "$HERE/_ref/vibe_kernels"
+mkdir -p "$HERE/_ref/vibe_kernels"
+cp "$REF/vibe_kernels/__init__.py" "$HERE/_ref/vibe_kernels/"
+for sub in common softmax rmsnorm indexing; do
+  cp -r "$REF/vibe_kernels/$sub" "$HERE/_ref/vibe_kernels/$sub"
+done
 find "$HERE/_ref/vibe_kernels" -name "__pycache__" -type d -prune -exec rm -rf {} +
 echo "installed $HERE/_ref/vibe_kernels"

@@ -386,19 +386,21 @@ def _lastdim_oracle(port, src_view_np, idx):
     return port.index_lastdim(flat, idx.reshape(-1)).reshape(src_view_np.shape[:-1] + idx.shape)
 
 
-STAGED = [(torch.float32, (40, 70001), 30000),    # 3 pieces, rows not 16-byte aligned: plain staging loads
-          (torch.float32, (33, 65536), 65536),    # 3 pieces, bulk copies, index list over two blocks
+STAGED = [(torch.float32, (40, 60001), 32768),    # 4 pieces, rows not 16-byte aligned: plain staging loads, 2 index chunks
+          (torch.float32, (33, 65536), 65536),    # 4 pieces, bulk copies, index list over four blocks
           (torch.bfloat16, (64, 50000), 40000),   # one piece, two index chunks
-          (torch.int64, (32, 12800), 9000),       # one piece of exactly 100 KiB
+          (torch.int64, (32, 12800), 8000),       # one piece of exactly 100 KiB
           (torch.float32, (35, 16384), 16384),
+          (torch.float32, (34, 16384), 16380),    # output rows not 16-byte aligned: scalar tile write-out
           (torch.bool, (32, 40000), 8192)]
 
 
 @pytest.mark.parametrize("dtype,shape,K", STAGED)
 def test_index_lastdim_staged_rows(ops, port, dtype, shape, K):
     """Shapes that take the staged kernel (rows brought into shared memory by bulk copies, the
-    index list held in registers): every element size, one and several pieces per row, one and
-    several index chunks, aligned and unaligned rows, wrapped negative indices, bad indices."""
+    index list held in registers, outputs collected in a shared-memory tile): every element
+    size, one and several pieces per row, one and several index chunks, aligned and unaligned
+    rows and outputs, wrapped negative indices, bad indices."""
     from vibetensor_b200 import _lib
     rng = np.random.default_rng(44)
     if dtype == torch.int64:

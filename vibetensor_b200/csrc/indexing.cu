@@ -675,52 +675,40 @@ __global__ void __launch_bounds__(kThreads) lastdim_kernel(const __grid_constant
 // is read ONCE per block and kept in registers (EPT entries per thread, position
 // k = chunk start + j * blockDim + t), and the block then walks its rows: each row is brought
 // into shared memory piece by piece with bulk asynchronous copies (two stages, so the next
-// piece loads while the current one is served), and every thread serves those of its entries
-// that fall inside the piece from shared memory, where a random 4-byte read costs a few
-// cycles.  Per output element the row is read once (coalesced, at DRAM speed) and the
-// output written once; a warp's stores cover 32 consecutive positions with about 1 / pieces
-// of the lanes active.  Index lists longer than one block's registers hold are split over
-// blockIdx.y (each such block stages the rows again; they come from L2).
+// piece loads while the current one is served), every thread moves those of its entries that
+// fall inside the piece from the staged piece into an OUTPUT tile that also lives in shared
+// memory, and after the row's last piece the tile goes out with full 16-byte stores.  Global
+// memory therefore sees only whole-sector traffic: the row read once per index chunk
+// (coalesced) and every output sector written exactly once -- partial-sector writes, which
+// cost a read-modify-write under ECC, never leave the SM.  Index lists longer than one block's
+// tile are split over blockIdx.y (each such block stages the rows again; they come from L2).
 constexpr int kStThreads = 1024;
+constexpr int kStagedSmemMax = 220 * 1024;  // dynamic shared memory the staged kernel may ask for
 static __device__ unsigned vb_index_fault;  // a bounded wait on a staged copy gave up
 
-// PACK: the row has at most 65536 elements, so two index values share one register and a thread
-// holds EPT = 64 entries in 32 registers (entries to skip are marked in a 64-bit mask instead of
-// by a sentinel value, since every 16-bit value is a valid position then).
-template <class E, int EPT, bool PACK>
+template <class E, int EPT>
 __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __grid_constant__ LastDimParams p,
                                                                        const int piece, const int npieces,
                                                                        const int use_bulk) {
-  static_assert(!PACK || EPT == 64, "packed entries: 64 per thread");
   extern __shared__ __align__(128) unsigned char st_raw[];
   __shared__ __align__(8) uint64_t bars[2];
   const int t = threadIdx.x;
   const size_t stage_bytes = (static_cast<size_t>(piece) * sizeof(E) + 127) / 128 * 128;
   E* const tile0 = reinterpret_cast<E*>(st_raw);
   E* const tile1 = reinterpret_cast<E*>(st_raw + stage_bytes);
-  // this block's index entries; unpacked form: an entry to skip holds 0xffffffff, which lies in no piece
+  E* const obuf = reinterpret_cast<E*>(st_raw + 2 * stage_bytes);  // [EPT * kStThreads] output tile
+  // this block's index entries; an entry to skip holds 0xffffffff, which lies in no piece
   const int64_t kc0 = static_cast<int64_t>(blockIdx.y) * (kStThreads * EPT);
-  constexpr int NV = PACK ? EPT / 2 : EPT;
-  uint32_t v[NV];
-  // PACK: entries that take no part (index out of range, or position past the end of the list);
-  // unpacked: only the out-of-range ones (the sentinel covers the rest)
-  uint64_t dead = 0;
+  uint32_t v[EPT];
+  uint32_t bad = 0;  // positions whose index is out of range: the gathered value is zero
 #pragma unroll
   for (int j = 0; j < EPT; ++j) {
     const int64_t k = kc0 + static_cast<int64_t>(j) * kStThreads + t;
-    uint32_t val = 0xffffffffu;
+    v[j] = 0xffffffffu;
     if (k < p.K) {
       int64_t x = p.idx.get(k);
-      if (normalize(x, p.K0, p.policy, p.status, blockIdx.x == 0)) val = static_cast<uint32_t>(x);
-      else dead |= 1ull << j;
-    } else if (PACK) {
-      dead |= 1ull << j;
-    }
-    if constexpr (PACK) {
-      if (j & 1) v[j >> 1] |= (val & 0xffffu) << 16;
-      else v[j >> 1] = val & 0xffffu;
-    } else {
-      v[j] = val;
+      if (normalize(x, p.K0, p.policy, p.status, blockIdx.x == 0)) v[j] = static_cast<uint32_t>(x);
+      else bad |= 1u << j;
     }
   }
   if (use_bulk && t == 0) {
@@ -731,6 +719,10 @@ __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __g
   __syncthreads();
   const uint32_t upiece = static_cast<uint32_t>(piece);
   const uint32_t k0 = static_cast<uint32_t>(p.K0);
+  const int64_t left = p.K - kc0;
+  const uint32_t ntile = static_cast<uint32_t>(left < kStThreads * EPT ? left : kStThreads * EPT);  // outputs of this block per row
+  constexpr int VE = 16 / sizeof(E);
+  const bool vec_out = (reinterpret_cast<uintptr_t>(p.other) % 16 == 0) && (p.K % VE == 0) && (ntile % VE == 0);
   // (row, piece) pairs in the order this block visits them; `nb, nq` run one pair ahead
   auto advance = [&](uint32_t& bb, int& qq) {
     if (++qq == npieces) {
@@ -769,32 +761,29 @@ __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __g
       }
       if (t == 0 && nb < p.B) issue(nb, nq, stage ^ 1);
     } else {
-      __syncthreads();  // readers of the previous piece are done
+      __syncthreads();  // readers of the previous piece, and of the output tile, are done
       const E* src = reinterpret_cast<const E*>(p.self) + p.rows.offset(b) + c0;
       for (uint32_t i = t; i < n; i += kStThreads) tl[i] = src[i];
       __syncthreads();
     }
     advance(nb, nq);
-    E* out = reinterpret_cast<E*>(p.other) + static_cast<int64_t>(b) * p.K + kc0 + t;
-    if (dead == 0) {
 #pragma unroll
-      for (int j = 0; j < EPT; ++j) {
-        uint32_t d;
-        if constexpr (PACK) d = ((j & 1) ? (v[j >> 1] >> 16) : (v[j >> 1] & 0xffffu)) - c0;
-        else d = v[j] - c0;
-        if (d < n) out[static_cast<int64_t>(j) * kStThreads] = tl[d];
+    for (int j = 0; j < EPT; ++j) {
+      const uint32_t d = v[j] - c0;
+      if (d < n) obuf[j * kStThreads + t] = tl[d];
+      else if (q == 0 && ((bad >> j) & 1u)) obuf[j * kStThreads + t] = E(0);
+    }
+    if (q == npieces - 1) {
+      __syncthreads();  // the tile is complete
+      E* out = reinterpret_cast<E*>(p.other) + static_cast<int64_t>(b) * p.K + kc0;
+      if (vec_out) {
+        const int4* s4 = reinterpret_cast<const int4*>(obuf);
+        int4* d4 = reinterpret_cast<int4*>(out);
+        for (uint32_t i = t; i < ntile / VE; i += kStThreads) d4[i] = s4[i];
+      } else {
+        for (uint32_t i = t; i < ntile; i += kStThreads) out[i] = obuf[i];
       }
-    } else {  // rare: this thread holds an entry that is out of range (or, packed, past the end)
-#pragma unroll
-      for (int j = 0; j < EPT; ++j) {
-        uint32_t d;
-        if constexpr (PACK) d = ((j & 1) ? (v[j >> 1] >> 16) : (v[j >> 1] & 0xffffu)) - c0;
-        else d = v[j] - c0;
-        const bool is_dead = (dead >> j) & 1ull;
-        if (!is_dead && d < n) out[static_cast<int64_t>(j) * kStThreads] = tl[d];
-        else if (is_dead && q == 0 && kc0 + static_cast<int64_t>(j) * kStThreads + t < p.K)
-          out[static_cast<int64_t>(j) * kStThreads] = E(0);  // a bad index: the gathered value is zero
-      }
+      // the next writes into the tile come after the barrier at the top of the next iteration
     }
     advance(b, q);
   }
@@ -1036,7 +1025,7 @@ vbt_b200_status scatter_add_rows_sorted(const char* name, const vbt_b200_tensor*
   return VBT_B200_OK;
 }
 
-template <class E, int EPT, bool PACK>
+template <class E, int EPT>
 vbt_b200_status launch_staged_ept(const LastDimParams& p, int piece, int npieces, int use_bulk, dim3 grid,
                                   size_t smem, cudaStream_t s) {
   // the opt-in to more than 48 KiB of dynamic shared memory is per function and per device
@@ -1047,23 +1036,23 @@ vbt_b200_status launch_staged_ept(const LastDimParams& p, int piece, int npieces
   {
     std::lock_guard<std::mutex> lk(mu);
     if (dev < 0 || dev >= 64 || !done[dev]) {
-      VB_CUDA(cudaFuncSetAttribute(lastdim_staged_kernel<E, EPT, PACK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   220 * 1024));
+      VB_CUDA(cudaFuncSetAttribute(lastdim_staged_kernel<E, EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kStagedSmemMax));
       if (dev >= 0 && dev < 64) done[dev] = true;
     }
   }
-  lastdim_staged_kernel<E, EPT, PACK><<<grid, kStThreads, smem, s>>>(p, piece, npieces, use_bulk);
+  lastdim_staged_kernel<E, EPT><<<grid, kStThreads, smem, s>>>(p, piece, npieces, use_bulk);
   return VBT_B200_OK;
 }
 template <class E>
 vbt_b200_status launch_staged(const LastDimParams& p, int ept, int piece, int npieces, int use_bulk, dim3 grid,
                               size_t smem, cudaStream_t s) {
-  switch (ept) {
-    case 8: return launch_staged_ept<E, 8, false>(p, piece, npieces, use_bulk, grid, smem, s);
-    case 16: return launch_staged_ept<E, 16, false>(p, piece, npieces, use_bulk, grid, smem, s);
-    case 64: return launch_staged_ept<E, 64, true>(p, piece, npieces, use_bulk, grid, smem, s);
-    default: return launch_staged_ept<E, 32, false>(p, piece, npieces, use_bulk, grid, smem, s);
+  constexpr int kCap = sizeof(E) == 8 ? 16 : 32;  // the output tile stays <= 128 KiB
+  if constexpr (kCap >= 32) {
+    if (ept == 32) return launch_staged_ept<E, 32>(p, piece, npieces, use_bulk, grid, smem, s);
   }
+  if (ept == 16) return launch_staged_ept<E, 16>(p, piece, npieces, use_bulk, grid, smem, s);
+  return launch_staged_ept<E, 8>(p, piece, npieces, use_bulk, grid, smem, s);
 }
 
 // self: rank >= 1, any strides; the index applies to its LAST dim.  other: dense
@@ -1118,16 +1107,25 @@ vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt
   p.mode = mode;
   p.dtype = self->dtype;
   // Long rows and many indices: serve the gather from shared memory.  Staging reads the whole
-  // row once per K-chunk; the direct kernel pays a 32-byte sector per element.
+  // row once per index chunk; the direct kernel pays a 32-byte sector per element.
   const int64_t row_bytes = p.K0 * p.es;
-  // 64 packed 16-bit entries per thread when the row is short enough for them and the index
-  // list would not fit one block's registers otherwise
-  const int ept = K <= 8 * kStThreads ? 8 : (K <= 16 * kStThreads ? 16 : (K <= 32 * kStThreads || p.K0 > 65536 ? 32 : 64));
-  const int64_t nchunks = (K + int64_t{kStThreads} * ept - 1) / (int64_t{kStThreads} * ept);
+  // entries per thread: the fewest index chunks first (every chunk stages the rows again), then
+  // the smallest output tile (which leaves the most shared memory for the row pieces)
+  const int ept_cap = p.es == 8 ? 16 : 32;  // output tile of a block: <= 128 KiB
+  int ept = 8;
+  int64_t nchunks = (K + int64_t{kStThreads} * 8 - 1) / (int64_t{kStThreads} * 8);
+  for (int e = 16; e <= ept_cap; e *= 2) {
+    const int64_t c = (K + int64_t{kStThreads} * e - 1) / (int64_t{kStThreads} * e);
+    if (c < nchunks) {
+      nchunks = c;
+      ept = e;
+    }
+  }
   if (mode == 0 && p.sk == 1 && K >= 4096 && B >= 32 && row_bytes >= 32 * 1024 && p.K0 <= 0x7fffffff &&
       nchunks * row_bytes * 2 <= K * 32 && nchunks <= 65535) {
-    constexpr int64_t kStageMax = 100 * 1024;
-    const int npieces = static_cast<int>((row_bytes + kStageMax - 1) / kStageMax);
+    const size_t tile_bytes = static_cast<size_t>(ept) * kStThreads * p.es;
+    const int64_t stage_max = (kStagedSmemMax - static_cast<int64_t>(tile_bytes)) / 2 / 1024 * 1024;
+    const int npieces = static_cast<int>((row_bytes + stage_max - 1) / stage_max);
     const int64_t per = (p.K0 + npieces - 1) / npieces;
     const int piece = static_cast<int>((per + 15) / 16 * 16);  // whole 16-byte units for every element size
     const size_t stage = (static_cast<size_t>(piece) * p.es + 127) / 128 * 128;
@@ -1137,12 +1135,13 @@ vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt
     const int sms = sm_count(scope.device());
     const unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(B, sms / nchunks)));
     const dim3 grid(gx, static_cast<unsigned>(nchunks));
+    const size_t smem = 2 * stage + tile_bytes;
     vbt_b200_status st;
     switch (p.es) {
-      case 1: st = launch_staged<uint8_t>(p, ept, piece, npieces, bulk, grid, 2 * stage, s); break;
-      case 2: st = launch_staged<uint16_t>(p, ept, piece, npieces, bulk, grid, 2 * stage, s); break;
-      case 4: st = launch_staged<uint32_t>(p, ept, piece, npieces, bulk, grid, 2 * stage, s); break;
-      default: st = launch_staged<uint64_t>(p, ept, piece, npieces, bulk, grid, 2 * stage, s); break;
+      case 1: st = launch_staged<uint8_t>(p, ept, piece, npieces, bulk, grid, smem, s); break;
+      case 2: st = launch_staged<uint16_t>(p, ept, piece, npieces, bulk, grid, smem, s); break;
+      case 4: st = launch_staged<uint32_t>(p, ept, piece, npieces, bulk, grid, smem, s); break;
+      default: st = launch_staged<uint64_t>(p, ept, piece, npieces, bulk, grid, smem, s); break;
     }
     VB_TRY(st);
     VB_LAUNCH_CHECK();
