@@ -141,7 +141,8 @@ def test_gather_scatter_and_lastdim(ops):
         ops.index_put_rows_(tgt.t, idx[:V].unique(), torch.ones((idx[:V].unique().numel(), D), device="cuda"))
         tgt.check(f"scatter overwrite {V}x{D}")
     L = _lib.lib()
-    for B, K0, K in ((5, 77, 33), (40, 70001, 30000), (33, 16384, 16384), (64, 50000, 40000), (32, 40000, 8191)):
+    for B, K0, K in ((5, 77, 33), (40, 70001, 30000), (33, 16384, 16384), (64, 50000, 40000), (32, 40000, 8191),
+                     (33, 65536, 65536), (12, 100003, 50001)):
         src = torch.randn((B, K0), device="cuda", generator=g)
         idx = torch.randint(-K0, K0, (K,), device="cuda", generator=g)
         out = Guarded((B, K), torch.float32, 1)

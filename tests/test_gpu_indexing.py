@@ -392,7 +392,9 @@ STAGED = [(torch.float32, (40, 60001), 32768),    # 4 pieces, rows not 16-byte a
           (torch.int64, (32, 12800), 8000),       # one piece of exactly 100 KiB
           (torch.float32, (35, 16384), 16384),
           (torch.float32, (34, 16384), 16380),    # output rows not 16-byte aligned: scalar tile write-out
-          (torch.bool, (32, 40000), 8192)]
+          (torch.bool, (32, 40000), 8192),
+          (torch.bfloat16, (32, 200000), 100000),  # 400 KB rows: six pieces, four index chunks
+          (torch.float32, (32, 100001), 65536)]    # nine pieces, rows not 16-byte aligned (plain staging loads)
 
 
 @pytest.mark.parametrize("dtype,shape,K", STAGED)

@@ -1,6 +1,9 @@
 """Builds libvbt_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-    python -m vibetensor_b200.build [--force] [--verbose]
+    python -m vibetensor_b200.build [--force] [--verbose] [--release]
+
+--release leaves -lineinfo out (a smaller library without the source-line tables profilers use);
+objects of the two kinds are cached side by side.
 
 One nvcc process per translation unit, run in parallel; objects are cached under
 csrc/_obj and rebuilt when the source or any header is newer.
@@ -22,7 +25,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libvbt_b200.so")
 
 NVCC_FLAGS = [
-    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++20",
+    "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++20",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--default-stream", "legacy",
 ]
 
@@ -41,8 +44,10 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, release: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
+    flags = NVCC_FLAGS + ([] if release else ["-lineinfo"])
+    suffix = ".rel.o" if release else ".o"
     os.makedirs(LIB_DIR, exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     hdrs = sorted(glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) +
@@ -51,10 +56,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     jobs = []
     objs = []
     for s in srcs:
-        o = os.path.join(OBJ, os.path.basename(s)[:-3] + ".o")
+        o = os.path.join(OBJ, os.path.basename(s)[:-3] + suffix)
         objs.append(o)
         if force or _stale(o, [s] + hdrs):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = [nvcc] + flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             jobs.append(cmd)
 
     def run(cmd):
@@ -68,12 +73,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
                     sys.stderr.write(" ".join(cmd[-4:]) + "\n" + r.stdout + r.stderr + "\n")
                 if r.returncode != 0:
                     raise RuntimeError("nvcc failed for " + cmd[-3])
-    if force or jobs or _stale(LIB, objs):
+    marker = os.path.join(OBJ, "linked_release" if release else "linked_lineinfo")
+    if force or jobs or _stale(LIB, objs) or not os.path.exists(marker):
         cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
                                                       "-cudart", "static"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
+        for m in ("linked_release", "linked_lineinfo"):
+            if os.path.exists(os.path.join(OBJ, m)):
+                os.remove(os.path.join(OBJ, m))
+        open(marker, "w").close()
     return LIB
 
 
@@ -81,5 +91,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--release", action="store_true")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.release))

@@ -682,48 +682,139 @@ __global__ void __launch_bounds__(kThreads) lastdim_kernel(const __grid_constant
 // (coalesced) and every output sector written exactly once -- partial-sector writes, which
 // cost a read-modify-write under ECC, never leave the SM.  Index lists longer than one block's
 // tile are split over blockIdx.y (each such block stages the rows again; they come from L2).
+// shared-memory accesses by 32-bit shared-space address: the inner loop below is issue-bound, and
+// a generic pointer costs it an address conversion per access
+template <class E> __device__ __forceinline__ E lds(uint32_t a);
+template <> __device__ __forceinline__ uint8_t lds<uint8_t>(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+  return static_cast<uint8_t>(v);
+}
+template <> __device__ __forceinline__ uint16_t lds<uint16_t>(uint32_t a) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return v;
+}
+template <> __device__ __forceinline__ uint32_t lds<uint32_t>(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+template <> __device__ __forceinline__ uint64_t lds<uint64_t>(uint32_t a) {
+  unsigned long long v;
+  asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v) : "r"(a));
+  return static_cast<uint64_t>(v);
+}
+__device__ __forceinline__ void sts(uint32_t a, uint8_t v) {
+  asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(static_cast<uint32_t>(v)) : "memory");
+}
+__device__ __forceinline__ void sts(uint32_t a, uint16_t v) { asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "h"(v) : "memory"); }
+__device__ __forceinline__ void sts(uint32_t a, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
+__device__ __forceinline__ void sts(uint32_t a, uint64_t v) {
+  asm volatile("st.shared.u64 [%0], %1;" ::"r"(a), "l"(static_cast<unsigned long long>(v)) : "memory");
+}
+
 constexpr int kStThreads = 1024;
 constexpr int kStagedSmemMax = 220 * 1024;  // dynamic shared memory the staged kernel may ask for
 static __device__ unsigned vb_index_fault;  // a bounded wait on a staged copy gave up
 
-template <class E, int EPT>
+constexpr int kStMaxPieces = 30;
+constexpr int kStMaxStages = 4;  // row pieces in flight + the one being served
+
+// GROUPED (rows of several pieces): before the first row the block regroups its index entries by
+// the piece their source position falls in -- a counting sort through shared memory, done once
+// -- so that a warp's 32 * EPT entries are consecutive in that order and belong to one piece,
+// sometimes two.  A warp then skips, with one uniform branch, every (row, piece) step that holds
+// none of its entries: an entry is touched once per row instead of once per row and piece, which
+// is what the issue slots and the shared-memory pipe were spent on.  A regrouped entry is one
+// 32-bit word: source position in the high bits, output slot of the tile in the low KBITS.
+template <class E, int EPT, bool GROUPED>
 __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __grid_constant__ LastDimParams p,
                                                                        const int piece, const int npieces,
-                                                                       const int use_bulk) {
+                                                                       const int use_bulk, const int nstages) {
   extern __shared__ __align__(128) unsigned char st_raw[];
-  __shared__ __align__(8) uint64_t bars[2];
-  const int t = threadIdx.x;
+  __shared__ __align__(8) uint64_t bars[kStMaxStages];
+  __shared__ uint32_t bstart[kStMaxPieces + 2];  // GROUPED: first regrouped entry of every piece (+ dead, + end)
+  __shared__ uint32_t cursor[kStMaxPieces + 1];
+  constexpr int KBITS = EPT == 32 ? 15 : (EPT == 16 ? 14 : 13);  // bits of a tile slot (EPT * 1024 slots)
+  constexpr uint32_t KMASK = (1u << KBITS) - 1u;
+  constexpr uint32_t DEADV = (1u << (32 - KBITS)) - 1u;  // GROUPED: source field of an entry without a source
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
   const size_t stage_bytes = (static_cast<size_t>(piece) * sizeof(E) + 127) / 128 * 128;
-  E* const tile0 = reinterpret_cast<E*>(st_raw);
-  E* const tile1 = reinterpret_cast<E*>(st_raw + stage_bytes);
-  E* const obuf = reinterpret_cast<E*>(st_raw + 2 * stage_bytes);  // [EPT * kStThreads] output tile
-  // this block's index entries; an entry to skip holds 0xffffffff, which lies in no piece
+  E* const obuf = reinterpret_cast<E*>(st_raw + nstages * stage_bytes);  // [EPT * kStThreads] output tile
+  auto stage_ptr = [&](int st) { return reinterpret_cast<E*>(st_raw + st * stage_bytes); };
   const int64_t kc0 = static_cast<int64_t>(blockIdx.y) * (kStThreads * EPT);
+  const int64_t left = p.K - kc0;
+  const uint32_t ntile = static_cast<uint32_t>(left < kStThreads * EPT ? left : kStThreads * EPT);  // outputs of this block per row
+  const uint32_t upiece = static_cast<uint32_t>(piece);
+  const uint32_t k0 = static_cast<uint32_t>(p.K0);
+  // this block's index entries.  Plain form: source position, 0xffffffff (in no piece) to skip.
   uint32_t v[EPT];
-  uint32_t bad = 0;  // positions whose index is out of range: the gathered value is zero
+  uint32_t bad = 0;  // plain form: positions whose index is out of range (the gathered value is zero)
 #pragma unroll
   for (int j = 0; j < EPT; ++j) {
-    const int64_t k = kc0 + static_cast<int64_t>(j) * kStThreads + t;
-    v[j] = 0xffffffffu;
-    if (k < p.K) {
-      int64_t x = p.idx.get(k);
-      if (normalize(x, p.K0, p.policy, p.status, blockIdx.x == 0)) v[j] = static_cast<uint32_t>(x);
-      else bad |= 1u << j;
+    const uint32_t slot = static_cast<uint32_t>(j) * kStThreads + t;
+    v[j] = GROUPED ? ((DEADV << KBITS) | slot) : 0xffffffffu;
+    if (slot < ntile) {
+      int64_t x = p.idx.get(kc0 + slot);
+      if (normalize(x, p.K0, p.policy, p.status, blockIdx.x == 0))
+        v[j] = GROUPED ? ((static_cast<uint32_t>(x) << KBITS) | slot) : static_cast<uint32_t>(x);
+      else
+        bad |= 1u << j;
     }
   }
+  if constexpr (GROUPED) {
+    // counting sort of the block's entries by piece (dead entries -- bad index, or past the end of
+    // the list -- form one more group at the end), through the shared memory the pipeline uses later
+    uint32_t* scratch = reinterpret_cast<uint32_t*>(st_raw);
+    for (int i = t; i <= npieces; i += kStThreads) cursor[i] = 0;
+    __syncthreads();
+    auto group_of = [&](uint32_t entry) {
+      const uint32_t src = entry >> KBITS;
+      return src == DEADV ? static_cast<uint32_t>(npieces) : src / upiece;
+    };
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+      const uint32_t g = group_of(v[j]);
+      const unsigned peers = __match_any_sync(0xffffffffu, g);
+      if (lane == __ffs(peers) - 1) atomicAdd(&cursor[g], static_cast<uint32_t>(__popc(peers)));
+    }
+    __syncthreads();
+    if (t == 0) {
+      uint32_t run = 0;
+      for (int i = 0; i <= npieces; ++i) {
+        const uint32_t c = cursor[i];
+        bstart[i] = run;
+        cursor[i] = run;
+        run += c;
+      }
+      bstart[npieces + 1] = run;  // == EPT * kStThreads
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+      const uint32_t g = group_of(v[j]);
+      const unsigned peers = __match_any_sync(0xffffffffu, g);
+      const int leader = __ffs(peers) - 1;
+      uint32_t base = 0;
+      if (lane == leader) base = atomicAdd(&cursor[g], static_cast<uint32_t>(__popc(peers)));
+      base = __shfl_sync(0xffffffffu, base, leader);
+      scratch[base + __popc(peers & ((1u << lane) - 1u))] = v[j];
+    }
+    __syncthreads();
+    // a warp takes 32 * EPT consecutive regrouped entries
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) v[j] = scratch[static_cast<uint32_t>(w) * (32 * EPT) + j * 32 + lane];
+    __syncthreads();  // scratch is free again before the first row piece lands in it
+  }
   if (use_bulk && t == 0) {
-    mbar_init(&bars[0], 1);
-    mbar_init(&bars[1], 1);
+    for (int st = 0; st < nstages; ++st) mbar_init(&bars[st], 1);
     mbar_init_fence();
   }
   __syncthreads();
-  const uint32_t upiece = static_cast<uint32_t>(piece);
-  const uint32_t k0 = static_cast<uint32_t>(p.K0);
-  const int64_t left = p.K - kc0;
-  const uint32_t ntile = static_cast<uint32_t>(left < kStThreads * EPT ? left : kStThreads * EPT);  // outputs of this block per row
   constexpr int VE = 16 / sizeof(E);
   const bool vec_out = (reinterpret_cast<uintptr_t>(p.other) % 16 == 0) && (p.K % VE == 0) && (ntile % VE == 0);
-  // (row, piece) pairs in the order this block visits them; `nb, nq` run one pair ahead
+  // (row, piece) pairs in the order this block visits them; `nb, nq` run nstages - 1 pairs ahead
   auto advance = [&](uint32_t& bb, int& qq) {
     if (++qq == npieces) {
       qq = 0;
@@ -737,29 +828,34 @@ __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __g
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     const uint32_t bytes = n * static_cast<uint32_t>(sizeof(E));
     mbar_arrive_expect_tx(&bars[stage], bytes);
-    bulk_copy_g2s(stage ? tile1 : tile0, src, bytes, &bars[stage]);
+    bulk_copy_g2s(stage_ptr(stage), src, bytes, &bars[stage]);
   };
+  // GROUPED: the regrouped entries this warp holds are [wr0, wr1)
+  const uint32_t wr0 = static_cast<uint32_t>(w) * (32 * EPT), wr1 = wr0 + 32 * EPT;
   uint32_t b = blockIdx.x, nb = blockIdx.x;  // B < 2^31 (checked by the host)
   int q = 0, nq = 0;
-  if (use_bulk && t == 0 && nb < p.B) issue(nb, nq, 0);
-  advance(nb, nq);
-  for (uint32_t it = 0; b < p.B; ++it) {
-    const int stage = static_cast<int>(it & 1u);
+  for (int st = 0; st + 1 < nstages; ++st) {  // fill the pipeline
+    if (use_bulk && t == 0 && nb < p.B) issue(nb, nq, st);
+    advance(nb, nq);
+  }
+  int stage = 0, ahead = nstages - 1;  // ahead: the stage the next copy goes to (consumed in the last iteration)
+  uint32_t phase = 0;                   // parity of this stage's current use
+  for (; b < p.B;) {
     const uint32_t c0 = static_cast<uint32_t>(q) * upiece;
     const uint32_t n = min(upiece, k0 - c0);
-    E* const tl = stage ? tile1 : tile0;
+    E* const tl = stage_ptr(stage);
     if (use_bulk) {
-      const bool ok = mbar_wait_bounded(&bars[stage], (it >> 1) & 1u);
+      const bool ok = mbar_wait_bounded(&bars[stage], phase);
       if (__syncthreads_or(!ok)) {
-        // give up: note the fault, let a copy that may still be in flight land, and leave
+        // give up: note the fault, let the copies that may still be in flight land, and leave
         if (t == 0) {
           atomicExch(&vb_index_fault, 1u);
-          mbar_wait_bounded(&bars[stage], (it >> 1) & 1u);
+          mbar_wait_bounded(&bars[stage], phase);
         }
         __syncthreads();
         return;
       }
-      if (t == 0 && nb < p.B) issue(nb, nq, stage ^ 1);
+      if (t == 0 && nb < p.B) issue(nb, nq, ahead);
     } else {
       __syncthreads();  // readers of the previous piece, and of the output tile, are done
       const E* src = reinterpret_cast<const E*>(p.self) + p.rows.offset(b) + c0;
@@ -767,11 +863,35 @@ __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __g
       __syncthreads();
     }
     advance(nb, nq);
+    const uint32_t tl_s = smem_addr(tl);
+    constexpr uint32_t ES = static_cast<uint32_t>(sizeof(E));
+    if constexpr (GROUPED) {
+      const uint32_t ob_s = smem_addr(obuf);
+      if (bstart[q] < wr1 && bstart[q + 1] > wr0) {  // this warp holds entries of piece q
 #pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-      const uint32_t d = v[j] - c0;
-      if (d < n) obuf[j * kStThreads + t] = tl[d];
-      else if (q == 0 && ((bad >> j) & 1u)) obuf[j * kStThreads + t] = E(0);
+        for (int j = 0; j < EPT; ++j) {
+          const uint32_t d = (v[j] >> KBITS) - c0;
+          if (d < n) sts(ob_s + (v[j] & KMASK) * ES, lds<E>(tl_s + d * ES));
+        }
+      }
+      if (q == 0 && bstart[npieces] < wr1 && bstart[npieces + 1] > wr0) {  // ... or dead entries
+#pragma unroll
+        for (int j = 0; j < EPT; ++j)
+          if ((v[j] >> KBITS) == DEADV && (v[j] & KMASK) < ntile) sts(ob_s + (v[j] & KMASK) * ES, E(0));
+      }
+    } else {
+      // entry j of this thread lands in tile slot j * kStThreads + t
+      const uint32_t ob_s = smem_addr(obuf) + static_cast<uint32_t>(t) * ES;
+#pragma unroll
+      for (int j = 0; j < EPT; ++j) {
+        const uint32_t d = v[j] - c0;
+        if (d < n) sts(ob_s + j * kStThreads * ES, lds<E>(tl_s + d * ES));
+      }
+      if (bad != 0 && q == 0) {  // rare: an out-of-range index gathers zero
+#pragma unroll
+        for (int j = 0; j < EPT; ++j)
+          if ((bad >> j) & 1u) sts(ob_s + j * kStThreads * ES, E(0));
+      }
     }
     if (q == npieces - 1) {
       __syncthreads();  // the tile is complete
@@ -786,6 +906,11 @@ __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __g
       // the next writes into the tile come after the barrier at the top of the next iteration
     }
     advance(b, q);
+    ahead = stage;
+    if (++stage == nstages) {
+      stage = 0;
+      phase ^= 1u;
+    }
   }
 }
 
@@ -1025,8 +1150,8 @@ vbt_b200_status scatter_add_rows_sorted(const char* name, const vbt_b200_tensor*
   return VBT_B200_OK;
 }
 
-template <class E, int EPT>
-vbt_b200_status launch_staged_ept(const LastDimParams& p, int piece, int npieces, int use_bulk, dim3 grid,
+template <class E, int EPT, bool GROUPED>
+vbt_b200_status launch_staged_ept(const LastDimParams& p, int piece, int npieces, int use_bulk, int nstages, dim3 grid,
                                   size_t smem, cudaStream_t s) {
   // the opt-in to more than 48 KiB of dynamic shared memory is per function and per device
   static std::mutex mu;
@@ -1036,23 +1161,34 @@ vbt_b200_status launch_staged_ept(const LastDimParams& p, int piece, int npieces
   {
     std::lock_guard<std::mutex> lk(mu);
     if (dev < 0 || dev >= 64 || !done[dev]) {
-      VB_CUDA(cudaFuncSetAttribute(lastdim_staged_kernel<E, EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      VB_CUDA(cudaFuncSetAttribute(lastdim_staged_kernel<E, EPT, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    kStagedSmemMax));
       if (dev >= 0 && dev < 64) done[dev] = true;
     }
   }
-  lastdim_staged_kernel<E, EPT><<<grid, kStThreads, smem, s>>>(p, piece, npieces, use_bulk);
+  lastdim_staged_kernel<E, EPT, GROUPED><<<grid, kStThreads, smem, s>>>(p, piece, npieces, use_bulk, nstages);
   return VBT_B200_OK;
 }
+template <class E, int EPT>
+vbt_b200_status launch_staged_grp(const LastDimParams& p, int piece, int npieces, int use_bulk, int nstages, dim3 grid,
+                                  size_t smem, cudaStream_t s) {
+  // regroup the entries by piece when there are several pieces, the packed entry can hold every
+  // source position, and the sort's scratch (4 bytes per entry) fits the shared memory asked for
+  constexpr int KBITS = EPT == 32 ? 15 : (EPT == 16 ? 14 : 13);
+  const bool grouped = npieces > 1 && npieces <= kStMaxPieces && p.K0 < (int64_t{1} << (32 - KBITS)) - 1 &&
+                       static_cast<size_t>(EPT) * kStThreads * 4 <= smem;
+  return grouped ? launch_staged_ept<E, EPT, true>(p, piece, npieces, use_bulk, nstages, grid, smem, s)
+                 : launch_staged_ept<E, EPT, false>(p, piece, npieces, use_bulk, nstages, grid, smem, s);
+}
 template <class E>
-vbt_b200_status launch_staged(const LastDimParams& p, int ept, int piece, int npieces, int use_bulk, dim3 grid,
-                              size_t smem, cudaStream_t s) {
+vbt_b200_status launch_staged(const LastDimParams& p, int ept, int piece, int npieces, int use_bulk, int nstages,
+                              dim3 grid, size_t smem, cudaStream_t s) {
   constexpr int kCap = sizeof(E) == 8 ? 16 : 32;  // the output tile stays <= 128 KiB
   if constexpr (kCap >= 32) {
-    if (ept == 32) return launch_staged_ept<E, 32>(p, piece, npieces, use_bulk, grid, smem, s);
+    if (ept == 32) return launch_staged_grp<E, 32>(p, piece, npieces, use_bulk, nstages, grid, smem, s);
   }
-  if (ept == 16) return launch_staged_ept<E, 16>(p, piece, npieces, use_bulk, grid, smem, s);
-  return launch_staged_ept<E, 8>(p, piece, npieces, use_bulk, grid, smem, s);
+  if (ept == 16) return launch_staged_grp<E, 16>(p, piece, npieces, use_bulk, nstages, grid, smem, s);
+  return launch_staged_grp<E, 8>(p, piece, npieces, use_bulk, nstages, grid, smem, s);
 }
 
 // self: rank >= 1, any strides; the index applies to its LAST dim.  other: dense
@@ -1121,27 +1257,32 @@ vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt
       ept = e;
     }
   }
+  // bulk copies need 16-byte aligned sources and sizes: every row start and every piece boundary
+  bool bulk = reinterpret_cast<uintptr_t>(self->data) % 16 == 0 && row_bytes % 16 == 0;
+  for (int i = 0; i < nl; ++i) bulk = bulk && (lst[i] * p.es) % 16 == 0;
   if (mode == 0 && p.sk == 1 && K >= 4096 && B >= 32 && row_bytes >= 32 * 1024 && p.K0 <= 0x7fffffff &&
       nchunks * row_bytes * 2 <= K * 32 && nchunks <= 65535) {
     const size_t tile_bytes = static_cast<size_t>(ept) * kStThreads * p.es;
-    const int64_t stage_max = (kStagedSmemMax - static_cast<int64_t>(tile_bytes)) / 2 / 1024 * 1024;
+    // two stages: the next piece (or row) loads while this one is served.  Deeper pipelines of
+    // smaller pieces measured slower: every piece costs a block-wide barrier, and with twelve
+    // pieces per row the barriers, not the copies, set the pace.
+    const int64_t avail = kStagedSmemMax - static_cast<int64_t>(tile_bytes);
+    const int nstages = 2;
+    const int64_t stage_max = avail / nstages / 1024 * 1024;
     const int npieces = static_cast<int>((row_bytes + stage_max - 1) / stage_max);
     const int64_t per = (p.K0 + npieces - 1) / npieces;
     const int piece = static_cast<int>((per + 15) / 16 * 16);  // whole 16-byte units for every element size
     const size_t stage = (static_cast<size_t>(piece) * p.es + 127) / 128 * 128;
-    // bulk copies need 16-byte aligned sources and sizes: every row start and every piece boundary
-    bool bulk = reinterpret_cast<uintptr_t>(self->data) % 16 == 0 && row_bytes % 16 == 0;
-    for (int i = 0; i < nl; ++i) bulk = bulk && (lst[i] * p.es) % 16 == 0;
     const int sms = sm_count(scope.device());
     const unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(B, sms / nchunks)));
     const dim3 grid(gx, static_cast<unsigned>(nchunks));
-    const size_t smem = 2 * stage + tile_bytes;
+    const size_t smem = nstages * stage + tile_bytes;
     vbt_b200_status st;
     switch (p.es) {
-      case 1: st = launch_staged<uint8_t>(p, ept, piece, npieces, bulk, grid, smem, s); break;
-      case 2: st = launch_staged<uint16_t>(p, ept, piece, npieces, bulk, grid, smem, s); break;
-      case 4: st = launch_staged<uint32_t>(p, ept, piece, npieces, bulk, grid, smem, s); break;
-      default: st = launch_staged<uint64_t>(p, ept, piece, npieces, bulk, grid, smem, s); break;
+      case 1: st = launch_staged<uint8_t>(p, ept, piece, npieces, bulk, nstages, grid, smem, s); break;
+      case 2: st = launch_staged<uint16_t>(p, ept, piece, npieces, bulk, nstages, grid, smem, s); break;
+      case 4: st = launch_staged<uint32_t>(p, ept, piece, npieces, bulk, nstages, grid, smem, s); break;
+      default: st = launch_staged<uint64_t>(p, ept, piece, npieces, bulk, nstages, grid, smem, s); break;
     }
     VB_TRY(st);
     VB_LAUNCH_CHECK();
