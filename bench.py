@@ -275,6 +275,16 @@ def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4", "ew")
             r["note"] = note
         res.append(r)
 
+    # the reference's own Triton kernels for the row ops, timed beside ours when an unmodified copy
+    # of its kernel package is present (single-GPU runs; baseline/install_ref.sh)
+    ref_k = None
+    try:
+        from baseline import ref_kernels
+        if ref_kernels.available():
+            ref_k = ref_kernels.load()
+    except Exception:
+        ref_k = None
+
     g = torch.Generator(device=dev)
     # ---- C1: [4096,4096] fp32 reductions, contiguous and transposed view; 4 buffers = 256 MiB > L2
     g.manual_seed(0)
@@ -298,6 +308,19 @@ def op_suite(torch, peak_gbs, scale="full", which=("c1", "c2", "c3", "c4", "ew")
             add("softmax", f"C4 {list(shape)} {str(dt)[6:]}", 2 * n * es, n, ms)
             ms = time_op(torch, lambda i: kernels.rmsnorm(xs[i % nbuf], gamma, 1e-6), 20)
             add("rmsnorm", f"C4 {list(shape)} {str(dt)[6:]}", 2 * n * es + shape[1] * 4 + shape[0] * 4, n, ms)
+            if ref_k is not None:
+                try:
+                    with torch.no_grad():
+                        ms = time_op(torch, lambda i: ref_k.softmax(xs[i % nbuf], -1), 10)
+                        add("softmax -- reference Triton kernel, same box", f"C4 {list(shape)} {str(dt)[6:]}",
+                            2 * n * es, n, ms, note="vibe_kernels/softmax/impl/triton_impl.py, unmodified; same algorithmic bytes")
+                        ms = time_op(torch, lambda i: ref_k.rmsnorm_fn.apply(xs[i % nbuf], gamma, 1e-6), 10)
+                        add("rmsnorm -- reference Triton kernel, same box", f"C4 {list(shape)} {str(dt)[6:]}",
+                            2 * n * es + shape[1] * 4 + shape[0] * 4, n, ms,
+                            note="vibe_kernels/rmsnorm/impl/triton_impl.py, unmodified; same algorithmic bytes")
+                except Exception as ex:
+                    res.append({"op": "reference Triton kernels", "config": f"C4 {list(shape)} {str(dt)[6:]}",
+                                "error": str(ex)[:200]})
             # backward: the saved tensor rotates through the forward's buffers and dy through as
             # many buffers of its own, so that neither stream is served from L2
             inv = kernels.rmsnorm(xs[0], gamma, 1e-6)[1]

@@ -191,3 +191,65 @@ def test_product_has_no_cpu_path():
         open(os.path.join(ROOT, "vibetensor_b200", "kernels.py")).read() + \
         open(os.path.join(ROOT, "vibetensor_b200", "fabric.py")).read()
     assert "oracle" not in src
+
+
+def test_null_data_and_bad_policy_are_rejected_before_any_launch(L):
+    """A descriptor with elements but no data pointer (a failed or empty allocation passed through
+    a binding) must come back as INVALID_ARGUMENT from every family -- a kernel given a null base
+    would fault on the device -- and so must an unknown index policy."""
+    null = lambda shape, dt=_lib.F32: fake(shape, dense(shape), dt, ptr=0)  # noqa: E731
+    x, o = fake([3, 4], [4, 1]), fake([3], [1])
+    da = _lib.i64_array([1])
+    for args in ((ctypes.byref(null([3])), None, ctypes.byref(x)), (ctypes.byref(o), None, ctypes.byref(null([3, 4])))):
+        assert L.vbt_b200_reduce(0, args[0], args[1], args[2], da, 1, 0, None, 0, None) == 1
+        assert b"null data pointer" in L.vbt_b200_last_error()
+    assert L.vbt_b200_reduce_noalloc(0, ctypes.byref(null([3])), None, ctypes.byref(x), da, 1, 0, None) == 1
+    assert L.vbt_b200_reduce_partial(0, ctypes.byref(o), ctypes.byref(null([3, 4])), da, 1, 0, None, 0, 0, None) == 1
+    oi = fake([3], [1], _lib.I64)
+    assert L.vbt_b200_reduce(5, ctypes.byref(o), ctypes.byref(null([3], _lib.I64)), ctypes.byref(x), da, 1, 0, None, 0,
+                             None) == 1
+    assert L.vbt_b200_reduce(5, ctypes.byref(o), ctypes.byref(oi), ctypes.byref(null([3, 4])), da, 1, 0, None, 0, None) == 1
+    # zero elements need no pointer
+    e, eo = null([0, 4]), null([0])
+    assert L.vbt_b200_reduce(0, ctypes.byref(eo), None, ctypes.byref(e), da, 1, 0, None, 0, None) == 0
+    tab, idx, out = fake([4, 3], [3, 1]), fake([2], [1], _lib.I64), fake([2, 3], [3, 1])
+    for t_, i_, o_ in ((null([4, 3]), idx, out), (tab, null([2], _lib.I64), out), (tab, idx, null([2, 3]))):
+        assert L.vbt_b200_index_rows(ctypes.byref(o_), ctypes.byref(t_), ctypes.byref(i_), 0, None, None) == 1
+        assert b"null data pointer" in L.vbt_b200_last_error()
+        assert L.vbt_b200_index_put_rows(ctypes.byref(t_), ctypes.byref(i_), ctypes.byref(o_), 1, 0, None, None) == 1
+        assert L.vbt_b200_index_put_rows_sorted(ctypes.byref(t_), ctypes.byref(i_), ctypes.byref(o_), 0, None, None, 0,
+                                                None) == 1
+    src, od = fake([5, 4], [4, 1]), fake([5, 2], [2, 1])
+    for s_, i_, o_ in ((null([5, 4]), idx, od), (src, null([2], _lib.I64), od), (src, idx, null([5, 2]))):
+        assert L.vbt_b200_index_lastdim(ctypes.byref(o_), ctypes.byref(s_), ctypes.byref(i_), 0, None, None) == 1
+        assert b"null data pointer" in L.vbt_b200_last_error()
+    for pol in (-1, 3, 99):
+        assert L.vbt_b200_index_lastdim(ctypes.byref(od), ctypes.byref(src), ctypes.byref(idx), pol, None, None) == 1
+        assert b"unknown index policy" in L.vbt_b200_last_error()
+        assert L.vbt_b200_index_put_lastdim(ctypes.byref(src), ctypes.byref(idx), ctypes.byref(od), 0, pol, None, None) == 1
+        assert L.vbt_b200_index_rows(ctypes.byref(out), ctypes.byref(tab), ctypes.byref(idx), pol, None, None) == 1
+    # a mask descriptor without sizes is rejected on the host, not dereferenced
+    bad_mask = _lib.VbtTensor()
+    bad_mask.data, bad_mask.dtype, bad_mask.ndim = 0x10000, _lib.BOOL, 1
+    cnt = ctypes.c_uint64()
+    assert L.vbt_b200_mask_select(ctypes.byref(bad_mask), None, 0, ctypes.byref(cnt), None, 0, None) == 1
+    # fabric: shape / dtype rules come first and carry the reference's prefix
+    a, b = fake([4, 4], [4, 1]), fake([4, 5], [5, 1])
+    mode = ctypes.c_int32()
+    assert L.vbt_b200_fabric_binary(0, ctypes.byref(a), ctypes.byref(a), ctypes.byref(b), 0, 0, 1, None, 0,
+                                    ctypes.byref(mode), None) == 2
+    assert L.vbt_b200_last_error() == b"[Fabric] vt::fabric_add: requires equal shapes"
+    c = fake([4, 4], [4, 1], _lib.BF16)
+    assert L.vbt_b200_fabric_binary(2, ctypes.byref(a), ctypes.byref(a), ctypes.byref(c), 0, 0, 1, None, 0,
+                                    ctypes.byref(mode), None) == 2
+    assert L.vbt_b200_last_error() == b"[Fabric] vt::fabric_mul: requires equal dtypes"
+
+
+def test_launch_info_and_counters_are_host_side_state(L):
+    info = _lib.LaunchInfo()
+    L.vbt_b200_reset_last_launch_info()
+    assert L.vbt_b200_last_launch_info(ctypes.byref(info)) == 0
+    assert info.family == 0 and info.launches == 0
+    L.vbt_b200_reset_launch_counts()
+    assert _lib.launch_counts() == {name: 0 for name in _lib.FAMILIES}
+    assert L.vbt_b200_last_launch_info(None) == 1
