@@ -514,14 +514,15 @@ VBT_B200_API vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_
  * Each rank owns an exchange buffer; ranks swap a handle to it once and map each other's
  * buffer (IPC between processes, plain peer access between GPUs of one process).  After that
  * vbt_b200_reduce_exchange is the whole sharded reduction: the block that finishes a tile of
- * the local result writes it into every rank's buffer with peer stores over NVLink, raises a
- * per-tile flag there, waits -- at most a few seconds, then it records an error instead -- for
- * all ranks' flags, folds the `world` values in rank order (so every rank ends with the same
- * bits), scales, casts and stores.  No collective library call and no kernel behind it.
+ * the local result writes every value, as one 8-byte word that also holds the call's epoch,
+ * into every rank's buffer with peer stores over NVLink, reads its own buffer until all ranks'
+ * words carry that epoch -- at most a few seconds, then it records an error instead -- folds
+ * the `world` values in rank order (so every rank ends with the same bits), scales, casts and
+ * stores.  No collective library call and no kernel behind it.
  * All ranks must make the same sequence of calls on a comm (as with any collective).
  *
  * vbt_b200_fabric_comm_create is the one place in this library that allocates device memory
- * (cudaMalloc of 2*world*(slot_floats + 1024)*4 bytes, at set-up; freed by _destroy).
+ * (cudaMalloc of 2*world*slot_floats*8 + 256 bytes, at set-up; freed by _destroy).
  * slot_floats bounds the number of output elements of a fused call. */
 #define VBT_B200_FABRIC_MAX_RANKS 8
 #define VBT_B200_FABRIC_HANDLE_BYTES 128
@@ -587,6 +588,8 @@ VBT_B200_API vbt_b200_status vbt_b200_scale_cast(void* out, int32_t out_dtype, c
 #define VBT_B200_IK_LASTDIM_STAGED 7  /* rows staged in shared memory by bulk copies, index
                                          list in registers; `splits` = pieces per row       */
 #define VBT_B200_IK_MASK_SELECT 8
+#define VBT_B200_IK_LASTDIM_WIDE 9    /* 4-byte rows of up to 65 536 elements: outputs in registers,
+                                         all shared memory for the row; `splits` = pieces   */
 /* ROWOP: */
 #define VBT_B200_WK_GROUP 1
 #define VBT_B200_WK_BLOCK 2

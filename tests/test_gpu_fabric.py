@@ -94,13 +94,21 @@ def _worker(rank, world, port, errq):
                     assert torch.equal(a, b), (name, dim, rep)
                 else:
                     torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-5)
-            want = port_.reduce(name, np.concatenate([s.cpu().numpy() for s in _gather_shards(dist, shard, rows, world)]),
-                                oracle.F32, dim=dim)
+            full = np.concatenate([s.cpu().numpy() for s in _gather_shards(dist, shard, rows, world)])
             got = fused.run().cpu().numpy()
             if name in ("max", "min"):
-                np.testing.assert_array_equal(got, want)
+                np.testing.assert_array_equal(got, port_.reduce(name, full, oracle.F32, dim=dim))
             else:
-                np.testing.assert_allclose(got, want, rtol=2e-5, atol=1e-4)
+                # against the fp64 truth, within 1e-5 of max(|truth|, sqrt(sum of squares)): the
+                # reference's own sequential fp32 loop is further from the truth than that on
+                # slices this long, so it cannot be the yardstick for a differently ordered sum
+                f64 = full.astype(np.float64)
+                truth = f64.sum(axis=dim)
+                scale = np.maximum(np.abs(truth), np.sqrt((f64 * f64).sum(axis=dim)))
+                if name == "mean":
+                    n = full.shape[0] if dim is not None else full.size
+                    truth, scale = truth / n, scale / n
+                assert np.all(np.abs(got.astype(np.float64) - truth) <= 1e-5 * scale), (name, dim)
             if fused.fused is not None:
                 fused.comm.check()
         # bf16 mean through the fused form: fp32 partials cross the link, one rounding at the end
@@ -134,10 +142,14 @@ def _worker(rank, world, port, errq):
         raise
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_rank_nccl_sharded_ops():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_nccl_sharded_ops(world):
+    """One process per GPU over NCCL; the fused exchange kernels run over CUDA IPC mappings of
+    every peer's exchange buffer, so 4 and 8 ranks cover the slot and flag indexing that 2 ranks
+    cannot (a rank's own slot sits between peers' slots)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    world = 2
     ctx = mp.get_context("spawn")
     errq = ctx.SimpleQueue()
     port = _free_port()

@@ -386,27 +386,35 @@ def _lastdim_oracle(port, src_view_np, idx):
     return port.index_lastdim(flat, idx.reshape(-1)).reshape(src_view_np.shape[:-1] + idx.shape)
 
 
-STAGED = [(torch.float32, (40, 60001), 32768),    # 4 pieces, rows not 16-byte aligned: plain staging loads, 2 index chunks
-          (torch.float32, (33, 65536), 65536),    # 4 pieces, bulk copies, index list over four blocks
-          (torch.bfloat16, (64, 50000), 40000),   # one piece, two index chunks
-          (torch.int64, (32, 12800), 8000),       # one piece of exactly 100 KiB
-          (torch.float32, (35, 16384), 16384),
-          (torch.float32, (34, 16384), 16380),    # output rows not 16-byte aligned: scalar tile write-out
-          (torch.bool, (32, 40000), 8192),
-          (torch.bfloat16, (32, 200000), 100000),  # 400 KB rows: six pieces, four index chunks
-          (torch.float32, (32, 100001), 65536)]    # nine pieces, rows not 16-byte aligned (plain staging loads)
+# (dtype, shape, index count, kernel id: 7 = output tile in shared memory, 9 = outputs in registers)
+STAGED = [(torch.float32, (40, 60001), 32768, 7),    # 4 pieces, rows not 16-byte aligned: plain staging loads, 2 index chunks
+          (torch.float32, (33, 65536), 65536, 9),    # 4 pieces of 64 KiB, two index chunks side by side
+          (torch.bfloat16, (64, 50000), 40000, 7),   # one piece, two index chunks
+          (torch.int64, (32, 12800), 8000, 7),       # one piece of exactly 100 KiB
+          (torch.float32, (35, 16384), 16384, 7),
+          (torch.float32, (34, 16384), 16380, 7),    # output rows not 16-byte aligned: scalar tile write-out
+          (torch.bool, (32, 40000), 8192, 7),
+          (torch.bfloat16, (32, 200000), 100000, 7),  # 400 KB rows: six pieces, four index chunks
+          (torch.float32, (32, 100001), 65536, 7),    # nine pieces, rows not 16-byte aligned (plain staging loads)
+          (torch.float32, (33, 40000), 50000, 9),     # three pieces; the second chunk's tile is partly empty
+          (torch.float32, (32, 65536), 32770, 9),     # output rows not 16-byte aligned: scalar stores; a 2-entry tile
+          (torch.int32, (64, 30000), 30000, 9),       # two pieces, one chunk
+          (torch.float32, (64, 16000), 32768, 9),     # one piece
+          (torch.float32, (150, 65532), 65536, 9)]    # more rows than row lanes; last piece shorter
 
 
-@pytest.mark.parametrize("dtype,shape,K", STAGED)
-def test_index_lastdim_staged_rows(ops, port, dtype, shape, K):
-    """Shapes that take the staged kernel (rows brought into shared memory by bulk copies, the
-    index list held in registers, outputs collected in a shared-memory tile): every element
-    size, one and several pieces per row, one and several index chunks, aligned and unaligned
-    rows and outputs, wrapped negative indices, bad indices."""
+@pytest.mark.parametrize("dtype,shape,K,kernel", STAGED)
+def test_index_lastdim_staged_rows(ops, port, dtype, shape, K, kernel):
+    """Shapes that take the staged kernels (rows brought into shared memory by bulk copies, the
+    index list held in registers, outputs collected in a shared-memory tile or -- long 4-byte
+    rows -- in registers): every element size, one and several pieces per row, one and several
+    index chunks, aligned and unaligned rows and outputs, wrapped negative indices, bad indices."""
     from vibetensor_b200 import _lib
     rng = np.random.default_rng(44)
     if dtype == torch.int64:
         src = rng.integers(-10 ** 12, 10 ** 12, shape).astype(np.int64)
+    elif dtype == torch.int32:
+        src = rng.integers(-2 ** 31, 2 ** 31, shape).astype(np.int32)
     elif dtype == torch.bool:
         src = (rng.random(shape) < 0.5).astype(np.uint8)
     else:
@@ -415,7 +423,7 @@ def test_index_lastdim_staged_rows(ops, port, dtype, shape, K):
     ts, ti = from_np(src, dtype), torch.from_numpy(idx).cuda()
     got = to_np(ops.index_lastdim(ts, ti))
     info = _lib.last_launch_info()
-    assert (info.family, info.kernel) == (3, 7), "expected the staged last-dim kernel"
+    assert (info.family, info.kernel) == (3, kernel), "expected the staged last-dim kernel"
     np.testing.assert_array_equal(got, port.index_lastdim(src, idx))
     bad = idx.copy()
     bad[::997] = shape[1] + 3
@@ -440,10 +448,10 @@ def test_index_lastdim_nd_strided_self(ops, port):
     tb = torch.from_numpy(base).cuda()
     idx = rng.integers(-32768, 32768, (4, 5000)).astype(np.int64)
     ti = torch.from_numpy(idx).cuda()
-    for sl in ((slice(None), slice(None, None, 2), slice(0, 32768)),      # aligned rows: bulk copies
-               (slice(None), slice(None, None, 2), slice(1, 32769))):     # rows start 4 bytes off
+    for sl, kernel in (((slice(None), slice(None, None, 2), slice(0, 32768)), 9),      # aligned rows: bulk copies
+                       ((slice(None), slice(None, None, 2), slice(1, 32769)), 7)):     # rows start 4 bytes off
         got = ops.index_lastdim(tb[sl], ti)
-        assert (_lib.last_launch_info().family, _lib.last_launch_info().kernel) == (3, 7)
+        assert (_lib.last_launch_info().family, _lib.last_launch_info().kernel) == (3, kernel)
         assert got.shape == (8, 5, 4, 5000)
         np.testing.assert_array_equal(got.cpu().numpy(), _lastdim_oracle(port, base[sl], idx))
     # small N-d shapes on the direct kernel: permuted leading dims, rank 1, rank 4

@@ -714,6 +714,38 @@ __device__ __forceinline__ void sts(uint32_t a, uint64_t v) {
   asm volatile("st.shared.u64 [%0], %1;" ::"r"(a), "l"(static_cast<unsigned long long>(v)) : "memory");
 }
 
+// v = shared[addr] if d < n (else v keeps its value) and shared[addr] = v if d < n, each as ONE
+// predicated instruction: a branch around the access costs a divergence-stack round trip per
+// entry, several times the access itself
+__device__ __forceinline__ void lds_if_below(uint8_t& v, uint32_t d, uint32_t n, uint32_t addr) {
+  uint32_t w = v;
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %1, %2;\n\t@p ld.shared.u8 %0, [%3];\n\t}" : "+r"(w) : "r"(d), "r"(n), "r"(addr));
+  v = static_cast<uint8_t>(w);
+}
+__device__ __forceinline__ void lds_if_below(uint16_t& v, uint32_t d, uint32_t n, uint32_t addr) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %1, %2;\n\t@p ld.shared.u16 %0, [%3];\n\t}" : "+h"(v) : "r"(d), "r"(n), "r"(addr));
+}
+__device__ __forceinline__ void lds_if_below(uint32_t& v, uint32_t d, uint32_t n, uint32_t addr) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %1, %2;\n\t@p ld.shared.u32 %0, [%3];\n\t}" : "+r"(v) : "r"(d), "r"(n), "r"(addr));
+}
+__device__ __forceinline__ void lds_if_below(uint64_t& v, uint32_t d, uint32_t n, uint32_t addr) {
+  unsigned long long w = v;
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %1, %2;\n\t@p ld.shared.u64 %0, [%3];\n\t}" : "+l"(w) : "r"(d), "r"(n), "r"(addr));
+  v = w;
+}
+__device__ __forceinline__ void sts_if_below(uint32_t addr, uint8_t v, uint32_t d, uint32_t n) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %2, %3;\n\t@p st.shared.u8 [%0], %1;\n\t}" ::"r"(addr), "r"(static_cast<uint32_t>(v)), "r"(d), "r"(n) : "memory");
+}
+__device__ __forceinline__ void sts_if_below(uint32_t addr, uint16_t v, uint32_t d, uint32_t n) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %2, %3;\n\t@p st.shared.u16 [%0], %1;\n\t}" ::"r"(addr), "h"(v), "r"(d), "r"(n) : "memory");
+}
+__device__ __forceinline__ void sts_if_below(uint32_t addr, uint32_t v, uint32_t d, uint32_t n) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %2, %3;\n\t@p st.shared.u32 [%0], %1;\n\t}" ::"r"(addr), "r"(v), "r"(d), "r"(n) : "memory");
+}
+__device__ __forceinline__ void sts_if_below(uint32_t addr, uint64_t v, uint32_t d, uint32_t n) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %2, %3;\n\t@p st.shared.u64 [%0], %1;\n\t}" ::"r"(addr), "l"(static_cast<unsigned long long>(v)), "r"(d), "r"(n) : "memory");
+}
+
 constexpr int kStThreads = 1024;
 constexpr int kStagedSmemMax = 220 * 1024;  // dynamic shared memory the staged kernel may ask for
 static __device__ unsigned vb_index_fault;  // a bounded wait on a staged copy gave up
@@ -865,13 +897,24 @@ __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __g
     advance(nb, nq);
     const uint32_t tl_s = smem_addr(tl);
     constexpr uint32_t ES = static_cast<uint32_t>(sizeof(E));
+    constexpr int kBatch = 8;
     if constexpr (GROUPED) {
       const uint32_t ob_s = smem_addr(obuf);
       if (bstart[q] < wr1 && bstart[q + 1] > wr0) {  // this warp holds entries of piece q
+        // batches of kBatch loads, then their stores: a store right behind its load would make
+        // every entry wait out the shared-memory latency (the next load may not pass the store)
 #pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-          const uint32_t d = (v[j] >> KBITS) - c0;
-          if (d < n) sts(ob_s + (v[j] & KMASK) * ES, lds<E>(tl_s + d * ES));
+        for (int j0 = 0; j0 < EPT; j0 += kBatch) {
+          E val[kBatch];
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u) {
+            const uint32_t d = (v[j0 + u] >> KBITS) - c0;
+            val[u] = E(0);
+            lds_if_below(val[u], d, n, tl_s + d * ES);
+          }
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            sts_if_below(ob_s + (v[j0 + u] & KMASK) * ES, val[u], (v[j0 + u] >> KBITS) - c0, n);
         }
       }
       if (q == 0 && bstart[npieces] < wr1 && bstart[npieces + 1] > wr0) {  // ... or dead entries
@@ -883,9 +926,16 @@ __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __g
       // entry j of this thread lands in tile slot j * kStThreads + t
       const uint32_t ob_s = smem_addr(obuf) + static_cast<uint32_t>(t) * ES;
 #pragma unroll
-      for (int j = 0; j < EPT; ++j) {
-        const uint32_t d = v[j] - c0;
-        if (d < n) sts(ob_s + j * kStThreads * ES, lds<E>(tl_s + d * ES));
+      for (int j0 = 0; j0 < EPT; j0 += kBatch) {
+        E val[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const uint32_t d = v[j0 + u] - c0;
+          val[u] = E(0);
+          lds_if_below(val[u], d, n, tl_s + d * ES);
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) sts_if_below(ob_s + (j0 + u) * kStThreads * ES, val[u], v[j0 + u] - c0, n);
       }
       if (bad != 0 && q == 0) {  // rare: an out-of-range index gathers zero
 #pragma unroll
@@ -904,6 +954,186 @@ __global__ void __launch_bounds__(kStThreads, 1) lastdim_staged_kernel(const __g
         for (uint32_t i = t; i < ntile; i += kStThreads) out[i] = obuf[i];
       }
       // the next writes into the tile come after the barrier at the top of the next iteration
+    }
+    advance(b, q);
+    ahead = stage;
+    if (++stage == nstages) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+}
+
+// Rows of 4-byte elements too long for the tile form above (the row AND an output tile do not fit
+// one SM's shared memory together) but at most 65 536 elements: the outputs stay in REGISTERS.  A
+// block of 1024 threads owns up to 32 768 consecutive output positions -- 32 per thread, in groups
+// of four consecutive positions so that they leave as 16-byte stores.  Their source positions fit
+// 16 bits each: half of them live in 8 registers, the other half in 32 KiB of shared memory (read
+// back with conflict-free 16-byte loads once per staged piece), which leaves the registers to the
+// outputs and lets a full complement of 32 warps hide the latencies.  The rest of the shared
+// memory belongs to the row: two or three stages filled by bulk asynchronous copies.  For every
+// staged piece a thread tests its entries (subtract, compare, predicated shared load -- a branch
+// around the load measured four times slower): no output tile, no second trip through shared
+// memory, one block-wide barrier per piece.  An index list longer than 32 768 is cut into EQUAL
+// chunks (blockIdx.y); the blocks of one row set visit the same rows at the same pace, so the
+// second and later readers of a row find it in L2.
+constexpr int kWdThreads = 1024;
+constexpr int kWdEpt = 32;
+#ifndef VB_WIDE_REG_WORDS
+#define VB_WIDE_REG_WORDS 2
+#endif
+constexpr int kWdRegWords = VB_WIDE_REG_WORDS;  // 16-byte words of entries (8 entries each) a thread keeps in registers
+constexpr int kWdEntryBytes = kWdThreads * (kWdEpt / 8 - kWdRegWords) * 16;  // the rest: shared memory
+constexpr int kWdSmemMax = 227 * 1024 - 1024;
+constexpr int kWdMaxStages = 4;
+#ifndef VB_LASTDIM_WIDE
+#define VB_LASTDIM_WIDE 1
+#endif
+#ifndef VB_WIDE_STAGES
+#define VB_WIDE_STAGES 3
+#endif
+#ifndef VB_WIDE_STAGE_MAX
+#define VB_WIDE_STAGE_MAX (96 * 1024)
+#endif
+__global__ void __launch_bounds__(kWdThreads, 1) lastdim_wide_kernel(const __grid_constant__ LastDimParams p,
+                                                                     const int piece, const int npieces,
+                                                                     const int nstages, const int kchunk) {
+  extern __shared__ __align__(128) unsigned char st_raw[];  // [entries: words x 1024 x 16 bytes][stages]
+  __shared__ __align__(8) uint64_t bars[kWdMaxStages];
+  using E = uint32_t;
+  const int t = threadIdx.x;
+  unsigned char* const stages = st_raw + kWdEntryBytes;
+  const uint32_t stage_bytes = (static_cast<uint32_t>(piece) * 4u + 127u) / 128u * 128u;
+  // the index list is cut into equal chunks of kchunk <= 32 768 positions (a multiple of 4), one per blockIdx.y
+  const int64_t kc0 = static_cast<int64_t>(blockIdx.y) * kchunk;
+  const int64_t left = p.K - kc0;
+  const uint32_t ntile = static_cast<uint32_t>(left < kchunk ? left : kchunk);
+  const uint32_t upiece = static_cast<uint32_t>(piece);
+  const uint32_t k0 = static_cast<uint32_t>(p.K0);
+  // 16-byte words of entries that hold any live slot (word k covers slots from k * 8192 on): the
+  // same for every thread, so skipping the rest is a uniform branch
+  const int nwords = static_cast<int>((ntile + 2 * kWdThreads * 4 - 1) / (2 * kWdThreads * 4));
+  // entry e of this thread is output slot (e / 4) * 4096 + t * 4 + e % 4 of the block's tile; the
+  // thread's k-th 16-byte word of entries (e = 8k .. 8k + 7) sits at [k][t], so a warp reads 512
+  // consecutive bytes.  Only this thread reads what it writes here: no barrier in between.
+  bool bad = false;  // some slot's index is out of range (it gathers zero)
+  const uint32_t ent_s = smem_addr(st_raw) + static_cast<uint32_t>(t) * 16u;
+  uint32_t er[kWdRegWords > 0 ? kWdRegWords : 1][4];
+#pragma unroll
+  for (int k = 0; k < kWdEpt / 8; ++k) {
+    uint32_t w[4];
+#pragma unroll
+    for (int h = 0; h < 8; ++h) {
+      const int e = k * 8 + h;
+      const uint32_t slot = static_cast<uint32_t>(e >> 2) * (kWdThreads * 4) + static_cast<uint32_t>(t) * 4u + (e & 3);
+      uint32_t src = 0;
+      if (slot < ntile) {
+        int64_t x = p.idx.get(kc0 + slot);
+        if (normalize(x, p.K0, p.policy, p.status, blockIdx.x == 0)) src = static_cast<uint32_t>(x);
+        else bad = true;
+      }
+      if (h & 1) w[h >> 1] |= src << 16;
+      else w[h >> 1] = src;
+    }
+    if (k < kWdRegWords) {
+#pragma unroll
+      for (int h = 0; h < 4; ++h) er[k < kWdRegWords ? k : 0][h] = w[h];
+    } else {
+      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(ent_s + (k - kWdRegWords) * (kWdThreads * 16)),
+                   "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                   : "memory");
+    }
+  }
+  if (t == 0) {
+    for (int st = 0; st < nstages; ++st) mbar_init(&bars[st], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  const bool vec_out = (reinterpret_cast<uintptr_t>(p.other) % 16 == 0) && (p.K % 4 == 0);
+  auto advance = [&](uint32_t& bb, int& qq) {
+    if (++qq == npieces) {
+      qq = 0;
+      bb += gridDim.x;
+    }
+  };
+  auto issue = [&](uint32_t bb, int qq, int stage) {  // thread 0 only; the stage's previous readers are past a barrier
+    const uint32_t c0 = static_cast<uint32_t>(qq) * upiece;
+    const uint32_t n = min(upiece, k0 - c0);
+    const E* src = reinterpret_cast<const E*>(p.self) + p.rows.offset(bb) + c0;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_arrive_expect_tx(&bars[stage], n * 4u);
+    bulk_copy_g2s(stages + stage * stage_bytes, src, n * 4u, &bars[stage]);
+  };
+  uint32_t b = blockIdx.x, nb = blockIdx.x;
+  int q = 0, nq = 0;
+  for (int st = 0; st + 1 < nstages; ++st) {  // fill the pipeline
+    if (t == 0 && nb < p.B) issue(nb, nq, st);
+    advance(nb, nq);
+  }
+  int stage = 0, ahead = nstages - 1;
+  uint32_t phase = 0;
+  uint32_t o[kWdEpt];
+#pragma unroll
+  for (int e = 0; e < kWdEpt; ++e) o[e] = 0;
+  for (; b < p.B;) {
+    const uint32_t c0 = static_cast<uint32_t>(q) * upiece;
+    const uint32_t n = min(upiece, k0 - c0);
+    const bool ok = mbar_wait_bounded(&bars[stage], phase);
+    if (__syncthreads_or(!ok)) {
+      // give up: note the fault, let the copies that may still be in flight land, and leave
+      if (t == 0) {
+        atomicExch(&vb_index_fault, 1u);
+        for (int st = 0; st < nstages; ++st) mbar_wait_bounded(&bars[st], st < stage ? phase ^ 1u : phase);
+      }
+      __syncthreads();
+      return;
+    }
+    if (t == 0 && nb < p.B) issue(nb, nq, ahead);
+    advance(nb, nq);
+    const uint32_t tl_s = smem_addr(stages + stage * stage_bytes) - c0 * 4u;  // address of source position 0
+#pragma unroll
+    for (int k = 0; k < kWdEpt / 8; ++k) {
+      if (k >= nwords) break;
+      uint32_t w[4];
+      if (k < kWdRegWords) {
+#pragma unroll
+        for (int h = 0; h < 4; ++h) w[h] = er[k < kWdRegWords ? k : 0][h];
+      } else {
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                     : "r"(ent_s + (k - kWdRegWords) * (kWdThreads * 16)));
+      }
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const uint32_t s0 = w[h] & 0xffffu, s1 = w[h] >> 16;
+        lds_if_below(o[k * 8 + 2 * h], s0 - c0, n, tl_s + s0 * 4u);
+        lds_if_below(o[k * 8 + 2 * h + 1], s1 - c0, n, tl_s + s1 * 4u);
+      }
+    }
+    if (q == npieces - 1) {
+      if (bad) {  // rare: find the slots again from the index list
+#pragma unroll
+        for (int e = 0; e < kWdEpt; ++e) {
+          const uint32_t slot = static_cast<uint32_t>(e >> 2) * (kWdThreads * 4) + static_cast<uint32_t>(t) * 4u + (e & 3);
+          if (slot < ntile) {
+            int64_t x = p.idx.get(kc0 + slot);
+            if (!normalize(x, p.K0, p.policy, nullptr, false)) o[e] = 0;
+          }
+        }
+      }
+      E* out = reinterpret_cast<E*>(p.other) + static_cast<int64_t>(b) * p.K + kc0;
+#pragma unroll
+      for (int g = 0; g < kWdEpt / 4; ++g) {
+        if (g >= 2 * nwords) break;
+        const uint32_t slot = static_cast<uint32_t>(g) * (kWdThreads * 4) + static_cast<uint32_t>(t) * 4u;
+        if (vec_out && slot + 3 < ntile) {
+          *reinterpret_cast<uint4*>(out + slot) = make_uint4(o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3]);
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (slot + u < ntile) out[slot + u] = o[4 * g + u];
+        }
+      }
     }
     advance(b, q);
     ahead = stage;
@@ -1260,8 +1490,48 @@ vbt_b200_status lastdim(const char* name, const vbt_b200_tensor* self, const vbt
   // bulk copies need 16-byte aligned sources and sizes: every row start and every piece boundary
   bool bulk = reinterpret_cast<uintptr_t>(self->data) % 16 == 0 && row_bytes % 16 == 0;
   for (int i = 0; i < nl; ++i) bulk = bulk && (lst[i] * p.es) % 16 == 0;
-  if (mode == 0 && p.sk == 1 && K >= 4096 && B >= 32 && row_bytes >= 32 * 1024 && p.K0 <= 0x7fffffff &&
-      nchunks * row_bytes * 2 <= K * 32 && nchunks <= 65535) {
+  const bool staged_ok = mode == 0 && p.sk == 1 && K >= 4096 && B >= 32 && row_bytes >= 32 * 1024 &&
+                         p.K0 <= 0x7fffffff && nchunks * row_bytes * 2 <= K * 32 && nchunks <= 65535;
+  // rows of 4-byte elements that the tile form would have to cut into pieces, and whose positions
+  // fit 16 bits: outputs in registers, the whole shared memory for the row
+  const size_t tile_bytes0 = static_cast<size_t>(ept) * kStThreads * p.es;
+  const int64_t wide_chunks = (K + int64_t{kWdThreads} * kWdEpt - 1) / (int64_t{kWdThreads} * kWdEpt);
+  const int wide_kchunk = static_cast<int>(((K + wide_chunks - 1) / wide_chunks + 3) / 4 * 4);  // equal shares
+  if (VB_LASTDIM_WIDE && staged_ok && bulk && p.es == 4 && p.K0 <= 65536 &&
+      row_bytes > (kStagedSmemMax - static_cast<int64_t>(tile_bytes0)) / 2 / 1024 * 1024 &&
+      wide_chunks * row_bytes * 2 <= K * 32) {
+    // as many stages as fit beside the entries, each a whole piece of <= 64 KiB
+    const int64_t room = kWdSmemMax - kWdEntryBytes;
+    // several chunks: the blocks that share a row drift apart by a piece or two, and a third
+    // stage lets the follower run ahead into lines the leader has already brought into L2
+    int nstages = wide_chunks > 1 ? VB_WIDE_STAGES : 2;
+    const int64_t stage_max = std::min<int64_t>(room / nstages / 1024 * 1024, VB_WIDE_STAGE_MAX);
+    const int npieces = static_cast<int>((row_bytes + stage_max - 1) / stage_max);
+    const int64_t per = (p.K0 + npieces - 1) / npieces;
+    const int piece = static_cast<int>((per + 31) / 32 * 32);  // whole 128-byte lines
+    const size_t stage = static_cast<size_t>(piece) * 4;
+    nstages = static_cast<int>(std::min<int64_t>(nstages, room / static_cast<int64_t>(stage)));
+    const int sms = sm_count(scope.device());
+    const unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(B, sms / wide_chunks)));
+    const dim3 grid(gx, static_cast<unsigned>(wide_chunks));
+    const size_t smem = kWdEntryBytes + nstages * stage;
+    static std::mutex mu;
+    static bool done[64] = {};
+    {
+      std::lock_guard<std::mutex> lk(mu);
+      const int dev = scope.device();
+      if (dev < 0 || dev >= 64 || !done[dev]) {
+        VB_CUDA(cudaFuncSetAttribute(lastdim_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWdSmemMax));
+        if (dev >= 0 && dev < 64) done[dev] = true;
+      }
+    }
+    lastdim_wide_kernel<<<grid, kWdThreads, smem, s>>>(p, piece, npieces, nstages, wide_kchunk);
+    VB_LAUNCH_CHECK();
+    note_launch(VBT_B200_FAMILY_INDEX, VBT_B200_IK_LASTDIM_WIDE, grid, dim3(kWdThreads), kWdEpt, npieces, 0, 1, B * K,
+                K, 0, s);
+    return VBT_B200_OK;
+  }
+  if (staged_ok) {
     const size_t tile_bytes = static_cast<size_t>(ept) * kStThreads * p.es;
     // two stages: the next piece (or row) loads while this one is served.  Deeper pipelines of
     // smaller pieces measured slower: every piece costs a block-wide barrier, and with twelve

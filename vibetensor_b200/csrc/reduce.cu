@@ -183,26 +183,27 @@ __device__ __forceinline__ typename R::acc_t block_reduce(typename R::acc_t a, t
 enum { OP_SUM = 0, OP_MEAN, OP_MAX, OP_MIN, OP_PROD, OP_ARGMAX, OP_ARGMIN };
 
 // Cross-GPU combine of the local results (sharded reductions, one process per GPU).  The block
-// that holds a tile's final local values writes them into slot [rank] of EVERY rank's exchange
-// buffer with plain peer stores over NVLink, publishes a per-tile flag holding the call's epoch
-// on every rank, waits (bounded) until all ranks' flags for the tile show that epoch in its
-// own buffer, and folds the `world` values in rank order -- the same order on every rank, so
-// all ranks end with bit-identical results -- before scaling, casting and storing.  Buffers
-// alternate between two halves by the epoch's parity, so a rank that is already one call ahead
-// never overwrites values a slower rank is still reading.  world == 0: no exchange.
+// that holds a tile's final local values writes each of them, as ONE 8-byte word holding the value
+// and the call's epoch, into slot [rank] of EVERY rank's exchange buffer with plain peer stores
+// over NVLink; the same thread then reads the `world` words of its value from its own buffer until
+// every one carries the epoch (a bounded wait), and folds them in rank order -- the same order on
+// every rank, so all ranks end with bit-identical results -- before scaling, casting and storing.
+// An aligned 8-byte store lands whole, so value and epoch need no fence and no separate flag: the
+// exchange costs one one-way trip over the link plus the poll, not a store / fence / flag / poll
+// chain.  Buffers alternate between two halves by the epoch's parity, so a rank that is already
+// one call ahead never overwrites words a slower rank is still reading.  world == 0: no exchange.
 constexpr int kXchgMaxRanks = VBT_B200_FABRIC_MAX_RANKS;
-constexpr int kXchgTiles = 1024;                             // flags per rank and half
+constexpr int kXchgTiles = 1024;                              // most tiles one call may exchange
 constexpr unsigned long long kXchgTimeoutNs = 5000000000ull;  // a peer that never arrives: give up after 5 s
 struct Xchg {
   int world;
   int rank;
   int owner;        // rank whose shard holds global position 0 (the NaN rule of max / min)
   unsigned epoch;
-  int slot_floats;  // floats per rank in a slot area
+  int slot_floats;  // values per rank in a slot area
   float scale;      // applied to the folded value (1 / global count for a mean)
-  float* slots[kXchgMaxRanks];     // rank r's slot area of this call's half: [world][slot_floats]
-  unsigned* flags[kXchgMaxRanks];  // rank r's flag area of this call's half: [world][kXchgTiles]
-  unsigned* status;                // this rank's error word
+  unsigned long long* slots[kXchgMaxRanks];  // rank r's slot area of this call's half: [world][slot_floats] words
+  unsigned* status;                          // this rank's error word
 };
 
 struct OutSpec {
@@ -250,12 +251,12 @@ __device__ __forceinline__ void finalize(const OutSpec& o, int64_t i, typename R
   }
 }
 
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -270,39 +271,32 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 template <class R>
 __device__ void exchange_finalize(const OutSpec& o, int tile, int vals_per_tile, int e, bool has, float v,
                                   int64_t out_i, float first) {
-  __shared__ int all_arrived;
+  if (!has) return;
   const Xchg& x = o.x;
   const int slot = tile * vals_per_tile + e;
-  if (has) {
-    if ((o.op == OP_MAX || o.op == OP_MIN) && o.nan_first && first != first) v = first;
-    for (int r = 0; r < x.world; ++r) x.slots[r][x.rank * x.slot_floats + slot] = v;
-    __threadfence_system();
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int r = 0; r < x.world; ++r) st_release_sys(x.flags[r] + x.rank * kXchgTiles + tile, x.epoch);
-    bool ok = true;
-    const unsigned long long t0 = global_timer_ns();
-    for (int r = 0; r < x.world && ok; ++r) {
-      const unsigned* f = x.flags[x.rank] + r * kXchgTiles + tile;
-      while (ld_acquire_sys(f) != x.epoch) {
+  if ((o.op == OP_MAX || o.op == OP_MIN) && o.nan_first && first != first) v = first;
+  const unsigned long long word = (static_cast<unsigned long long>(x.epoch) << 32) | __float_as_uint(v);
+  for (int r = 0; r < x.world; ++r) st_relaxed_sys(x.slots[r] + x.rank * x.slot_floats + slot, word);
+  const unsigned long long* mine = x.slots[x.rank] + slot;
+  float acc = R::init(), fo = 0.f;
+  const unsigned long long t0 = global_timer_ns();
+  for (int r = 0; r < x.world; ++r) {
+    unsigned long long w = ld_relaxed_sys(mine + r * x.slot_floats);
+    for (unsigned tries = 0; static_cast<unsigned>(w >> 32) != x.epoch; ++tries) {
+      if ((tries & 15u) == 15u) {
         if (global_timer_ns() - t0 > kXchgTimeoutNs) {
-          ok = false;
-          break;
+          atomicExch(x.status, 1u);  // the host reads this word; the output stays unwritten
+          return;
         }
-        __nanosleep(200);
+        __nanosleep(100);
       }
+      w = ld_relaxed_sys(mine + r * x.slot_floats);
     }
-    if (!ok) atomicExch(x.status, 1u);  // the host reads this word; the output stays unwritten
-    all_arrived = ok ? 1 : 0;
+    const float vr = __uint_as_float(static_cast<unsigned>(w));
+    acc = R::combine(acc, vr);
+    if (r == x.owner) fo = vr;
   }
-  __syncthreads();
-  if (!all_arrived || !has) return;
-  const float* mine = x.slots[x.rank];
-  float acc = R::init();
-  for (int r = 0; r < x.world; ++r) acc = R::combine(acc, __ldcg(mine + r * x.slot_floats + slot));
   if (o.op == OP_MAX || o.op == OP_MIN) {
-    const float fo = __ldcg(mine + x.owner * x.slot_floats + slot);
     if (fo != fo) acc = fo;  // only the owner of global position 0 can have published a NaN
   }
   store_value(o, out_i, acc * x.scale);
@@ -1185,8 +1179,8 @@ vbt_b200_status vbt_b200_reduce_partial(int32_t op, const vbt_b200_tensor* parti
 // Fabric exchange: the buffers behind the fused sharded reductions (one process per GPU, or
 // several GPUs in one process), and vbt_b200_reduce_exchange.
 //
-// Every rank owns one device buffer: two halves (call parity) of [world][slot_floats] floats,
-// two halves of [world][kXchgTiles] flags, and an error word.  Ranks exchange a handle to it
+// Every rank owns one device buffer: two halves (call parity) of [world][slot_floats] 8-byte
+// words (value, epoch) and an error word.  Ranks exchange a handle to it
 // (an IPC memory handle plus, for ranks of the same process, the raw pointer) and map each
 // other's buffer; after that a sharded reduction is ONE kernel launch per rank -- no
 // collective library call, no scale-and-cast launch behind it.
@@ -1215,9 +1209,8 @@ struct CommHandle {  // what ranks exchange; VBT_B200_FABRIC_HANDLE_BYTES covers
 };
 static_assert(sizeof(CommHandle) <= VBT_B200_FABRIC_HANDLE_BYTES, "handle size");
 
-size_t comm_slot_bytes(const vbt_b200_fabric_comm& c) { return static_cast<size_t>(c.world) * c.slot_floats * 4; }
-size_t comm_flag_bytes(const vbt_b200_fabric_comm& c) { return static_cast<size_t>(c.world) * kXchgTiles * 4; }
-size_t comm_total_bytes(const vbt_b200_fabric_comm& c) { return 2 * comm_slot_bytes(c) + 2 * comm_flag_bytes(c) + 256; }
+size_t comm_slot_bytes(const vbt_b200_fabric_comm& c) { return static_cast<size_t>(c.world) * c.slot_floats * 8; }
+size_t comm_total_bytes(const vbt_b200_fabric_comm& c) { return 2 * comm_slot_bytes(c) + 256; }
 }  // namespace
 }  // namespace vb
 
@@ -1328,7 +1321,7 @@ vbt_b200_status vbt_b200_fabric_comm_status(vbt_b200_fabric_comm* c, void* strea
   VB_CUDA(cudaSetDevice(c->device));
   unsigned word = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  char* status = c->local + 2 * comm_slot_bytes(*c) + 2 * comm_flag_bytes(*c);
+  char* status = c->local + 2 * comm_slot_bytes(*c);
   cudaError_t e = cudaMemcpyAsync(&word, status, 4, cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e == cudaSuccess && word != 0) e = cudaMemsetAsync(status, 0, 4, s);
@@ -1375,10 +1368,9 @@ vbt_b200_status vbt_b200_reduce_exchange(int32_t op, const vbt_b200_tensor* out,
   x.scale = scale;
   const size_t half = x.epoch & 1u;
   for (int r = 0; r < comm->world; ++r) {
-    x.slots[r] = reinterpret_cast<float*>(comm->base[r] + half * comm_slot_bytes(*comm));
-    x.flags[r] = reinterpret_cast<unsigned*>(comm->base[r] + 2 * comm_slot_bytes(*comm) + half * comm_flag_bytes(*comm));
+    x.slots[r] = reinterpret_cast<unsigned long long*>(comm->base[r] + half * comm_slot_bytes(*comm));
   }
-  x.status = reinterpret_cast<unsigned*>(comm->local + 2 * comm_slot_bytes(*comm) + 2 * comm_flag_bytes(*comm));
+  x.status = reinterpret_cast<unsigned*>(comm->local + 2 * comm_slot_bytes(*comm));
   const vbt_b200_status st =
       reduce_impl(op, out, nullptr, shard, dims, ndims, keepdim, workspace, workspace_bytes,
                   (flags & VBT_B200_PARTIAL_WS_ZEROED) != 0, comm->rank == first_owner_rank, stream, &x);
