@@ -338,9 +338,6 @@ __global__ void __launch_bounds__(kThreads) row_warp_kernel(const __grid_constan
   if (row >= p.rows) return;
   const int lane = threadIdx.x & 31;
   const T* x = static_cast<const T*>(p.x) + p.kept.offset(static_cast<uint32_t>(row));
-  // the slice's element 0 (the NaN rule of max / min needs it at the end): fetched here, with the
-  // first loads, so that it is not a dependent round trip in the block's tail
-  const A first = lane == 0 ? widen(x[0]) : A(0);
   typename R::acc_t acc = R::init();
   const int64_t nvec = p.n / V;
   using idx_t = typename R::idx_t;
@@ -356,7 +353,7 @@ __global__ void __launch_bounds__(kThreads) row_warp_kernel(const __grid_constan
     if (i < p.n) R::accum(acc, widen(x[i]), static_cast<idx_t>(i));
   }
   acc = warp_reduce<R>(acc);
-  if (lane == 0) finalize<R, A>(p.o, row, acc, first);
+  if (lane == 0) finalize<R, A>(p.o, row, acc, widen(x[0]));
 }
 
 // `splits` blocks per slice (grid = rows x splits).  One sweep of a slice's blocks covers
@@ -373,7 +370,6 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
   const int64_t row = blockIdx.x;
   const int split = blockIdx.y;
   const T* x = static_cast<const T*>(p.x) + p.kept.offset(static_cast<uint32_t>(row));
-  const A first = threadIdx.x == 0 ? widen(x[0]) : A(0);  // fetched with the first loads, not in the tail
   acc_t acc[U];
 #pragma unroll
   for (int u = 0; u < U; ++u) acc[u] = R::init();
@@ -424,11 +420,11 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
   if (p.splits == 1) {
     if constexpr (kCanExchange<R>) {
       if (p.o.x.world > 0) {
-        exchange_finalize<R>(p.o, static_cast<int>(row), 1, 0, threadIdx.x == 0, a, row, first);
+        exchange_finalize<R>(p.o, static_cast<int>(row), 1, 0, threadIdx.x == 0, a, row, widen(x[0]));
         return;
       }
     }
-    if (threadIdx.x == 0) finalize<R, A>(p.o, row, a, first);
+    if (threadIdx.x == 0) finalize<R, A>(p.o, row, a, widen(x[0]));
     return;
   }
   acc_t* part = static_cast<acc_t*>(p.ws_partials) + row * p.splits;
@@ -450,11 +446,11 @@ __global__ void __launch_bounds__(kThreads) row_block_kernel(const __grid_consta
   if (threadIdx.x == 0) p.ws_counters[row] = 0u;  // every block of this slice has drawn its ticket: leave the counter as found
   if constexpr (kCanExchange<R>) {
     if (p.o.x.world > 0) {
-      exchange_finalize<R>(p.o, static_cast<int>(row), 1, 0, threadIdx.x == 0, f, row, first);
+      exchange_finalize<R>(p.o, static_cast<int>(row), 1, 0, threadIdx.x == 0, f, row, widen(x[0]));
       return;
     }
   }
-  if (threadIdx.x == 0) finalize<R, A>(p.o, row, f, first);
+  if (threadIdx.x == 0) finalize<R, A>(p.o, row, f, widen(x[0]));
 }
 
 // ------------------------------------------------------------------------------------
@@ -487,14 +483,6 @@ __global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ C
   const T* x = static_cast<const T*>(p.x) + p.outer.offset(static_cast<uint32_t>(a)) + col;
   const int64_t r0 = static_cast<int64_t>(split) * p.chunk;
   const int64_t r1 = min(p.Rn, r0 + p.chunk);
-  // element 0 of the column this thread will finalize (thread c owns column c of the tile): fetched
-  // here, with the first loads, so that the NaN rule of max / min costs no round trip in the tail
-  A first = A(0);
-  {
-    const int64_t fc = static_cast<int64_t>(ct) * (32 * V) + threadIdx.x;
-    if (threadIdx.x < 32 * V && fc < p.B)
-      first = widen(static_cast<const T*>(p.x)[p.outer.offset(static_cast<uint32_t>(a)) + fc]);
-  }
   acc_t acc[V];
 #pragma unroll
   for (int j = 0; j < V; ++j) acc[j] = R::init();
@@ -531,14 +519,16 @@ __global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ C
     for (int ww = 0; ww < kWarps; ++ww) colacc = R::combine(colacc, smem[ww][c]);
   }
   const int64_t out_i = a * p.B + gcol;
+  const T* first_p = static_cast<const T*>(p.x) + p.outer.offset(static_cast<uint32_t>(a)) + gcol;
   if (p.splits == 1) {
     if constexpr (kCanExchange<R>) {
       if (p.o.x.world > 0) {
-        exchange_finalize<R>(p.o, static_cast<int>(a * p.ctiles + ct), ncols, c, owner, colacc, out_i, first);
+        exchange_finalize<R>(p.o, static_cast<int>(a * p.ctiles + ct), ncols, c, owner, colacc, out_i,
+                             owner ? widen(*first_p) : 0.f);
         return;
       }
     }
-    if (owner) finalize<R, A>(p.o, out_i, colacc, first);
+    if (owner) finalize<R, A>(p.o, out_i, colacc, widen(*first_p));
     return;
   }
   acc_t* part = static_cast<acc_t*>(p.ws_partials) +
@@ -556,24 +546,26 @@ __global__ void __launch_bounds__(kThreads) col_kernel(const __grid_constant__ C
   if (threadIdx.x == 0) p.ws_counters[a * p.ctiles + ct] = 0u;  // all tickets drawn: leave the counter as found
   acc_t f = R::init();
   if (owner) {
-    // chunk order, eight independent loads in flight at a time (a loop of load-then-combine
-    // would pay one L2 round trip per chunk)
-    for (int s0 = 0; s0 < p.splits; s0 += 8) {
-      acc_t t[8];
+    // chunk order, kFoldBatch independent loads in flight at a time (a loop of load-then-combine
+    // would pay one L2 round trip per chunk; the usual 37 chunks take three trips)
+    constexpr int kFoldBatch = sizeof(acc_t) <= 8 ? 16 : 8;
+    for (int s0 = 0; s0 < p.splits; s0 += kFoldBatch) {
+      acc_t t[kFoldBatch];
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
+      for (int u = 0; u < kFoldBatch; ++u)
         t[u] = s0 + u < p.splits ? ld_cg(part + static_cast<int64_t>(s0 + u) * ncols + c) : R::init();
 #pragma unroll
-      for (int u = 0; u < 8; ++u) f = R::combine(f, t[u]);
+      for (int u = 0; u < kFoldBatch; ++u) f = R::combine(f, t[u]);
     }
   }
   if constexpr (kCanExchange<R>) {
     if (p.o.x.world > 0) {
-      exchange_finalize<R>(p.o, static_cast<int>(a * p.ctiles + ct), ncols, c, owner, f, out_i, first);
+      exchange_finalize<R>(p.o, static_cast<int>(a * p.ctiles + ct), ncols, c, owner, f, out_i,
+                           owner ? widen(*first_p) : 0.f);
       return;
     }
   }
-  if (owner) finalize<R, A>(p.o, out_i, f, first);
+  if (owner) finalize<R, A>(p.o, out_i, f, widen(*first_p));
 }
 
 // COL through a thread-block cluster: the blocks that split R for one column tile form a
@@ -595,12 +587,6 @@ __global__ void __launch_bounds__(kThreads) col_cluster_kernel(const __grid_cons
   const T* x = static_cast<const T*>(p.x) + p.outer.offset(static_cast<uint32_t>(a)) + col;
   const int64_t r0 = static_cast<int64_t>(split) * p.chunk;
   const int64_t r1 = min(p.Rn, r0 + p.chunk);
-  A first = A(0);  // as in col_kernel; only the cluster's first block uses it
-  if (split == 0) {
-    const int64_t fc = static_cast<int64_t>(ct) * (32 * V) + threadIdx.x;
-    if (threadIdx.x < 32 * V && fc < p.B)
-      first = widen(static_cast<const T*>(p.x)[p.outer.offset(static_cast<uint32_t>(a)) + fc]);
-  }
   acc_t acc[V];
 #pragma unroll
   for (int j = 0; j < V; ++j) acc[j] = R::init();
@@ -652,7 +638,8 @@ __global__ void __launch_bounds__(kThreads) col_cluster_kernel(const __grid_cons
     acc_t f = R::init();
     const unsigned nb = cluster.num_blocks();
     for (unsigned r = 0; r < nb; ++r) f = R::combine(f, cluster.map_shared_rank(part_s, r)[c]);  // chunk order
-    finalize<R, A>(p.o, a * p.B + gcol, f, first);
+    const T* first_p = static_cast<const T*>(p.x) + p.outer.offset(static_cast<uint32_t>(a)) + gcol;
+    finalize<R, A>(p.o, a * p.B + gcol, f, widen(*first_p));
   }
   cluster.sync();  // nobody leaves while block 0 may still read its shared memory
 }
@@ -676,12 +663,11 @@ __global__ void __launch_bounds__(kThreads) generic_kernel(const __grid_constant
   if (oi >= p.nout) return;
   const int lane = threadIdx.x & 31;
   const T* x = static_cast<const T*>(p.x) + p.kept.offset(static_cast<uint32_t>(oi));
-  const A first = lane == 0 ? widen(x[0]) : A(0);
   typename R::acc_t acc = R::init();
   for (uint32_t j = lane; j < p.nred; j += 32)
     R::accum(acc, widen(x[p.red.offset(j)]), static_cast<typename R::idx_t>(j));
   acc = warp_reduce<R>(acc);
-  if (lane == 0) finalize<R, A>(p.o, oi, acc, first);
+  if (lane == 0) finalize<R, A>(p.o, oi, acc, widen(x[0]));
 }
 
 // fills an output with a constant (empty reduction domains)
