@@ -202,14 +202,14 @@ template <> struct AddVec<int32_t> {
 // registers and sends one vector atomic per run and 16-byte chunk.  With 1024 updates per block
 // the Zipf(1.1) workload issues 0.53 atomics per update (256 per block: 0.65; 4096: 0.43, but
 // the sort and the lower occupancy cost more than that saves).
-// The value rows come in by asynchronous copies: every warp owns a ring of kRing row slots in
-// shared memory and keeps kRing rows in flight while it adds up the oldest one.  A lane reads
+// The value rows come in by asynchronous copies: every warp owns a ring of row slots in shared
+// memory (8 KiB: eight rows of 1 KiB) and keeps that many rows in flight while it adds up the oldest one.  A lane reads
 // back only the 16-byte chunks it copied itself, so the ring needs no barrier:
 // cp.async.wait_group orders a lane's own copies.  K = 16-byte chunks per lane and row pass.
 #ifndef VB_SCATTER_RING_DEPTH
 #define VB_SCATTER_RING_DEPTH 8
 #endif
-constexpr int kRing = VB_SCATTER_RING_DEPTH;
+constexpr int kRingBytesPerWarp = VB_SCATTER_RING_DEPTH * 1024;  // 8 rows of 1 KiB in flight per warp; fewer, wider slots for wider rows
 #ifndef VB_SCATTER_BATCH
 #define VB_SCATTER_BATCH 1024
 #endif
@@ -219,6 +219,7 @@ template <class T, int K>
 __global__ void __launch_bounds__(kThreads) scatter_add_ring_kernel(const __grid_constant__ ScatterParams p) {
   using AV = AddVec<T>;
   using acc_t = typename AV::acc_t;
+  constexpr int kRing = kRingBytesPerWarp / (K * 512) > 8 ? 8 : kRingBytesPerWarp / (K * 512);
   extern __shared__ __align__(16) unsigned char ring_raw[];  // [sorted keys][warp][slot][K * 32 lanes] 16-byte chunks
   uint64_t* const keys = reinterpret_cast<uint64_t*>(ring_raw);  // (row << kPosBits) | position, sorted
   unsigned char* const ring0 = ring_raw + kRingBatch * 8;
@@ -555,104 +556,92 @@ struct SortedScatterParams {
   uint32_t cpr;
 };
 
-template <class T> struct PlainStore;
-template <> struct PlainStore<float> {
-  __device__ static void st(char* dst, const float4& a) { *reinterpret_cast<float4*>(dst) = a; }
-};
-template <> struct PlainStore<int64_t> {
-  __device__ static void st(char* dst, const AddVec<int64_t>::acc_t& a) {
-    *reinterpret_cast<ulonglong2*>(dst) = make_ulonglong2(a.a, a.b);
-  }
-};
-template <> struct PlainStore<int32_t> {
-  __device__ static void st(char* dst, const uint4& a) { *reinterpret_cast<uint4*>(dst) = a; }
-};
-
-// One warp per slice of 32 sorted entries.  A run (equal keys) that lies wholly inside the
-// slice has this warp as the only writer of its row: the row's old contents are fetched
-// TOGETHER with the run's first update (so the read of the destination is one more load in
-// flight, not a dependent round trip at the end of the run), the updates are added to them in
-// update order, and the sum is stored back.  Runs that continue from the previous slice or
-// into the next one are summed from zero and added with atomics.
+// One warp per slice of 32 sorted entries.  The warp walks the slice in order, adds up every
+// run of equal rows in registers (in update order) and adds the run's sum to the row once, with
+// the same vector atomics as the other engine -- exact for the integer tables this engine is
+// the default for; a float row receives `row + (u1 + u2 + ...)`.  A run that spills into the
+// next slice is finished by that slice's warp with an add of its own.  The value rows arrive
+// through the warp's ring of kSortedRing shared-memory slots filled by asynchronous copies, so
+// kSortedRing rows are in flight per warp at all times (the register form this replaces had two).
+constexpr int kSortedRing = 8;
 template <class T, int K>
 __global__ void __launch_bounds__(kThreads) scatter_add_sorted_kernel(const __grid_constant__ SortedScatterParams p) {
   using AV = AddVec<T>;
   using acc_t = typename AV::acc_t;
-  const int lane = threadIdx.x & 31;
-  const int64_t slice = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+  extern __shared__ __align__(16) unsigned char ring_raw[];  // [warp][slot][K * 32 lanes] 16-byte chunks
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int64_t slice = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + w;
   const int64_t s0 = slice * 32;
   if (s0 >= p.N) return;
   const uint32_t skip = static_cast<uint32_t>(p.V);
   const int64_t me = s0 + lane;
   const uint32_t my_key = me < p.N ? p.keys[me] : skip;
   const uint32_t my_pos = me < p.N ? p.vals[me] : 0u;
-  // does the slice's first run continue the previous slice's last one / its last run go on?
-  const uint32_t prev_last = s0 > 0 ? p.keys[s0 - 1] : 0xffffffffu;
-  const uint32_t next_first = s0 + 32 < p.N ? p.keys[s0 + 32] : 0xffffffffu;
   const int64_t row_bytes = static_cast<int64_t>(p.cpr) * 16;
-  constexpr int U = 2;
+  constexpr uint32_t kSlotBytes = K * 32 * 16;
+  const uint32_t my_ring = smem_addr(ring_raw) + static_cast<uint32_t>(w) * (kSortedRing * kSlotBytes) + static_cast<uint32_t>(lane) * 16u;
   for (uint32_t cb = 0; cb < p.cpr; cb += 32 * K) {
     acc_t acc[K];
 #pragma unroll
     for (int k = 0; k < K; ++k) acc[k] = AV::zero();
-    uint32_t cur = skip;      // row of the open run (skip = none)
-    bool cur_shared = false;  // the open run also has updates in a neighbouring slice
-    auto flush = [&](uint32_t row, bool shared) {
+    uint32_t cur = skip;  // row of the open run (skip = none)
+    auto flush = [&](uint32_t row) {
       char* dst = p.table + static_cast<int64_t>(row) * row_bytes;
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const uint32_t c = cb + k * 32 + lane;
-        if (c < p.cpr) {
-          if (shared) AV::flush(dst + static_cast<int64_t>(c) * 16, acc[k]);
-          else PlainStore<T>::st(dst + static_cast<int64_t>(c) * 16, acc[k]);
-        }
+        if (c < p.cpr) AV::flush(dst + static_cast<int64_t>(c) * 16, acc[k]);
         acc[k] = AV::zero();
       }
     };
-    uint32_t key_before = 0xffffffffu;  // key of the entry in front of the group (none before entry 0)
-    for (int e0 = 0; e0 < 32; e0 += U) {
-      uint32_t key[U];
-      bool head[U], shared[U];
-      int4 raw[U][K], old[U][K];
+    // entry e -> ring slot e % kSortedRing; one commit group per entry, empty for skipped ones
+    auto issue = [&](int e) {
+      const uint32_t key = __shfl_sync(0xffffffffu, my_key, e & 31);
+      const uint32_t pos = __shfl_sync(0xffffffffu, my_pos, e & 31);
+      if (e < 32 && key != skip) {
+        const char* src = p.values + static_cast<int64_t>(pos) * row_bytes;
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        key[u] = __shfl_sync(0xffffffffu, my_key, e0 + u);
-        const uint32_t pos = __shfl_sync(0xffffffffu, my_pos, e0 + u);
-        const uint32_t before = u == 0 ? key_before : key[u - 1];
-        head[u] = key[u] != skip && (e0 + u == 0 || key[u] != before);
-        shared[u] = (e0 + u == 0 && key[u] == prev_last) || key[u] == next_first;
-        if (key[u] != skip) {
-          const char* src = p.values + static_cast<int64_t>(pos) * row_bytes;
-          const char* dst = p.table + static_cast<int64_t>(key[u]) * row_bytes;
-          const bool fetch_old = head[u] && !shared[u];
+        for (int k = 0; k < K; ++k) {
+          const uint32_t c = cb + k * 32 + lane;
+          if (c < p.cpr)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(my_ring + (e % kSortedRing) * kSlotBytes + k * 512u),
+                         "l"(src + static_cast<int64_t>(c) * 16)
+                         : "memory");
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int e = 0; e < kSortedRing; ++e) issue(e);
+#pragma unroll 1
+    for (int e0 = 0; e0 < 32; e0 += kSortedRing) {
+#pragma unroll
+      for (int r = 0; r < kSortedRing; ++r) {
+        const int e = e0 + r;
+        asm volatile("cp.async.wait_group %0;" ::"n"(kSortedRing - 1) : "memory");
+        const uint32_t key = __shfl_sync(0xffffffffu, my_key, e);
+        if (key != skip) {  // skipped updates sort to the very end
+          if (key != cur) {
+            if (cur != skip) flush(cur);
+            cur = key;
+          }
 #pragma unroll
           for (int k = 0; k < K; ++k) {
             const uint32_t c = cb + k * 32 + lane;
-            raw[u][k] = c < p.cpr ? *reinterpret_cast<const int4*>(src + static_cast<int64_t>(c) * 16)
-                                  : make_int4(0, 0, 0, 0);
-            old[u][k] = (fetch_old && c < p.cpr) ? *reinterpret_cast<const int4*>(dst + static_cast<int64_t>(c) * 16)
-                                                 : make_int4(0, 0, 0, 0);
+            if (c < p.cpr) {
+              int4 raw;
+              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                           : "r"(my_ring + r * kSlotBytes + k * 512u));
+              AV::add(acc[k], raw);
+            }
           }
         }
-      }
-      key_before = key[U - 1];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (key[u] == skip) continue;  // skipped updates sort to the very end
-        if (head[u]) {
-          if (cur != skip) flush(cur, cur_shared);
-          cur = key[u];
-          cur_shared = shared[u];
-          if (!cur_shared) {
-#pragma unroll
-            for (int k = 0; k < K; ++k) AV::add(acc[k], old[u][k]);  // start from the row's contents
-          }
-        }
-#pragma unroll
-        for (int k = 0; k < K; ++k) AV::add(acc[k], raw[u][k]);
+        issue(e + kSortedRing);  // the slot just read is free again (same lane wrote and read it)
       }
     }
-    if (cur != skip) flush(cur, cur_shared);
+    if (cur != skip) flush(cur);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
 }
 
@@ -731,27 +720,6 @@ __global__ void __launch_bounds__(kThreads) lastdim_kernel(const __grid_constant
 // tile are split over blockIdx.y (each such block stages the rows again; they come from L2).
 // shared-memory accesses by 32-bit shared-space address: the inner loop below is issue-bound, and
 // a generic pointer costs it an address conversion per access
-template <class E> __device__ __forceinline__ E lds(uint32_t a);
-template <> __device__ __forceinline__ uint8_t lds<uint8_t>(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
-  return static_cast<uint8_t>(v);
-}
-template <> __device__ __forceinline__ uint16_t lds<uint16_t>(uint32_t a) {
-  uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
-  return v;
-}
-template <> __device__ __forceinline__ uint32_t lds<uint32_t>(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-template <> __device__ __forceinline__ uint64_t lds<uint64_t>(uint32_t a) {
-  unsigned long long v;
-  asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v) : "r"(a));
-  return static_cast<uint64_t>(v);
-}
 __device__ __forceinline__ void sts(uint32_t a, uint8_t v) {
   asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(static_cast<uint32_t>(v)) : "memory");
 }
@@ -1305,9 +1273,10 @@ vbt_b200_status scatter_add_typed(const ScatterParams& p, const ScatterElemParam
                                   cudaStream_t s) {
   if (chunked) {
     const unsigned g = static_cast<unsigned>((p.N + kRingBatch - 1) / kRingBatch);
-    // sorted keys + a ring of kRing row slots per warp; more than 48 KiB needs the per-function opt-in
+    // sorted keys + a ring of row slots per warp; more than 48 KiB needs the per-function opt-in
     auto go = [&](auto kern, int K) -> vbt_b200_status {
-      const size_t smem = static_cast<size_t>(kRingBatch) * 8 + static_cast<size_t>(kThreads / 32) * kRing * K * 512;
+      const int ring = std::min(8, kRingBytesPerWarp / (K * 512));
+      const size_t smem = static_cast<size_t>(kRingBatch) * 8 + static_cast<size_t>(kThreads / 32) * ring * K * 512;
       static std::mutex mu;
       static bool done[3][64] = {};
       int dev = 0;
@@ -1403,8 +1372,24 @@ template <class T>
 void launch_sorted(const SortedScatterParams& p, cudaStream_t s) {
   const int64_t slices = (p.N + 31) / 32;
   const unsigned g = static_cast<unsigned>((slices + kThreads / 32 - 1) / (kThreads / 32));
-  if (p.cpr <= 32) scatter_add_sorted_kernel<T, 1><<<g, kThreads, 0, s>>>(p);
-  else scatter_add_sorted_kernel<T, 2><<<g, kThreads, 0, s>>>(p);
+  // a ring of kSortedRing row slots per warp: 32 KiB (K = 1) or 64 KiB (K = 2, needs the opt-in)
+  if (p.cpr <= 32) {
+    scatter_add_sorted_kernel<T, 1><<<g, kThreads, (kThreads / 32) * kSortedRing * 512, s>>>(p);
+  } else {
+    constexpr int kSmem = (kThreads / 32) * kSortedRing * 1024;
+    static std::mutex mu;
+    static bool done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+      std::lock_guard<std::mutex> lk(mu);
+      if (dev < 0 || dev >= 64 || !done[dev]) {
+        cudaFuncSetAttribute(scatter_add_sorted_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (dev >= 0 && dev < 64) done[dev] = true;
+      }
+    }
+    scatter_add_sorted_kernel<T, 2><<<g, kThreads, kSmem, s>>>(p);
+  }
 }
 
 vbt_b200_status scatter_add_rows_sorted(const char* name, const vbt_b200_tensor* table,
