@@ -615,6 +615,20 @@ def run_ours(args):
                         "elements_per_s": ne / (ms * 1e-3), "gb_per_s_whole_job": ne * 2 / (ms * 1e-3) / 1e9})
         del xb, fb, prep_mean
 
+    # ---- vt::fabric_add with one operand on a peer GPU (rank 0 drives GPUs 0 and 1; the other
+    # ranks wait on the rendezvous store, not on a device-side barrier)
+    fabric_bin = None
+    if n > 1 and not args.no_sharded_extras:
+        store = dist.distributed_c10d._get_default_store()
+        if rank == 0:
+            try:
+                fabric_bin = fabric_binary_leg(torch, ops, dev)
+            except Exception as ex:
+                fabric_bin = [{"op": "fabric_add", "error": str(ex)[:200]}]
+            store.set("vbt_b200_fabric_leg_done", "1")
+        else:
+            store.wait(["vbt_b200_fabric_leg_done"])
+
     # ---- e2e: the shard starts in pinned host memory every step
     e2e = None
     if not args.no_e2e:
@@ -671,6 +685,8 @@ def run_ours(args):
                        "reference_sum_on_sample": ref_parity},
             "sharded_ops": sharded,
         }
+        if fabric_bin is not None:
+            line["fabric_elementwise"] = fabric_bin
         if cpu is not None:
             line["cpu_baseline"] = cpu
         if suite is not None:
@@ -705,6 +721,37 @@ def bind_to_gpu_numa_node(gpu_index: int):
         return node
     except Exception:
         return None
+
+
+def fabric_binary_leg(torch, ops, dev):
+    """vt::fabric_add on two GPUs of one process: a and the result on `dev`, b on the next GPU.
+    Peer-load mode reads b in place over NVLink inside the elementwise kernel; copy-fallback
+    copies it to local scratch first and then runs the local kernel."""
+    d0 = dev.index
+    d1 = (d0 + 1) % torch.cuda.device_count()
+    nel = 1 << 28
+    a = torch.randn(nel, device=dev)
+    b = torch.randn(nel, device=torch.device("cuda", d1))
+    out = torch.empty_like(a)
+    want = a + b.to(dev)
+    res = []
+    for label, policy in (("peer_load", False), ("copy_fallback", "always")):
+        _, mode = ops.fabric_binary("add", a, b, compute_device=d0, use_copy_fallback=policy, out=out)
+        torch.cuda.synchronize(dev)
+        ok = bool(torch.equal(out, want))
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(5)]
+        for e0, e1 in evs:
+            e0.record()
+            ops.fabric_binary("add", a, b, compute_device=d0, use_copy_fallback=policy, out=out)
+            e1.record()
+        torch.cuda.synchronize(dev)
+        ms = sorted(e0.elapsed_time(e1) for e0, e1 in evs)[2]
+        res.append({"op": "fabric_add fp32", "config": f"[{nel}] a, out on GPU {d0}; b on GPU {d1}", "mode": mode,
+                    "requested": label, "ms": ms, "link_gbs": nel * 4 / (ms * 1e-3) / 1e9,
+                    "frac_of_measured_peer_copy_770gbs": nel * 4 / (ms * 1e-3) / 1e9 / 770.0, "matches_local_add": ok,
+                    "note": "bound by NVLink: 4 bytes of b per element cross the link (measured peer copy on this pool: "
+                            "770 GB/s per direction)"})
+    return res
 
 
 def run_e2e(torch, dist, ops, shard, n, args):

@@ -114,7 +114,7 @@ struct ExtR {
   using idx_t = int32_t;  // unused
   static constexpr bool kIndexed = false;
   __device__ static acc_t init() { return MAX ? lowest<A>() : highest<A>(); }
-  __device__ static void accum(acc_t& a, A v, idx_t) { if (MAX ? (v > a) : (v < a)) a = v; }
+  __device__ static void accum(acc_t& a, A v, idx_t) { a = (MAX ? (v > a) : (v < a)) ? v : a; }
   __device__ static acc_t combine(acc_t a, acc_t b) { return (MAX ? (b > a) : (b < a)) ? b : a; }
 };
 // argmax / argmin: first extremum wins (tensor_bindings.cc:630-682).  I is the index type
@@ -330,30 +330,52 @@ struct RowParams {
   OutSpec o;
 };
 
-// one warp per slice; n is small
+// One warp per slice: short slices, and -- for argmax / argmin -- slices of up to 32 KiB when
+// there are enough of them to fill the GPU.  A block per 16 KiB slice spends most of its
+// instructions on the reduction tree (eight warp trees, a shared-memory stage, two barriers for
+// sixteen elements per thread: the ncu capture of argmax on the C1 shape showed 77 % of the
+// issue slots busy); a warp that walks the whole slice pays one tree.  U vectors in flight per
+// lane, four accumulators; every accumulator sees its indices in increasing order.
 template <class T, class R, int V>
 __global__ void __launch_bounds__(kThreads) row_warp_kernel(const __grid_constant__ RowParams p) {
   using A = typename Widen<T>::type;
+  using acc_t = typename R::acc_t;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
   if (row >= p.rows) return;
   const int lane = threadIdx.x & 31;
   const T* x = static_cast<const T*>(p.x) + p.kept.offset(static_cast<uint32_t>(row));
-  typename R::acc_t acc = R::init();
+  constexpr int U = V >= 8 ? 4 : 8;
+  acc_t acc[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) acc[u] = R::init();
   const int64_t nvec = p.n / V;
   using idx_t = typename R::idx_t;
-  for (int64_t i = lane; i < nvec; i += 32) {
+  int64_t i = lane;
+  for (; i + (U - 1) * 32 < nvec; i += U * 32) {
+    A w[U][V];
+#pragma unroll
+    for (int u = 0; u < U; ++u) load_widen<T, V>(x + (i + u * 32) * V, w[u]);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const idx_t base = static_cast<idx_t>(i + u * 32) * V;
+#pragma unroll
+      for (int j = 0; j < V; ++j) R::accum(acc[u & 3], w[u][j], base + j);
+    }
+  }
+  for (; i < nvec; i += 32) {
     A w[V];
     load_widen<T, V>(x + i * V, w);
     const idx_t base = static_cast<idx_t>(i) * V;
 #pragma unroll
-    for (int j = 0; j < V; ++j) R::accum(acc, w[j], base + j);
+    for (int j = 0; j < V; ++j) R::accum(acc[0], w[j], base + j);
   }
   if constexpr (V > 1) {
-    const int64_t i = nvec * V + lane;
-    if (i < p.n) R::accum(acc, widen(x[i]), static_cast<idx_t>(i));
+    const int64_t t = nvec * V + lane;
+    if (t < p.n) R::accum(acc[0], widen(x[t]), static_cast<idx_t>(t));
   }
-  acc = warp_reduce<R>(acc);
-  if (lane == 0) finalize<R, A>(p.o, row, acc, widen(x[0]));
+  acc_t a = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
+  a = warp_reduce<R>(a);
+  if (lane == 0) finalize<R, A>(p.o, row, a, widen(x[0]));
 }
 
 // `splits` blocks per slice (grid = rows x splits).  One sweep of a slice's blocks covers
@@ -774,7 +796,12 @@ vbt_b200_status make_plan(int op, const vbt_b200_tensor& self, const int64_t* di
     // ROW
     const int64_t n = pl->rsize[0];
     pl->V = (base % 16 == 0 && all_multiple(pl->kstride, pl->nk, vmax)) ? vmax : 1;
-    if (n * es <= 4096 && pl->nout >= 64) {
+    // argmax / argmin also take it for slices of up to 32 KiB when there are enough of them: their
+    // (value, index) reduction tree is what a block per 16 KiB slice spends its time on (15.3 us
+    // against 12.7 us on [4096,4096] fp32); sum and max are faster with a block per slice there
+    // (11.3 against 12.3 us: a block asks for its 16 KiB at once)
+    const bool indexed = op == OP_ARGMAX || op == OP_ARGMIN;
+    if ((n * es <= 4096 && pl->nout >= 64) || (indexed && n * es <= 32768 && pl->nout >= int64_t{sms} * 16)) {
       pl->shape = kRowWarp;
       return VBT_B200_OK;
     }
