@@ -578,6 +578,7 @@ VBT_B200_API vbt_b200_status vbt_b200_scale_cast(void* out, int32_t out_dtype, c
 #define VBT_B200_RK_COL_CLUSTER 4  /* the same folded inside a thread-block cluster         */
 #define VBT_B200_RK_GENERIC 5
 #define VBT_B200_RK_FILL 6         /* empty reduction domain: constant fill                 */
+#define VBT_B200_RK_ROW_ONCE 7     /* a 128-thread block per slice, one unrolled pass       */
 /* INDEX: */
 #define VBT_B200_IK_ROWS_COPY 1
 #define VBT_B200_IK_ROWS_COPY_ELEM 2

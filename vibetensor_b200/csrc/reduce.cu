@@ -45,6 +45,9 @@ constexpr size_t kTicketBytes = 4096;  // fixed ticket area at the start of ever
 #define VB_ROW_U 4
 #endif
 constexpr int kRowU = VB_ROW_U;
+#ifndef VB_COL_CLUSTER
+#define VB_COL_CLUSTER 1
+#endif
 // blocks per SM the long-slice ROW kernel is split into when few outputs share the GPU
 #ifndef VB_ROW_BLOCKS_PER_SM
 #define VB_ROW_BLOCKS_PER_SM 4
@@ -376,6 +379,71 @@ __global__ void __launch_bounds__(kThreads) row_warp_kernel(const __grid_constan
   acc_t a = R::combine(R::combine(acc[0], acc[1]), R::combine(acc[2], acc[3]));
   a = warp_reduce<R>(a);
   if (lane == 0) finalize<R, A>(p.o, row, a, widen(x[0]));
+}
+
+// A block per slice that one unrolled pass covers (at most 256 threads x 4 vectors): no loop, no
+// sweep arithmetic, 32-bit indices, and the slice's first element taken from the vector thread 0
+// holds anyway.  The general kernel below executes about 200 warp instructions per warp for the
+// twenty that load and add a 16 KiB slice's share (ncu on the C1 shapes: 6.4 M warp instructions,
+// issue slots 55 % busy), and its run time follows the instruction count -- sum 11.3 us, max
+// 12.9 us, argmax 15.3 us on the same 64 MiB -- so the fixed part is what this kernel cuts:
+// straight-line code, and half the warps for slices of 512 vectors and less (measured on
+// [4096,4096] fp32: max 12.5 -> 11.0 us, mean 11.7 -> 11.3 us; bf16 sum 10.4 -> 6.8 us).
+#ifndef VB_ROW_ONCE
+#define VB_ROW_ONCE 1
+#endif
+constexpr int kOnceU = 4;  // vectors per thread: 256 threads for slices of more than 512 vectors, else 128
+template <class T, class R, int V, int kOnceThreads>
+__global__ void __launch_bounds__(kOnceThreads) row_once_kernel(const __grid_constant__ RowParams p) {
+  using A = typename Widen<T>::type;
+  using acc_t = typename R::acc_t;
+  using idx_t = typename R::idx_t;
+  constexpr int U = kOnceU;
+  constexpr int kOnceWarps = kOnceThreads / 32;
+  __shared__ acc_t smem[kOnceWarps];
+  const uint32_t row = blockIdx.x;
+  const int t = threadIdx.x;
+  const T* x = static_cast<const T*>(p.x) + (p.kept.n == 1 ? static_cast<int64_t>(row) * p.kept.stride[0] : p.kept.offset(row));
+  const uint32_t n = static_cast<uint32_t>(p.n), nvec = n / V;
+  A w[U][V];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const uint32_t iv = static_cast<uint32_t>(u) * kOnceThreads + t;
+    if (iv < nvec) {
+      load_widen<T, V>(x + iv * V, w[u]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) w[u][j] = A(0);
+    }
+  }
+  acc_t acc[2] = {R::init(), R::init()};
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const uint32_t iv = static_cast<uint32_t>(u) * kOnceThreads + t;
+    if (iv < nvec) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) R::accum(acc[u & 1], w[u][j], static_cast<idx_t>(iv * V + j));
+    }
+  }
+  A first = w[0][0];  // thread 0: element 0 of the slice, when the slice has a whole vector
+  if constexpr (V > 1) {
+    const uint32_t te = nvec * V + t;  // elements after the last whole vector
+    if (te < n) {
+      const A v = widen(x[te]);
+      R::accum(acc[1], v, static_cast<idx_t>(te));
+      if (nvec == 0) first = v;
+    }
+  }
+  acc_t a = R::combine(acc[0], acc[1]);
+  a = warp_reduce<R>(a);
+  const int lane = t & 31, wi = t >> 5;
+  if (lane == 0) smem[wi] = a;
+  __syncthreads();
+  if (t == 0) {
+#pragma unroll
+    for (int k = 1; k < kOnceWarps; ++k) a = R::combine(a, smem[k]);
+    finalize<R, A>(p.o, row, a, first);
+  }
 }
 
 // `splits` blocks per slice (grid = rows x splits).  One sweep of a slice's blocks covers
@@ -852,7 +920,7 @@ vbt_b200_status make_plan(int op, const vbt_b200_tensor& self, const int64_t* di
         // up to 256 MiB of input and enough column tiles to fill the GPU with clusters of
         // <= 16 blocks: take the cluster path (the workspace stays sized as the fallback)
         const int64_t bytes = pl->nout * Rn * es;
-        if (bytes <= (int64_t{256} << 20) && Rn >= 512) {
+        if (VB_COL_CLUSTER && bytes <= (int64_t{256} << 20) && Rn >= 512) {
           int cl = 16;
           while (cl > 2 && static_cast<int64_t>(pl->ctiles) * A * cl > int64_t{sms} * 5) cl >>= 1;
           if (static_cast<int64_t>(pl->ctiles) * A * cl >= sms) pl->cluster = cl;
@@ -923,6 +991,16 @@ vbt_b200_status launch(const Plan& pl, const vbt_b200_tensor& self, const OutSpe
         }
       }
       dim3 g(static_cast<unsigned>(pl.nout), static_cast<unsigned>(pl.splits));
+      if (VB_ROW_ONCE && pl.splits == 1 && pl.V > 1 && o.x.world == 0 && pl.nred <= int64_t{256} * kOnceU * VMAX &&
+          pl.nout >= 64) {
+        const bool wide = pl.nred > int64_t{128} * kOnceU * VMAX;
+        if (wide) row_once_kernel<T, R, VMAX, 256><<<g.x, 256, 0, s>>>(p);
+        else row_once_kernel<T, R, VMAX, 128><<<g.x, 128, 0, s>>>(p);
+        VB_LAUNCH_CHECK();
+        note_launch(VBT_B200_FAMILY_REDUCE, VBT_B200_RK_ROW_ONCE, dim3(g.x), dim3(wide ? 256 : 128), pl.V, 1, 0, 1, pl.nout,
+                    pl.nred, 0, s);
+        return VBT_B200_OK;
+      }
       if (pl.V > 1) row_block_kernel<T, R, VMAX, kRowU><<<g, kThreads, 0, s>>>(p);
       else row_block_kernel<T, R, 1, kRowU><<<g, kThreads, 0, s>>>(p);
       VB_LAUNCH_CHECK();
