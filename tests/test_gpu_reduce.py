@@ -87,6 +87,61 @@ def test_half_types(ops, port, name, dtype, shape, dim):
     _check(ops, port, name, x, dtype, dim)
 
 
+ONCE = [  # (dtype, base shape, columns kept, kernel the sum takes: 7 = one-pass block per slice)
+    (torch.float32, (200, 2004), 2003, 7),    # 500 vectors + 3 tail elements, 128 threads
+    (torch.float32, (200, 1004), 1003, 1),    # 4 KiB and less: one warp per slice
+    (torch.float32, (64, 4096), 4096, 7),     # exactly 256 threads x 4 vectors
+    (torch.float32, (100, 4), 3, 1),          # no whole vector: the tail path holds element 0
+    (torch.float32, (70, 2052), 2049, 7),     # 512 vectors + 1: 256 threads, last pass nearly empty
+    (torch.bfloat16, (300, 8192), 8190, 7),   # 8-element vectors, 6 tail elements
+    (torch.int64, (128, 2048), 2047, 7),      # 2-element vectors
+    (torch.float32, (63, 4096), 4096, 2),     # fewer than 64 slices: the general block kernel
+    (torch.float32, (64, 4100), 4100, 2)]     # one vector too long for one pass
+
+
+@pytest.mark.parametrize("dtype,base,cols,kernel", ONCE)
+def test_one_pass_row_kernel(ops, port, dtype, base, cols, kernel):
+    """Slices of at most 1024 vectors with 64 or more outputs take the one-pass kernel (a block per
+    slice, straight-line code): whole and partial last vectors, both block sizes, every vector
+    width, ties and a NaN at position 0 for the extrema, and the shapes just outside its range."""
+    from vibetensor_b200 import _lib
+    rng = np.random.default_rng(51)
+    x = rand_storage(rng, base, dtype)
+    t = from_np(x, dtype)[:, :cols]
+    xv = np.ascontiguousarray(x[:, :cols])
+    for name in ("sum", "mean", "max", "min", "argmax", "argmin") if dtype != torch.int64 else ("sum", "max", "argmin"):
+        _check(ops, port, name, xv, dtype, -1, view=t)
+        if name == "sum":
+            info = _lib.last_launch_info()
+            assert (info.family, info.kernel) == (2, kernel), (info.family, info.kernel)
+    if dtype == torch.float32:
+        y = xv.copy()
+        y[::3, 0] = np.nan                       # NaN at position 0 wins for max / min ...
+        y[1::3, min(5, cols - 1)] = np.nan       # ... and is ignored anywhere else (rows that have both keep rule 1)
+        y[2::3, :] = 1.5                         # all ties: the first index
+        ty = torch.from_numpy(np.ascontiguousarray(y)).cuda()
+        for name in ("max", "min", "argmax", "argmin"):
+            _check(ops, port, name, np.ascontiguousarray(y), dtype, -1, view=ty)
+
+
+def test_argmax_long_slices_take_one_warp_per_slice(ops, port):
+    """argmax / argmin over many slices of 4 - 32 KiB: one warp per slice, four accumulators per lane;
+    ties across accumulators, lanes and the tail must still resolve to the first index."""
+    from vibetensor_b200 import _lib
+    rng = np.random.default_rng(52)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rows = sms * 16 + 5
+    for cols in (4096, 1500, 8190):
+        x = rng.integers(-3, 4, (rows, cols)).astype(np.float32)   # few distinct values: ties everywhere
+        x[7, :] = 2.0
+        x[8, 0] = np.nan
+        t = torch.from_numpy(x).cuda()
+        for name in ("argmax", "argmin"):
+            _check(ops, port, name, x, torch.float32, -1, view=t)
+            info = _lib.last_launch_info()
+            assert (info.family, info.kernel) == (2, 1), (info.family, info.kernel)
+
+
 def test_keepdim_and_multi_dim(ops, port, ref):
     x = GOLD["red3_x"]
     t = torch.from_numpy(x).cuda()
