@@ -351,8 +351,8 @@ VBT_B200_API vbt_b200_status vbt_b200_index_rows(const vbt_b200_tensor* out, con
  *                                             writers wins, as on the reference's CUDA path)
  * table[idx[i], :] += values[i, :]           (accumulate != 0; F32, I64, I32, BF16/F16)
  * table dense rows ([V, D], column stride 1), values [N, D] dense.  Duplicates are
- * pre-summed inside each thread block before one atomic per distinct row and column
- * vector reaches memory.  I64/I32 results are exact (wrap-around); F32 is order-free
+ * pre-summed inside each thread block (1024 consecutive updates, sorted by row in shared
+ * memory) before one atomic per distinct row and column vector reaches memory.  I64/I32 results are exact (wrap-around); F32 is order-free
  * only up to rounding.  Uses no scratch memory. */
 VBT_B200_API vbt_b200_status vbt_b200_index_put_rows(const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
                                         const vbt_b200_tensor* values, int32_t accumulate,
@@ -362,11 +362,12 @@ VBT_B200_API vbt_b200_status vbt_b200_index_put_rows(const vbt_b200_tensor* tabl
  * integers and for heavily repeated rows.  It does what the reference's opt-in sort +
  * reduce-by-key path does (advanced_index_put_make_kv_cuda_kernel + CUB SortPairs +
  * ReduceByKey + scatter, src/vbt/core/indexing_advanced_cuda.cu:1460-1557, :2888-3055) with
- * an LSD radix sort written here.  Each destination row is summed in update order by one
- * warp and written with a plain read-add-write; only rows with more updates than one warp's
- * slice (32) see atomics.  INT64 / INT32 exact; F32 bit-identical to a sequential loop for
- * every row updated from one slice when the row starts at zero.  `workspace` (16-byte
- * aligned, vbt_b200_index_put_rows_sorted_workspace_bytes(N) bytes, about 16 bytes per
+ * an LSD radix sort written here.  A warp walks 256 consecutive sorted updates, sums every run
+ * of equal rows in update order and adds the run's sum to the row once (row += u1 + u2 + ...);
+ * a run that crosses a slice boundary is finished by the next warp with an add of its own.
+ * INT64 / INT32 exact; F32 bit-identical to a sequential loop for every row that starts at
+ * zero (or is updated once) and whose updates lie in one slice.  `workspace` (16-byte
+ * aligned, vbt_b200_index_put_rows_sorted_workspace_bytes(N) bytes, about 18 bytes per
  * index) needs no initialisation.  Shapes the sorted kernels do not take (rows that are not
  * whole 16-byte chunks) are served by the atomic path with the same result. */
 VBT_B200_API size_t vbt_b200_index_put_rows_sorted_workspace_bytes(int64_t num_indices);
