@@ -10,6 +10,10 @@ sampling is stated in each test.
       output; scatter_add int64 bit-exact and fp32 within 1e-5 of the per-element mass, through
       both engines (atomics, sorted), with the oracle fed chunks of <= 390 625 indices in index
       order as the reference's 1e8-element cap forces (src/vbt/core/indexing_advanced.cc:100-103).
+      The reference's CUDA advanced-index form x[..., idx] on [4096, 65536] fp32 with 65 536
+      uniform int64 indices, and a bool mask of 2^28 elements turned into indices: 64 sampled
+      rows against the oracle plus the whole output against a second, independent gather;
+      the mask's indices against numpy on sampled windows plus count and monotonicity.
   C3  bf16 where(a > 0, a + b*c, 0) into the transpose(1,3) view of a [64,1024,512,128] output
       (seed 1): 64 sampled [128 x 1024] planes bit-exact, guard bands around the storage intact.
   C4  softmax / RMSNorm forward and backward on [32768,4096] and [262144,128], fp32 and bf16
@@ -109,6 +113,50 @@ def test_c2_scatter_add_int64_both_engines_bit_exact(ops, port, c2):
         ops.index_put_rows_(acc, ti, tu, accumulate=True, deterministic=deterministic)
         np.testing.assert_array_equal(acc.cpu().numpy(), want, err_msg=f"deterministic={deterministic}")
         del acc
+
+
+def test_c2_index_lastdim_at_size_sampled_rows_and_whole_output(ops, port):
+    """x[..., idx] at the bench shape: the register-output kernel with two index chunks.  64
+    sampled rows bit-exact against the oracle; every row against torch's own gather (an
+    independent implementation, here only as a second checker); wrapped negative indices."""
+    from vibetensor_b200 import _lib
+    rng = np.random.default_rng(5)
+    B, K0 = 4096, 65536
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    x = torch.randn((B, K0), device="cuda", generator=g)
+    idx = rng.integers(-K0, K0, K0).astype(np.int64)
+    ti = torch.from_numpy(idx).cuda()
+    got = ops.index_lastdim(x, ti)
+    info = _lib.last_launch_info()
+    assert (info.family, info.kernel) == (3, 9), "expected the register-output last-dim kernel"
+    rows = np.sort(rng.choice(B, 64, replace=False))
+    xs = x[torch.from_numpy(rows).cuda()].cpu().numpy()
+    np.testing.assert_array_equal(got[torch.from_numpy(rows).cuda()].cpu().numpy(), port.index_lastdim(xs, idx))
+    pos = torch.from_numpy(np.where(idx < 0, idx + K0, idx)).cuda()
+    for r0 in range(0, B, 512):   # in slabs: the second checker's output is as large as ours
+        assert torch.equal(got[r0:r0 + 512], x[r0:r0 + 512][:, pos]), f"rows {r0}.."
+
+
+def test_c2_mask_to_indices_at_size(ops):
+    """bool mask of 2^28 elements, about half true: ascending int64 indices of the true
+    elements.  Count, strict monotonicity and membership over the whole output; exact
+    positions against numpy on sampled windows."""
+    n = 1 << 28
+    g = torch.Generator(device="cuda")
+    g.manual_seed(6)
+    mask = torch.rand(n, device="cuda", generator=g) < 0.5
+    idx = ops.mask_to_indices(mask)
+    assert idx.dtype == torch.int64 and idx.numel() == int(mask.sum().item())
+    assert bool((idx[1:] > idx[:-1]).all())
+    assert bool(mask[idx].all())
+    m = mask.cpu().numpy()
+    got = idx.cpu().numpy()
+    for lo in (0, 12_345_678, n - (1 << 20)):
+        hi = lo + (1 << 20)
+        want = lo + np.flatnonzero(m[lo:hi])
+        a, b = np.searchsorted(got, lo), np.searchsorted(got, hi)
+        np.testing.assert_array_equal(got[a:b], want)
 
 
 # ------------------------------------------------------------------------------------------
