@@ -265,6 +265,22 @@ TensorImpl vbt_cuda_masked_fill_impl(const TensorImpl& self, const TensorImpl& m
   return where(mask, value, self);
 }
 
+// vt::polygamma(n, x): n a one-element tensor on x's device (cuda_elementwise.cu:3853-3876)
+TensorImpl vbt_cuda_polygamma_impl(const TensorImpl& n, const TensorImpl& a) {
+  require_cuda(a, "vt::polygamma");
+  require_cuda(n, "vt::polygamma");
+  if (n.device().index != a.device().index) throw std::invalid_argument("vt::polygamma: device mismatch");
+  const vbt_b200_tensor dn = view_of(n), da = view_of(a);
+  TensorImpl out = dense_out(std::vector<int64_t>(a.sizes().begin(), a.sizes().end()), a.dtype(), a.device());
+  const Launch l(a);
+  const vbt_b200_tensor dout = view_of(out);
+  check(vbt_b200_polygamma(&dout, &dn, &da, l.handle()));  // scalar / dtype rules and their messages: the library's
+  l.record(out);
+  l.record(n);
+  l.record(a);
+  return out;
+}
+
 TensorImpl vbt_cuda_sum_impl(const TensorImpl& self, std::vector<int64_t> dims, bool keepdim) {
   return reduce(VBT_B200_R_SUM, "vt::sum", self, dims, keepdim);
 }
@@ -296,6 +312,7 @@ void vbt_register_cuda_elementwise_kernels() {
     VBT_B200_TERNARY(REG)
     REG(where, 0)
     REG(masked_fill, 0)
+    REG(polygamma, 0)
 #undef REG
   });
 }

@@ -102,7 +102,7 @@ static vt_tensor pick_like(const vt_tensor* args, const vbt_b200_tensor* d, int 
   return NULL;
 }
 
-enum family { F_UNARY, F_BINARY, F_TERNARY, F_WHERE };
+enum family { F_UNARY, F_BINARY, F_TERNARY, F_WHERE, F_POLYGAMMA };
 
 /* one body for every registered op */
 static vt_status run(enum family fam, int32_t op, vt_stream s, const vt_tensor* args, size_t nargs,
@@ -113,7 +113,7 @@ static vt_status run(enum family fam, int32_t op, vt_stream s, const vt_tensor* 
   }
   *out = NULL;
   if (!H) return VT_STATUS_INTERNAL;
-  const size_t want = fam == F_UNARY ? 1 : (fam == F_BINARY ? 2 : 3);
+  const size_t want = fam == F_UNARY ? 1 : ((fam == F_BINARY || fam == F_POLYGAMMA) ? 2 : 3);
   if (nargs != want || !args) {
     set_err("vbt_b200 plugin: wrong number of tensor arguments");
     return VT_STATUS_INVALID_ARG;
@@ -138,7 +138,8 @@ static vt_status run(enum family fam, int32_t op, vt_stream s, const vt_tensor* 
   }
   /* where(cond, x, y): the result is like x or y, never like the BOOL condition */
   vt_status st = VT_STATUS_OK;
-  vt_tensor like = pick_like(args, d, (int)nargs, fam == F_WHERE ? 0x6u : 0x7u, &st);
+  /* polygamma(n, x): like x, never like the one-element order tensor */
+  vt_tensor like = pick_like(args, d, (int)nargs, fam == F_WHERE ? 0x6u : (fam == F_POLYGAMMA ? 0x2u : 0x7u), &st);
   if (!like) return st;
   vt_tensor c = NULL;
   st = H->tensor_new_dense_like(like, &c);
@@ -155,6 +156,7 @@ static vt_status run(enum family fam, int32_t op, vt_stream s, const vt_tensor* 
     case F_UNARY: r = vbt_b200_unary(op, &dc, &d[0], stream); break;
     case F_BINARY: r = vbt_b200_binary(op, &dc, &d[0], &d[1], stream); break;
     case F_TERNARY: r = vbt_b200_ternary(op, &dc, &d[0], &d[1], &d[2], stream); break;
+    case F_POLYGAMMA: r = vbt_b200_polygamma(&dc, &d[0], &d[1], stream); break;
     default: r = vbt_b200_where(&dc, &d[0], &d[1], &d[2], stream); break;
   }
   if (r != VBT_B200_OK) return map_status(r);
@@ -211,6 +213,11 @@ TERNARY_OPS(DEF_TERNARY)
 static vt_status k_where(vt_stream s, const vt_tensor* a, size_t n, vt_tensor* out) {
   return run(F_WHERE, 0, s, a, n, out);
 }
+/* vt::polygamma(n, x): a binary schema, n a one-element tensor (cuda_elementwise.cu:3853-3876) */
+static vt_status k_polygamma(vt_stream s, vt_tensor n, vt_tensor x, vt_tensor* out) {
+  const vt_tensor args[2] = {n, x};
+  return run(F_POLYGAMMA, 0, s, args, 2, out);
+}
 /* masked_fill(self, mask, value) = where(mask, value, self) (cuda_elementwise.cu:3924-3926) */
 static vt_status k_masked_fill(vt_stream s, const vt_tensor* a, size_t n, vt_tensor* out) {
   if (n != 3 || !a) return run(F_WHERE, 0, s, a, n, out);
@@ -257,6 +264,7 @@ VBT_PLUGIN_EXPORT vt_status vbt_plugin_init(const struct vbt_host_api* host, str
   TERNARY_OPS(REG_BOXED)
   REG_BOXED(where, 0)
   REG_BOXED(masked_fill, 0)
+  REG_K2(polygamma, 0)
   out_api->abi_version = VBT_PLUGIN_ABI_VERSION;
   out_api->name = "vbt_b200: sm_100a elementwise kernels";
   return VT_STATUS_OK;

@@ -52,6 +52,9 @@ VBT_B200_API int32_t vbt_b200_compiled_arch(void);
 #define VBT_B200_F32 3
 #define VBT_B200_F16 4
 #define VBT_B200_BF16 5
+#define VBT_B200_F64 6   /* ordinal reserved (the reference has no Float64 CUDA kernels on this path) */
+#define VBT_B200_C64 7   /* two float32: vt::add, vt::mul and copy only, as in the reference            */
+#define VBT_B200_C128 8  /* two float64: likewise                                                       */
 
 /* Maximum rank accepted, the reference's CUDA broadcast limit
  * (src/vbt/ops/cuda_elementwise.cu:2974-2979). */
@@ -211,6 +214,15 @@ VBT_B200_API vbt_b200_status vbt_b200_where(const vbt_b200_tensor* out, const vb
 VBT_B200_API vbt_b200_status vbt_b200_binary_scalar(int32_t op, const vbt_b200_tensor* out,
                                        const vbt_b200_tensor* a, const void* scalar,
                                        int32_t scalar_on_left, void* stream);
+/* vt::polygamma(n, x) (vbt_cuda_polygamma_impl, src/vbt/ops/cuda_elementwise.cu:1288-1330, :3853-3876):
+ * n is a ONE-element floating tensor on x's device and of x's dtype, out has x's shape and dtype.
+ * As in the reference only order n == 2 is computed (any other order gives NaN): the recurrence
+ * psi''(x) = psi''(x + 1) - 2 / x^3 up to x >= 10 (at most 100 steps), then the three-term
+ * asymptotic series, all in double; poles (x a non-positive integer) and x < -1e6 give NaN.
+ * Errors: "vt::polygamma: expected n to be a scalar tensor", "... expected n to have floating
+ * dtype", "... dtype mismatch". */
+VBT_B200_API vbt_b200_status vbt_b200_polygamma(const vbt_b200_tensor* out, const vbt_b200_tensor* n,
+                                   const vbt_b200_tensor* x, void* stream);
 /* Strided copy out <- a (same dtype, a broadcast to out's shape): clone_cuda /
  * clone_strided_to_contig_kernel (src/vbt/core/tensor_ops_cuda.cu:83-91). */
 VBT_B200_API vbt_b200_status vbt_b200_copy(const vbt_b200_tensor* out, const vbt_b200_tensor* a, void* stream);

@@ -312,6 +312,55 @@ class Port:
     def offset_elems(self, linear, sizes, strides):
         return self.L.vbo_offset_elems(int(linear), len(sizes), _arr(sizes), _arr(strides))
 
+    # The tail of the elementwise table, restated in numpy (elementwise, a handful of operations per
+    # element; numpy rounds every float32 / float64 operation separately, which is what the reference's
+    # expressions do without contraction).
+    @staticmethod
+    def complex_binary(name, a, b):
+        """vt::add / vt::mul on Complex64 / Complex128 (src/vbt/ops/cuda_elementwise.cu:162-190):
+        add = (a.re + b.re, a.im + b.im); mul = (a.re*b.re - a.im*b.im, a.re*b.im + a.im*b.re)."""
+        a, b = np.broadcast_arrays(np.asarray(a), np.asarray(b))
+        assert a.dtype == b.dtype and a.dtype in (np.complex64, np.complex128)
+        f = np.float32 if a.dtype == np.complex64 else np.float64
+        ar, ai, br, bi = (np.ascontiguousarray(v, f) for v in (a.real, a.imag, b.real, b.imag))
+        if name == "add":
+            re, im = ar + br, ai + bi
+        elif name == "mul":
+            re, im = ar * br - ai * bi, ar * bi + ai * br
+        else:
+            raise ValueError(f"vt::{name}: unsupported dtype")
+        out = np.empty(a.shape, a.dtype)
+        out.real, out.imag = re, im
+        return out
+
+    @staticmethod
+    def polygamma(n, x, dtype):
+        """vt::polygamma (src/vbt/ops/cuda_elementwise.cu:1288-1330): only order 2 is computed, in
+        double: NaN at the poles and below -1e6; psi''(x) -= 2/x^3, x += 1 while x < 10 (at most 100
+        steps); then -1/x^2 - 1/x^3 - 1/(2 x^4); rounded to the tensor's dtype.  x in storage form."""
+        xs = np.asarray(x)
+        xf = to_f32(xs, dtype).astype(np.float64)
+        nan = np.full(xf.shape, np.nan)
+        if float(n) != 2.0:
+            return to_storage(nan.astype(np.float32), dtype)
+        xx = xf.copy()
+        bad = ((xx <= 0.0) & (xx == np.floor(xx))) | (xx < -1e6) | np.isnan(xx)
+        xx[bad] = 1.0
+        acc = np.zeros_like(xx)
+        for _ in range(100):
+            m = xx < 10.0
+            if not m.any():
+                break
+            acc[m] -= 2.0 / (xx[m] * xx[m] * xx[m])
+            xx[m] += 1.0
+        i1 = 1.0 / xx
+        i2 = i1 * i1
+        i3 = i2 * i1
+        i4 = i3 * i1
+        res = acc + (-i2 - i3 - 0.5 * i4)
+        res[bad] = np.nan
+        return to_storage(res.astype(np.float32), dtype)
+
 
 # ----------------------------------------------------------------------------------------
 # the reference's own CPU code

@@ -295,6 +295,8 @@ def test_every_registered_kernel_against_the_oracle(host, port, dtype):
                                     else 1000, shape).astype(np.int64) for _ in range(arity)]
             elif name == "where" or name == "masked_fill":
                 ins = None
+            elif name == "polygamma":
+                ins = "polygamma"
             elif name == "nan_to_num" and dtype != torch.float32:
                 continue
             elif name == "acosh":
@@ -318,6 +320,12 @@ def test_every_registered_kernel_against_the_oracle(host, port, dtype):
                 else:
                     st, out = _call(host, fq, [ts.of(tx), ts.of(tc), ts.of(ty)])   # (self, mask, value)
                     want = port.where(cond, y, x, code)
+            elif ins == "polygamma":   # (n, x): n a one-element tensor, the result is like x
+                x = oracle.to_storage((8 * rng.random(shape) - 2).astype(np.float32), code)
+                two = oracle.to_storage(np.array([2.0], np.float32), code)
+                tens = [from_np(two, dtype), from_np(x, dtype)]
+                st, out = _call(host, fq, [ts.of(t) for t in tens])
+                want = port.polygamma(2.0, x, code)
             else:
                 tens = [from_np(a, op_dtype) for a in ins]
                 st, out = _call(host, fq, [ts.of(t) for t in tens])

@@ -533,3 +533,68 @@ def test_transposed_operands_use_the_tiled_transpose_path(ops, port, dtype, shap
         np.testing.assert_array_equal(to_np(out), port.where(cond, y, xt, CODE[dtype]))
     if len(shape) == 2 and min(shape) >= 16:
         assert ops.ti_plan(torch.empty(xt.shape, dtype=dtype, device="cuda"), tt)[2] == 3
+
+
+@pytest.mark.parametrize("cdt", [torch.complex64, torch.complex128])
+def test_complex_add_mul_and_copy(ops, port, cdt):
+    """Complex64 / Complex128 take vt::add, vt::mul (src/vbt/ops/cuda_elementwise.cu:162-190,
+    :3169-3188) and strided copies; every other op rejects them.  Bit-exact against the oracle's
+    separately rounded products: contiguous, broadcast, a transposed view, a ragged strided view."""
+    rng = np.random.default_rng(61)
+    ndt = np.complex64 if cdt == torch.complex64 else np.complex128
+    mk = lambda shape: (rng.standard_normal(shape) + 1j * rng.standard_normal(shape)).astype(ndt)  # noqa: E731
+    a, b = mk((37, 65)), mk((37, 65))
+    ta, tb = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    for name in ("add", "mul"):
+        got = ops.binary(name, ta, tb).cpu().numpy()
+        np.testing.assert_array_equal(got, port.complex_binary(name, a, b), err_msg=name)
+        # broadcast row and column operands
+        r, c = mk((1, 65)), mk((37, 1))
+        got = ops.binary(name, torch.from_numpy(r).cuda(), torch.from_numpy(c).cuda()).cpu().numpy()
+        np.testing.assert_array_equal(got, port.complex_binary(name, r, c), err_msg=name + " broadcast")
+        # one operand transposed, output a strided slice of a larger buffer
+        sq = mk((48, 48))
+        tsq = torch.from_numpy(sq).cuda()
+        big = torch.zeros((48, 100), dtype=cdt, device="cuda")
+        ops.binary(name, tsq, tsq.t(), out=big[:, 3:99:2])
+        np.testing.assert_array_equal(big[:, 3:99:2].cpu().numpy(), port.complex_binary(name, sq, sq.T), err_msg=name + " strided")
+        assert not big[:, 4:99:2].any() and not big[:, :3].any()
+    np.testing.assert_array_equal(ops.contiguous(ta.t()).cpu().numpy(), a.T)
+    np.testing.assert_array_equal(ops.contiguous(ta[::3, 1::2]).cpu().numpy(), a[::3, 1::2])
+    for name in ("sub", "div", "maximum", "eq"):
+        with pytest.raises(ValueError, match="unsupported dtype"):
+            ops.binary(name, ta, tb)
+    with pytest.raises(ValueError, match="dtype mismatch"):
+        ops.binary("add", ta, tb.to(torch.complex128 if cdt == torch.complex64 else torch.complex64))
+
+
+@pytest.mark.parametrize("dtype", FLOATS)
+def test_polygamma(ops, port, dtype):
+    """vt::polygamma(n, x) (cuda_elementwise.cu:1288-1330, :3853-3876): order 2 against the
+    oracle's restatement of the same recurrence + asymptotic series, NaN at poles and for every
+    other order, the scalar-tensor rule for n, a strided x."""
+    rng = np.random.default_rng(62)
+    x = 6 * rng.standard_normal((33, 70), dtype=np.float32)
+    x.flat[:10] = [1.0, 0.5, 2.0, 10.0, 25.0, 0.0, -1.0, -2.0, -0.5, -3.25]
+    xs = oracle.to_storage(x, CODE[dtype])
+    tx = from_np(xs, dtype)
+    two = torch.tensor([2.0], device="cuda").to(dtype)
+    got = to_np(ops.polygamma(two, tx))
+    want = port.polygamma(2.0, xs, CODE[dtype])
+    g, w = as_f32(got, dtype), as_f32(want, dtype)
+    np.testing.assert_array_equal(np.isnan(g), np.isnan(w))
+    fin = np.isfinite(w)
+    if dtype == torch.float32:
+        np.testing.assert_allclose(g[fin], w[fin], rtol=1e-6, atol=0)
+        assert abs(g.flat[0] - (-2.4041138063)) < 1e-6     # psi''(1) = -2 zeta(3)
+    else:
+        np.testing.assert_array_equal(got[fin], want[fin])   # the double result rounds once to the storage type
+    assert np.isnan(g.flat[5]) and np.isnan(g.flat[6]) and np.isnan(g.flat[7]) and np.isfinite(g.flat[8])
+    for order in (0.0, 1.0, 3.0):
+        n = torch.tensor([order], device="cuda").to(dtype)
+        assert np.isnan(as_f32(to_np(ops.polygamma(n, tx)), dtype)).all()
+    view = tx.t()[::2]
+    got_v = to_np(ops.polygamma(two.reshape(1, 1), view))
+    np.testing.assert_array_equal(got_v, np.ascontiguousarray(got.T[::2]))
+    with pytest.raises(ValueError, match="expected n to be a scalar tensor"):
+        ops.polygamma(torch.zeros(2, device="cuda").to(dtype), tx)

@@ -253,3 +253,34 @@ def test_launch_info_and_counters_are_host_side_state(L):
     L.vbt_b200_reset_launch_counts()
     assert _lib.launch_counts() == {name: 0 for name in _lib.FAMILIES}
     assert L.vbt_b200_last_launch_info(None) == 1
+
+
+def test_polygamma_and_complex_argument_rules_without_a_gpu(L):
+    """vt::polygamma's argument checks carry the reference's messages
+    (src/vbt/ops/cuda_elementwise.cu:3853-3872); complex tensors are taken by vt::add / vt::mul
+    only (:3169-3188) -- everything is decided before a launch."""
+    x, o = fake([3, 4], [4, 1]), fake([3, 4], [4, 1])
+    n1, n2 = fake([1], [1]), fake([2], [1])
+    assert L.vbt_b200_polygamma(ctypes.byref(o), ctypes.byref(n2), ctypes.byref(x), None) == 1
+    assert b"vt::polygamma: expected n to be a scalar tensor" in L.vbt_b200_last_error()
+    ni = fake([1], [1], _lib.I64)
+    assert L.vbt_b200_polygamma(ctypes.byref(o), ctypes.byref(ni), ctypes.byref(x), None) == 1
+    assert b"vt::polygamma: expected n to have floating dtype" in L.vbt_b200_last_error()
+    nh = fake([1], [1], _lib.F16)
+    assert L.vbt_b200_polygamma(ctypes.byref(o), ctypes.byref(nh), ctypes.byref(x), None) == 1
+    assert b"vt::polygamma: dtype mismatch" in L.vbt_b200_last_error()
+    assert L.vbt_b200_polygamma(ctypes.byref(o), None, ctypes.byref(x), None) == 1
+    e = fake([0, 4], [4, 1])
+    assert L.vbt_b200_polygamma(ctypes.byref(e), ctypes.byref(n1), ctypes.byref(e), None) == 0  # nothing to do
+    ca, co = fake([3, 4], [4, 1], _lib.C64), fake([3, 4], [4, 1], _lib.C64)
+    for op in range(_lib.lib().vbt_b200_binary_op_count() if hasattr(_lib.lib(), "vbt_b200_binary_op_count") else 14):
+        if op in (0, 2):
+            continue
+        assert L.vbt_b200_binary(op, ctypes.byref(co), ctypes.byref(ca), ctypes.byref(ca), None) == 1, op
+        assert b"unsupported dtype" in L.vbt_b200_last_error()
+    cb = fake([3, 4], [4, 1], _lib.C128)
+    assert L.vbt_b200_binary(0, ctypes.byref(co), ctypes.byref(ca), ctypes.byref(cb), None) == 1
+    assert b"vt::add: dtype mismatch" in L.vbt_b200_last_error()
+    assert L.vbt_b200_binary(2, ctypes.byref(cb), ctypes.byref(ca), ctypes.byref(ca), None) == 1
+    assert b"vt::mul: output dtype mismatch" in L.vbt_b200_last_error()
+    assert L.vbt_b200_unary(0, ctypes.byref(co), ctypes.byref(ca), None) == 1   # no complex unary ops

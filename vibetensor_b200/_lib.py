@@ -15,9 +15,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libvbt_b200.so")
 
 BOOL, I32, I64, F32, F16, BF16 = 0, 1, 2, 3, 4, 5
+C64, C128 = 7, 8  # vt::add, vt::mul and copy only
 _TORCH_TO_CODE = {
     torch.bool: BOOL, torch.int32: I32, torch.int64: I64, torch.float32: F32,
     torch.float16: F16, torch.bfloat16: BF16, torch.uint8: BOOL,
+    torch.complex64: C64, torch.complex128: C128,
 }
 MAX_NDIM = 25
 FABRIC_HANDLE_BYTES = 128
@@ -54,6 +56,7 @@ SIGNATURES = {
     "vbt_b200_ternary": (_i32, [_i32, _P, _P, _P, _P, _vp]),
     "vbt_b200_where": (_i32, [_P, _P, _P, _P, _vp]),
     "vbt_b200_binary_scalar": (_i32, [_i32, _P, _P, _vp, _i32, _vp]),
+    "vbt_b200_polygamma": (_i32, [_P, _P, _P, _vp]),
     "vbt_b200_copy": (_i32, [_P, _P, _vp]),
     "vbt_b200_add": (_i32, [_P, _P, _P, _vp]),
     "vbt_b200_sub": (_i32, [_P, _P, _P, _vp]),

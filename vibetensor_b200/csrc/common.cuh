@@ -97,6 +97,8 @@ inline int itemsize(int dtype) {
     case VBT_B200_F32: return 4;
     case VBT_B200_F16: return 2;
     case VBT_B200_BF16: return 2;
+    case VBT_B200_C64: return 8;
+    case VBT_B200_C128: return 16;
   }
   return 0;
 }

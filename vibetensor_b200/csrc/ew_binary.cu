@@ -26,6 +26,9 @@ vbt_b200_status binary_ext(int32_t op, const vbt_b200_tensor* out, const vbt_b20
                            const vbt_b200_tensor* b, void* stream);
 vbt_b200_status binary_scalar_ext(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                                   const void* scalar, int32_t scalar_on_left, void* stream);
+// ew_complex.cu
+vbt_b200_status complex_binary(int32_t op, const char* name, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
+                               const vbt_b200_tensor* b, void* stream);
 }  // namespace vb
 
 extern "C" vbt_b200_status vbt_b200_binary(int32_t op, const vbt_b200_tensor* out,
@@ -35,6 +38,8 @@ extern "C" vbt_b200_status vbt_b200_binary(int32_t op, const vbt_b200_tensor* ou
   const char* name = "binary";
   VB_ARG(b != nullptr, "binary: null tensor descriptor");
   if (op >= kBinaryCore && op < VBT_B200_B_COUNT) return binary_ext(op, out, a, b, stream);
+  if (out && a && op >= 0 && op < kBinaryCore && (a->dtype == VBT_B200_C64 || a->dtype == VBT_B200_C128))
+    return complex_binary(op, kBinaryNames[op], out, a, b, stream);  // vt::add / vt::mul only (cuda_elementwise.cu:3169-3188)
   VB_TRY(check_binary(op, out, a, b->dtype, &name));
   const int dt = a->dtype;
   const vbt_b200_tensor* ops[3] = {out, a, b};

@@ -10,6 +10,7 @@ static const char* const kUnaryNames[kUnaryCore] = {
     "vt::softplus", "vt::relu6", "vt::hardtanh"};
 vbt_b200_status unary_ext(int32_t op, const vbt_b200_tensor* out, const vbt_b200_tensor* a,
                           void* stream);  // ew_unary_ext.cu
+vbt_b200_status copy16(const TiPlan& plan, cudaStream_t s);  // ew_complex.cu
 }  // namespace vb
 
 extern "C" vbt_b200_status vbt_b200_unary(int32_t op, const vbt_b200_tensor* out,
@@ -59,6 +60,7 @@ extern "C" vbt_b200_status vbt_b200_copy(const vbt_b200_tensor* out, const vbt_b
     case 2: return launch_ew<CopyF<uint16_t>, uint16_t, uint16_t, uint16_t, uint16_t, 1>(plan, {}, s);
     case 4: return launch_ew<CopyF<uint32_t>, uint32_t, uint32_t, uint32_t, uint32_t, 1>(plan, {}, s);
     case 8: return launch_ew<CopyF<uint64_t>, uint64_t, uint64_t, uint64_t, uint64_t, 1>(plan, {}, s);
+    case 16: return copy16(plan, s);
   }
   return fail(VBT_B200_INVALID_ARGUMENT, "copy: unsupported dtype");
 }

@@ -138,6 +138,17 @@ def where(cond, x, y, out=None) -> torch.Tensor:
     return o
 
 
+def polygamma(n: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """vt::polygamma(n, x): n a one-element floating tensor of x's dtype on x's device.  As in the
+    reference only order 2 is computed; other orders give NaN (cuda_elementwise.cu:1288-1330)."""
+    _require_cuda(n, x)
+    if out is None:
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    do, dn, dx = desc(out), desc(n), desc(x)
+    check(lib().vbt_b200_polygamma(do.ref, dn.ref, dx.ref, stream_ptr(out)))
+    return out
+
+
 def masked_fill(self_, mask, value, out=None):
     """vt::masked_fill = where(mask, value, self) (cuda_elementwise.cu:3924-3926)."""
     return where(mask, value, self_, out=out)
