@@ -1264,7 +1264,8 @@ __global__ void __launch_bounds__(kWdThreads, 1) lastdim_wide_kernel(const __gri
       if ((t & 31) == 0) {
         __threadfence_block();  // this warp's reads of the stage come before its count
         if (atomicAdd(&served[stage], 1u) == kWdThreads / 32 - 1) {
-          served[stage] = 0;  // next touched after the refill below has landed
+          __threadfence_block();  // the other warps' counts (and the reads in front of them) come before the refill
+          served[stage] = 0;      // next touched after the refill below has landed
           if (nb < p.B) issue(nb, nq, stage);
         }
       }
