@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(kThreads) count_rows_kernel(IndexSrc idx, int6
 // order -- bit-identical to a sequential loop -- and independent of scheduling.
 //
 // Sort: LSD radix, 8 bits per pass over just the bits the row range needs; per pass a
-// block histogram, one exclusive scan, and a stable scatter (ranks from __match_any_sync).
+// block histogram, one exclusive scan, and a stable scatter (ranks from per-bit ballots).
 // ------------------------------------------------------------------------------------
 constexpr int kSortThreads = 256;
 constexpr int kSortItems = 16;                            // per thread
@@ -428,6 +428,21 @@ struct KeyParams {
 // scatter -- and the first pass's count kernel also makes the keys from the index tensor
 // (key = V for an update that must be skipped: it sorts last).
 
+// Lanes of the warp that hold the same digit as this lane (this lane included); lanes with
+// valid == false match nobody.  One ballot per digit bit: the hardware's match.any measured slower
+// the more lanes agree -- the pass over the skewed high digit took twice the time of the others.
+template <int BITS>
+__device__ __forceinline__ unsigned same_digit_lanes(uint32_t digit, bool valid) {
+  unsigned peers = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+  for (int b = 0; b < BITS; ++b) {
+    const bool bit = (digit >> b) & 1u;
+    const unsigned m = __ballot_sync(0xffffffffu, bit);
+    peers &= bit ? m : ~m;
+  }
+  return valid ? peers : 0u;
+}
+
 // hist[d * nblocks + b] = number of items of block b whose digit is d
 // and totals[d] += the same counts (totals is zero on entry)
 template <int RB, bool FIRST>
@@ -442,7 +457,7 @@ __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(const __grid_c
 #pragma unroll
   for (int k = 0; k < kSortItems; ++k) {
     const int64_t i = base + k * kSortThreads + threadIdx.x;
-    uint32_t digit = NB + (threadIdx.x & 31);  // past the end: a value no other lane holds
+    uint32_t digit = 0;
     if (i < n) {
       uint32_t key;
       if constexpr (FIRST) {
@@ -459,8 +474,8 @@ __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(const __grid_c
       digit = (key >> shift) & (NB - 1);
     }
     // one shared-memory atomic per distinct digit of the warp: a hot row puts many equal digits in a warp
-    const unsigned peers = __match_any_sync(0xffffffffu, digit);
-    if (digit < NB && (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&h[digit], static_cast<uint32_t>(__popc(peers)));
+    const unsigned peers = same_digit_lanes<RB>(digit, i < n);
+    if (peers && (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&h[digit], static_cast<uint32_t>(__popc(peers)));
   }
   __syncthreads();
   for (int d = threadIdx.x; d < NB; d += kSortThreads) {
@@ -520,7 +535,7 @@ __global__ void __launch_bounds__(1024) radix_scan_kernel(uint32_t* hist, int nb
 }
 
 // Stable scatter of one 4096-item tile by the current digit.  The tile is first put in digit order
-// in shared memory (rank within the warp's run by match_any, then warp and digit prefixes), and
+// in shared memory (rank within the warp's run by per-bit ballots, then warp and digit prefixes), and
 // only then written out: consecutive threads write consecutive addresses of a digit's run.  (The
 // first form wrote every item straight to its final place -- 32 lanes, up to 32 sectors per store
 // -- and took 43 us per pass on 4 M items where the traffic is worth 11 us.)
@@ -558,7 +573,7 @@ __global__ void __launch_bounds__(kSortThreads, 3) radix_scatter_kernel(const ui
     const int64_t i = wbase + r * 32 + lane;
     const bool valid = i < n;
     const uint32_t d = (key[r] >> shift) & (NB - 1);
-    const unsigned peers = __match_any_sync(0xffffffffu, valid ? d : static_cast<uint32_t>(NB) + lane);
+    const unsigned peers = same_digit_lanes<RB>(d, valid);
     const uint32_t before = __popc(peers & ((1u << lane) - 1u));
     rank[r] = valid ? cnt(w, d) + before : 0u;
     __syncwarp();
