@@ -256,28 +256,27 @@ __global__ void __launch_bounds__(kBwdThreads, VPL * (16 / sizeof(T)) <= 16 ? 2 
               make_float4(gg[k][4 * q], gg[k][4 * q + 1], gg[k][4 * q + 2], gg[k][4 * q + 3]);
       }
     } else {
-      // fold the R row slots of this block in slot order, then one partial row per block
-      __shared__ float fold[kBwdThreads * (VPL * V <= 16 ? VPL * V : 1)];
+      // fold the R row slots of this block in slot order, then one partial row per block.
+      // fold[item][thread] with the item rows padded by TPR words: the threads' stores and the
+      // folding loads (consecutive lanes = consecutive positions in the row, then the next item)
+      // both spread over the banks
       constexpr int kPer = VPL * V;  // floats per thread; only reached with kPer <= 16
+      constexpr int kPitch = kBwdThreads + TPR;
+      __shared__ float fold[(VPL * V <= 16 ? VPL * V : 1) * kPitch];
       __syncthreads();
 #pragma unroll
       for (int k = 0; k < VPL; ++k)
 #pragma unroll
-        for (int e = 0; e < V; ++e) fold[(rl * TPR + tl) * kPer + k * V + e] = gg[k][e];
+        for (int e = 0; e < V; ++e) fold[(k * V + e) * kPitch + t] = gg[k][e];
       __syncthreads();
-      if (rl == 0) {
+      for (int m = t; m < TPR * kPer; m += kBwdThreads) {
+        const int pos = m % TPR, item = m / TPR;
+        const int j = pos + (item / V) * TPR;
+        if (j >= nvec) continue;
+        float sum = 0.f;
 #pragma unroll
-        for (int k = 0; k < VPL; ++k) {
-          const int j = tl + k * TPR;
-          if (j >= nvec) continue;
-#pragma unroll
-          for (int e = 0; e < V; ++e) {
-            float sum = 0.f;
-#pragma unroll
-            for (int r = 0; r < R; ++r) sum += fold[(r * TPR + tl) * kPer + k * V + e];
-            wrow[static_cast<int64_t>(j) * V + e] = sum;
-          }
-        }
+        for (int r = 0; r < R; ++r) sum += fold[item * kPitch + r * TPR + pos];
+        wrow[static_cast<int64_t>(j) * V + item % V] = sum;
       }
     }
   }
@@ -329,30 +328,38 @@ __global__ void __launch_bounds__(kBwdThreads) rowop_bwd_stream_kernel(const __g
   }
 }
 
-// dgamma[c] = sum over the partial rows, in row order: 8 warps take rows w, w+8, ... of a
-// 32-column strip (eight loads in flight each), then the warps are folded in warp order.
-__global__ void __launch_bounds__(256) dgamma_fold_kernel(float* dgamma, const float* ws, int nparts, int64_t cols) {
-  __shared__ float sm[8][33];
+// dgamma[c] = sum over the partial rows, in a fixed order.  A block owns a strip of 8 columns
+// (one 32-byte sector per partial row): lane & 7 is the column, the four lane groups of the 32
+// warps take 128 rows per step, so the ~600 partial rows of a launch are five loads per thread,
+// all in flight at once.  Lane groups are then folded by shuffles and the warps in warp order.
+// (The first form -- 32 columns per block, 8 warps -- ran 4 blocks for 128 columns and took
+// 10 us of a 42 us backward pass.)
+constexpr int kFoldThreads = 1024;
+__global__ void __launch_bounds__(kFoldThreads) dgamma_fold_kernel(float* dgamma, const float* ws, int nparts, int64_t cols) {
+  __shared__ float sm[kFoldThreads / 32][8];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + lane;
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * 8 + (lane & 7);
   float acc = 0.f;
   if (c < cols) {
-    int r = w;
-    for (; r + 56 < nparts; r += 64) {
+    for (int r = w * 4 + (lane >> 3); r < nparts; r += 8 * 128) {
       float v[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = __ldcg(ws + static_cast<int64_t>(r + 8 * u) * cols + c);
+      for (int u = 0; u < 8; ++u) {
+        const int rr = r + 128 * u;
+        v[u] = rr < nparts ? __ldcg(ws + static_cast<int64_t>(rr) * cols + c) : 0.f;
+      }
 #pragma unroll
       for (int u = 0; u < 8; ++u) acc += v[u];
     }
-    for (; r < nparts; r += 8) acc += __ldcg(ws + static_cast<int64_t>(r) * cols + c);
   }
-  sm[w][lane] = acc;
+  acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+  if (lane < 8) sm[w][lane] = acc;
   __syncthreads();
-  if (w == 0 && c < cols) {
+  if (w == 0 && lane < 8 && c < cols) {
     float s = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) s += sm[k][lane];
+    for (int k = 0; k < kFoldThreads / 32; ++k) s += sm[k][lane];
     dgamma[c] = s;
   }
 }
@@ -493,7 +500,7 @@ vbt_b200_status vbt_b200_rmsnorm_backward(void* dx, float* dgamma, const void* d
   unsigned parts = 0;
   VB_TRY(dispatch_bwd<B_RMSNORM>(dtype, p, s, scope.device(), name, &parts));
   if (dgamma) {
-    dgamma_fold_kernel<<<static_cast<unsigned>((cols + 31) / 32), 256, 0, s>>>(dgamma, p.ws, static_cast<int>(parts), cols);
+    dgamma_fold_kernel<<<static_cast<unsigned>((cols + 7) / 8), kFoldThreads, 0, s>>>(dgamma, p.ws, static_cast<int>(parts), cols);
     VB_LAUNCH_CHECK();
   }
   return VBT_B200_OK;
