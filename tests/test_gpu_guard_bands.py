@@ -181,6 +181,7 @@ def test_mask_select_and_scale_cast(ops):
         _lib.check(L.vbt_b200_mask_select(dm.ref, ctypes.c_void_p(small.t.data_ptr()), cap, ctypes.c_void_p(cnt.t.data_ptr()),
                                           ctypes.c_void_p(ws.t.data_ptr()), need.value, _lib.stream_ptr(mask)))
         small.check(f"mask_select capacity n={n}")
+        assert torch.equal(small.t[:min(cap, k)], torch.nonzero(mask).reshape(-1)[:cap])
     for n in (1, 7, 1031, 4096):
         part = torch.randn(n, device="cuda", generator=g)
         for dt in (torch.float32, torch.bfloat16):
