@@ -447,8 +447,8 @@ __device__ __forceinline__ unsigned same_digit_lanes(uint32_t digit, bool valid)
 // and totals[d] += the same counts (totals is zero on entry)
 template <int RB, bool FIRST>
 __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(const __grid_constant__ KeyParams kp, const uint32_t* keys,
-                                                                  int64_t n, int shift, uint32_t* hist, int nblocks,
-                                                                  uint32_t* totals) {
+                                                                  int64_t n, uint32_t mul, int shift, uint32_t* hist,
+                                                                  int nblocks, uint32_t* totals) {
   constexpr int NB = 1 << RB;
   __shared__ uint32_t h[NB];
   for (int d = threadIdx.x; d < NB; d += kSortThreads) h[d] = 0;
@@ -471,7 +471,7 @@ __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(const __grid_c
       } else {
         key = keys[i];
       }
-      digit = (key >> shift) & (NB - 1);
+      digit = ((key * mul) >> shift) & (NB - 1);
     }
     // one shared-memory atomic per distinct digit of the warp: a hot row puts many equal digits in a warp
     const unsigned peers = same_digit_lanes<RB>(digit, i < n);
@@ -542,8 +542,8 @@ __global__ void __launch_bounds__(1024) radix_scan_kernel(uint32_t* hist, int nb
 template <int RB>
 __global__ void __launch_bounds__(kSortThreads, 3) radix_scatter_kernel(const uint32_t* keys_in, const uint32_t* vals_in,
                                                                      uint32_t* keys_out, uint32_t* vals_out,
-                                                                     int64_t n, int shift, const uint32_t* hist,
-                                                                     int nblocks) {
+                                                                     int64_t n, uint32_t mul, int shift,
+                                                                     const uint32_t* hist, int nblocks) {
   constexpr int NB = 1 << RB;
   extern __shared__ uint32_t scat_raw[];  // [kSortWarps][NB] counts, [NB] tile starts, [NB] output bases, keys, values
   uint32_t* const cnt_raw = scat_raw;
@@ -572,7 +572,7 @@ __global__ void __launch_bounds__(kSortThreads, 3) radix_scatter_kernel(const ui
   for (int r = 0; r < kSortItems; ++r) {
     const int64_t i = wbase + r * 32 + lane;
     const bool valid = i < n;
-    const uint32_t d = (key[r] >> shift) & (NB - 1);
+    const uint32_t d = ((key[r] * mul) >> shift) & (NB - 1);
     const unsigned peers = same_digit_lanes<RB>(d, valid);
     const uint32_t before = __popc(peers & ((1u << lane) - 1u));
     rank[r] = valid ? cnt(w, d) + before : 0u;
@@ -623,7 +623,7 @@ __global__ void __launch_bounds__(kSortThreads, 3) radix_scatter_kernel(const ui
   for (int r = 0; r < kSortItems; ++r) {
     const int64_t i = wbase + r * 32 + lane;
     if (i < n) {
-      const uint32_t d = (key[r] >> shift) & (NB - 1);
+      const uint32_t d = ((key[r] * mul) >> shift) & (NB - 1);
       const uint32_t pos = tstart[d] + cnt(w, d) + rank[r];
       sk[pos] = key[r];
       sv[pos] = val[r];
@@ -634,7 +634,7 @@ __global__ void __launch_bounds__(kSortThreads, 3) radix_scatter_kernel(const ui
   const uint32_t tile_n = static_cast<uint32_t>(left < kSortTile ? left : kSortTile);
   for (uint32_t i = t; i < tile_n; i += kSortThreads) {
     const uint32_t k = sk[i];
-    const uint32_t dst = gbase[(k >> shift) & (NB - 1)] + i;
+    const uint32_t dst = gbase[((k * mul) >> shift) & (NB - 1)] + i;
     keys_out[dst] = k;
     vals_out[dst] = sv[i];
   }
@@ -1476,11 +1476,12 @@ size_t sorted_workspace_bytes(int64_t n) {
 // one pass of the sort; FIRST also makes the keys
 template <int RB>
 vbt_b200_status radix_pass(const KeyParams& kp, bool first, uint32_t* const keys[2], uint32_t* const vals[2], int cur,
-                           int64_t N, int shift, uint32_t* hist, int nblocks, uint32_t* tot, cudaStream_t s) {
+                           int64_t N, uint32_t mul, int shift, uint32_t* hist, int nblocks, uint32_t* tot,
+                           cudaStream_t s) {
   constexpr int NB = 1 << RB;
   constexpr int kScatterSmem = (kSortWarps * NB + 2 * NB + 2 * kSortTile) * 4;
-  if (first) radix_hist_kernel<RB, true><<<nblocks, kSortThreads, 0, s>>>(kp, keys[cur], N, shift, hist, nblocks, tot);
-  else radix_hist_kernel<RB, false><<<nblocks, kSortThreads, 0, s>>>(kp, keys[cur], N, shift, hist, nblocks, tot);
+  if (first) radix_hist_kernel<RB, true><<<nblocks, kSortThreads, 0, s>>>(kp, keys[cur], N, mul, shift, hist, nblocks, tot);
+  else radix_hist_kernel<RB, false><<<nblocks, kSortThreads, 0, s>>>(kp, keys[cur], N, mul, shift, hist, nblocks, tot);
   radix_scan_kernel<RB><<<NB, 1024, 0, s>>>(hist, nblocks, tot);
   if (kScatterSmem > 48 * 1024) {
     static std::mutex mu;
@@ -1494,7 +1495,7 @@ vbt_b200_status radix_pass(const KeyParams& kp, bool first, uint32_t* const keys
     }
   }
   radix_scatter_kernel<RB><<<nblocks, kSortThreads, kScatterSmem, s>>>(keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1],
-                                                                       N, shift, hist, nblocks);
+                                                                       N, mul, shift, hist, nblocks);
   return VBT_B200_OK;
 }
 
@@ -1571,12 +1572,23 @@ vbt_b200_status scatter_add_rows_sorted(const char* name, const vbt_b200_tensor*
   // whole scatter-add): per-block counts and offsets grow with bins x blocks, and their
   // digit-major layout makes those accesses uncoalesced.
   const int rb = bits <= 11 && bits > 8 ? 11 : 8;
-  const int passes = (bits + rb - 1) / rb;
+  // The accumulating kernel needs equal rows NEXT TO each other, not the rows in order.  Rows that
+  // take more than 16 bits are therefore grouped by the top 16 bits of a multiplicative hash of the
+  // row -- two passes whatever the table's height.  The rows of a hash bucket stay in update
+  // order, so another row of the same bucket can cut a run in two: that costs one more add to the
+  // row, nothing else (a strided set of rows, which would fill a bucket of the plain low bits,
+  // is spread by the multiply).  Measured on 2^20 rows, 4 M Zipf(1.1) updates: fp32 0.924 -> 0.876 ms
+  // (sort 176 -> 125 us, accumulation 745 -> 757 us); int64 rows, whose adds go out as two 8-byte
+  // atomics per 16 bytes, lost in the accumulation what the sort gained and keep the full sort.
+  const bool hashed = bits > 16 && es == 4;
+  const int passes = hashed ? 2 : (bits + rb - 1) / rb;
+  const uint32_t mul = hashed ? 0x9E3779B1u : 1u;
   int cur = 0;
   for (int ps = 0; ps < passes; ++ps) {
     uint32_t* tot = totals + ps * kMaxRadixBins;
-    if (rb == 11) VB_TRY(radix_pass<11>(kp, ps == 0, keys, vals, cur, N, ps * rb, hist, nblocks, tot, s));
-    else VB_TRY(radix_pass<8>(kp, ps == 0, keys, vals, cur, N, ps * rb, hist, nblocks, tot, s));
+    const int shift = hashed ? 16 + 8 * ps : ps * rb;
+    if (rb == 11) VB_TRY(radix_pass<11>(kp, ps == 0, keys, vals, cur, N, mul, shift, hist, nblocks, tot, s));
+    else VB_TRY(radix_pass<8>(kp, ps == 0, keys, vals, cur, N, mul, shift, hist, nblocks, tot, s));
     cur ^= 1;
   }
   SortedScatterParams sp{};

@@ -452,7 +452,9 @@ def index_put_rows_(table: torch.Tensor, idx: torch.Tensor, values: torch.Tensor
     """``table.index_put_((idx,), values, accumulate)`` for a 2-D table and [N, D] values.
 
     accumulate=True has two engines: block-local aggregation + atomics (no scratch), and
-    sort-by-row + per-row sums (scratch of ~16 bytes per index, order-independent results).
+    group-by-row + per-run sums (scratch of ~18 bytes per index; a radix sort by row, or by a
+    16-bit hash of the row for 4-byte tables of more than 65536 rows; integer results are exact
+    and order-independent, a float row receives a few large partial sums instead of many updates).
     ``deterministic=None`` picks the sorted engine for integer tables with many updates,
     where it is also the faster one; True / False force the choice."""
     _require_cuda(table, idx, values)
