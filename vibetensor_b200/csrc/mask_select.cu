@@ -24,6 +24,7 @@ constexpr int kMsItems = 16;                       // mask bytes per thread and 
 constexpr int kMsSub = 4;                          // sub-tiles a block walks
 constexpr int kMsSubTile = kMsThreads * kMsItems;  // 4096 mask bytes
 constexpr int kMsTile = kMsSubTile * kMsSub;       // 16384 mask bytes per block
+constexpr int kMsCountBlocksPerSm = 5;             // resident blocks of the count kernel (48 registers)
 
 struct MaskParams {
   const uint8_t* mask;
@@ -70,7 +71,7 @@ __device__ __forceinline__ uint32_t load_flags(const MaskParams& p, int64_t firs
 // A block walks tiles blockIdx.x, + gridDim.x, ...; the 16-byte loads of its next tile are issued
 // before the flags of the current one are worked out, so the block always has loads in flight.
 // (One tile per block, loads -> arithmetic -> reduction -> exit, reached 4.7 TB/s.)
-__global__ void __launch_bounds__(kMsThreads) mask_count_kernel(const __grid_constant__ MaskParams p,
+__global__ void __launch_bounds__(kMsThreads, kMsCountBlocksPerSm) mask_count_kernel(const __grid_constant__ MaskParams p,
                                                                 unsigned* tile_counts, uint16_t* flag_words,
                                                                 int64_t ntiles) {
   __shared__ unsigned red[2][kMsThreads / 32];
@@ -320,7 +321,7 @@ vbt_b200_status vbt_b200_mask_select(const vbt_b200_tensor* mask, int64_t* out_i
   MaskParams p{};
   p.mask = base; p.n = n; p.stride = stride;
   p.vec = (stride == 1 && reinterpret_cast<uintptr_t>(base) % 16 == 0) ? 1 : 0;
-  const int64_t count_blocks = std::min<int64_t>(ntiles, int64_t{sm_count(scope.device())} * 8);
+  const int64_t count_blocks = std::min<int64_t>(ntiles, int64_t{sm_count(scope.device())} * kMsCountBlocksPerSm);
   mask_count_kernel<<<static_cast<unsigned>(count_blocks), kMsThreads, 0, s>>>(p, counts, flag_words, ntiles);
   VB_LAUNCH_CHECK();
   mask_scan_kernel<<<1, 1024, 0, s>>>(counts, offsets, ntiles, reinterpret_cast<unsigned long long*>(count_out));
