@@ -204,8 +204,9 @@ def workload_config(n, fused=False):
     if n == 1:
         coll = "none"
     elif fused:
-        coll = ("inside the reduce kernel: 4-byte partials written to every rank's exchange buffer with peer "
-                "stores over NVLink, per-rank flags, fold in rank order (no collective library call)")
+        coll = ("inside the reduce kernel: every partial goes to every rank's exchange buffer as one 8-byte word "
+                "(value + the call's epoch) by peer stores over NVLink; the reader polls the word itself and folds "
+                "in rank order (no flags, no fence, no collective library call)")
     else:
         coll = "ncclAllReduce(sum, 4 bytes) after the local kernel"
     return {"workload": "c5_sharded_sum_f32_2p32" if TOTAL_ELEMS == 1 << 32 else "c5_sharded_sum_f32_reduced",
