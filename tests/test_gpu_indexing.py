@@ -274,9 +274,10 @@ def test_sorted_scatter_add(ops, port, V, D, N):
     assert (err <= 1e-5 * mass + 1e-30).all(), err.max()
 
 
-def test_sorted_scatter_add_unique_rows_is_bit_exact_and_flags_bad_indices(ops, port):
+@pytest.mark.parametrize("V", [4000, 200000])   # a full sort by row / rows grouped by a 16-bit hash (4-byte tables, > 65536 rows)
+def test_sorted_scatter_add_unique_rows_is_bit_exact_and_flags_bad_indices(ops, port, V):
     rng = np.random.default_rng(37)
-    V, D, N = 4000, 64, 3000
+    D, N = 64, 3000
     idx = rng.permutation(V)[:N].astype(np.int64)
     vf = rng.standard_normal((N, D), dtype=np.float32)
     init = rng.standard_normal((V, D), dtype=np.float32)
@@ -324,6 +325,11 @@ def test_mask_strided_unaligned_and_truthy_bytes(ops):
     for view, ref in ((t[1:], raw[1:]), (t[::3], raw[::3]), (t[5::7], raw[5::7])):
         got = ops.mask_to_indices(view.view(torch.bool))
         np.testing.assert_array_equal(got.cpu().numpy(), np.flatnonzero(ref))
+    # dense and aligned (the 16-byte path, whole tiles fetched ahead, and a ragged last tile): every byte value
+    full = rng.integers(0, 256, 16384 * 5 + 77).astype(np.uint8)
+    full[rng.random(full.size) < 0.5] = 0
+    got = ops.mask_to_indices(torch.from_numpy(full).cuda().view(torch.bool))
+    np.testing.assert_array_equal(got.cpu().numpy(), np.flatnonzero(full))
     assert ops.mask_to_indices(torch.zeros((0,), dtype=torch.bool, device="cuda")).numel() == 0
     with pytest.raises(ValueError, match="boolean mask"):
         ops.mask_to_indices(torch.ones((2, 2), dtype=torch.bool, device="cuda"))
