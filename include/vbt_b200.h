@@ -369,16 +369,19 @@ VBT_B200_API vbt_b200_status vbt_b200_index_rows(const vbt_b200_tensor* out, con
 VBT_B200_API vbt_b200_status vbt_b200_index_put_rows(const vbt_b200_tensor* table, const vbt_b200_tensor* idx,
                                         const vbt_b200_tensor* values, int32_t accumulate,
                                         int32_t policy, void* index_status, void* stream);
-/* table[idx[i], :] += values[i, :] by SORTING the updates by destination row first: the
- * deterministic counterpart of the accumulate path above, and the fast one for 64-bit
- * integers and for heavily repeated rows.  It does what the reference's opt-in sort +
- * reduce-by-key path does (advanced_index_put_make_kv_cuda_kernel + CUB SortPairs +
+/* table[idx[i], :] += values[i, :] by bringing the updates of one destination row TOGETHER first:
+ * the counterpart of the accumulate path above that adds run sums instead of single updates --
+ * the fast one for 64-bit integers and for large update counts.  It does what the reference's
+ * opt-in sort + reduce-by-key path does (advanced_index_put_make_kv_cuda_kernel + CUB SortPairs +
  * ReduceByKey + scatter, src/vbt/core/indexing_advanced_cuda.cu:1460-1557, :2888-3055) with
- * an LSD radix sort written here.  A warp walks 256 consecutive sorted updates, sums every run
- * of equal rows in update order and adds the run's sum to the row once (row += u1 + u2 + ...);
- * a run that crosses a slice boundary is finished by the next warp with an add of its own.
- * INT64 / INT32 exact; F32 bit-identical to a sequential loop for every row that starts at
- * zero (or is updated once) and whose updates lie in one slice.  `workspace` (16-byte
+ * an LSD radix sort written here.  Tables of 4-byte elements with more than 65536 rows are not
+ * sorted by row but grouped by a 16-bit hash of the row (two passes whatever the height): equal
+ * rows still end up next to each other, in update order, unless another row of the same hash
+ * bucket falls between them, which costs that row one more add.  A warp walks 256 consecutive
+ * entries, sums every run of equal rows in update order and adds the run's sum to the row once
+ * (row += u1 + u2 + ...); a run that crosses a slice boundary is finished by the next warp with
+ * an add of its own.  INT64 / INT32 exact; F32 bit-identical to a sequential loop for every row
+ * that starts at zero (or is updated once) and whose updates form one run.  `workspace` (16-byte
  * aligned, vbt_b200_index_put_rows_sorted_workspace_bytes(N) bytes, about 18 bytes per
  * index) needs no initialisation.  Shapes the sorted kernels do not take (rows that are not
  * whole 16-byte chunks) are served by the atomic path with the same result. */
