@@ -531,6 +531,13 @@ def test_transposed_operands_use_the_tiled_transpose_path(ops, port, dtype, shap
         cond = rng.integers(0, 2, xt.shape).astype(np.uint8)
         ops.where(from_np(cond, torch.bool), ty, tt, out=out)   # transposed output and operand
         np.testing.assert_array_equal(to_np(out), port.where(cond, y, xt, CODE[dtype]))
+        # a transposed condition, two dense operands: one of them rides in the free staging slot
+        c2 = rng.integers(0, 2, shape).astype(np.uint8)
+        y2 = rand_storage(rng, xt.shape, dtype)
+        got = to_np(ops.where(from_np(c2, torch.bool).transpose(-1, -2), ty, from_np(y2, dtype)))
+        np.testing.assert_array_equal(got, port.where(np.swapaxes(c2, -1, -2), y, y2, CODE[dtype]))
+        got = to_np(ops.mul(tt, ty))                        # transposed * dense, the other way round
+        np.testing.assert_array_equal(got, port.binary("mul", xt, y, CODE[dtype]))
     if len(shape) == 2 and min(shape) >= 16:
         assert ops.ti_plan(torch.empty(xt.shape, dtype=dtype, device="cuda"), tt)[2] == 3
 

@@ -479,11 +479,15 @@ ew_transpose_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, c
 // XOR-swizzled by the row's group index: the 16 lanes of a half-warp then hit 16 different banks
 // on the store, and the vector reads along i are conflict-free.  Needs sizes, strides and bases
 // that keep groups of four aligned; the host checks.
+// LIE: one more input lies like the output (unit stride along dim 0, groups of four aligned; bits
+// 4..6 of `tmask` say which) and is brought into the staging slot that the transposed inputs leave
+// free.  A separate instantiation: with the extra paths compiled into the one kernel, the where()
+// of the four-launch chain -- which cannot use them -- ran 14 % slower.
 // one-input ops (copies, unary ops on a transposed view) walk four tiles per block; with more
 // operands in play that order measured slower than one tile per block
 template <int NIN> constexpr int kTr4TilesPerBlock = NIN == 1 ? 4 : 1;
 
-template <class F, class TO, class T1, class T2, class T3, int NIN>
+template <class F, class TO, class T1, class T2, class T3, int NIN, bool LIE = false>
 __global__ void __launch_bounds__(kEwThreads)
 ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, const int tmask) {
   constexpr int TILE = 64;
@@ -560,9 +564,30 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
       }
     }
   };
+  // an input that is read as it lies (bits 4..6 of tmask: unit stride along dim 0, groups of four
+  // aligned) goes into the free staging slot by asynchronous copies issued BEFORE the transposed
+  // input is staged, so that a tile costs one round trip to memory, not two; every thread reads
+  // back only what it copied itself
+  unsigned char* const lie = sm[kTrMaxStaged - 1];
+  auto copy_as_it_lies = [&](const auto* gsrc, int64_t st1) {
+    using E = std::remove_cv_t<std::remove_pointer_t<decltype(gsrc)>>;
+#pragma unroll
+    for (int r = 0; r < TILE / 16; ++r) {
+      const int jl = w * 2 + h + 16 * r;
+      const int64_t i = i0 + q * 4, j = j0 + jl;
+      if (i < size0 && j < p.size1)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(lie)) + static_cast<uint32_t>((jl * TILE + q * 4) * sizeof(E))),
+                     "l"(gsrc + i + j * st1), "n"(4 * sizeof(E))
+                     : "memory");
+    }
+  };
+  if constexpr (LIE && sizeof(T1) <= 4) { if (tmask & 16) copy_as_it_lies(g1, a1); }
+  if constexpr (LIE && NIN >= 2 && sizeof(T2) <= 4) { if (tmask & 32) copy_as_it_lies(g2, b1); }
+  if constexpr (LIE && NIN >= 3 && sizeof(T3) <= 4) { if (tmask & 64) copy_as_it_lies(g3, c1); }
   if constexpr (sizeof(T1) <= 4) { if (tmask & 1) stage(s1, g1, a0); }
   if constexpr (NIN >= 2 && sizeof(T2) <= 4) { if (tmask & 2) stage(s2, g2, b0); }
   if constexpr (NIN >= 3 && sizeof(T3) <= 4) { if (tmask & 4) stage(s3, g3, c0); }
+  if constexpr (LIE) asm volatile("cp.async.wait_all;" ::: "memory");
   __syncthreads();
   const bool k1 = !(tmask & 1) && a0 == 0 && a1 == 0;
   const bool k2 = NIN >= 2 && !(tmask & 2) && b0 == 0 && b1 == 0;
@@ -586,7 +611,9 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
       if constexpr (sizeof(T1) <= 4) {
         if (tmask & 1) va = *reinterpret_cast<const Vec<T1, 4>*>(s1 + so);
       }
-      if (!(tmask & 1) || sizeof(T1) > 4) {
+      if (LIE && sizeof(T1) <= 4 && (tmask & 16)) {
+        va = *reinterpret_cast<const Vec<T1, 4>*>(lie + (jl * TILE + q * 4) * sizeof(T1));
+      } else if (!(tmask & 1) || sizeof(T1) > 4) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) va.v[e] = k1 ? ka : g1[(i + e) * a0 + j * a1];
       }
@@ -594,7 +621,9 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
         if constexpr (sizeof(T2) <= 4) {
           if (tmask & 2) vb = *reinterpret_cast<const Vec<T2, 4>*>(s2 + so);
         }
-        if (!(tmask & 2) || sizeof(T2) > 4) {
+        if (LIE && sizeof(T2) <= 4 && (tmask & 32)) {
+          vb = *reinterpret_cast<const Vec<T2, 4>*>(lie + (jl * TILE + q * 4) * sizeof(T2));
+        } else if (!(tmask & 2) || sizeof(T2) > 4) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) vb.v[e] = k2 ? kb : g2[(i + e) * b0 + j * b1];
         }
@@ -603,7 +632,9 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
         if constexpr (sizeof(T3) <= 4) {
           if (tmask & 4) vc = *reinterpret_cast<const Vec<T3, 4>*>(s3 + so);
         }
-        if (!(tmask & 4) || sizeof(T3) > 4) {
+        if (LIE && sizeof(T3) <= 4 && (tmask & 64)) {
+          vc = *reinterpret_cast<const Vec<T3, 4>*>(lie + (jl * TILE + q * 4) * sizeof(T3));
+        } else if (!(tmask & 4) || sizeof(T3) > 4) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) vc.v[e] = k3 ? kc : g3[(i + e) * c0 + j * c1];
         }
@@ -711,6 +742,19 @@ vbt_b200_status launch_ew(const TiPlan& plan, const F& f, cudaStream_t stream) {
           tp.div_t1 = FastDiv(static_cast<uint32_t>(q1));
           tp.n0v = static_cast<uint32_t>(tpl.shape[0]);
           tp.size1 = tpl.shape[1];
+          // one input that lies like the output may use the staging slot the transposed ones leave free
+          int lies = 0;
+          if (staged < kTrMaxStaged)
+            for (int k = 1; k <= NIN && !lies; ++k)
+              if (!((use_mask >> (k - 1)) & 1) && tpl.esize[k] <= 4 && group_ok(k, false, 4)) lies = 16 << (k - 1);
+          if constexpr (NIN >= 2) {
+            if (lies) {
+              ew_transpose4_kernel<F, TO, T1, T2, T3, NIN, true><<<static_cast<unsigned>(q0 * q1 * outer), kEwThreads, 0, stream>>>(tp, f, use_mask | lies);
+              VB_LAUNCH_CHECK();
+              note(3, static_cast<unsigned>(q0 * q1 * outer), 4);
+              return VBT_B200_OK;
+            }
+          }
           ew_transpose4_kernel<F, TO, T1, T2, T3, NIN><<<static_cast<unsigned>(q0 * q1 * outer), kEwThreads, 0, stream>>>(tp, f, use_mask);
           VB_LAUNCH_CHECK();
           note(3, static_cast<unsigned>(q0 * q1 * outer), 4);
