@@ -521,6 +521,90 @@ ew_transpose4_kernel(const __grid_constant__ TiledParams<NIN + 1> p, const F f, 
   const int64_t c0 = p.s0[NIN >= 3 ? 3 : 0], c1 = p.s1[NIN >= 3 ? 3 : 0];
   // a block walks kTiles consecutive tiles along dim 1: the offset decoding above is paid once
   constexpr int kTiles = kTr4TilesPerBlock<NIN>;
+  if constexpr (NIN == 1 && sizeof(T1) <= 4) {
+    // One transposed input (a copy or a unary op on a transposed view): the tiles alternate
+    // between the two staging slots, and the loads of tile t + 1 are in flight -- in registers --
+    // while tile t is written out.  One barrier per tile.  Same shared-memory layout as below.
+    constexpr int kRounds = sizeof(T1) == 2 ? TILE / 32 : TILE / 16;
+    constexpr int kWordsPerRound = sizeof(T1) == 1 ? 1 : 4;
+    uint32_t raw[kRounds * kWordsPerRound];
+    auto load_tile = [&](int64_t j0) {
+      const int64_t j = j0 + q * 4;
+      if (j >= p.size1) return;
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        if constexpr (sizeof(T1) == 2) {
+          const int64_t i = i0 + 2 * (w * 2 + h + 16 * r);
+          if (i >= size0) continue;  // size0 is a multiple of four: the odd row exists too
+          const uint2 ve = *reinterpret_cast<const uint2*>(g1 + i * a0 + j);
+          const uint2 vo = *reinterpret_cast<const uint2*>(g1 + (i + 1) * a0 + j);
+          raw[4 * r] = ve.x; raw[4 * r + 1] = ve.y; raw[4 * r + 2] = vo.x; raw[4 * r + 3] = vo.y;
+        } else if constexpr (sizeof(T1) == 4) {
+          const int64_t i = i0 + w * 2 + h + 16 * r;
+          if (i >= size0) continue;
+          const uint4 v = *reinterpret_cast<const uint4*>(g1 + i * a0 + j);
+          raw[4 * r] = v.x; raw[4 * r + 1] = v.y; raw[4 * r + 2] = v.z; raw[4 * r + 3] = v.w;
+        } else {
+          const int64_t i = i0 + w * 2 + h + 16 * r;
+          if (i >= size0) continue;
+          raw[r] = *reinterpret_cast<const uint32_t*>(g1 + i * a0 + j);
+        }
+      }
+    };
+    auto put_tile = [&](unsigned char* slot, int64_t j0) {
+      if (j0 + q * 4 >= p.size1) return;
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        if constexpr (sizeof(T1) == 2) {
+          const int pi = w * 2 + h + 16 * r;
+          if (i0 + 2 * pi >= size0) continue;
+          uint32_t* d = reinterpret_cast<uint32_t*>(slot) + (q * 4) * (TILE / 2);
+          const int wi = pi ^ (2 * q);
+          d[0 * (TILE / 2) + wi] = __byte_perm(raw[4 * r], raw[4 * r + 2], 0x5410);
+          d[1 * (TILE / 2) + wi] = __byte_perm(raw[4 * r], raw[4 * r + 2], 0x7632);
+          d[2 * (TILE / 2) + wi] = __byte_perm(raw[4 * r + 1], raw[4 * r + 3], 0x5410);
+          d[3 * (TILE / 2) + wi] = __byte_perm(raw[4 * r + 1], raw[4 * r + 3], 0x7632);
+        } else {
+          const int il = w * 2 + h + 16 * r;
+          if (i0 + il >= size0) continue;
+          const int col = (((il >> 2) ^ q) << 2) + (il & 3);
+          if constexpr (sizeof(T1) == 4) {
+            uint32_t* d = reinterpret_cast<uint32_t*>(slot) + (q * 4) * TILE + col;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) d[e * TILE] = raw[4 * r + e];
+          } else {
+            uint8_t* d = reinterpret_cast<uint8_t*>(slot) + (q * 4) * TILE + col;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) d[e * TILE] = static_cast<uint8_t>(raw[r] >> (8 * e));
+          }
+        }
+      }
+    };
+    TO* const go = reinterpret_cast<TO*>(p.ptr[0]) + base[0];
+    const int64_t first_j0 = static_cast<int64_t>(t1) * kTiles * TILE;
+    if (first_j0 < p.size1) load_tile(first_j0);
+#pragma unroll 1
+    for (int tt = 0; tt < kTiles; ++tt) {
+      const int64_t j0 = first_j0 + static_cast<int64_t>(tt) * TILE;
+      if (j0 >= p.size1) break;
+      unsigned char* const slot = sm[tt & 1];
+      put_tile(slot, j0);
+      __syncthreads();  // also: every thread has left the tile that used this slot two turns ago
+      if (tt + 1 < kTiles && j0 + TILE < p.size1) load_tile(j0 + TILE);
+      const T1* const st = reinterpret_cast<const T1*>(slot);
+#pragma unroll
+      for (int r = 0; r < TILE / 16; ++r) {
+        const int jl = w * 2 + h + 16 * r;
+        const int64_t i = i0 + q * 4, j = j0 + jl;
+        if (i < size0 && j < p.size1) {
+          const Vec<T1, 4> va = *reinterpret_cast<const Vec<T1, 4>*>(st + jl * TILE + ((q ^ ((jl >> 2) & 15)) << 2));
+          const Vec<TO, 4> o = apply_vec<F, TO, T1, T2, T3, NIN, 4>(f, va, Vec<T2, 4>{}, Vec<T3, 4>{});
+          *reinterpret_cast<Vec<TO, 4>*>(go + i + j * p.s1[0]) = o;
+        }
+      }
+    }
+    return;
+  }
 #pragma unroll 1
   for (int tt = 0; tt < kTiles; ++tt) {
   const int64_t j0 = (static_cast<int64_t>(t1) * kTiles + tt) * TILE;
