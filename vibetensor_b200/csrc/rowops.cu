@@ -266,10 +266,35 @@ __global__ void __launch_bounds__(THREADS) rowop_block_kernel(const __grid_const
     phase ^= 1;
     return r;
   };
+  // 32-bit rows: the block's next row is fetched (raw, 16 bytes per vector) before the current one
+  // is worked on, so its loads are in flight through the row's barriers and stores ([32768,4096]
+  // fp32: softmax 0.946 -> 0.955, RMSNorm 0.914 -> 0.956 of the measured bandwidth).  16-bit rows
+  // hold twice the floats per vector; with the extra registers they fell from 0.98 to 0.76.
+  constexpr bool kAhead = sizeof(T) == 4;
+  Vec<T, V> ahead[kAhead ? VPL : 1];
+  auto fetch = [&](int64_t row) {
+    const T* xr = static_cast<const T*>(p.x) + row * p.x_row_stride;
+#pragma unroll
+    for (int k = 0; k < (kAhead ? VPL : 0); ++k) {
+      const int j = t + k * THREADS;
+      if (j < nvec) ahead[k] = *reinterpret_cast<const Vec<T, V>*>(xr + static_cast<int64_t>(j) * V);
+    }
+  };
+  if (kAhead && static_cast<int64_t>(blockIdx.x) < p.rows) fetch(blockIdx.x);
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
     float v[VPL][V];
     bool valid[VPL];
-    load_row<T, VPL>(static_cast<const T*>(p.x) + row * p.x_row_stride, t, THREADS, nvec, v, valid);
+    if constexpr (kAhead) {
+#pragma unroll
+      for (int k = 0; k < VPL; ++k) {
+        valid[k] = t + k * THREADS < nvec;
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[k][e] = valid[k] ? to_f(ahead[k].v[e]) : 0.f;
+      }
+      if (row + gridDim.x < p.rows) fetch(row + gridDim.x);
+    } else {
+      load_row<T, VPL>(static_cast<const T*>(p.x) + row * p.x_row_stride, t, THREADS, nvec, v, valid);
+    }
     float inv = 0.f;
     row_math<T, KIND, VPL>(v, valid, ones, p, [&](float a) { return block_fold(a, true); },
                            [&](float a) { return block_fold(a, false); }, &inv);
