@@ -508,7 +508,7 @@ def test_large_dim_over_2_31_elements_linearity(ops):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int64, torch.bool])
 @pytest.mark.parametrize("shape", [(100, 70), (33, 1000), (16, 16), (4, 50, 37), (3, 2, 64, 48), (128, 192),
-                                   (68, 132), (2, 260, 64)])
+                                   (68, 132), (2, 260, 64), (520, 1032), (1028, 260)])
 def test_transposed_operands_use_the_tiled_transpose_path(ops, port, dtype, shape):
     """contiguous() of a transposed view, an op between a tensor and its transpose, where()
     into a transposed output: inputs contiguous along another dim than the output."""
