@@ -284,3 +284,15 @@ def test_polygamma_and_complex_argument_rules_without_a_gpu(L):
     assert L.vbt_b200_binary(2, ctypes.byref(cb), ctypes.byref(ca), ctypes.byref(ca), None) == 1
     assert b"vt::mul: output dtype mismatch" in L.vbt_b200_last_error()
     assert L.vbt_b200_unary(0, ctypes.byref(co), ctypes.byref(ca), None) == 1   # no complex unary ops
+
+
+def test_scatter_add_engine_choice_follows_the_measured_crossovers():
+    """ops.index_put_rows_(accumulate=True, deterministic=None): integer tables group from 2^19
+    updates on, float32 from 2^21, 16-bit tables never (the grouping kernels do not take them)."""
+    import torch
+    from vibetensor_b200 import ops
+    assert not ops.grouping_engine_pays(torch.int64, (1 << 19) - 1)
+    assert ops.grouping_engine_pays(torch.int64, 1 << 19) and ops.grouping_engine_pays(torch.int32, 1 << 22)
+    assert not ops.grouping_engine_pays(torch.float32, 1 << 20)
+    assert ops.grouping_engine_pays(torch.float32, 1 << 21)
+    assert not ops.grouping_engine_pays(torch.bfloat16, 1 << 24) and not ops.grouping_engine_pays(torch.float16, 1 << 24)
